@@ -1,0 +1,60 @@
+// Grouped (per-expert) BF16 products of the prefill path.
+//
+// A problem is a list of row tiles; tile t multiplies rows
+// [tile_row0[t], tile_row0[t] + tile_rows[t]) of A by the weight matrix of
+// expert tile_expert[t] (B is [n, k] row-major, i.e. C = A . B^T, FP32
+// accumulation).  With tile_expert == nullptr the product is dense over
+// `dense_rows` rows in tiles of kTileRows.
+//
+// Epilogues (rounding points of native/src/native_moe_prefill.hip.cpp):
+//   kGemmExpertGateUp  act = bf16(f32(bf16(silu(bf16 g))) * bf16 u)      (:384-402)
+//   kGemmSharedGateUp  act = bf16(silu(bf16 g) * bf16 u)                 (:210-219)
+//   kGemmExpertDown    out = bf16(acc * routing_weight[flat row])        (fused_moe down,
+//                            MUL_ROUTED_WEIGHT; manifest.json:4672-4689)
+//   kGemmSharedDown    out = bf16(bf16(sigmoid gate)[row] * bf16(acc))   (:221-232)
+// In the two gate_up modes column i of the output pairs weight rows i (gate) and
+// n + i (up; b1 when it is a separate tensor).
+#pragma once
+
+#include "common.cuh"
+
+namespace aima {
+
+constexpr int kTileRowsSimt = 128;  // must equal kTileRows of the dispatch plan
+
+enum GemmMode {
+  kGemmExpertGateUp = 0,
+  kGemmSharedGateUp = 1,
+  kGemmExpertDown = 2,
+  kGemmSharedDown = 3,
+};
+
+struct GroupedGemm {
+  const int32_t* tile_expert;
+  const int32_t* tile_row0;
+  const int32_t* tile_rows;
+  const int32_t* tile_count;   // device scalar; nullptr in dense mode
+  int max_tiles;               // launch bound on the tile count
+  int dense_rows;
+  const __nv_bfloat16* a;      // [rows, k]
+  int lda;
+  int k;
+  const __nv_bfloat16* b0;     // gate (or only) weight matrix / expert slab
+  const __nv_bfloat16* b1;     // separate "up" matrix (shared expert) or nullptr
+  size_t b_expert_stride;      // elements between experts in b0
+  int n;                       // output columns
+  __nv_bfloat16* c;            // [rows, n]
+  int ldc;
+  const float* row_scale;      // routing weights [T*8] or sigmoid gate [T]
+  const int32_t* sorted_rows;  // flat routed row of each sorted position
+};
+
+cudaError_t launch_grouped_gemm(GemmMode mode, const GroupedGemm& problem,
+                                cudaStream_t stream);
+
+// CUDA-core implementation kept as an on-device cross-check of the tensor-core
+// kernel (selected per call by the qualification flag).
+cudaError_t launch_grouped_gemm_simt(GemmMode mode, const GroupedGemm& problem,
+                                     cudaStream_t stream);
+
+}  // namespace aima

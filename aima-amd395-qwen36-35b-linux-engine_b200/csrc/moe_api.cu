@@ -1,0 +1,541 @@
+// Host side of the C ABI declared in include/aima_moe.h.
+//
+// Mirrors the fail-closed style of the reference runtime's owners
+// (native/src/native_moe_prefill.hip.cpp:44-87, 550-599, 711-715): every size,
+// residency and alias rule is checked before anything is enqueued, each check
+// has its own message, and nothing throws across the boundary.
+#include "../../include/aima_moe.h"
+
+#include "decode_kernel.cuh"
+#include "pointwise.cuh"
+#include "prefill.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+using namespace aima;
+
+namespace {
+
+thread_local char g_last_error[512] = "";
+
+int fail(int code, const char* format, ...) {
+  va_list args;
+  va_start(args, format);
+  std::vsnprintf(g_last_error, sizeof g_last_error, format, args);
+  va_end(args);
+  return code;
+}
+
+int fail_cuda(cudaError_t error, const char* operation) {
+  std::snprintf(g_last_error, sizeof g_last_error, "%s: %s (%s)", operation,
+                cudaGetErrorName(error), cudaGetErrorString(error));
+  (void)cudaGetLastError();
+  return static_cast<int>(error);
+}
+
+constexpr uint64_t kRouterBytes = 2ull * kExperts * kHidden;
+constexpr uint64_t kGateUpBytesPerExpert = 2ull * 2 * kInter * kHidden;
+constexpr uint64_t kDownBytesPerExpert = 2ull * kHidden * kInter;
+constexpr uint64_t kSharedGateBytes = 2ull * kHidden;
+constexpr uint64_t kSharedProjBytes = 2ull * kSharedInter * kHidden;
+constexpr uint64_t kNormBytes = 2ull * kHidden;
+
+size_t align_up(size_t value, size_t alignment) {
+  return (value + alignment - 1) / alignment * alignment;
+}
+
+}  // namespace
+
+struct aima_moe_handle {
+  aima_moe_config config{};
+  int device = -1;
+  int sm_count = 0;
+  int decode_grid = 0;
+  int experts_local = 0;
+  int expert_lo = 0;
+  LayerPtrs host_layers[kMaxLayers]{};
+  bool bound[kMaxLayers]{};
+  LayerPtrs* dev_layers = nullptr;
+
+  // decode scratch (one allocation)
+  uint8_t* decode_scratch = nullptr;
+  size_t decode_scratch_bytes = 0;
+  __nv_bfloat16* xbuf0 = nullptr;
+  __nv_bfloat16* xbuf1 = nullptr;
+  float* logits = nullptr;
+  uint16_t* act = nullptr;
+  float* gate_logit = nullptr;
+  unsigned long long* bar_counter = nullptr;
+  unsigned long long* bar_base = nullptr;
+  int* status = nullptr;
+
+  PrefillWorkspace prefill;
+
+  const float* router_bias = nullptr;
+  int quant_eighths = 0;
+
+  aima_moe_metrics metrics{};
+  cudaStream_t last_stream = nullptr;
+  std::mutex mutex;
+};
+
+namespace {
+
+int validate_config(const aima_moe_config* config) {
+  if (config == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "config is null");
+  if (config->struct_bytes != sizeof(aima_moe_config))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_config size mismatch: got %u, built for %zu",
+                config->struct_bytes, sizeof(aima_moe_config));
+  if (config->hidden != kHidden || config->experts != kExperts || config->top_k != kTopK ||
+      config->expert_inter != kInter || config->shared_inter != kSharedInter)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED,
+                "only hidden 2048 / 256 experts / top-8 / intermediate 512 / shared 512 is built");
+  if (config->layers == 0 || config->layers > kMaxLayers)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "layers must be 1..%d", kMaxLayers);
+  if (config->world != 1 && config->world != 2 && config->world != 4 && config->world != 8)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "world must be 1, 2, 4 or 8");
+  if (config->rank >= config->world)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "rank %u out of range for world %u",
+                config->rank, config->world);
+  if (!(config->rms_eps > 0.0f) || !(config->rms_eps < 1.0f))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "rms_eps must be in (0, 1)");
+  if (config->max_prefill_tokens > 262144u)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "max_prefill_tokens exceeds 262144");
+  return AIMA_MOE_OK;
+}
+
+size_t decode_scratch_size() {
+  // xbuf0, xbuf1 (4 KB each), logits 1 KB, act 9216 B, gate logit, counters, status
+  return 4096 + 4096 + 1024 + align_up(9 * kInter * 2, 256) + 256 + 256 + 256;
+}
+
+int check_device_tensor(const void* pointer, uint64_t bytes, uint64_t expected,
+                        const char* name) {
+  if (pointer == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "weight %s is null", name);
+  if (bytes != expected)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "weight %s has %llu bytes, expected %llu", name,
+                static_cast<unsigned long long>(bytes), static_cast<unsigned long long>(expected));
+  if (reinterpret_cast<uintptr_t>(pointer) % 16 != 0)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "weight %s is not 16-byte aligned", name);
+  cudaPointerAttributes attributes{};
+  const cudaError_t error = cudaPointerGetAttributes(&attributes, pointer);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaPointerGetAttributes");
+  if (attributes.type != cudaMemoryTypeDevice && attributes.type != cudaMemoryTypeManaged)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "weight %s is not device resident", name);
+  return AIMA_MOE_OK;
+}
+
+bool ranges_overlap(const void* a, size_t a_bytes, const void* b, size_t b_bytes) {
+  const uintptr_t a0 = reinterpret_cast<uintptr_t>(a);
+  const uintptr_t b0 = reinterpret_cast<uintptr_t>(b);
+  return a0 < b0 + b_bytes && b0 < a0 + a_bytes;
+}
+
+int reset_decode_sync(aima_moe_handle* handle) {
+  cudaError_t error = cudaMemset(handle->bar_counter, 0, 256);
+  if (error == cudaSuccess) error = cudaMemset(handle->bar_base, 0, 256);
+  if (error == cudaSuccess) error = cudaMemset(handle->status, 0, 256);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaMemset decode sync words");
+  return AIMA_MOE_OK;
+}
+
+int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t n_layers,
+                        const void* x_in, void* x_out, const aima_moe_debug_views* debug,
+                        void* stream) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if (x_in == nullptr || x_out == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "decode input/output is null");
+  if (n_layers == 0 || first_layer >= handle->config.layers ||
+      n_layers > handle->config.layers - first_layer)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "decode layer range [%u, %u) is out of range",
+                first_layer, first_layer + n_layers);
+  for (uint32_t layer = first_layer; layer < first_layer + n_layers; ++layer) {
+    if (!handle->bound[layer])
+      return fail(AIMA_MOE_ERR_NOT_BOUND, "layer %u has no bound weights", layer);
+    if (handle->host_layers[layer].norm_weight == nullptr)
+      return fail(AIMA_MOE_ERR_NOT_BOUND, "layer %u has no post-attention norm weight", layer);
+  }
+  if (ranges_overlap(x_in, kHidden * 2, x_out, kHidden * 2))
+    return fail(AIMA_MOE_ERR_ALIAS, "decode output aliases its input");
+  if (reinterpret_cast<uintptr_t>(x_in) % 16 != 0 || reinterpret_cast<uintptr_t>(x_out) % 16 != 0)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "decode vectors must be 16-byte aligned");
+  if (debug != nullptr && debug->struct_bytes != sizeof(aima_moe_debug_views))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_debug_views size mismatch");
+  if (handle->config.world != 1)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "expert-parallel decode is not built yet");
+
+  DecodeParams params{};
+  params.layers = handle->dev_layers;
+  params.x_in = static_cast<const __nv_bfloat16*>(x_in);
+  params.x_out = static_cast<__nv_bfloat16*>(x_out);
+  params.xbuf0 = handle->xbuf0;
+  params.xbuf1 = handle->xbuf1;
+  params.logits = handle->logits;
+  params.act = handle->act;
+  params.gate_logit = handle->gate_logit;
+  params.bar_counter = handle->bar_counter;
+  params.bar_base = handle->bar_base;
+  params.status = handle->status;
+  params.router_bias = handle->router_bias;
+  params.quant_eighths = handle->quant_eighths;
+  params.eps = handle->config.rms_eps;
+  params.first_layer = static_cast<int>(first_layer);
+  params.n_layers = static_cast<int>(n_layers);
+  params.expert_lo = handle->expert_lo;
+  params.expert_hi = handle->expert_lo + handle->experts_local;
+  if (debug != nullptr) {
+    params.dbg_h2 = static_cast<__nv_bfloat16*>(debug->h2);
+    params.dbg_logits = static_cast<float*>(debug->router_logits);
+    params.dbg_ids = static_cast<int*>(debug->topk_ids);
+    params.dbg_scores = static_cast<float*>(debug->topk_scores);
+    params.dbg_weights = static_cast<__nv_bfloat16*>(debug->topk_weights);
+    params.dbg_shared_scaled = static_cast<__nv_bfloat16*>(debug->shared_scaled);
+    params.dbg_routed = static_cast<__nv_bfloat16*>(debug->routed);
+  }
+  const cudaError_t error =
+      launch_moe_decode(params, handle->decode_grid, static_cast<cudaStream_t>(stream));
+  if (error != cudaSuccess) return fail_cuda(error, "launch moe_decode_persistent_kernel");
+  handle->last_stream = static_cast<cudaStream_t>(stream);
+  handle->metrics.decode_calls += 1;
+  handle->metrics.kernel_launches += 1;
+  return AIMA_MOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+#define AIMA_EXPORT __attribute__((visibility("default")))
+
+AIMA_EXPORT uint32_t aima_moe_abi_version(void) { return (1u << 16) | 0u; }
+
+AIMA_EXPORT const char* aima_moe_last_error_string(void) { return g_last_error; }
+
+AIMA_EXPORT int aima_moe_query_workspace(const aima_moe_config* config, uint64_t* bytes) {
+  const int status = validate_config(config);
+  if (status != AIMA_MOE_OK) return status;
+  if (bytes == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "bytes is null");
+  *bytes = decode_scratch_size() + sizeof(LayerPtrs) * kMaxLayers +
+           prefill_workspace_bytes(config->max_prefill_tokens);
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle** out_handle) {
+  int status = validate_config(config);
+  if (status != AIMA_MOE_OK) return status;
+  if (out_handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle out-pointer is null");
+  *out_handle = nullptr;
+
+  int device = -1;
+  cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(AIMA_MOE_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(error));
+  }
+  cudaDeviceProp properties{};
+  error = cudaGetDeviceProperties(&properties, device);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaGetDeviceProperties");
+  if (properties.major != 10)
+    return fail(AIMA_MOE_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
+                device, properties.major, properties.minor);
+  const int grid = properties.multiProcessorCount < kDecodeMaxBlocks
+                       ? properties.multiProcessorCount
+                       : kDecodeMaxBlocks;
+  if (grid < kDecodeMinBlocks)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "device exposes %d SMs; the decode kernel needs at least %d",
+                properties.multiProcessorCount, kDecodeMinBlocks);
+  if (!properties.cooperativeLaunch)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "device does not support cooperative launch");
+
+  aima_moe_handle* handle = new (std::nothrow) aima_moe_handle();
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INTERNAL, "out of host memory");
+  handle->config = *config;
+  handle->device = device;
+  handle->sm_count = properties.multiProcessorCount;
+  handle->decode_grid = grid;
+  handle->experts_local = kExperts / static_cast<int>(config->world);
+  handle->expert_lo = handle->experts_local * static_cast<int>(config->rank);
+
+  auto cleanup = [&](int code) {
+    if (handle->dev_layers) cudaFree(handle->dev_layers);
+    if (handle->decode_scratch) cudaFree(handle->decode_scratch);
+    prefill_workspace_free(&handle->prefill);
+    delete handle;
+    return code;
+  };
+
+  error = cudaMalloc(&handle->dev_layers, sizeof(LayerPtrs) * kMaxLayers);
+  if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc layer table"));
+  error = cudaMemset(handle->dev_layers, 0, sizeof(LayerPtrs) * kMaxLayers);
+  if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMemset layer table"));
+
+  handle->decode_scratch_bytes = decode_scratch_size();
+  error = cudaMalloc(&handle->decode_scratch, handle->decode_scratch_bytes);
+  if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc decode scratch"));
+  error = cudaMemset(handle->decode_scratch, 0, handle->decode_scratch_bytes);
+  if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMemset decode scratch"));
+  uint8_t* cursor = handle->decode_scratch;
+  handle->xbuf0 = reinterpret_cast<__nv_bfloat16*>(cursor); cursor += 4096;
+  handle->xbuf1 = reinterpret_cast<__nv_bfloat16*>(cursor); cursor += 4096;
+  handle->logits = reinterpret_cast<float*>(cursor); cursor += 1024;
+  handle->act = reinterpret_cast<uint16_t*>(cursor); cursor += align_up(9 * kInter * 2, 256);
+  handle->gate_logit = reinterpret_cast<float*>(cursor); cursor += 256;
+  handle->bar_counter = reinterpret_cast<unsigned long long*>(cursor); cursor += 128;
+  handle->bar_base = reinterpret_cast<unsigned long long*>(cursor); cursor += 128;
+  handle->status = reinterpret_cast<int*>(cursor); cursor += 256;
+
+  if (config->max_prefill_tokens > 0) {
+    status = prefill_workspace_allocate(&handle->prefill, config->max_prefill_tokens,
+                                        handle->sm_count, g_last_error, sizeof g_last_error);
+    if (status != AIMA_MOE_OK) return cleanup(status);
+  }
+  handle->metrics.struct_bytes = sizeof(aima_moe_metrics);
+  handle->metrics.workspace_bytes = handle->decode_scratch_bytes + sizeof(LayerPtrs) * kMaxLayers +
+                                    handle->prefill.total_bytes;
+  *out_handle = handle;
+  g_last_error[0] = '\0';
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_bind_layer(aima_moe_handle* handle, uint32_t layer,
+                                    const aima_moe_layer_weights* weights) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if (weights == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "weights is null");
+  if (weights->struct_bytes != sizeof(aima_moe_layer_weights))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_layer_weights size mismatch");
+  if (layer >= handle->config.layers)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "layer %u out of range (layers = %u)", layer,
+                handle->config.layers);
+  const uint64_t local = static_cast<uint64_t>(handle->experts_local);
+  int status;
+  if ((status = check_device_tensor(weights->router, weights->router_bytes, kRouterBytes,
+                                    "mlp.gate.weight")) != AIMA_MOE_OK) return status;
+  if ((status = check_device_tensor(weights->expert_gate_up, weights->expert_gate_up_bytes,
+                                    local * kGateUpBytesPerExpert,
+                                    "mlp.experts.gate_up_proj")) != AIMA_MOE_OK) return status;
+  if ((status = check_device_tensor(weights->expert_down, weights->expert_down_bytes,
+                                    local * kDownBytesPerExpert,
+                                    "mlp.experts.down_proj")) != AIMA_MOE_OK) return status;
+  if ((status = check_device_tensor(weights->shared_expert_gate, weights->shared_expert_gate_bytes,
+                                    kSharedGateBytes, "mlp.shared_expert_gate.weight")) != AIMA_MOE_OK)
+    return status;
+  if ((status = check_device_tensor(weights->shared_gate_proj, weights->shared_gate_proj_bytes,
+                                    kSharedProjBytes, "mlp.shared_expert.gate_proj.weight")) != AIMA_MOE_OK)
+    return status;
+  if ((status = check_device_tensor(weights->shared_up_proj, weights->shared_up_proj_bytes,
+                                    kSharedProjBytes, "mlp.shared_expert.up_proj.weight")) != AIMA_MOE_OK)
+    return status;
+  if ((status = check_device_tensor(weights->shared_down_proj, weights->shared_down_proj_bytes,
+                                    kSharedProjBytes, "mlp.shared_expert.down_proj.weight")) != AIMA_MOE_OK)
+    return status;
+  if (weights->post_attention_norm != nullptr &&
+      (status = check_device_tensor(weights->post_attention_norm, weights->post_attention_norm_bytes,
+                                    kNormBytes, "post_attention_layernorm.weight")) != AIMA_MOE_OK)
+    return status;
+
+  LayerPtrs pointers{};
+  pointers.router = static_cast<const __nv_bfloat16*>(weights->router);
+  pointers.expert_gate_up = static_cast<const __nv_bfloat16*>(weights->expert_gate_up);
+  pointers.expert_down = static_cast<const __nv_bfloat16*>(weights->expert_down);
+  pointers.shared_gate = static_cast<const __nv_bfloat16*>(weights->shared_expert_gate);
+  pointers.shared_gate_proj = static_cast<const __nv_bfloat16*>(weights->shared_gate_proj);
+  pointers.shared_up_proj = static_cast<const __nv_bfloat16*>(weights->shared_up_proj);
+  pointers.shared_down_proj = static_cast<const __nv_bfloat16*>(weights->shared_down_proj);
+  pointers.norm_weight = static_cast<const __nv_bfloat16*>(weights->post_attention_norm);
+  const cudaError_t error = cudaMemcpy(handle->dev_layers + layer, &pointers, sizeof pointers,
+                                       cudaMemcpyHostToDevice);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy layer table entry");
+  handle->host_layers[layer] = pointers;
+  handle->bound[layer] = true;
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_set_router_hooks(aima_moe_handle* handle, const void* bias_f32,
+                                          int quantize_eighths) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  handle->router_bias = static_cast<const float*>(bias_f32);
+  handle->quant_eighths = quantize_eighths ? 1 : 0;
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_decode_launch(aima_moe_handle* handle, uint32_t layer,
+                                       const void* after_attn, void* out,
+                                       const aima_moe_debug_views* debug, void* stream) {
+  return launch_decode_range(handle, layer, 1, after_attn, out, debug, stream);
+}
+
+AIMA_EXPORT int aima_moe_decode_stack_launch(aima_moe_handle* handle, uint32_t first_layer,
+                                             uint32_t n_layers, const void* x_in, void* x_out,
+                                             void* stream) {
+  return launch_decode_range(handle, first_layer, n_layers, x_in, x_out, nullptr, stream);
+}
+
+AIMA_EXPORT int aima_moe_prefill_launch(aima_moe_handle* handle, uint32_t layer, const void* h2,
+                                        const void* residual, void* out, uint32_t tokens,
+                                        const aima_moe_debug_views* debug, void* stream) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if (h2 == nullptr || residual == nullptr || out == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "prefill input/output is null");
+  if (tokens == 0) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "tokens is zero");
+  if (tokens > handle->config.max_prefill_tokens)
+    return fail(AIMA_MOE_ERR_CAPACITY, "tokens %u exceed prepared capacity %u", tokens,
+                handle->config.max_prefill_tokens);
+  if (layer >= handle->config.layers || !handle->bound[layer])
+    return fail(AIMA_MOE_ERR_NOT_BOUND, "layer %u has no bound weights", layer);
+  const size_t bytes = static_cast<size_t>(tokens) * kHidden * 2;
+  if (ranges_overlap(out, bytes, h2, bytes) || ranges_overlap(out, bytes, residual, bytes))
+    return fail(AIMA_MOE_ERR_ALIAS, "prefill output aliases an input");
+  if (debug != nullptr && debug->struct_bytes != sizeof(aima_moe_debug_views))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_debug_views size mismatch");
+  if (handle->config.world != 1)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "expert-parallel prefill is not built yet");
+  PrefillCall call{};
+  call.layer = handle->host_layers[layer];
+  call.h2 = h2;
+  call.residual = residual;
+  call.out = out;
+  call.tokens = static_cast<int>(tokens);
+  call.router_bias = handle->router_bias;
+  call.quant_eighths = handle->quant_eighths;
+  call.debug = debug;
+  int launches = 0;
+  const int status = prefill_layer_launch(&handle->prefill, call, static_cast<cudaStream_t>(stream),
+                                          &launches, g_last_error, sizeof g_last_error);
+  if (status != AIMA_MOE_OK) return status;
+  handle->last_stream = static_cast<cudaStream_t>(stream);
+  handle->metrics.prefill_calls += 1;
+  handle->metrics.kernel_launches += static_cast<uint64_t>(launches);
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t first_layer,
+                                              uint32_t n_layers, const void* x_in, void* x_out,
+                                              uint32_t tokens, void* stream) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if (x_in == nullptr || x_out == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "prefill stack input/output is null");
+  if (tokens == 0 || tokens > handle->config.max_prefill_tokens)
+    return fail(AIMA_MOE_ERR_CAPACITY, "tokens %u outside prepared capacity %u", tokens,
+                handle->config.max_prefill_tokens);
+  if (n_layers == 0 || first_layer >= handle->config.layers ||
+      n_layers > handle->config.layers - first_layer)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "prefill layer range is out of range");
+  for (uint32_t layer = first_layer; layer < first_layer + n_layers; ++layer) {
+    if (!handle->bound[layer] || handle->host_layers[layer].norm_weight == nullptr)
+      return fail(AIMA_MOE_ERR_NOT_BOUND, "layer %u lacks weights or its norm weight", layer);
+  }
+  if (handle->config.world != 1)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "expert-parallel prefill is not built yet");
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  const size_t bytes = static_cast<size_t>(tokens) * kHidden * 2;
+  // x ping-pongs between two workspace buffers; h2 lives in a third.
+  const void* current = x_in;
+  for (uint32_t step = 0; step < n_layers; ++step) {
+    const uint32_t layer = first_layer + step;
+    void* target = (step + 1 == n_layers) ? x_out
+                   : (step & 1u) ? handle->prefill.stack_x1 : handle->prefill.stack_x0;
+    if (target == x_out && ranges_overlap(x_out, bytes, current, bytes)) {
+      // final layer would write over its own residual input: stage through a buffer
+      target = (step & 1u) ? handle->prefill.stack_x1 : handle->prefill.stack_x0;
+    }
+    cudaError_t error = launch_rmsnorm_rows(current, nullptr, handle->host_layers[layer].norm_weight,
+                                            nullptr, handle->prefill.stack_h2,
+                                            static_cast<int>(tokens), handle->config.rms_eps,
+                                            cuda_stream);
+    if (error != cudaSuccess) return fail_cuda(error, "launch rmsnorm_rows_kernel");
+    PrefillCall call{};
+    call.layer = handle->host_layers[layer];
+    call.h2 = handle->prefill.stack_h2;
+    call.residual = current;
+    call.out = target;
+    call.tokens = static_cast<int>(tokens);
+    call.router_bias = handle->router_bias;
+    call.quant_eighths = handle->quant_eighths;
+    int launches = 0;
+    const int status = prefill_layer_launch(&handle->prefill, call, cuda_stream, &launches,
+                                            g_last_error, sizeof g_last_error);
+    if (status != AIMA_MOE_OK) return status;
+    handle->metrics.kernel_launches += static_cast<uint64_t>(launches) + 1;
+    if (step + 1 == n_layers && target != x_out) {
+      error = cudaMemcpyAsync(x_out, target, bytes, cudaMemcpyDeviceToDevice, cuda_stream);
+      if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpyAsync prefill stack output");
+    }
+    current = target;
+  }
+  handle->last_stream = cuda_stream;
+  handle->metrics.prefill_calls += n_layers;
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_rmsnorm_launch(const void* x, const void* residual, const void* weight,
+                                        void* residual_out, void* norm_out, uint32_t rows,
+                                        float eps, void* stream) {
+  if (x == nullptr || weight == nullptr || norm_out == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "rmsnorm pointer is null");
+  if (rows == 0) return AIMA_MOE_OK;
+  const cudaError_t error = launch_rmsnorm_rows(x, residual, weight, residual_out, norm_out,
+                                                static_cast<int>(rows), eps,
+                                                static_cast<cudaStream_t>(stream));
+  if (error != cudaSuccess) return fail_cuda(error, "launch rmsnorm_rows_kernel");
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_gemv_bf16_launch(const void* weight, const void* x, void* out, uint32_t m,
+                                          uint32_t k, void* stream) {
+  if (weight == nullptr || x == nullptr || out == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "gemv pointer is null");
+  if (m == 0 || k == 0 || k % 256 != 0 || k > 4096)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "gemv needs k a multiple of 256 up to 4096 and m > 0");
+  const cudaError_t error = launch_gemv_bf16(weight, x, out, static_cast<int>(m),
+                                             static_cast<int>(k), static_cast<cudaStream_t>(stream));
+  if (error != cudaSuccess) return fail_cuda(error, "launch gemv_bf16_kernel");
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics* metrics) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  cudaError_t error = cudaStreamSynchronize(handle->last_stream);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaStreamSynchronize");
+  int device_status = 0;
+  error = cudaMemcpy(&device_status, handle->status, sizeof device_status, cudaMemcpyDeviceToHost);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy status word");
+  handle->metrics.device_status = device_status;
+  if (handle->prefill.total_bytes != 0) {
+    error = cudaMemcpy(&handle->metrics.last_padded_routed_rows, handle->prefill.padded_rows,
+                       sizeof(int32_t), cudaMemcpyDeviceToHost);
+    if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy padded row count");
+  }
+  if (metrics != nullptr) {
+    if (metrics->struct_bytes != sizeof(aima_moe_metrics))
+      return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_metrics size mismatch");
+    *metrics = handle->metrics;
+  }
+  if (device_status != 0) {
+    const int reset = reset_decode_sync(handle);
+    if (reset != AIMA_MOE_OK) return reset;
+    return fail(AIMA_MOE_ERR_TIMEOUT, "a bounded device-side wait ran out (status %d); sync state reset",
+                device_status);
+  }
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_release(aima_moe_handle* handle) {
+  if (handle == nullptr) return AIMA_MOE_OK;
+  cudaFree(handle->dev_layers);
+  cudaFree(handle->decode_scratch);
+  prefill_workspace_free(&handle->prefill);
+  delete handle;
+  return AIMA_MOE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,594 @@
+// Prefill MoE half-layer on the GPU: router + top-8, dispatch plan, gather,
+// grouped expert products, shared expert, weighted combine.
+//
+// Stage list and rounding points follow the reference orchestration
+// (native/src/native_moe_prefill.hip.cpp:790-893):
+//   router GEMM -> BF16 logits -> router_topk8_softmax_256_kernel (:234-323)
+//   moe_align_block32_256_kernel (:325-382)            -> here: a deterministic
+//       counting sort into a per-expert offset table (no padding rows)
+//   fused_moe_kernel gate_up -> expert_silu_multiply_kernel (:384-402)
+//   fused_moe_kernel down (x routing weight)           -> moe_sum8_kernel (:404-431)
+//   shared expert (:210-232, 790-826), bf16_add_pair_kernel
+//   (native/src/native_pointwise.hip.cpp:94-107)
+#include "prefill.cuh"
+
+#include "grouped_gemm.cuh"
+
+#include <cstdio>
+#include <math_constants.h>
+
+namespace aima {
+namespace {
+
+// ---------------------------------------------------------------------------
+// Router: canonical FP32 logits of all 256 experts (+ the shared-expert gate
+// row), BF16 rounding, the reference's selection rule and softmax.
+// One warp per token, 16 tokens per block; router rows are staged through
+// shared memory 32 at a time.
+// ---------------------------------------------------------------------------
+constexpr int kRouterWarps = 16;
+constexpr int kRouterChunkRows = 32;
+constexpr int kRouterSmemBytes = kRouterChunkRows * kHidden * 2 + kRouterWarps * 8 * 8;
+
+__global__ void __launch_bounds__(kRouterWarps * 32, 1)
+prefill_router_kernel(const __nv_bfloat16* __restrict__ h2,
+                      const __nv_bfloat16* __restrict__ router,
+                      const __nv_bfloat16* __restrict__ shared_gate,
+                      const float* __restrict__ bias, int quant_eighths, int tokens,
+                      int32_t* __restrict__ ids, float* __restrict__ scores,
+                      float* __restrict__ weights, float* __restrict__ shared_sigmoid,
+                      float* __restrict__ dbg_logits, __nv_bfloat16* __restrict__ dbg_weights) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  uint4* rows_s = reinterpret_cast<uint4*>(smem);
+  float* sel_v_s = reinterpret_cast<float*>(smem + kRouterChunkRows * kHidden * 2);
+  int* sel_i_s = reinterpret_cast<int*>(sel_v_s + kRouterWarps * 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * kRouterWarps + warp;
+  const bool valid = token < tokens;
+
+  float xr[64];
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (valid) v = *(reinterpret_cast<const uint4*>(h2 + static_cast<size_t>(token) * kHidden) + g * 32 + lane);
+    unpack8(v, xr + 8 * g);
+  }
+
+  float v[8];   // lane l holds the logit of expert 32 q + l in v[q]
+  float gate_dot = 0.0f;
+#pragma unroll
+  for (int chunk = 0; chunk < 9; ++chunk) {
+    const int n_rows = (chunk < 8) ? kRouterChunkRows : 1;
+    const __nv_bfloat16* src = (chunk < 8) ? router + static_cast<size_t>(chunk) * kRouterChunkRows * kHidden
+                                           : shared_gate;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_rows * (kHidden / 8); i += blockDim.x) {
+      rows_s[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+    }
+    __syncthreads();
+    if (chunk < 8) {
+      float mine = 0.0f;
+      for (int r = 0; r < kRouterChunkRows; r += 2) {
+        const uint4* r0 = rows_s + r * (kHidden / 8) + lane;
+        const uint4* r1 = r0 + (kHidden / 8);
+        float a = 0.0f, b = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          a = fma8(xr + 8 * i, r0[i * 32], a);
+          b = fma8(xr + 8 * i, r1[i * 32], b);
+        }
+        a = butterfly_sum(a);
+        b = butterfly_sum(b);
+        if (lane == r) mine = a;
+        if (lane == r + 1) mine = b;
+      }
+      v[chunk] = mine;
+    } else {
+      const uint4* r0 = rows_s + lane;
+      float a = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a = fma8(xr + 8 * i, r0[i * 32], a);
+      gate_dot = butterfly_sum(a);
+    }
+  }
+  if (!valid) return;
+
+  // harness hooks, then the BF16 rounding the reference's router GEMM applies
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    float x = v[q];
+    if (bias != nullptr) x = __fadd_rn(x, bias[32 * q + lane]);
+    if (quant_eighths) x = __fmul_rn(rintf(__fmul_rn(x, 8.0f)), 0.125f);
+    v[q] = round_bf16(x);
+    if (dbg_logits != nullptr) dbg_logits[static_cast<size_t>(token) * kExperts + 32 * q + lane] = v[q];
+  }
+
+  // threshold = 8th largest value counting repeats
+  float threshold;
+  {
+    float w[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) w[q] = v[q];
+    float best = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kTopK; ++r) {
+      best = w[0];
+      int best_id = lane;
+#pragma unroll
+      for (int q = 1; q < 8; ++q) {
+        if (w[q] > best) { best = w[q]; best_id = 32 * q + lane; }
+      }
+#pragma unroll
+      for (int s = 16; s >= 1; s >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, s);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_id, s);
+        if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (best_id == 32 * q + lane) w[q] = -CUDART_INF_F;
+      }
+    }
+    threshold = best;
+  }
+
+  // values above the threshold in expert order, then threshold ties in expert
+  // order until eight are held
+  float* sel_v = sel_v_s + warp * 8;
+  int* sel_i = sel_i_s + warp * 8;
+  const unsigned lt_mask = (1u << lane) - 1u;
+  int held = 0;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const bool take = v[q] > threshold;
+    const unsigned m = __ballot_sync(0xffffffffu, take);
+    if (take) {
+      const int pos = held + __popc(m & lt_mask);
+      sel_v[pos] = v[q];
+      sel_i[pos] = 32 * q + lane;
+    }
+    held += __popc(m);
+  }
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const bool take = v[q] == threshold;
+    const unsigned m = __ballot_sync(0xffffffffu, take);
+    if (take) {
+      const int pos = held + __popc(m & lt_mask);
+      if (pos < kTopK) {
+        sel_v[pos] = v[q];
+        sel_i[pos] = 32 * q + lane;
+      }
+    }
+    held += __popc(m);
+  }
+  __syncwarp();
+  float sv[kTopK];
+  int si[kTopK];
+#pragma unroll
+  for (int r = 0; r < kTopK; ++r) { sv[r] = sel_v[r]; si[r] = sel_i[r]; }
+  // fixed 8-wide bitonic network; a pair is exchanged when
+  // (value[left] > value[right]) equals the "ascending" flag of the left index
+#pragma unroll
+  for (int width = 2; width <= kTopK; width *= 2) {
+#pragma unroll
+    for (int stride = width / 2; stride > 0; stride /= 2) {
+#pragma unroll
+      for (int left = 0; left < kTopK; ++left) {
+        const int right = left ^ stride;
+        if (right > left) {
+          const bool ascending = (left & width) != 0;
+          if ((sv[left] > sv[right]) == ascending) {
+            const float tv = sv[left]; sv[left] = sv[right]; sv[right] = tv;
+            const int ti = si[left]; si[left] = si[right]; si[right] = ti;
+          }
+        }
+      }
+    }
+  }
+  float ex[kTopK];
+  float denom = 0.0f;
+#pragma unroll
+  for (int r = 0; r < kTopK; ++r) {
+    ex[r] = det_expf(__fsub_rn(sv[r], sv[0]));
+    denom = __fadd_rn(denom, ex[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < kTopK; ++r) {
+    if (lane == r) {
+      const size_t o = static_cast<size_t>(token) * kTopK + r;
+      const uint16_t wb = float_to_bf16_bits(__fdiv_rn(ex[r], denom));
+      ids[o] = si[r];
+      scores[o] = sv[r];
+      weights[o] = bf16_bits_to_float(wb);
+      if (dbg_weights != nullptr) reinterpret_cast<uint16_t*>(dbg_weights)[o] = wb;
+    }
+  }
+  if (lane == 0) {
+    shared_sigmoid[token] = round_bf16(det_sigmoid(round_bf16(gate_dot)));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Dispatch plan: stable counting sort of the 8T routed rows by expert.
+// A "unit" is the 256 consecutive flat rows one warp owns.
+// ---------------------------------------------------------------------------
+constexpr int kPlanWarps = 8;
+
+__global__ void __launch_bounds__(kPlanWarps * 32)
+plan_count_kernel(const int32_t* __restrict__ ids, int routed_rows,
+                  int32_t* __restrict__ unit_counts) {
+  __shared__ int cnt[kPlanWarps][kExperts];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int e = lane; e < kExperts; e += 32) cnt[warp][e] = 0;
+  __syncwarp();
+  const int unit = blockIdx.x * kPlanWarps + warp;
+  const int row0 = unit * kPlanRowsPerWarp;
+  if (row0 >= routed_rows) return;
+  for (int round = 0; round < kPlanRowsPerWarp / 32; ++round) {
+    const int row = row0 + round * 32 + lane;
+    const bool valid = row < routed_rows;
+    const unsigned active = __ballot_sync(0xffffffffu, valid);
+    if (valid) {
+      const int e = ids[row];
+      const unsigned same = __match_any_sync(active, e);
+      if ((same & ((1u << lane) - 1u)) == 0u) cnt[warp][e] += __popc(same);
+    }
+    __syncwarp();
+  }
+  for (int e = lane; e < kExperts; e += 32) {
+    unit_counts[static_cast<size_t>(unit) * kExperts + e] = cnt[warp][e];
+  }
+}
+
+// One block of 256 threads: per-expert totals, exclusive offsets, per-unit
+// exclusive prefixes (in place), the tile list and the reference's block-32
+// padded row count.
+__global__ void __launch_bounds__(kExperts)
+plan_scan_kernel(int32_t* __restrict__ unit_counts, int units,
+                 int32_t* __restrict__ expert_counts, int32_t* __restrict__ expert_offsets,
+                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row0,
+                 int32_t* __restrict__ tile_rows, int32_t* __restrict__ tile_count,
+                 int32_t* __restrict__ padded_rows) {
+  __shared__ int counts[kExperts];
+  __shared__ int offsets[kExperts + 1];
+  __shared__ int tile_base[kExperts + 1];
+  const int e = threadIdx.x;
+  int running = 0;
+  for (int u = 0; u < units; ++u) {
+    const size_t index = static_cast<size_t>(u) * kExperts + e;
+    const int c = unit_counts[index];
+    unit_counts[index] = running;
+    running += c;
+  }
+  counts[e] = running;
+  __syncthreads();
+  if (e == 0) {
+    int offset = 0, tiles = 0, padded = 0;
+    for (int i = 0; i < kExperts; ++i) {
+      offsets[i] = offset;
+      tile_base[i] = tiles;
+      offset += counts[i];
+      tiles += (counts[i] + kTileRows - 1) / kTileRows;
+      padded += (counts[i] + 31) / 32 * 32;
+    }
+    offsets[kExperts] = offset;
+    tile_base[kExperts] = tiles;
+    *tile_count = tiles;
+    *padded_rows = padded;
+  }
+  __syncthreads();
+  expert_counts[e] = counts[e];
+  expert_offsets[e] = offsets[e];
+  if (e == 0) expert_offsets[kExperts] = offsets[kExperts];
+  const int n_tiles = tile_base[e + 1] - tile_base[e];
+  for (int t = 0; t < n_tiles; ++t) {
+    const int index = tile_base[e] + t;
+    tile_expert[index] = e;
+    tile_row0[index] = offsets[e] + t * kTileRows;
+    tile_rows[index] = min(kTileRows, counts[e] - t * kTileRows);
+  }
+}
+
+__global__ void __launch_bounds__(kPlanWarps * 32)
+plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows,
+                    const int32_t* __restrict__ unit_prefix,
+                    const int32_t* __restrict__ expert_offsets,
+                    int32_t* __restrict__ sorted_rows, int32_t* __restrict__ row_position) {
+  __shared__ int next[kPlanWarps][kExperts];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int unit = blockIdx.x * kPlanWarps + warp;
+  const int row0 = unit * kPlanRowsPerWarp;
+  if (row0 >= routed_rows) return;
+  for (int e = lane; e < kExperts; e += 32) {
+    next[warp][e] = expert_offsets[e] + unit_prefix[static_cast<size_t>(unit) * kExperts + e];
+  }
+  __syncwarp();
+  for (int round = 0; round < kPlanRowsPerWarp / 32; ++round) {
+    const int row = row0 + round * 32 + lane;
+    const bool valid = row < routed_rows;
+    const unsigned active = __ballot_sync(0xffffffffu, valid);
+    if (valid) {
+      const int e = ids[row];
+      const unsigned same = __match_any_sync(active, e);
+      const int rank = __popc(same & ((1u << lane) - 1u));
+      const int pos = next[warp][e] + rank;
+      sorted_rows[pos] = row;
+      row_position[row] = pos;
+      __syncwarp(active);
+      if (rank == 0) next[warp][e] += __popc(same);
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Gather of h2 rows into expert order; one warp per routed row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ h2, const int32_t* __restrict__ sorted_rows,
+                   int routed_rows, __nv_bfloat16* __restrict__ gathered) {
+  const int lane = threadIdx.x & 31;
+  const int pos = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (pos >= routed_rows) return;
+  const int token = sorted_rows[pos] >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(h2 + static_cast<size_t>(token) * kHidden);
+  uint4* dst = reinterpret_cast<uint4*>(gathered + static_cast<size_t>(pos) * kHidden);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i * 32 + lane] = __ldg(src + i * 32 + lane);
+}
+
+// ---------------------------------------------------------------------------
+// Combine: routed = bf16((((r0+r4)+(r1+r5))+(r2+r6))+(r3+r7)) over the eight
+// weighted expert outputs of a token, combined = bf16(routed + shared),
+// out = bf16(residual + combined).  One block of 256 threads per token.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
+               const int32_t* __restrict__ row_position,
+               const __nv_bfloat16* __restrict__ shared_scaled,
+               const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
+               __nv_bfloat16* __restrict__ dbg_routed) {
+  const int token = blockIdx.x;
+  const int t = threadIdx.x;
+  float slot[kTopK][8];
+#pragma unroll
+  for (int s = 0; s < kTopK; ++s) {
+    const int pos = row_position[token * kTopK + s];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(expert_down + static_cast<size_t>(pos) * kHidden) + t),
+            slot[s]);
+  }
+  float sh[8], rs[8];
+  const size_t base = static_cast<size_t>(token) * kHidden;
+  unpack8(__ldg(reinterpret_cast<const uint4*>(shared_scaled + base) + t), sh);
+  unpack8(__ldg(reinterpret_cast<const uint4*>(residual + base) + t), rs);
+  uint32_t packed[4], packed_routed[4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float s04 = __fadd_rn(slot[0][j], slot[4][j]);
+    const float s15 = __fadd_rn(slot[1][j], slot[5][j]);
+    const float s26 = __fadd_rn(slot[2][j], slot[6][j]);
+    const float s37 = __fadd_rn(slot[3][j], slot[7][j]);
+    float sum = __fadd_rn(s04, s15);
+    sum = __fadd_rn(sum, s26);
+    sum = __fadd_rn(sum, s37);
+    const uint16_t routed_bits = float_to_bf16_bits(sum);
+    const float combined = round_bf16(__fadd_rn(bf16_bits_to_float(routed_bits), sh[j]));
+    const uint16_t o = float_to_bf16_bits(__fadd_rn(rs[j], combined));
+    if (j & 1) {
+      packed[j / 2] |= static_cast<uint32_t>(o) << 16;
+      packed_routed[j / 2] |= static_cast<uint32_t>(routed_bits) << 16;
+    } else {
+      packed[j / 2] = o;
+      packed_routed[j / 2] = routed_bits;
+    }
+  }
+  reinterpret_cast<uint4*>(out + base)[t] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  if (dbg_routed != nullptr) {
+    reinterpret_cast<uint4*>(dbg_routed + base)[t] =
+        make_uint4(packed_routed[0], packed_routed[1], packed_routed[2], packed_routed[3]);
+  }
+}
+
+int set_error(char* error, size_t error_bytes, cudaError_t code, const char* what) {
+  std::snprintf(error, error_bytes, "%s: %s (%s)", what, cudaGetErrorName(code),
+                cudaGetErrorString(code));
+  (void)cudaGetLastError();
+  return static_cast<int>(code);
+}
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+struct Layout {
+  size_t ids, scores, weights, sigmoid, unit_counts, counts, offsets, sorted, position,
+      tile_expert, tile_row0, tile_rows, tile_count, padded, gathered, act, down, shared_act,
+      shared_scaled, x0, x1, h2, total;
+};
+
+Layout layout_for(size_t T) {
+  Layout l{};
+  size_t cursor = 0;
+  auto take = [&](size_t bytes) { const size_t at = cursor; cursor += align256(bytes); return at; };
+  const size_t rows = T * kTopK;
+  const size_t units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
+  const size_t tiles = static_cast<size_t>(max_tiles_for(static_cast<int>(T)));
+  l.ids = take(rows * 4);
+  l.scores = take(rows * 4);
+  l.weights = take(rows * 4);
+  l.sigmoid = take(T * 4);
+  l.unit_counts = take(units * kExperts * 4);
+  l.counts = take(kExperts * 4);
+  l.offsets = take((kExperts + 1) * 4);
+  l.sorted = take(rows * 4);
+  l.position = take(rows * 4);
+  l.tile_expert = take(tiles * 4);
+  l.tile_row0 = take(tiles * 4);
+  l.tile_rows = take(tiles * 4);
+  l.tile_count = take(4);
+  l.padded = take(4);
+  l.gathered = take(rows * kHidden * 2);
+  l.act = take(rows * kInter * 2);
+  l.down = take(rows * kHidden * 2);
+  l.shared_act = take(T * kSharedInter * 2);
+  l.shared_scaled = take(T * kHidden * 2);
+  l.x0 = take(T * kHidden * 2);
+  l.x1 = take(T * kHidden * 2);
+  l.h2 = take(T * kHidden * 2);
+  l.total = cursor;
+  return l;
+}
+
+}  // namespace
+
+size_t prefill_workspace_bytes(uint32_t capacity_tokens) {
+  return capacity_tokens == 0 ? 0 : layout_for(capacity_tokens).total;
+}
+
+int prefill_workspace_allocate(PrefillWorkspace* ws, uint32_t capacity_tokens, int sm_count,
+                               char* error, size_t error_bytes) {
+  const Layout l = layout_for(capacity_tokens);
+  cudaError_t code = cudaMalloc(&ws->base, l.total);
+  if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMalloc prefill workspace");
+  code = cudaMemset(ws->base, 0, l.total);
+  if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemset prefill workspace");
+  ws->total_bytes = l.total;
+  ws->capacity = static_cast<int>(capacity_tokens);
+  ws->sm_count = sm_count;
+  uint8_t* b = ws->base;
+  ws->topk_ids = reinterpret_cast<int32_t*>(b + l.ids);
+  ws->topk_scores = reinterpret_cast<float*>(b + l.scores);
+  ws->topk_weights = reinterpret_cast<float*>(b + l.weights);
+  ws->shared_sigmoid = reinterpret_cast<float*>(b + l.sigmoid);
+  ws->unit_counts = reinterpret_cast<int32_t*>(b + l.unit_counts);
+  ws->expert_counts = reinterpret_cast<int32_t*>(b + l.counts);
+  ws->expert_offsets = reinterpret_cast<int32_t*>(b + l.offsets);
+  ws->sorted_rows = reinterpret_cast<int32_t*>(b + l.sorted);
+  ws->row_position = reinterpret_cast<int32_t*>(b + l.position);
+  ws->tile_expert = reinterpret_cast<int32_t*>(b + l.tile_expert);
+  ws->tile_row0 = reinterpret_cast<int32_t*>(b + l.tile_row0);
+  ws->tile_rows = reinterpret_cast<int32_t*>(b + l.tile_rows);
+  ws->tile_count = reinterpret_cast<int32_t*>(b + l.tile_count);
+  ws->padded_rows = reinterpret_cast<int32_t*>(b + l.padded);
+  ws->gathered = reinterpret_cast<__nv_bfloat16*>(b + l.gathered);
+  ws->expert_act = reinterpret_cast<__nv_bfloat16*>(b + l.act);
+  ws->expert_down = reinterpret_cast<__nv_bfloat16*>(b + l.down);
+  ws->shared_act = reinterpret_cast<__nv_bfloat16*>(b + l.shared_act);
+  ws->shared_scaled = reinterpret_cast<__nv_bfloat16*>(b + l.shared_scaled);
+  ws->stack_x0 = reinterpret_cast<__nv_bfloat16*>(b + l.x0);
+  ws->stack_x1 = reinterpret_cast<__nv_bfloat16*>(b + l.x1);
+  ws->stack_h2 = reinterpret_cast<__nv_bfloat16*>(b + l.h2);
+  return AIMA_MOE_OK;
+}
+
+void prefill_workspace_free(PrefillWorkspace* ws) {
+  if (ws->base != nullptr) cudaFree(ws->base);
+  *ws = PrefillWorkspace{};
+}
+
+int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStream_t stream,
+                         int* launches, char* error, size_t error_bytes) {
+  const int T = call.tokens;
+  const int rows = T * kTopK;
+  const aima_moe_debug_views* dbg = call.debug;
+  int count = 0;
+  cudaError_t code;
+
+  static bool router_configured = false;
+  if (!router_configured) {
+    code = cudaFuncSetAttribute(prefill_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kRouterSmemBytes);
+    if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaFuncSetAttribute router");
+    router_configured = true;
+  }
+  prefill_router_kernel<<<(T + kRouterWarps - 1) / kRouterWarps, kRouterWarps * 32, kRouterSmemBytes, stream>>>(
+      static_cast<const __nv_bfloat16*>(call.h2), call.layer.router, call.layer.shared_gate,
+      call.router_bias, call.quant_eighths, T, ws->topk_ids, ws->topk_scores, ws->topk_weights,
+      ws->shared_sigmoid, dbg ? static_cast<float*>(dbg->router_logits) : nullptr,
+      dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "prefill_router_kernel");
+  ++count;
+
+  const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
+  const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
+  plan_count_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ws->topk_ids, rows, ws->unit_counts);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_count_kernel");
+  plan_scan_kernel<<<1, kExperts, 0, stream>>>(ws->unit_counts, units, ws->expert_counts,
+                                               ws->expert_offsets, ws->tile_expert, ws->tile_row0,
+                                               ws->tile_rows, ws->tile_count, ws->padded_rows);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_scan_kernel");
+  plan_scatter_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(
+      ws->topk_ids, rows, ws->unit_counts, ws->expert_offsets, ws->sorted_rows, ws->row_position);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_scatter_kernel");
+  count += 3;
+
+  gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(call.h2), ws->sorted_rows, rows, ws->gathered);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "gather_rows_kernel");
+  ++count;
+
+  // routed experts: gate_up + SwiGLU, then down x routing weight
+  GroupedGemm g{};
+  g.tile_expert = ws->tile_expert; g.tile_row0 = ws->tile_row0; g.tile_rows = ws->tile_rows;
+  g.tile_count = ws->tile_count; g.max_tiles = max_tiles_for(T); g.dense_rows = 0;
+  g.a = ws->gathered; g.lda = kHidden; g.k = kHidden;
+  g.b0 = call.layer.expert_gate_up; g.b1 = nullptr;
+  g.b_expert_stride = static_cast<size_t>(2 * kInter) * kHidden;
+  g.n = kInter; g.c = ws->expert_act; g.ldc = kInter;
+  g.row_scale = nullptr; g.sorted_rows = nullptr;
+  if ((code = launch_grouped_gemm(kGemmExpertGateUp, g, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm expert gate_up");
+  g.a = ws->expert_act; g.lda = kInter; g.k = kInter;
+  g.b0 = call.layer.expert_down; g.b_expert_stride = static_cast<size_t>(kHidden) * kInter;
+  g.n = kHidden; g.c = ws->expert_down; g.ldc = kHidden;
+  g.row_scale = ws->topk_weights; g.sorted_rows = ws->sorted_rows;
+  if ((code = launch_grouped_gemm(kGemmExpertDown, g, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm expert down");
+  count += 2;
+
+  // shared expert as dense products over all tokens
+  GroupedGemm s{};
+  s.tile_expert = nullptr; s.tile_row0 = nullptr; s.tile_rows = nullptr; s.tile_count = nullptr;
+  s.max_tiles = (T + kTileRows - 1) / kTileRows; s.dense_rows = T;
+  s.a = static_cast<const __nv_bfloat16*>(call.h2); s.lda = kHidden; s.k = kHidden;
+  s.b0 = call.layer.shared_gate_proj; s.b1 = call.layer.shared_up_proj; s.b_expert_stride = 0;
+  s.n = kSharedInter; s.c = ws->shared_act; s.ldc = kSharedInter;
+  if ((code = launch_grouped_gemm(kGemmSharedGateUp, s, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm shared gate_up");
+  s.a = ws->shared_act; s.lda = kSharedInter; s.k = kSharedInter;
+  s.b0 = call.layer.shared_down_proj; s.b1 = nullptr;
+  s.n = kHidden; s.c = ws->shared_scaled; s.ldc = kHidden;
+  s.row_scale = ws->shared_sigmoid;
+  if ((code = launch_grouped_gemm(kGemmSharedDown, s, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm shared down");
+  count += 2;
+
+  combine_kernel<<<T, 256, 0, stream>>>(ws->expert_down, ws->row_position, ws->shared_scaled,
+                                        static_cast<const __nv_bfloat16*>(call.residual),
+                                        static_cast<__nv_bfloat16*>(call.out),
+                                        dbg ? static_cast<__nv_bfloat16*>(dbg->routed) : nullptr);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "combine_kernel");
+  ++count;
+
+  if (dbg != nullptr) {
+    auto copy = [&](void* dst, const void* src, size_t bytes) {
+      if (dst != nullptr) return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream);
+      return cudaSuccess;
+    };
+    code = copy(dbg->h2, call.h2, static_cast<size_t>(T) * kHidden * 2);
+    if (code == cudaSuccess) code = copy(dbg->topk_ids, ws->topk_ids, static_cast<size_t>(rows) * 4);
+    if (code == cudaSuccess) code = copy(dbg->topk_scores, ws->topk_scores, static_cast<size_t>(rows) * 4);
+    if (code == cudaSuccess) code = copy(dbg->shared_scaled, ws->shared_scaled, static_cast<size_t>(T) * kHidden * 2);
+    if (code == cudaSuccess) code = copy(dbg->expert_counts, ws->expert_counts, kExperts * 4);
+    if (code == cudaSuccess) code = copy(dbg->expert_offsets, ws->expert_offsets, (kExperts + 1) * 4);
+    if (code == cudaSuccess) code = copy(dbg->sorted_rows, ws->sorted_rows, static_cast<size_t>(rows) * 4);
+    if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemcpyAsync debug views");
+  }
+  *launches = count;
+  return AIMA_MOE_OK;
+}
+
+}  // namespace aima

@@ -1,0 +1,72 @@
+// Prefill MoE half-layer: workspace, per-call description and launcher.
+#pragma once
+
+#include "../../include/aima_moe.h"
+#include "common.cuh"
+
+namespace aima {
+
+constexpr int kTileRows = 128;      // rows of one grouped-GEMM tile (one expert)
+constexpr int kPlanRowsPerWarp = 256;
+
+// Device buffers owned by a handle for prefill calls of up to `capacity` tokens.
+struct PrefillWorkspace {
+  size_t total_bytes = 0;
+  int capacity = 0;
+  int sm_count = 0;
+  uint8_t* base = nullptr;
+  // router outputs
+  int32_t* topk_ids = nullptr;        // [T, 8]
+  float* topk_scores = nullptr;       // [T, 8]
+  float* topk_weights = nullptr;      // [T, 8] BF16-rounded, stored as FP32
+  float* shared_sigmoid = nullptr;    // [T]    bf16(sigmoid(bf16 gate logit)) as FP32
+  // dispatch plan
+  int32_t* unit_counts = nullptr;     // [units, 256] per-warp-unit histogram / prefix
+  int32_t* expert_counts = nullptr;   // [256]
+  int32_t* expert_offsets = nullptr;  // [257]
+  int32_t* sorted_rows = nullptr;     // [8T]  flat (token*8+slot) rows grouped by expert
+  int32_t* row_position = nullptr;    // [8T]  inverse of sorted_rows
+  int32_t* tile_expert = nullptr;     // [max_tiles]
+  int32_t* tile_row0 = nullptr;       // [max_tiles]
+  int32_t* tile_rows = nullptr;       // [max_tiles]
+  int32_t* tile_count = nullptr;      // [1]
+  int32_t* padded_rows = nullptr;     // [1] block-32 padded row count of the reference plan
+  // activations
+  __nv_bfloat16* gathered = nullptr;      // [8T, 2048] h2 rows in sorted order
+  __nv_bfloat16* expert_act = nullptr;    // [8T, 512]
+  __nv_bfloat16* expert_down = nullptr;   // [8T, 2048] weighted, sorted order
+  __nv_bfloat16* shared_act = nullptr;    // [T, 512]
+  __nv_bfloat16* shared_scaled = nullptr; // [T, 2048]
+  // layer-stack buffers
+  __nv_bfloat16* stack_x0 = nullptr;      // [T, 2048]
+  __nv_bfloat16* stack_x1 = nullptr;
+  __nv_bfloat16* stack_h2 = nullptr;
+};
+
+struct PrefillCall {
+  LayerPtrs layer;
+  const void* h2;
+  const void* residual;
+  void* out;
+  int tokens;
+  const float* router_bias;
+  int quant_eighths;
+  const aima_moe_debug_views* debug;
+};
+
+size_t prefill_workspace_bytes(uint32_t capacity_tokens);
+int prefill_workspace_allocate(PrefillWorkspace* workspace, uint32_t capacity_tokens,
+                               int sm_count, char* error, size_t error_bytes);
+void prefill_workspace_free(PrefillWorkspace* workspace);
+
+// Enqueues the whole half-layer on `stream`; `launches` receives the number of
+// kernels enqueued.  Returns an AIMA_MOE_* status.
+int prefill_layer_launch(PrefillWorkspace* workspace, const PrefillCall& call,
+                         cudaStream_t stream, int* launches, char* error,
+                         size_t error_bytes);
+
+inline int max_tiles_for(int tokens) {
+  return tokens * kTopK / kTileRows + kExperts;
+}
+
+}  // namespace aima

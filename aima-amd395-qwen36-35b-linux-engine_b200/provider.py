@@ -1,0 +1,311 @@
+"""ctypes binding of the C ABI in include/aima_moe.h and a provider object with
+the call shape of the reference's Python drop-in point.
+
+The reference loads native providers with ``ctypes.CDLL(path, RTLD_LOCAL)``,
+passes tensors as ``c_void_p(tensor.data_ptr())`` and the stream as
+``c_void_p(torch.cuda.current_stream().cuda_stream)``
+(benchmarks/shape-lab/q8192_compound_provider.py:59-66, 132-141), and calls
+``launch_selected_moe(post_attention=h2, residual_hidden=after_attn,
+weights=<dict of tensors>, model_layer=<int>) -> hidden``
+(benchmarks/shape-lab/four_layer_mini_engine.py:8491-8502; the stub that
+raises "not admitted" is q8192_compound_provider.py:388-389).  MoeProvider
+keeps that signature.
+
+There is no CPU fallback: if the shared library is missing or no sm_100 device
+is present, construction fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int32, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+from typing import Any, Mapping
+
+HIDDEN = 2048
+EXPERTS = 256
+TOP_K = 8
+EXPERT_INTER = 512
+SHARED_INTER = 512
+MAX_LAYERS = 64
+
+_LIB_NAME = "libaima_moe_b200.so"
+
+
+class AimaMoeError(RuntimeError):
+    def __init__(self, status: int, message: str) -> None:
+        super().__init__(f"aima_moe status {status}: {message}")
+        self.status = status
+
+
+class Config(ctypes.Structure):
+    _fields_ = [
+        ("struct_bytes", c_uint32), ("hidden", c_uint32), ("experts", c_uint32),
+        ("top_k", c_uint32), ("expert_inter", c_uint32), ("shared_inter", c_uint32),
+        ("layers", c_uint32), ("max_prefill_tokens", c_uint32), ("world", c_uint32),
+        ("rank", c_uint32), ("rms_eps", c_float), ("flags", c_uint32),
+    ]
+
+
+class LayerWeights(ctypes.Structure):
+    _fields_ = [
+        ("struct_bytes", c_uint32), ("reserved", c_uint32),
+        ("router", c_void_p), ("router_bytes", c_uint64),
+        ("expert_gate_up", c_void_p), ("expert_gate_up_bytes", c_uint64),
+        ("expert_down", c_void_p), ("expert_down_bytes", c_uint64),
+        ("shared_expert_gate", c_void_p), ("shared_expert_gate_bytes", c_uint64),
+        ("shared_gate_proj", c_void_p), ("shared_gate_proj_bytes", c_uint64),
+        ("shared_up_proj", c_void_p), ("shared_up_proj_bytes", c_uint64),
+        ("shared_down_proj", c_void_p), ("shared_down_proj_bytes", c_uint64),
+        ("post_attention_norm", c_void_p), ("post_attention_norm_bytes", c_uint64),
+    ]
+
+
+class DebugViews(ctypes.Structure):
+    _fields_ = [
+        ("struct_bytes", c_uint32), ("reserved", c_uint32),
+        ("h2", c_void_p), ("router_logits", c_void_p), ("topk_ids", c_void_p),
+        ("topk_scores", c_void_p), ("topk_weights", c_void_p), ("shared_scaled", c_void_p),
+        ("routed", c_void_p), ("expert_counts", c_void_p), ("expert_offsets", c_void_p),
+        ("sorted_rows", c_void_p),
+    ]
+
+
+class Metrics(ctypes.Structure):
+    _fields_ = [
+        ("struct_bytes", c_uint32), ("reserved", c_uint32),
+        ("prefill_calls", c_uint64), ("decode_calls", c_uint64), ("kernel_launches", c_uint64),
+        ("workspace_bytes", c_uint64), ("derived_weight_bytes", c_uint64),
+        ("last_padded_routed_rows", c_int32), ("device_status", c_int32),
+    ]
+
+
+# every symbol include/aima_moe.h declares: (name, restype, argtypes)
+EXPORTS = [
+    ("aima_moe_abi_version", c_uint32, []),
+    ("aima_moe_last_error_string", c_char_p, []),
+    ("aima_moe_query_workspace", c_int, [ctypes.POINTER(Config), ctypes.POINTER(c_uint64)]),
+    ("aima_moe_prepare", c_int, [ctypes.POINTER(Config), ctypes.POINTER(c_void_p)]),
+    ("aima_moe_bind_layer", c_int, [c_void_p, c_uint32, ctypes.POINTER(LayerWeights)]),
+    ("aima_moe_set_router_hooks", c_int, [c_void_p, c_void_p, c_int]),
+    ("aima_moe_prefill_launch", c_int,
+     [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_uint32, ctypes.POINTER(DebugViews), c_void_p]),
+    ("aima_moe_decode_launch", c_int,
+     [c_void_p, c_uint32, c_void_p, c_void_p, ctypes.POINTER(DebugViews), c_void_p]),
+    ("aima_moe_decode_stack_launch", c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
+    ("aima_moe_prefill_stack_launch", c_int,
+     [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_uint32, c_void_p]),
+    ("aima_moe_rmsnorm_launch", c_int,
+     [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_float, c_void_p]),
+    ("aima_moe_gemv_bf16_launch", c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    ("aima_moe_sync_metrics", c_int, [c_void_p, ctypes.POINTER(Metrics)]),
+    ("aima_moe_release", c_int, [c_void_p]),
+]
+
+
+def library_path() -> Path:
+    return Path(__file__).resolve().parent / _LIB_NAME
+
+
+class MoeLibrary:
+    """The loaded shared library with typed entry points."""
+
+    def __init__(self, path: Path | None = None) -> None:
+        path = Path(path) if path is not None else library_path()
+        if not path.is_file():
+            raise FileNotFoundError(
+                f"{path} is missing: build it with aima-amd395-qwen36-35b-linux-engine_b200/build.py; "
+                "there is no CPU or PyTorch fallback for this path")
+        self.path = path
+        self.cdll = ctypes.CDLL(str(path), mode=ctypes.RTLD_LOCAL)
+        for name, restype, argtypes in EXPORTS:
+            function = getattr(self.cdll, name)
+            function.restype = restype
+            function.argtypes = argtypes
+            setattr(self, name, function)
+
+    def check(self, status: int) -> None:
+        if status != 0:
+            message = self.aima_moe_last_error_string() or b""
+            raise AimaMoeError(status, message.decode("utf-8", "replace"))
+
+
+_LIBRARY: MoeLibrary | None = None
+
+
+def load_library() -> MoeLibrary:
+    global _LIBRARY
+    if _LIBRARY is None:
+        _LIBRARY = MoeLibrary()
+    return _LIBRARY
+
+
+def _ptr(tensor: Any) -> c_void_p:
+    if tensor is None:
+        return c_void_p(0)
+    if not tensor.is_cuda or not tensor.is_contiguous():
+        raise RuntimeError("aima_moe tensors must be contiguous CUDA tensors")
+    return c_void_p(int(tensor.data_ptr()))
+
+
+def _nbytes(tensor: Any) -> int:
+    return 0 if tensor is None else int(tensor.numel() * tensor.element_size())
+
+
+def _stream(torch: Any) -> c_void_p:
+    return c_void_p(int(torch.cuda.current_stream().cuda_stream))
+
+
+# reference weight-dict keys (four_layer_mini_engine.py: weights["router"],
+# ["expert_gate_up"], ["expert_down"], ["shared_gate"], ["shared_gate_proj"],
+# ["shared_up_proj"], ["shared_down_proj"], ["post_attention_layernorm"])
+WEIGHT_KEYS = ("router", "expert_gate_up", "expert_down", "shared_gate", "shared_gate_proj",
+               "shared_up_proj", "shared_down_proj")
+
+
+class MoeProvider:
+    """Owns one aima_moe handle on the current CUDA device."""
+
+    def __init__(self, layers: int, max_prefill_tokens: int = 0, world: int = 1, rank: int = 0,
+                 rms_eps: float = 1.0e-6, library: MoeLibrary | None = None) -> None:
+        import torch  # device memory and streams only
+
+        if not torch.cuda.is_available():
+            raise RuntimeError("aima_moe needs a CUDA device (sm_100a); there is no CPU fallback")
+        self._torch = torch
+        self.lib = library or load_library()
+        self.layers = layers
+        self.max_prefill_tokens = max_prefill_tokens
+        self.config = Config(ctypes.sizeof(Config), HIDDEN, EXPERTS, TOP_K, EXPERT_INTER, SHARED_INTER,
+                             layers, max_prefill_tokens, world, rank, rms_eps, 0)
+        handle = c_void_p()
+        self.lib.check(self.lib.aima_moe_prepare(ctypes.byref(self.config), ctypes.byref(handle)))
+        self.handle = handle
+        self._keepalive: dict[int, Mapping[str, Any]] = {}
+        self._hook_bias = None
+        self.calls = {"selected_moe": 0, "decode": 0}
+
+    # -- setup ---------------------------------------------------------------
+    def bind_layer(self, layer: int, weights: Mapping[str, Any]) -> None:
+        w = LayerWeights()
+        w.struct_bytes = ctypes.sizeof(LayerWeights)
+        fields = {
+            "router": weights["router"], "expert_gate_up": weights["expert_gate_up"],
+            "expert_down": weights["expert_down"], "shared_expert_gate": weights["shared_gate"],
+            "shared_gate_proj": weights["shared_gate_proj"], "shared_up_proj": weights["shared_up_proj"],
+            "shared_down_proj": weights["shared_down_proj"],
+            "post_attention_norm": weights.get("post_attention_layernorm"),
+        }
+        for name, tensor in fields.items():
+            setattr(w, name, _ptr(tensor))
+            setattr(w, name + "_bytes", _nbytes(tensor))
+        self.lib.check(self.lib.aima_moe_bind_layer(self.handle, layer, ctypes.byref(w)))
+        self._keepalive[layer] = dict(weights)
+
+    def set_router_hooks(self, bias: Any = None, quantize_eighths: bool = False) -> None:
+        self._hook_bias = bias
+        self.lib.check(self.lib.aima_moe_set_router_hooks(self.handle, _ptr(bias), int(quantize_eighths)))
+
+    # -- debug views ---------------------------------------------------------
+    def make_debug(self, tokens: int, prefill: bool) -> tuple[DebugViews, dict[str, Any]]:
+        torch = self._torch
+        dev = torch.device("cuda", torch.cuda.current_device())
+        t = {
+            "h2": torch.empty(tokens, HIDDEN, dtype=torch.bfloat16, device=dev),
+            "router_logits": torch.empty(tokens, EXPERTS, dtype=torch.float32, device=dev),
+            "topk_ids": torch.empty(tokens, TOP_K, dtype=torch.int32, device=dev),
+            "topk_scores": torch.empty(tokens, TOP_K, dtype=torch.float32, device=dev),
+            "topk_weights": torch.empty(tokens, TOP_K, dtype=torch.bfloat16, device=dev),
+            "shared_scaled": torch.empty(tokens, HIDDEN, dtype=torch.bfloat16, device=dev),
+            "routed": torch.empty(tokens, HIDDEN, dtype=torch.bfloat16, device=dev),
+        }
+        if prefill:
+            t["expert_counts"] = torch.empty(EXPERTS, dtype=torch.int32, device=dev)
+            t["expert_offsets"] = torch.empty(EXPERTS + 1, dtype=torch.int32, device=dev)
+            t["sorted_rows"] = torch.empty(tokens * TOP_K, dtype=torch.int32, device=dev)
+        views = DebugViews()
+        views.struct_bytes = ctypes.sizeof(DebugViews)
+        for name, tensor in t.items():
+            setattr(views, name, _ptr(tensor))
+        return views, t
+
+    # -- launches ------------------------------------------------------------
+    def launch_selected_moe(self, *, post_attention: Any, residual_hidden: Any,
+                            weights: Mapping[str, Any] | None = None, model_layer: int,
+                            out: Any = None, debug: DebugViews | None = None) -> Any:
+        """Prefill MoE half of `model_layer`: h2, after_attn -> next hidden [T, 2048]."""
+        torch = self._torch
+        if weights is not None and model_layer not in self._keepalive:
+            self.bind_layer(model_layer, weights)
+        tokens = int(post_attention.shape[0])
+        if out is None:
+            out = torch.empty_like(residual_hidden)
+        self.lib.check(self.lib.aima_moe_prefill_launch(
+            self.handle, model_layer, _ptr(post_attention), _ptr(residual_hidden), _ptr(out), tokens,
+            ctypes.byref(debug) if debug is not None else None, _stream(torch)))
+        self.calls["selected_moe"] += 1
+        return out
+
+    def decode_layer(self, after_attn: Any, model_layer: int, out: Any = None,
+                     debug: DebugViews | None = None) -> Any:
+        torch = self._torch
+        if out is None:
+            out = torch.empty_like(after_attn)
+        self.lib.check(self.lib.aima_moe_decode_launch(
+            self.handle, model_layer, _ptr(after_attn), _ptr(out),
+            ctypes.byref(debug) if debug is not None else None, _stream(torch)))
+        self.calls["decode"] += 1
+        return out
+
+    def decode_stack(self, x_in: Any, x_out: Any, first_layer: int = 0, n_layers: int | None = None) -> Any:
+        torch = self._torch
+        n = self.layers - first_layer if n_layers is None else n_layers
+        self.lib.check(self.lib.aima_moe_decode_stack_launch(
+            self.handle, first_layer, n, _ptr(x_in), _ptr(x_out), _stream(torch)))
+        self.calls["decode"] += n
+        return x_out
+
+    def prefill_stack(self, x_in: Any, x_out: Any, first_layer: int = 0, n_layers: int | None = None) -> Any:
+        torch = self._torch
+        n = self.layers - first_layer if n_layers is None else n_layers
+        self.lib.check(self.lib.aima_moe_prefill_stack_launch(
+            self.handle, first_layer, n, _ptr(x_in), _ptr(x_out), int(x_in.shape[0]), _stream(torch)))
+        return x_out
+
+    def rmsnorm(self, x: Any, weight: Any, residual: Any = None, eps: float = 1.0e-6) -> tuple[Any, Any]:
+        torch = self._torch
+        rows = int(x.numel() // HIDDEN)
+        norm_out = torch.empty_like(x)
+        residual_out = torch.empty_like(x) if residual is not None else None
+        self.lib.check(self.lib.aima_moe_rmsnorm_launch(
+            _ptr(x), _ptr(residual), _ptr(weight), _ptr(residual_out), _ptr(norm_out), rows, eps,
+            _stream(torch)))
+        return residual_out, norm_out
+
+    def gemv(self, weight: Any, x: Any) -> Any:
+        torch = self._torch
+        m, k = int(weight.shape[0]), int(weight.shape[1])
+        out = torch.empty(m, dtype=torch.bfloat16, device=weight.device)
+        self.lib.check(self.lib.aima_moe_gemv_bf16_launch(_ptr(weight), _ptr(x), _ptr(out), m, k, _stream(torch)))
+        return out
+
+    def sync_metrics(self) -> Metrics:
+        metrics = Metrics()
+        metrics.struct_bytes = ctypes.sizeof(Metrics)
+        self.lib.check(self.lib.aima_moe_sync_metrics(self.handle, ctypes.byref(metrics)))
+        return metrics
+
+    def stats(self) -> dict[str, Any]:
+        return {"prepared": self.handle is not None, "call_counts": dict(self.calls),
+                "library": str(self.lib.path)}
+
+    def release(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.aima_moe_release(self.handle)
+            self.handle = None
+            self._keepalive.clear()
+
+    def __del__(self) -> None:  # best effort
+        try:
+            self.release()
+        except Exception:
+            pass

@@ -1,0 +1,298 @@
+#!/usr/bin/env python3
+"""Benchmark of the routed-MoE hot path (BASELINE config 1: batch-1 decode through 40 stacked
+MoE layers; a "step" is one token through the whole stack).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is tokens/s with inputs resident in HBM; `e2e` is the same loop
+driven through the public provider call with the token vector copied from pinned host memory and
+the result read back every step; `roofline` is the algorithmic weight bytes per token
+(2 307 194 880 B = 40 x 57 679 872 B) over the measured time against the measured HBM copy
+bandwidth; `cpu_baseline` times the torch-CPU statement of the reference's MoE path on this
+machine's cores on a bounded sample.  `--impl reference` times only that CPU path.
+Synthetic seeded weights (BF16 N(0, 0.02)) and inputs (BF16 N(0, 1)) stand in for the checkpoint.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LAYERS = 40
+HIDDEN = 2048
+SEED = 1234
+BYTES_PER_LAYER_TOKEN = 1_048_576 + 50_331_648 + 6_295_552 + 4_096       # router, 8 experts, shared, norm
+BYTES_PER_TOKEN = LAYERS * BYTES_PER_LAYER_TOKEN                          # 2 307 194 880
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int) -> None:
+        self.device_index = device_index
+        self.lines: list[str] = []
+        self.process: subprocess.Popen | None = None
+        self.thread: threading.Thread | None = None
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.device_index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        assert self.process is not None and self.process.stdout is not None
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, max_clocks, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clocks.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(max_clocks) if max_clocks else None,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def cpu_reference_tokens_per_second(sample_layers: int, sample_tokens: int, threads: int) -> dict:
+    """Times the torch-CPU statement of the reference's MoE path for one token per layer and
+    extrapolates linearly to the 40-layer stack."""
+    import torch
+
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import moe_torch_ref as ref
+    from __graft_entry__ import load_package
+
+    synth = load_package().synth
+    torch.set_num_threads(threads)
+    generator = torch.Generator().manual_seed(SEED)
+    layers = []
+    for layer in range(sample_layers):
+        weights = synth.layer_small_weights(SEED, layer)
+        # timing does not depend on values: one randn block reused for all experts
+        block = (torch.randn(8, 1024, HIDDEN, generator=generator) * 0.02).to(torch.bfloat16)
+        weights["expert_gate_up"] = block.repeat(32, 1, 1)
+        down = (torch.randn(8, HIDDEN, 512, generator=generator) * 0.02).to(torch.bfloat16)
+        weights["expert_down"] = down.repeat(32, 1, 1)
+        layers.append(weights)
+    x = synth.activations(SEED, 1, "residual", 0)
+
+    def one_token(x):
+        for weights in layers:
+            h2 = ref.rmsnorm(x, weights["post_attention_layernorm"])
+            x = ref.moe_half_layer(h2, x, weights, form="expanded")["out"]
+        return x
+
+    one_token(x)                                   # warm-up
+    start = time.perf_counter()
+    for _ in range(sample_tokens):
+        x = one_token(x)
+    elapsed = time.perf_counter() - start
+    per_layer = elapsed / (sample_tokens * sample_layers)
+    return {"value": 1.0 / (per_layer * LAYERS), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{sample_tokens} tokens x {sample_layers} layers of the torch-CPU statement of the "
+                      f"reference MoE path (router, top-8, expanded bmm experts, shared expert), "
+                      f"per-layer time x {LAYERS}",
+            "seconds": elapsed}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    warm = cpu_reference_tokens_per_second(1, max(1, min(args.warmup, 2)), threads)
+    del warm
+    steps = max(1, min(args.steps, 24))
+    result = cpu_reference_tokens_per_second(2, steps, threads)
+    value = result["value"]
+    line = {
+        "impl": "reference", "metric": "moe_decode_b1_tokens_per_second", "value": value,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "decode_b1_stack40 (BASELINE config 1)", "layers": LAYERS,
+                   "timed_tokens": steps, "note": "CPU path; bounded sample extrapolated to 40 layers"},
+        "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args) -> None:
+    import torch
+    from __graft_entry__ import load_package
+
+    package = load_package()
+    synth = package.synth
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    provider = package.MoeProvider(layers=LAYERS, max_prefill_tokens=0)
+    keep = []
+    for layer in range(LAYERS):
+        weights = synth.layer_weights_cuda_fast(SEED, layer, device)
+        provider.bind_layer(layer, weights)
+        keep.append(weights)
+    torch.cuda.synchronize()
+
+    x0 = synth.activations(SEED, 1, "residual", 0)[0]
+    buffers = [x0.to(device), torch.empty(HIDDEN, dtype=torch.bfloat16, device=device)]
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident loop ----
+    for step in range(args.warmup):
+        provider.decode_stack(buffers[step & 1], buffers[(step + 1) & 1])
+    provider.sync_metrics()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for step in range(args.steps):
+        provider.decode_stack(buffers[(args.warmup + step) & 1], buffers[(args.warmup + step + 1) & 1])
+    stop.record()
+    barrier()
+    device_ms = start.elapsed_time(stop)
+    provider.sync_metrics()
+
+    # ---- end to end through the public call with host buffers ----
+    host_in = torch.empty(HIDDEN, dtype=torch.bfloat16).pin_memory()
+    host_out = torch.empty(HIDDEN, dtype=torch.bfloat16).pin_memory()
+    host_in.copy_(x0)
+    dev_in = torch.empty(HIDDEN, dtype=torch.bfloat16, device=device)
+    dev_out = torch.empty(HIDDEN, dtype=torch.bfloat16, device=device)
+
+    def e2e_step():
+        dev_in.copy_(host_in, non_blocking=True)
+        provider.decode_stack(dev_in, dev_out)
+        host_out.copy_(dev_out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        host_in.copy_(host_out)                    # the token feeds back through host memory
+
+    for _ in range(max(3, args.warmup)):
+        e2e_step()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e_start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e_stop.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop)
+    clocks = sampler.stop()
+    provider.sync_metrics()
+
+    if distributed:
+        times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        device_ms, e2e_ms = (float(v) for v in times.tolist())
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        tokens = args.steps * world                # replicas: every rank decodes its own token stream
+        value = tokens / (device_ms / 1000.0)
+        achieved = BYTES_PER_TOKEN * args.steps / (device_ms / 1000.0) / 1.0e9
+        line = {
+            "metric": "moe_decode_b1_tokens_per_second", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "decode_b1_stack40 (BASELINE config 1)", "layers": LAYERS,
+                       "hidden": HIDDEN, "experts": 256, "top_k": 8,
+                       "l2": "inputs larger than L2 (2.3 GB of weights per step)",
+                       "multi_gpu": "independent replicas" if world > 1 else "single GPU"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_kind,
+                         "bytes_per_step": BYTES_PER_TOKEN},
+            "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s",
+                    "h2d_bytes_per_step": HIDDEN * 2, "d2h_bytes_per_step": HIDDEN * 2},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            baseline = cpu_reference_tokens_per_second(2, 6, os.cpu_count() or 1)
+            line["cpu_baseline"] = {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line))
+    provider.release()
+    if distributed:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=512)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

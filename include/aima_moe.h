@@ -1,0 +1,215 @@
+/*
+ * aima_moe.h -- C ABI of the B200 (sm_100a) routed mixture-of-experts provider.
+ *
+ * The library replaces the MoE half of one transformer layer of the reference
+ * runtime (router -> top-8 -> dispatch plan -> grouped SwiGLU experts +
+ * sigmoid-gated shared expert -> weighted combine -> residual add):
+ *
+ *   prefill  probe_native_q8192_moe_prefill_layer0_oracle
+ *            (native/include/aima/native_moe_prefill.h:91-97,
+ *             native/src/native_moe_prefill.hip.cpp:543-905)
+ *   decode   the MoE half inside run_native_linear_layer / run_native_full_layer
+ *            (native/src/native_linear_layer.hip.cpp:163-187,
+ *             native/src/native_full_layer.hip.cpp:180-203)
+ *
+ * Conventions follow the provider ABI the reference runtime already loads with
+ * dlopen / ctypes (benchmarks/shape-lab/native/src/qrt_ck_fmha_q8192_provider.cpp
+ * :214-325): plain C symbols, raw device pointers, a `void* stream`, and an int
+ * status (0 = success).  Positive statuses are cudaError_t values, negative ones
+ * are the AIMA_MOE_ERR_* codes below.  Nothing throws across this boundary.
+ *
+ * Shapes are those of the Qwen3.6-35B-A3B class model: hidden 2048, 256 routed
+ * experts, top-8, expert intermediate 512, shared intermediate 512.  All
+ * activations and weights are BF16 (uint16_t bit patterns), accumulation FP32.
+ *
+ * Ownership: the caller owns inputs, outputs and weights.  The library
+ * allocates device memory only inside aima_moe_prepare / aima_moe_bind_layer;
+ * every *_launch call is asynchronous on the supplied stream and allocates
+ * nothing.  One host thread per handle at a time.
+ */
+#ifndef AIMA_MOE_H_
+#define AIMA_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AIMA_MOE_HIDDEN 2048
+#define AIMA_MOE_EXPERTS 256
+#define AIMA_MOE_TOP_K 8
+#define AIMA_MOE_EXPERT_INTER 512
+#define AIMA_MOE_SHARED_INTER 512
+#define AIMA_MOE_MAX_LAYERS 64
+
+enum {
+  AIMA_MOE_OK = 0,
+  AIMA_MOE_ERR_INVALID_ARGUMENT = -1, /* null pointer, bad size, bad layer     */
+  AIMA_MOE_ERR_UNSUPPORTED = -2,      /* shape / device the build cannot serve */
+  AIMA_MOE_ERR_NOT_BOUND = -3,        /* layer weights were never bound        */
+  AIMA_MOE_ERR_ALIAS = -4,            /* output aliases an input               */
+  AIMA_MOE_ERR_TIMEOUT = -5,          /* a bounded device-side wait ran out    */
+  AIMA_MOE_ERR_INTERNAL = -6,
+  AIMA_MOE_ERR_NO_DEVICE = -7,        /* no CUDA device / not an sm_100 part   */
+  AIMA_MOE_ERR_CAPACITY = -8          /* tokens exceed the prepared capacity   */
+};
+
+typedef struct aima_moe_handle aima_moe_handle;
+
+/* Replaces the constexpr shape block of native_moe_prefill.hip.cpp:28-34 and
+ * the owners built in NativeResidentEngine::load
+ * (native/src/native_resident_engine.hip.cpp:395-684). */
+typedef struct aima_moe_config {
+  uint32_t struct_bytes;     /* sizeof(aima_moe_config), ABI check            */
+  uint32_t hidden;           /* must be 2048                                  */
+  uint32_t experts;          /* must be 256                                   */
+  uint32_t top_k;            /* must be 8                                     */
+  uint32_t expert_inter;     /* must be 512                                   */
+  uint32_t shared_inter;     /* must be 512                                   */
+  uint32_t layers;           /* 1 .. AIMA_MOE_MAX_LAYERS                      */
+  uint32_t max_prefill_tokens; /* workspace capacity per prefill call; 0 =
+                                  decode only                                 */
+  uint32_t world;            /* expert-parallel ranks (1, 2, 4, 8)            */
+  uint32_t rank;             /* this process' rank                            */
+  float rms_eps;             /* 1e-6 in the reference                         */
+  uint32_t flags;            /* AIMA_MOE_FLAG_*                               */
+} aima_moe_config;
+
+#define AIMA_MOE_FLAG_NONE 0u
+
+/* One layer's tensors in checkpoint layout
+ * (doc/reference/amd395-qwen36-35b-a3b-bf16/qwen36-shape-manifest.json:162-180,
+ * byte sizes enforced as in native_moe_prefill.hip.cpp:588-599 and
+ * native/src/native_decode_bindings.hip.cpp:125-135).  With world > 1,
+ * expert_gate_up / expert_down hold only this rank's contiguous slab of
+ * experts [rank * 256 / world, (rank + 1) * 256 / world). */
+typedef struct aima_moe_layer_weights {
+  uint32_t struct_bytes;
+  uint32_t reserved;
+  const void* router;            uint64_t router_bytes;            /* [256,2048]   1 048 576 */
+  const void* expert_gate_up;    uint64_t expert_gate_up_bytes;    /* [E_local,1024,2048]    */
+  const void* expert_down;       uint64_t expert_down_bytes;       /* [E_local,2048,512]     */
+  const void* shared_expert_gate; uint64_t shared_expert_gate_bytes; /* [1,2048]   4 096     */
+  const void* shared_gate_proj;  uint64_t shared_gate_proj_bytes;  /* [512,2048]   2 097 152 */
+  const void* shared_up_proj;    uint64_t shared_up_proj_bytes;    /* [512,2048]   2 097 152 */
+  const void* shared_down_proj;  uint64_t shared_down_proj_bytes;  /* [2048,512]   2 097 152 */
+  const void* post_attention_norm; uint64_t post_attention_norm_bytes; /* [2048] 4 096; may be
+                                     NULL when only aima_moe_prefill_launch is used */
+} aima_moe_layer_weights;
+
+/* Optional per-call views for qualification, the counterpart of the stage
+ * buffers compare_native_oracle_tensor reads
+ * (native/src/native_moe_prefill.hip.cpp:914-979).  Every member is a device
+ * pointer or NULL. */
+typedef struct aima_moe_debug_views {
+  uint32_t struct_bytes;
+  uint32_t reserved;
+  void* h2;              /* bf16 [T,2048]  (decode: the norm the kernel formed) */
+  void* router_logits;   /* f32  [T,256]   values the selection rule saw        */
+  void* topk_ids;        /* i32  [T,8]                                           */
+  void* topk_scores;     /* f32  [T,8]                                           */
+  void* topk_weights;    /* bf16 [T,8]                                           */
+  void* shared_scaled;   /* bf16 [T,2048]                                        */
+  void* routed;          /* bf16 [T,2048]                                        */
+  void* expert_counts;   /* i32  [256]     prefill only                          */
+  void* expert_offsets;  /* i32  [257]     prefill only                          */
+  void* sorted_rows;     /* i32  [8T]      prefill only                          */
+} aima_moe_debug_views;
+
+/* Counters in the spirit of NativeMoePrefillMetrics
+ * (native/include/aima/native_moe_prefill.h:22-35). */
+typedef struct aima_moe_metrics {
+  uint32_t struct_bytes;
+  uint32_t reserved;
+  uint64_t prefill_calls;
+  uint64_t decode_calls;
+  uint64_t kernel_launches;      /* kernels of this library enqueued so far   */
+  uint64_t workspace_bytes;      /* device bytes owned by the handle          */
+  uint64_t derived_weight_bytes; /* device bytes of re-laid-out weight copies */
+  int32_t last_padded_routed_rows; /* block-32 padded rows of the last prefill
+                                      call fetched with aima_moe_sync_metrics */
+  int32_t device_status;         /* last device status word read              */
+} aima_moe_metrics;
+
+/* Validates the configuration, selects the current CUDA device, allocates the
+ * workspace.  Replaces the owner construction in
+ * native/src/native_resident_engine.hip.cpp:453-571. */
+int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle** handle);
+
+/* Checks and records one layer's weight pointers (name -> tensor resolution of
+ * native_moe_prefill.hip.cpp:588-599, native_decode_bindings.hip.cpp:73-106). */
+int aima_moe_bind_layer(aima_moe_handle* handle, uint32_t layer,
+                        const aima_moe_layer_weights* weights);
+
+/* Harness hook without a counterpart in the reference: an additive FP32 router
+ * bias [256] (device pointer, may be NULL) and rounding of router logits to
+ * multiples of 1/8, used to build skewed and tie-heavy routing in benchmarks. */
+int aima_moe_set_router_hooks(aima_moe_handle* handle, const void* bias_f32,
+                              int quantize_eighths);
+
+/* Prefill MoE half of `layer` for `tokens` rows.
+ * h2 = post-attention RMSNorm output, residual = after_attn, both bf16
+ * [tokens,2048]; out bf16 [tokens,2048] = bf16(residual + bf16(routed + shared)).
+ * Replaces probe_native_q8192_moe_prefill_layer0_oracle in its production form
+ * (collect_oracle_comparisons = false), native_resident_engine.hip.cpp:1061-1094. */
+int aima_moe_prefill_launch(aima_moe_handle* handle, uint32_t layer,
+                            const void* h2, const void* residual, void* out,
+                            uint32_t tokens, const aima_moe_debug_views* debug,
+                            void* stream);
+
+/* Decode (one token) MoE half of `layer`: forms h2 = RMSNorm(after_attn) with
+ * the bound post-attention norm weight, then router, shared expert, the eight
+ * routed experts and the residual add.  after_attn, out: bf16 [2048].
+ * Replaces launches[base+4 .. base+9] and the native ops between them in
+ * native_linear_layer.hip.cpp:163-187. */
+int aima_moe_decode_launch(aima_moe_handle* handle, uint32_t layer,
+                           const void* after_attn, void* out,
+                           const aima_moe_debug_views* debug, void* stream);
+
+/* Decode through `n_layers` consecutive layers starting at `first_layer` in one
+ * persistent launch; layer l+1 consumes layer l's output as its residual
+ * stream.  x_in, x_out: bf16 [2048], must not alias. */
+int aima_moe_decode_stack_launch(aima_moe_handle* handle, uint32_t first_layer,
+                                 uint32_t n_layers, const void* x_in,
+                                 void* x_out, void* stream);
+
+/* Prefill through consecutive layers: per layer h2 = RMSNorm(x), residual = x.
+ * x_in, x_out: bf16 [tokens,2048]; x_out may equal x_in. */
+int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t first_layer,
+                                  uint32_t n_layers, const void* x_in,
+                                  void* x_out, uint32_t tokens, void* stream);
+
+/* Residual add + RMSNorm with the (weight + 1) rule
+ * (native/src/native_pointwise.hip.cpp:109-182).  residual may be NULL (plain
+ * norm); residual_out may be NULL. */
+int aima_moe_rmsnorm_launch(const void* x, const void* residual,
+                            const void* weight, void* residual_out,
+                            void* norm_out, uint32_t rows, float eps,
+                            void* stream);
+
+/* Batch-1 GEMV out[m] = bf16(x[k] . W[m,k]), k in {512, 2048, 4096}: the
+ * contract of launch_bf16_wvsplitk (native/src/bf16_wvsplitk.hip.cpp:337-366). */
+int aima_moe_gemv_bf16_launch(const void* weight, const void* x, void* out,
+                              uint32_t m, uint32_t k, void* stream);
+
+/* Synchronises the handle's last stream, reads the device status word and the
+ * padded-row counter; returns AIMA_MOE_ERR_TIMEOUT if a bounded wait ran out. */
+int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics* metrics);
+
+/* Device bytes prepare() would allocate for this configuration. */
+int aima_moe_query_workspace(const aima_moe_config* config, uint64_t* bytes);
+
+int aima_moe_release(aima_moe_handle* handle);
+
+/* Message of the last failing call on this thread ("" if none). */
+const char* aima_moe_last_error_string(void);
+
+/* ABI version of this header: major << 16 | minor. */
+uint32_t aima_moe_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIMA_MOE_H_ */

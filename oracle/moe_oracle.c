@@ -1,0 +1,547 @@
+/*
+ * CPU oracle for the routed mixture-of-experts layer (TEST INFRASTRUCTURE ONLY).
+ *
+ * This file is a plain-C restatement of the reference engine's MoE half-layer
+ * and is used only as the checker in tests, in the smoke check and as the timed
+ * CPU baseline of the benchmark.  The product (the CUDA library) never links,
+ * loads or calls it.
+ *
+ * PARITY UNPINNED for routed-expert values: the reference repository ships no
+ * numeric fixtures for this path (its oracle .bin files are not committed).
+ * What is pinned here: the order-independent known-answer hashes of the
+ * reference's wvSplitK pattern probe (native/src/bf16_wvsplitk.hip.cpp:218-333,
+ * benchmarks/results/native-wvsplitk-v0.1.0.json:52,73), the all-ones GEMM
+ * value (native/src/bf16_gemm.hip.cpp:281-291) and, through committed golden
+ * vectors produced with torch CPU ops, the torch statement of the layer
+ * (benchmarks/shape-lab/four_layer_mini_engine.py:7775-7804, 8286-8303,
+ * 8634-8639, 5127-5128).
+ *
+ * Floating-point contract.  The reference leaves FP32 summation order to its
+ * libraries (hipBLASLt, Triton tl.sum).  Routing must be bit-exact, so this
+ * oracle fixes ONE order, the same one the CUDA kernels use:
+ *
+ *   dot(x, w, K)   32 partial sums p[l]; p[l] accumulates, with fused
+ *                  multiply-add and in ascending k, every k whose 8-element
+ *                  group index (k / 8) is congruent to l modulo 32; the 32
+ *                  partials are then combined by the butterfly
+ *                  p[l] += p[l ^ s] for s = 16, 8, 4, 2, 1.
+ *   sumsq(x)       256 partial sums over 8 consecutive elements each, butterfly
+ *                  inside each group of 32 partials, then the 8 group sums are
+ *                  added left to right.
+ *   exp            aima_or_expf below (range reduction + degree-6 polynomial,
+ *                  only IEEE fma/mul/add, so CPU and GPU agree bit for bit).
+ *   rsqrt          (float)(1.0 / sqrt((double)v)) -- the reference demands the
+ *                  correctly rounded FP32 reciprocal square root
+ *                  (native/src/native_pointwise.hip.cpp:37-69).
+ *
+ * Build: gcc -O2 -fPIC -shared -fopenmp -mfma -ffp-contract=off (see Makefile).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define AIMA_H 2048      /* hidden size                                        */
+#define AIMA_E 256       /* routed experts                                     */
+#define AIMA_K 8         /* experts per token                                  */
+#define AIMA_I 512       /* expert intermediate size (gate_up rows = 2 * I)    */
+#define AIMA_SI 512      /* shared-expert intermediate size                    */
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ----------------------------------------------------------------------- */
+/* scalar helpers                                                           */
+/* ----------------------------------------------------------------------- */
+
+static inline float bf2f(uint16_t bits) {
+  uint32_t u = (uint32_t)bits << 16;
+  float f;
+  memcpy(&f, &u, sizeof f);
+  return f;
+}
+
+/* round-to-nearest-even FP32 -> BF16 (finite inputs; NaN kept quiet) */
+static inline uint16_t f2bf(float f) {
+  uint32_t u;
+  memcpy(&u, &f, sizeof u);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+float aima_or_bf16_to_float(uint16_t b) { return bf2f(b); }
+uint16_t aima_or_float_to_bf16(float f) { return f2bf(f); }
+
+/* Deterministic e^x.  2^n * P(r), n = rint(x * log2 e), r = x - n ln 2. */
+float aima_or_expf(float x) {
+  x = fminf(fmaxf(x, -87.0f), 88.0f);
+  const float t = x * 1.44269504088896341f;
+  const float n = rintf(t);
+  float r = fmaf(n, -0.693145751953125f, x);
+  r = fmaf(n, -1.42860682030941723e-06f, r);
+  float p = 1.0f / 720.0f;
+  p = fmaf(p, r, 1.0f / 120.0f);
+  p = fmaf(p, r, 1.0f / 24.0f);
+  p = fmaf(p, r, 1.0f / 6.0f);
+  p = fmaf(p, r, 0.5f);
+  p = fmaf(p, r, 1.0f);
+  p = fmaf(p, r, 1.0f);
+  const int32_t e = (int32_t)n + 127;
+  const uint32_t scale_bits = (uint32_t)e << 23;
+  float scale;
+  memcpy(&scale, &scale_bits, sizeof scale);
+  return p * scale;
+}
+
+static inline float silu_f32(float g) {
+  return g / (1.0f + aima_or_expf(-g));
+}
+static inline float sigmoid_f32(float g) {
+  return 1.0f / (1.0f + aima_or_expf(-g));
+}
+
+/* canonical dot product, K a multiple of 256 */
+float aima_or_dot(const uint16_t* x, const uint16_t* w, int k_size) {
+  float p[32];
+  for (int l = 0; l < 32; ++l) p[l] = 0.0f;
+  for (int i = 0; i < k_size / 256; ++i) {
+    for (int l = 0; l < 32; ++l) {
+      const int base = 256 * i + 8 * l;
+      float acc = p[l];
+      for (int j = 0; j < 8; ++j) {
+        acc = fmaf(bf2f(x[base + j]), bf2f(w[base + j]), acc);
+      }
+      p[l] = acc;
+    }
+  }
+  for (int s = 16; s >= 1; s >>= 1) {
+    float q[32];
+    for (int l = 0; l < 32; ++l) q[l] = p[l] + p[l ^ s];
+    memcpy(p, q, sizeof p);
+  }
+  return p[0];
+}
+
+/* canonical sum of squares of one 2048-wide row */
+static float sumsq_2048(const uint16_t* x) {
+  float part[256];
+  for (int t = 0; t < 256; ++t) {
+    float acc = 0.0f;
+    for (int j = 0; j < 8; ++j) {
+      const float v = bf2f(x[8 * t + j]);
+      acc = fmaf(v, v, acc);
+    }
+    part[t] = acc;
+  }
+  float total = 0.0f;
+  for (int g = 0; g < 8; ++g) {
+    float p[32];
+    memcpy(p, part + 32 * g, sizeof p);
+    for (int s = 16; s >= 1; s >>= 1) {
+      float q[32];
+      for (int l = 0; l < 32; ++l) q[l] = p[l] + p[l ^ s];
+      memcpy(p, q, sizeof p);
+    }
+    total = (g == 0) ? p[0] : total + p[0];
+  }
+  return total;
+}
+
+static inline float rsqrt_cr(float v) {
+  return (float)(1.0 / sqrt((double)v));
+}
+
+/* ----------------------------------------------------------------------- */
+/* RMSNorm                                                                  */
+/* native/src/native_pointwise.hip.cpp:109-182 (prefill_rmsnorm_2048_kernel, */
+/* prefill_add_rmsnorm_2048_kernel); four_layer_mini_engine.py:844-885,      */
+/* 5127-5128: out = bf16(v * rsqrt(mean(v^2) + eps) * (weight + 1)).         */
+/* With `residual` non-null the input is first replaced by bf16(x + residual)*/
+/* which is also written to residual_out.                                    */
+/* ----------------------------------------------------------------------- */
+void aima_or_rmsnorm(const uint16_t* x, const uint16_t* residual,
+                     const uint16_t* weight, uint16_t* residual_out,
+                     uint16_t* norm_out, int rows, float eps) {
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < rows; ++row) {
+    uint16_t v[AIMA_H];
+    const uint16_t* xr = x + (size_t)row * AIMA_H;
+    if (residual != NULL) {
+      const uint16_t* rr = residual + (size_t)row * AIMA_H;
+      for (int h = 0; h < AIMA_H; ++h) v[h] = f2bf(bf2f(xr[h]) + bf2f(rr[h]));
+      if (residual_out != NULL)
+        memcpy(residual_out + (size_t)row * AIMA_H, v, sizeof v);
+    } else {
+      memcpy(v, xr, sizeof v);
+    }
+    const float inv = rsqrt_cr(sumsq_2048(v) / (float)AIMA_H + eps);
+    uint16_t* out = norm_out + (size_t)row * AIMA_H;
+    for (int h = 0; h < AIMA_H; ++h) {
+      const float scaled = bf2f(v[h]) * inv;
+      out[h] = f2bf(scaled * (bf2f(weight[h]) + 1.0f));
+    }
+  }
+}
+
+/* ----------------------------------------------------------------------- */
+/* Router                                                                   */
+/* ----------------------------------------------------------------------- */
+
+/* FP32 router logits of one token; optional harness-only hooks: an additive
+ * per-expert bias and rounding to multiples of 1/8 (the reference has neither;
+ * they exist to produce skewed and tie-heavy routing in benchmarks).
+ * Prefill: native/src/native_moe_prefill.hip.cpp:829 (router GEMM, FP32
+ * accumulate).  Decode: four_layer_mini_engine.py:391-415. */
+void aima_or_router_logits(const uint16_t* h2, const uint16_t* router,
+                           const float* bias, int quant_eighths,
+                           float* logits) {
+  for (int e = 0; e < AIMA_E; ++e) {
+    float v = aima_or_dot(h2, router + (size_t)e * AIMA_H, AIMA_H);
+    if (bias != NULL) v = v + bias[e];
+    if (quant_eighths) v = rintf(v * 8.0f) * 0.125f;
+    logits[e] = v;
+  }
+}
+
+static void softmax8(const float* s, float* scores, uint16_t* weights) {
+  /* native_moe_prefill.hip.cpp:308-322 and four_layer_mini_engine.py:469-471:
+   * exp(s_r - s_0) / sum, s_0 being the largest selected value. */
+  float ex[AIMA_K];
+  float denom = 0.0f;
+  for (int r = 0; r < AIMA_K; ++r) {
+    ex[r] = aima_or_expf(s[r] - s[0]);
+    denom = denom + ex[r];
+  }
+  for (int r = 0; r < AIMA_K; ++r) {
+    scores[r] = s[r];
+    weights[r] = f2bf(ex[r] / denom);
+  }
+}
+
+/* Prefill selection rule, native/src/native_moe_prefill.hip.cpp:234-323
+ * (router_topk8_softmax_256_kernel).  `logits` are the values the rule sees
+ * (already BF16-rounded by the caller for the prefill path).
+ *   1. threshold = the 8th largest value, counting repeats;
+ *   2. take every index whose value exceeds the threshold in ascending index
+ *      order, then indices equal to the threshold, ascending, until 8 are held;
+ *   3. order the 8 with the fixed bitonic network that exchanges the pair
+ *      (left, left ^ stride) when (value[left] > value[right]) equals the
+ *      "ascending" flag (left & width) != 0. */
+void aima_or_topk_prefill(const float* logits, int32_t* ids, float* scores,
+                          uint16_t* weights) {
+  int taken[AIMA_K];
+  float threshold = 0.0f;
+  for (int r = 0; r < AIMA_K; ++r) {
+    float best = -INFINITY;
+    int best_e = -1;
+    for (int e = 0; e < AIMA_E; ++e) {
+      int used = 0;
+      for (int q = 0; q < r; ++q) used |= (taken[q] == e);
+      if (!used && logits[e] > best) {
+        best = logits[e];
+        best_e = e;
+      }
+    }
+    taken[r] = best_e;
+    threshold = best;
+  }
+  float sv[AIMA_K];
+  int si[AIMA_K];
+  int n = 0;
+  for (int e = 0; e < AIMA_E; ++e)
+    if (logits[e] > threshold) { sv[n] = logits[e]; si[n] = e; ++n; }
+  for (int e = 0; e < AIMA_E && n < AIMA_K; ++e)
+    if (logits[e] == threshold) { sv[n] = logits[e]; si[n] = e; ++n; }
+  for (int width = 2; width <= AIMA_K; width *= 2) {
+    for (int stride = width / 2; stride > 0; stride /= 2) {
+      for (int left = 0; left < AIMA_K; ++left) {
+        const int right = left ^ stride;
+        if (right <= left) continue;
+        const int ascending = (left & width) != 0;
+        if ((sv[left] > sv[right]) == ascending) {
+          const float tv = sv[left]; sv[left] = sv[right]; sv[right] = tv;
+          const int ti = si[left]; si[left] = si[right]; si[right] = ti;
+        }
+      }
+    }
+  }
+  for (int r = 0; r < AIMA_K; ++r) ids[r] = si[r];
+  softmax8(sv, scores, weights);
+}
+
+/* Decode selection rule, four_layer_mini_engine.py:416-423, 438-444, 462-468
+ * (triton_router_topk_stage1/stage2): eight rounds of arg-max, equal values
+ * resolved to the lowest expert id; result in selection order. */
+void aima_or_topk_decode(const float* logits, int32_t* ids, float* scores,
+                         uint16_t* weights) {
+  float v[AIMA_E];
+  memcpy(v, logits, sizeof v);
+  float sv[AIMA_K];
+  for (int r = 0; r < AIMA_K; ++r) {
+    float best = -INFINITY;
+    int best_e = AIMA_E;
+    for (int e = 0; e < AIMA_E; ++e)
+      if (v[e] > best) { best = v[e]; best_e = e; }
+    if (best_e == AIMA_E) best_e = r; /* all -inf: cannot occur for finite input */
+    ids[r] = best_e;
+    sv[r] = best;
+    v[best_e] = -INFINITY;
+  }
+  softmax8(sv, scores, weights);
+}
+
+/* ----------------------------------------------------------------------- */
+/* Layer weights in checkpoint layout                                       */
+/* (doc/reference/amd395-qwen36-35b-a3b-bf16/qwen36-shape-manifest.json:162-180)
+ * Expert tensors are passed per expert so that tests may materialise only the
+ * experts a case selects; a NULL entry that gets selected is an error.       */
+/* ----------------------------------------------------------------------- */
+typedef struct {
+  const uint16_t* router;            /* [256, 2048]                           */
+  const uint16_t* const* gate_up;    /* 256 pointers to [1024, 2048]          */
+  const uint16_t* const* down;       /* 256 pointers to [2048, 512]           */
+  const uint16_t* shared_gate;       /* [1, 2048]                             */
+  const uint16_t* shared_gate_proj;  /* [512, 2048]                           */
+  const uint16_t* shared_up_proj;    /* [512, 2048]                           */
+  const uint16_t* shared_down_proj;  /* [2048, 512]                           */
+  const uint16_t* norm_weight;       /* [2048] post-attention RMSNorm, or NULL*/
+  const float* router_bias;          /* [256] or NULL (harness hook)          */
+  int32_t router_quant_eighths;      /* harness hook                          */
+} aima_or_layer;
+
+typedef struct {
+  uint16_t* h2;            /* [T, 2048]   (decode: computed; prefill: echo)   */
+  float* logits;           /* [T, 256]    values the selection rule saw       */
+  int32_t* ids;            /* [T, 8]                                          */
+  float* scores;           /* [T, 8]                                          */
+  uint16_t* weights;       /* [T, 8]                                          */
+  uint16_t* shared_scaled; /* [T, 2048]                                       */
+  uint16_t* routed;        /* [T, 2048]                                       */
+} aima_or_debug;
+
+/* shared expert.  prefill: native_moe_prefill.hip.cpp:210-232, 790-826;
+ * decode: native/src/native_pointwise.hip.cpp:184-205 + the fused 1025-wide
+ * projection (four_layer_mini_engine.py:304-326); torch statement :8286-8303.
+ * Both modes round the three projections and the down product to BF16. */
+static void shared_expert(const uint16_t* h2, const aima_or_layer* L,
+                          uint16_t* shared_scaled) {
+  const uint16_t gate_logit = f2bf(aima_or_dot(h2, L->shared_gate, AIMA_H));
+  uint16_t act[AIMA_SI];
+  for (int i = 0; i < AIMA_SI; ++i) {
+    const float g = bf2f(f2bf(aima_or_dot(
+        h2, L->shared_gate_proj + (size_t)i * AIMA_H, AIMA_H)));
+    const float u = bf2f(f2bf(aima_or_dot(
+        h2, L->shared_up_proj + (size_t)i * AIMA_H, AIMA_H)));
+    act[i] = f2bf(silu_f32(g) * u);
+  }
+  const float sig = bf2f(f2bf(sigmoid_f32(bf2f(gate_logit))));
+  for (int h = 0; h < AIMA_H; ++h) {
+    const float d = bf2f(f2bf(aima_or_dot(
+        act, L->shared_down_proj + (size_t)h * AIMA_SI, AIMA_SI)));
+    shared_scaled[h] = f2bf(sig * d);
+  }
+}
+
+/* Decode MoE half of one layer for ONE token.
+ * native/src/native_linear_layer.hip.cpp:163-187 (sequence),
+ * four_layer_mini_engine.py:1152-1220 (raw_row_gate_up_activation_kernel,
+ * raw_row_down_sum_kernel), native_pointwise.hip.cpp:94-107 (add pair).
+ * after_attn [2048] -> out [2048].  Returns 0, or -1 if a selected expert's
+ * weights were not supplied. */
+int aima_or_decode_layer(const uint16_t* after_attn, const aima_or_layer* L,
+                         float eps, uint16_t* out, aima_or_debug* dbg) {
+  uint16_t h2[AIMA_H];
+  aima_or_rmsnorm(after_attn, NULL, L->norm_weight, NULL, h2, 1, eps);
+  float logits[AIMA_E];
+  aima_or_router_logits(h2, L->router, L->router_bias,
+                        L->router_quant_eighths, logits);
+  int32_t ids[AIMA_K];
+  float scores[AIMA_K];
+  uint16_t weights[AIMA_K];
+  aima_or_topk_decode(logits, ids, scores, weights);
+  for (int r = 0; r < AIMA_K; ++r)
+    if (L->gate_up[ids[r]] == NULL || L->down[ids[r]] == NULL) return -1;
+
+  uint16_t shared_scaled[AIMA_H];
+  shared_expert(h2, L, shared_scaled);
+
+  uint16_t act[AIMA_K * AIMA_I];
+#pragma omp parallel for schedule(static) collapse(2)
+  for (int r = 0; r < AIMA_K; ++r) {
+    for (int i = 0; i < AIMA_I; ++i) {
+      const uint16_t* wg = L->gate_up[ids[r]] + (size_t)i * AIMA_H;
+      const uint16_t* wu = wg + (size_t)AIMA_I * AIMA_H;
+      const float g = aima_or_dot(h2, wg, AIMA_H);
+      const float u = aima_or_dot(h2, wu, AIMA_H);
+      act[r * AIMA_I + i] = f2bf(silu_f32(g) * u);
+    }
+  }
+  uint16_t routed[AIMA_H];
+#pragma omp parallel for schedule(static)
+  for (int h = 0; h < AIMA_H; ++h) {
+    float acc = 0.0f;
+    for (int r = 0; r < AIMA_K; ++r) {
+      const float d = aima_or_dot(act + r * AIMA_I,
+                                  L->down[ids[r]] + (size_t)h * AIMA_I, AIMA_I);
+      acc = fmaf(bf2f(weights[r]), d, acc);
+    }
+    routed[h] = f2bf(acc);
+    const float combined = bf2f(f2bf(bf2f(routed[h]) + bf2f(shared_scaled[h])));
+    out[h] = f2bf(bf2f(after_attn[h]) + combined);
+  }
+  if (dbg != NULL) {
+    if (dbg->h2) memcpy(dbg->h2, h2, sizeof h2);
+    if (dbg->logits) memcpy(dbg->logits, logits, sizeof logits);
+    if (dbg->ids) memcpy(dbg->ids, ids, sizeof ids);
+    if (dbg->scores) memcpy(dbg->scores, scores, sizeof scores);
+    if (dbg->weights) memcpy(dbg->weights, weights, sizeof weights);
+    if (dbg->shared_scaled) memcpy(dbg->shared_scaled, shared_scaled, sizeof shared_scaled);
+    if (dbg->routed) memcpy(dbg->routed, routed, sizeof routed);
+  }
+  return 0;
+}
+
+/* Prefill MoE half of one layer for the `n_sel` tokens listed in `sel`
+ * (NULL = tokens 0..n_sel-1).  native/src/native_moe_prefill.hip.cpp:790-893:
+ * BF16-rounded router logits -> prefill selection rule; expert gate_up product
+ * rounded to BF16, act = bf16(f32(bf16(silu(g))) * u) (:384-402); down product
+ * times the BF16 routing weight rounded to BF16 per slot; slots summed as
+ * (((r0+r4)+(r1+r5))+(r2+r6))+(r3+r7) in FP32 (:404-431); then
+ * native_pointwise.hip.cpp:94-107.  Outputs are indexed by position in `sel`.
+ * h2/residual are the full [T, 2048] inputs. */
+int aima_or_prefill_layer(const uint16_t* h2_all, const uint16_t* residual_all,
+                          const aima_or_layer* L, const int32_t* sel, int n_sel,
+                          uint16_t* out, aima_or_debug* dbg) {
+  int failed = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int s = 0; s < n_sel; ++s) {
+    const size_t t = sel ? (size_t)sel[s] : (size_t)s;
+    const uint16_t* h2 = h2_all + t * AIMA_H;
+    const uint16_t* resid = residual_all + t * AIMA_H;
+    float logits[AIMA_E];
+    aima_or_router_logits(h2, L->router, L->router_bias,
+                          L->router_quant_eighths, logits);
+    for (int e = 0; e < AIMA_E; ++e) logits[e] = bf2f(f2bf(logits[e]));
+    int32_t ids[AIMA_K];
+    float scores[AIMA_K];
+    uint16_t weights[AIMA_K];
+    aima_or_topk_prefill(logits, ids, scores, weights);
+    int missing = 0;
+    for (int r = 0; r < AIMA_K; ++r)
+      if (L->gate_up[ids[r]] == NULL || L->down[ids[r]] == NULL) missing = 1;
+    if (missing) { failed = 1; continue; }
+
+    uint16_t shared_scaled[AIMA_H];
+    shared_expert(h2, L, shared_scaled);
+
+    uint16_t* slot_out = (uint16_t*)malloc(sizeof(uint16_t) * AIMA_K * AIMA_H);
+    for (int r = 0; r < AIMA_K; ++r) {
+      uint16_t act[AIMA_I];
+      for (int i = 0; i < AIMA_I; ++i) {
+        const uint16_t* wg = L->gate_up[ids[r]] + (size_t)i * AIMA_H;
+        const uint16_t* wu = wg + (size_t)AIMA_I * AIMA_H;
+        const float g = bf2f(f2bf(aima_or_dot(h2, wg, AIMA_H)));
+        const float u = bf2f(f2bf(aima_or_dot(h2, wu, AIMA_H)));
+        const float silu = bf2f(f2bf(silu_f32(g)));
+        act[i] = f2bf(silu * u);
+      }
+      const float wr = bf2f(weights[r]);
+      for (int h = 0; h < AIMA_H; ++h) {
+        const float d = aima_or_dot(act, L->down[ids[r]] + (size_t)h * AIMA_I,
+                                    AIMA_I);
+        slot_out[r * AIMA_H + h] = f2bf(d * wr);
+      }
+    }
+    uint16_t routed[AIMA_H];
+    for (int h = 0; h < AIMA_H; ++h) {
+      const float s04 = bf2f(slot_out[h]) + bf2f(slot_out[4 * AIMA_H + h]);
+      const float s15 = bf2f(slot_out[AIMA_H + h]) + bf2f(slot_out[5 * AIMA_H + h]);
+      const float s26 = bf2f(slot_out[2 * AIMA_H + h]) + bf2f(slot_out[6 * AIMA_H + h]);
+      const float s37 = bf2f(slot_out[3 * AIMA_H + h]) + bf2f(slot_out[7 * AIMA_H + h]);
+      float sum = s04 + s15;
+      sum = sum + s26;
+      sum = sum + s37;
+      routed[h] = f2bf(sum);
+      const float combined = bf2f(f2bf(bf2f(routed[h]) + bf2f(shared_scaled[h])));
+      out[(size_t)s * AIMA_H + h] = f2bf(bf2f(resid[h]) + combined);
+    }
+    free(slot_out);
+    if (dbg != NULL) {
+      if (dbg->h2) memcpy(dbg->h2 + (size_t)s * AIMA_H, h2, sizeof(uint16_t) * AIMA_H);
+      if (dbg->logits) memcpy(dbg->logits + (size_t)s * AIMA_E, logits, sizeof logits);
+      if (dbg->ids) memcpy(dbg->ids + (size_t)s * AIMA_K, ids, sizeof ids);
+      if (dbg->scores) memcpy(dbg->scores + (size_t)s * AIMA_K, scores, sizeof scores);
+      if (dbg->weights) memcpy(dbg->weights + (size_t)s * AIMA_K, weights, sizeof weights);
+      if (dbg->shared_scaled) memcpy(dbg->shared_scaled + (size_t)s * AIMA_H, shared_scaled, sizeof shared_scaled);
+      if (dbg->routed) memcpy(dbg->routed + (size_t)s * AIMA_H, routed, sizeof routed);
+    }
+  }
+  return failed ? -1 : 0;
+}
+
+/* ----------------------------------------------------------------------- */
+/* Dispatch plan                                                            */
+/* ----------------------------------------------------------------------- */
+
+/* Deterministic token -> expert plan: per-expert counts, exclusive offsets and
+ * the routed rows (flat index token * 8 + slot) grouped by expert, ascending
+ * flat index inside an expert (four_layer_mini_engine.py:7806-7823: stable sort
+ * of the flattened ids).  Also the reference's block-32 padded row count
+ * (native_moe_prefill.hip.cpp:325-382, num_tokens_post_padded). */
+void aima_or_dispatch_plan(const int32_t* ids, int tokens, int32_t* counts,
+                           int32_t* offsets /* [257] */, int32_t* sorted_rows,
+                           int32_t* padded_rows_block32) {
+  const int rows = tokens * AIMA_K;
+  for (int e = 0; e < AIMA_E; ++e) counts[e] = 0;
+  for (int i = 0; i < rows; ++i) counts[ids[i]] += 1;
+  offsets[0] = 0;
+  int padded = 0;
+  for (int e = 0; e < AIMA_E; ++e) {
+    offsets[e + 1] = offsets[e] + counts[e];
+    padded += (counts[e] + 31) / 32 * 32;
+  }
+  if (padded_rows_block32) *padded_rows_block32 = padded;
+  if (sorted_rows) {
+    int32_t cursor[AIMA_E];
+    memcpy(cursor, offsets, sizeof cursor);
+    for (int i = 0; i < rows; ++i) sorted_rows[cursor[ids[i]]++] = i;
+  }
+}
+
+/* Batch-1 GEMV out[m] = bf16(dot(x, W[m, :])), the contract of
+ * launch_bf16_wvsplitk (native/src/bf16_wvsplitk.hip.cpp:337-366). */
+void aima_or_gemv(const uint16_t* weight, const uint16_t* x, uint16_t* out,
+                  int m, int k) {
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < m; ++row)
+    out[row] = f2bf(aima_or_dot(x, weight + (size_t)row * k, k));
+}
+
+/* Comparison metrics of compare_native_oracle_tensor
+ * (native/src/native_layer_oracle.hip.cpp:136-228) for BF16 tensors:
+ * result[0] exact element count, [1] max abs error, [2] relative L2 error,
+ * [3] cosine similarity, [4] finite element count. */
+void aima_or_compare_bf16(const uint16_t* expected, const uint16_t* actual,
+                          size_t n, double* result) {
+  double exact = 0, max_abs = 0, se = 0, see = 0, saa = 0, dot = 0, finite = 0;
+  for (size_t i = 0; i < n; ++i) {
+    const double e = bf2f(expected[i]);
+    const double a = bf2f(actual[i]);
+    if (expected[i] == actual[i]) exact += 1;
+    if (isfinite(a)) finite += 1;
+    const double d = a - e;
+    if (fabs(d) > max_abs) max_abs = fabs(d);
+    se += d * d; see += e * e; saa += a * a; dot += e * a;
+  }
+  result[0] = exact;
+  result[1] = max_abs;
+  result[2] = sqrt(se / fmax(see, 1.0e-30));
+  result[3] = dot / sqrt(fmax(see * saa, 1.0e-30));
+  result[4] = finite;
+}
+
+#ifdef __cplusplus
+}
+#endif

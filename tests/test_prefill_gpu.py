@@ -1,0 +1,177 @@
+"""GPU parity of the prefill path through the C ABI: routing bit-exact against the CPU oracle
+(ids with the reference's tie order, scores, weights), the dispatch plan exact, layer outputs
+within the stated BF16 tolerance, and agreement with the committed torch golden vectors."""
+from __future__ import annotations
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SEED = 1234
+MAX_ABS = 2.0e-2      # BASELINE north_star tolerance on the MoE output (routed + shared)
+COSINE = 0.9999
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+@pytest.fixture(scope="module")
+def provider(package, gpu_layers):
+    provider = package.MoeProvider(layers=2, max_prefill_tokens=1024)
+    for layer in range(2):
+        provider.bind_layer(layer, gpu_layers(layer)["cuda"])
+    yield provider
+    provider.release()
+
+
+def _cosine(a, b):
+    a, b = a.double().reshape(-1), b.double().reshape(-1)
+    return float((a @ b) / (a.norm() * b.norm()).clamp_min(1e-30))
+
+
+def _run(provider, layer, h2, resid):
+    device = torch.device("cuda", 0)
+    tokens = h2.shape[0]
+    views, tensors = provider.make_debug(tokens, prefill=True)
+    out = provider.launch_selected_moe(post_attention=h2.to(device), residual_hidden=resid.to(device),
+                                       model_layer=layer, debug=views)
+    metrics = provider.sync_metrics()
+    return out.cpu(), {k: v.cpu() for k, v in tensors.items()}, metrics
+
+
+def _check_against_oracle(oracle, layer_view, h2, resid, out, dbg, metrics, select=None):
+    tokens = h2.shape[0]
+    routing = oracle.router_prefill(h2, layer_view)
+    assert torch.equal(dbg["router_logits"], routing["logits"])
+    assert torch.equal(dbg["topk_ids"], routing["ids"])                 # order included
+    assert torch.equal(dbg["topk_scores"], routing["scores"])
+    assert torch.equal(dbg["topk_weights"], routing["weights"])
+    plan = oracle.dispatch_plan(routing["ids"])
+    assert torch.equal(dbg["expert_counts"], plan["counts"])
+    assert torch.equal(dbg["expert_offsets"], plan["offsets"])
+    assert torch.equal(dbg["sorted_rows"], plan["sorted_rows"])
+    assert metrics.last_padded_routed_rows == plan["padded_rows"]
+    rows = list(range(tokens)) if select is None else select
+    want = oracle.prefill_layer(h2, resid, layer_view, select=rows)
+    got_moe = dbg["routed"][rows].float() + dbg["shared_scaled"][rows].float()
+    want_moe = want["routed"].float() + want["shared_scaled"].float()
+    assert torch.isfinite(out.float()).all()
+    assert (got_moe - want_moe).abs().max() <= MAX_ABS
+    assert _cosine(got_moe, want_moe) >= COSINE
+    assert _cosine(dbg["shared_scaled"][rows], want["shared_scaled"]) >= COSINE
+    assert _cosine(dbg["routed"][rows], want["routed"]) >= COSINE
+    # final hidden = bf16(residual + bf16(routed + shared)) from the GPU's own stage outputs
+    combined = (dbg["routed"].float() + dbg["shared_scaled"].float()).to(torch.bfloat16)
+    assert torch.equal(out, (resid.float() + combined.float()).to(torch.bfloat16))
+    ulp = want["out"].float().abs() * 2.0 ** -7
+    assert ((out[rows].float() - want["out"].float()).abs() <= ulp + MAX_ABS).all()
+
+
+@pytest.mark.parametrize("tokens", [1, 7, 16, 33, 257])
+def test_prefill_layer_matches_oracle(provider, oracle, gpu_layers, synth, tokens):
+    layer = tokens % 2
+    h2 = synth.activations(SEED + tokens, tokens, "input", layer)
+    resid = synth.activations(SEED + tokens, tokens, "residual", layer)
+    out, dbg, metrics = _run(provider, layer, h2, resid)
+    select = None if tokens <= 33 else list(range(0, tokens, 16)) + [tokens - 1]
+    _check_against_oracle(oracle, gpu_layers(layer)["oracle"], h2, resid, out, dbg, metrics, select)
+
+
+def test_prefill_tie_stress_routing_is_bit_exact(provider, oracle, gpu_layers, synth):
+    """Router logits rounded to multiples of 1/8: many exact ties, ids must keep the reference's
+    order (BASELINE config 4c)."""
+    tokens = 512
+    provider.set_router_hooks(None, quantize_eighths=True)
+    try:
+        h2 = synth.activations(SEED + 900, tokens, "input", 0)
+        resid = synth.activations(SEED + 900, tokens, "residual", 0)
+        out, dbg, metrics = _run(provider, 0, h2, resid)
+        tied = oracle.OracleLayer(gpu_layers(0)["cpu"], quant_eighths=True)
+        routing = oracle.router_prefill(h2, tied)
+        assert torch.equal(dbg["topk_ids"], routing["ids"])
+        assert torch.equal(dbg["topk_weights"], routing["weights"])
+        scores = routing["scores"]
+        assert int((scores[:, :-1] == scores[:, 1:]).sum()) > tokens      # ties are everywhere
+        _check_against_oracle(oracle, tied, h2, resid, out, dbg, metrics, select=[0, 100, 511])
+    finally:
+        provider.set_router_hooks(None, quantize_eighths=False)
+
+
+def test_prefill_hot_and_skewed_routing(provider, oracle, gpu_layers, synth):
+    device = torch.device("cuda", 0)
+    tokens = 300
+    h2 = synth.activations(SEED + 901, tokens, "input", 1)
+    resid = synth.activations(SEED + 901, tokens, "residual", 1)
+    hot = [0, 31, 32, 100, 101, 200, 254, 255]
+    for bias in (synth.hot_expert_bias(hot), synth.zipf_router_bias(SEED)):
+        provider.set_router_hooks(bias.to(device), quantize_eighths=False)
+        try:
+            out, dbg, metrics = _run(provider, 1, h2, resid)
+            view = oracle.OracleLayer(gpu_layers(1)["cpu"], router_bias=bias)
+            _check_against_oracle(oracle, view, h2, resid, out, dbg, metrics, select=[0, 1, 150, 299])
+        finally:
+            provider.set_router_hooks(None, quantize_eighths=False)
+    # hot case: exactly eight populated experts, 248 empty ones
+    provider.set_router_hooks(synth.hot_expert_bias(hot).to(device), quantize_eighths=False)
+    try:
+        _, dbg, _ = _run(provider, 1, h2, resid)
+        counts = dbg["expert_counts"]
+        assert counts[hot].tolist() == [tokens] * 8 and int(counts.sum()) == tokens * 8
+    finally:
+        provider.set_router_hooks(None, quantize_eighths=False)
+
+
+@pytest.mark.parametrize("tokens", [1, 16])
+def test_prefill_matches_torch_golden(provider, gpu_layers, synth, tokens):
+    """BASELINE config 0 against the committed torch-CPU vectors (tests/golden/make_golden.py)."""
+    data = np.load(GOLDEN / f"config0_T{tokens}.npz")
+    seed, layer, _ = (int(v) for v in data["seed"])
+    assert seed == SEED and layer == 0
+    h2 = synth.activations(seed, tokens, "input", layer)
+    resid = synth.activations(seed, tokens, "residual", layer)
+    out, dbg, _ = _run(provider, layer, h2, resid)
+
+    def bf16(bits):
+        return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+
+    golden_sets = torch.from_numpy(data["topk_indices"]).sort(dim=-1).values
+    same = (dbg["topk_ids"].long().sort(dim=-1).values == golden_sets).all(dim=-1)
+    assert same.float().mean() >= 0.9
+    rows = same.nonzero().reshape(-1)
+    golden_moe = bf16(data["moe_out"]).float() + bf16(data["shared_out"]).float()
+    got_moe = dbg["routed"].float() + dbg["shared_scaled"].float()
+    assert (got_moe[rows] - golden_moe[rows]).abs().max() <= MAX_ABS
+    assert _cosine(got_moe[rows], golden_moe[rows]) >= COSINE
+
+
+def test_prefill_stack_matches_chained_layers(provider, oracle, gpu_layers, synth):
+    """Two layers through the stack entry point equal norm + single-layer calls chained by hand."""
+    device = torch.device("cuda", 0)
+    tokens = 64
+    x = synth.activations(SEED + 902, tokens, "residual", 0).to(device)
+    y = torch.empty_like(x)
+    provider.prefill_stack(x, y, first_layer=0, n_layers=2)
+    current = x
+    for layer in range(2):
+        _, h2 = provider.rmsnorm(current, gpu_layers(layer)["cuda"]["post_attention_layernorm"])
+        current = provider.launch_selected_moe(post_attention=h2, residual_hidden=current, model_layer=layer)
+    provider.sync_metrics()
+    assert torch.equal(y.cpu(), current.cpu())
+    # teacher-forced check of layer 0 against the oracle
+    _, h2 = provider.rmsnorm(x, gpu_layers(0)["cuda"]["post_attention_layernorm"])
+    _, h2_cpu = oracle.rmsnorm(x.cpu(), gpu_layers(0)["cpu"]["post_attention_layernorm"])
+    assert torch.equal(h2.cpu(), h2_cpu)
+
+
+def test_prefill_argument_checks(provider, package, synth):
+    device = torch.device("cuda", 0)
+    h2 = synth.activations(1, 4).to(device)
+    with pytest.raises(package.AimaMoeError) as alias:
+        provider.launch_selected_moe(post_attention=h2, residual_hidden=h2.clone(), model_layer=0, out=h2)
+    assert alias.value.status == -4
+    big = torch.zeros(2048, 2048, dtype=torch.bfloat16, device=device)
+    with pytest.raises(package.AimaMoeError) as capacity:
+        provider.launch_selected_moe(post_attention=big, residual_hidden=big.clone(), model_layer=0)
+    assert capacity.value.status == -8
