@@ -210,17 +210,29 @@ __device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
 }
 
 // Bounded wait on an mbarrier phase.  Returns false when the budget ran out or
-// another thread of the block already raised `abort_flag`.
+// another thread of the block already raised `abort_flag`.  `diag` (may be
+// nullptr) receives {spins, elapsed ns lo, barrier word lo, barrier word hi}
+// when this call is the one that ran out of budget.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
+                                                  volatile int* abort_flag,
+                                                  unsigned* diag = nullptr) {
   if (mbar_test(bar, parity)) return true;
   const unsigned long long start = global_timer_ns();
   unsigned spins = 0;
   while (!mbar_test(bar, parity)) {
     if ((++spins & 255u) == 0u) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - start > kWaitBudgetNs) {
+      const unsigned long long elapsed = global_timer_ns() - start;
+      if (elapsed > kWaitBudgetNs) {
         *abort_flag = kStatusTimeoutMbarrier;
+        if (diag != nullptr) {
+          unsigned lo, hi;
+          asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(bar) : "memory");
+          diag[0] = spins;
+          diag[1] = static_cast<unsigned>(elapsed >> 10);
+          diag[2] = lo;
+          diag[3] = hi;
+        }
         return false;
       }
     }

@@ -37,6 +37,11 @@
 namespace aima {
 namespace {
 
+// Ring of weight "pair" slots.  Item i always lands in slot i % kRingSlots and is
+// always consumed by warp i % kRingSlots: a parity wait on an mbarrier is only
+// meaningful when the waiter is at most one phase behind, so consecutive uses
+// of a slot must be consumed in order by one warp.  Warps kRingSlots..14 only
+// take part in the top-8 and down-projection phases.
 constexpr int kRingSlots = 10;
 constexpr int kSlotBytes = 8192;               // two 4 KB weight rows
 constexpr int kRowBytes = kHidden * 2;         // 4096
@@ -67,6 +72,7 @@ struct Misc {
   volatile int decision;   // block-uniform "keep going" verdict (see uniform_alive)
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
+static_assert(kRingSlots <= kDecodeConsumerWarps, "each ring slot needs its own consumer warp");
 
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" :: "n"(kDecodeConsumerThreads) : "memory");
@@ -76,6 +82,25 @@ __device__ __forceinline__ void raise_status(const DecodeParams& p,
                                              volatile int* abort_flag, int code) {
   atomicCAS(p.status, 0, code);
   *abort_flag = code;
+}
+
+// Records where the first bounded wait gave up: status[1] = site, [2] = block,
+// [3] = warp, [4] = item / layer detail.  Sites: 1 producer slot acquire,
+// 2 consumer item (router / shared rows), 3 consumer item (routed rows),
+// 4 down-projection region, 5 grid barrier, 6 expert-id hand-over.
+__device__ __forceinline__ void record_site(const DecodeParams& p, int site, int detail,
+                                            const unsigned* diag = nullptr) {
+  if (atomicCAS(p.status + 1, 0, site) == 0) {
+    p.status[2] = blockIdx.x;
+    p.status[3] = threadIdx.x >> 5;
+    p.status[4] = detail;
+    if (diag != nullptr) {
+      p.status[5] = static_cast<int>(diag[0]);
+      p.status[6] = static_cast<int>(diag[1]);
+      p.status[7] = static_cast<int>(diag[2]);
+      p.status[8] = static_cast<int>(diag[3]);
+    }
+  }
 }
 
 // Grid-wide barrier over the consumer threads of all blocks.
@@ -95,6 +120,7 @@ __device__ __forceinline__ bool grid_barrier(const DecodeParams& p,
         if (remote != 0) { *abort_flag = remote; break; }
         if (global_timer_ns() - start > kWaitBudgetNs) {
           raise_status(p, abort_flag, kStatusTimeoutGridBarrier);
+          record_site(p, 5, static_cast<int>(target));
           break;
         }
       }
@@ -150,6 +176,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(down_bar, 1);
+    // every ring slot starts out released: complete phase 0 of its empty barrier
+    for (int s = 0; s < kRingSlots; ++s) mbar_arrive(empty_bar(s));
     misc->ids_layer = 0;
     misc->abort_flag = 0;
     misc->decision = 1;
@@ -179,8 +207,12 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     auto acquire = [&](unsigned item) -> int {
       const int s = item % kRingSlots;
       const unsigned use = item / kRingSlots;
-      if (!mbar_wait_bounded(empty_bar(s), (use & 1u) ^ 1u, abort_flag)) {
-        if (*abort_flag == kStatusTimeoutMbarrier) atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+      unsigned diag[4] = {0, 0, 0, 0};
+      if (!mbar_wait_bounded(empty_bar(s), use & 1u, abort_flag, diag)) {
+        if (*abort_flag == kStatusTimeoutMbarrier) {
+          atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+          record_site(p, 1, static_cast<int>(item), diag);
+        }
         return -1;
       }
       return s;
@@ -232,6 +264,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
               if (*abort_flag != 0) { alive = false; break; }
               if (global_timer_ns() - start > kWaitBudgetNs) {
                 raise_status(p, abort_flag, kStatusTimeoutIds);
+                record_site(p, 6, li);
                 alive = false;
                 break;
               }
@@ -302,11 +335,15 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     bool alive = true;
 
     // wait for item `item`, return slot pointer (nullptr on abort)
-    auto wait_item = [&](unsigned item) -> const uint8_t* {
+    auto wait_item = [&](unsigned item, int site) -> const uint8_t* {
       const int s = item % kRingSlots;
       const unsigned use = item / kRingSlots;
-      if (!mbar_wait_bounded(full_bar(s), use & 1u, abort_flag)) {
-        if (*abort_flag == kStatusTimeoutMbarrier) atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+      unsigned diag[4] = {0, 0, 0, 0};
+      if (!mbar_wait_bounded(full_bar(s), use & 1u, abort_flag, diag)) {
+        if (*abort_flag == kStatusTimeoutMbarrier) {
+          atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+          record_site(p, site, static_cast<int>(item), diag);
+        }
         return nullptr;
       }
       return ring + s * kSlotBytes;
@@ -378,8 +415,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       const int n_r_items = 1 + n_shared_pairs + (owns_gate_row ? 1 : 0);
       for (int k = 0; k < n_r_items && alive; ++k) {
         const unsigned item = seq + k;
-        if (static_cast<int>(item % kDecodeConsumerWarps) != warp) continue;
-        const uint8_t* slot = wait_item(item);
+        if (static_cast<int>(item % kRingSlots) != warp) continue;
+        const uint8_t* slot = wait_item(item, 2);
         if (slot == nullptr) { alive = false; break; }
         float a, b;
         pair_dot(slot, xr, a, b);
@@ -478,8 +515,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       const int p1 = static_cast<int>((static_cast<long long>(c + 1) * n_pairs) / G);
       for (int pi = p0; pi < p1 && alive; ++pi) {
         const unsigned item = seq + (pi - p0);
-        if (static_cast<int>(item % kDecodeConsumerWarps) != warp) continue;
-        const uint8_t* slot = wait_item(item);
+        if (static_cast<int>(item % kRingSlots) != warp) continue;
+        const uint8_t* slot = wait_item(item, 3);
         if (slot == nullptr) { alive = false; break; }
         float a, b;
         pair_dot(slot, xr, a, b);
@@ -495,7 +532,10 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       }
       consumer_sync();
       if (!mbar_wait_bounded(down_bar, li & 1u, abort_flag)) {
-        if (*abort_flag == kStatusTimeoutMbarrier) atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+        if (*abort_flag == kStatusTimeoutMbarrier) {
+          atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+          record_site(p, 4, li);
+        }
         alive = false;
       }
       if (alive) {

@@ -506,9 +506,10 @@ AIMA_EXPORT int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics*
   std::lock_guard<std::mutex> lock(handle->mutex);
   cudaError_t error = cudaStreamSynchronize(handle->last_stream);
   if (error != cudaSuccess) return fail_cuda(error, "cudaStreamSynchronize");
-  int device_status = 0;
-  error = cudaMemcpy(&device_status, handle->status, sizeof device_status, cudaMemcpyDeviceToHost);
+  int status_words[12] = {};
+  error = cudaMemcpy(status_words, handle->status, sizeof status_words, cudaMemcpyDeviceToHost);
   if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy status word");
+  const int device_status = status_words[0];
   handle->metrics.device_status = device_status;
   if (handle->prefill.total_bytes != 0) {
     error = cudaMemcpy(&handle->metrics.last_padded_routed_rows, handle->prefill.padded_rows,
@@ -523,8 +524,12 @@ AIMA_EXPORT int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics*
   if (device_status != 0) {
     const int reset = reset_decode_sync(handle);
     if (reset != AIMA_MOE_OK) return reset;
-    return fail(AIMA_MOE_ERR_TIMEOUT, "a bounded device-side wait ran out (status %d); sync state reset",
-                device_status);
+    return fail(AIMA_MOE_ERR_TIMEOUT,
+                "a bounded device-side wait ran out (status %d, site %d, block %d, warp %d, detail %d, "
+                "spins %d, elapsed_us %d, barrier %08x:%08x); sync state reset",
+                device_status, status_words[1], status_words[2], status_words[3], status_words[4],
+                status_words[5], status_words[6], static_cast<unsigned>(status_words[8]),
+                static_cast<unsigned>(status_words[7]));
   }
   return AIMA_MOE_OK;
 }
