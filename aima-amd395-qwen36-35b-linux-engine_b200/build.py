@@ -14,7 +14,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libaima_moe_b200.so"
-SOURCES = ["moe_api.cu", "decode_kernel.cu", "pointwise.cu", "prefill.cu", "grouped_gemm_simt.cu"]
+SOURCES = ["moe_api.cu", "decode_kernel.cu", "decode_noalloc.cu", "pointwise.cu", "prefill.cu",
+           "grouped_gemm_simt.cu"]
 
 
 def nvcc_path() -> str:

@@ -50,6 +50,13 @@ size_t align_up(size_t value, size_t alignment) {
 
 }  // namespace
 
+namespace aima {
+// Lets other translation units of the library report through aima_moe_last_error_string().
+void set_last_error_message(const char* message) {
+  std::snprintf(g_last_error, sizeof g_last_error, "%s", message);
+}
+}  // namespace aima
+
 struct aima_moe_handle {
   aima_moe_config config{};
   int device = -1;

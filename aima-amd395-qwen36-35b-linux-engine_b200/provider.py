@@ -97,6 +97,8 @@ EXPORTS = [
     ("aima_moe_rmsnorm_launch", c_int,
      [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_float, c_void_p]),
     ("aima_moe_gemv_bf16_launch", c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    ("aima_moe_decode_layers_noalloc", c_int,
+     [ctypes.POINTER(LayerWeights), c_uint32, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     ("aima_moe_sync_metrics", c_int, [c_void_p, ctypes.POINTER(Metrics)]),
     ("aima_moe_release", c_int, [c_void_p]),
 ]
@@ -160,6 +162,40 @@ def _stream(torch: Any) -> c_void_p:
 # ["shared_up_proj"], ["shared_down_proj"], ["post_attention_layernorm"])
 WEIGHT_KEYS = ("router", "expert_gate_up", "expert_down", "shared_gate", "shared_gate_proj",
                "shared_up_proj", "shared_down_proj")
+
+
+NOALLOC_MAX_LAYERS = 8
+
+
+def layer_weights_struct(weights: Mapping[str, Any]) -> LayerWeights:
+    """Fills the C struct from a reference-style weight dict of CUDA tensors."""
+    w = LayerWeights()
+    w.struct_bytes = ctypes.sizeof(LayerWeights)
+    fields = {
+        "router": weights["router"], "expert_gate_up": weights["expert_gate_up"],
+        "expert_down": weights["expert_down"], "shared_expert_gate": weights["shared_gate"],
+        "shared_gate_proj": weights["shared_gate_proj"], "shared_up_proj": weights["shared_up_proj"],
+        "shared_down_proj": weights["shared_down_proj"],
+        "post_attention_norm": weights.get("post_attention_layernorm"),
+    }
+    for name, tensor in fields.items():
+        setattr(w, name, _ptr(tensor))
+        setattr(w, name + "_bytes", _nbytes(tensor))
+    return w
+
+
+def decode_layers_noalloc(layer_dicts: list, x_in: Any, x_out: Any, rms_eps: float = 1.0e-6,
+                          device_status: Any = None, library: MoeLibrary | None = None) -> Any:
+    """Calls the allocation-free decode entry point for a host that must not allocate device
+    memory: no handle, the kernel's scratch is the library's static device array.  x_in / x_out
+    are BF16 [2048] CUDA tensors, layer_dicts the per-layer weight dicts (at most 8)."""
+    import torch
+
+    lib = library or load_library()
+    array = (LayerWeights * len(layer_dicts))(*[layer_weights_struct(w) for w in layer_dicts])
+    lib.check(lib.aima_moe_decode_layers_noalloc(
+        array, len(layer_dicts), _ptr(x_in), _ptr(x_out), rms_eps, _ptr(device_status), _stream(torch)))
+    return x_out
 
 
 class MoeProvider:

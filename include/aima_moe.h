@@ -194,6 +194,36 @@ int aima_moe_rmsnorm_launch(const void* x, const void* residual,
 int aima_moe_gemv_bf16_launch(const void* weight, const void* x, void* out,
                               uint32_t m, uint32_t k, void* stream);
 
+/* Decode without any allocation -- this entry point has no counterpart in the
+ * reference.  It exists for hosts that must not, or cannot, allocate device
+ * memory once they are running: processes that have already given all free HBM
+ * to their own weight / KV-cache arenas, and request paths that may not reach
+ * cudaMalloc or cudaFree because those calls synchronise the device.  Such hosts
+ * cannot use aima_moe_prepare(), which allocates.
+ *
+ * Runs `n_layers` (1 .. AIMA_MOE_NOALLOC_MAX_LAYERS) consecutive decode layers
+ * for one token, exactly like aima_moe_decode_stack_launch: x_in, x_out are
+ * bf16 [2048] device vectors that must not alias; `layers[i]` describes layer i
+ * with all 256 experts and its post-attention norm weight.  The kernel's scratch
+ * lives in one static device array of AIMA_MOE_NOALLOC_SCRATCH_BYTES that every
+ * GPU loading the library holds until the process exits; the call itself uses
+ * no cudaMalloc / cudaFree or other allocating routine.  If `device_status` is
+ * not NULL, the kernel's status word (0 = healthy, see AIMA_MOE_ERR_TIMEOUT) is
+ * copied to that device int32 on the stream after the kernel.
+ *
+ * The first call on each device resolves the address of the static array (the
+ * device must be current); make that first call before starting any stream
+ * capture.  All calls on a device share the one array and it keeps the previous
+ * call's contents (the call clears the words that must start at zero), so two
+ * calls whose kernels overlap on the GPU -- different streams, or different host
+ * threads -- race with each other: issue them on one stream or order them with
+ * events.  More layers than the maximum are refused with AIMA_MOE_ERR_CAPACITY. */
+#define AIMA_MOE_NOALLOC_MAX_LAYERS 8
+#define AIMA_MOE_NOALLOC_SCRATCH_BYTES 24576
+int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_t n_layers,
+                                   const void* x_in, void* x_out, float rms_eps,
+                                   int32_t* device_status, void* stream);
+
 /* Synchronises the handle's last stream, reads the device status word and the
  * padded-row counter; returns AIMA_MOE_ERR_TIMEOUT if a bounded wait ran out. */
 int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics* metrics);

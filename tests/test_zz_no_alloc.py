@@ -1,0 +1,73 @@
+"""GPU test of the allocation-free decode entry point (collected last on purpose).
+
+aima_moe_decode_layers_noalloc serves hosts that may not allocate device memory while they run
+(all HBM already handed to their own arenas, or a request path on which cudaMalloc's device-wide
+synchronisation is not acceptable).  It must give the same bits as the handle-based
+aima_moe_decode_stack_launch, on two calls in a row (the second call reuses the static scratch
+array with the first call's contents in it), both in a fresh process and after the other tests.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SEED = 4321
+LAYERS = 3
+
+
+@pytest.fixture(scope="module")
+def layers(package, built_library):
+    device = torch.device("cuda", 0)
+    return [package.synth.layer_weights_cuda_fast(SEED, layer, device) for layer in range(LAYERS)]
+
+
+def test_noalloc_decode_matches_the_handle_based_entry_point(package, layers):
+    device = torch.device("cuda", 0)
+    provider = package.MoeProvider(layers=LAYERS)
+    try:
+        for layer, weights in enumerate(layers):
+            provider.bind_layer(layer, weights)
+        status = torch.full((1,), -1, dtype=torch.int32, device=device)
+        for call in range(2):
+            x = package.synth.activations(SEED + call, 1, "residual", 0)[0].to(device)
+            want = torch.empty_like(x)
+            provider.decode_stack(x, want, first_layer=0, n_layers=LAYERS)
+            provider.sync_metrics()
+            got = torch.zeros_like(x)
+            package.provider.decode_layers_noalloc(layers, x, got, device_status=status)
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+            assert torch.equal(got, want), f"call {call}"          # bit-exact, as in the decode tests
+        # a single layer through the static scratch as well
+        x = package.synth.activations(SEED + 7, 1, "residual", 0)[0].to(device)
+        want = provider.decode_layer(x, 1)
+        got = torch.zeros_like(x)
+        package.provider.decode_layers_noalloc([layers[1]], x, got)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    finally:
+        provider.release()
+
+
+def test_noalloc_decode_rejects_what_it_cannot_hold(package, layers):
+    device = torch.device("cuda", 0)
+    x = package.synth.activations(SEED, 1, "residual", 0)[0].to(device)
+    y = torch.empty_like(x)
+    too_many = [layers[0]] * (package.provider.NOALLOC_MAX_LAYERS + 1)
+    with pytest.raises(package.AimaMoeError) as capacity:
+        package.provider.decode_layers_noalloc(too_many, x, y)
+    assert capacity.value.status == -8 and "AIMA_MOE_NOALLOC_MAX_LAYERS" in str(capacity.value)
+    with pytest.raises(package.AimaMoeError) as alias:
+        package.provider.decode_layers_noalloc([layers[0]], x, x)
+    assert alias.value.status == -4
+    without_norm = dict(layers[0])
+    without_norm.pop("post_attention_layernorm")
+    with pytest.raises(package.AimaMoeError) as missing:
+        package.provider.decode_layers_noalloc([without_norm], x, y)
+    assert missing.value.status == -1
+    lib = package.load_library()
+    assert lib.aima_moe_decode_layers_noalloc(None, 1, None, None, ctypes.c_float(1e-6), None, None) == -1
