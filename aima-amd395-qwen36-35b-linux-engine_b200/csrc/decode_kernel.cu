@@ -369,6 +369,13 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       b = butterfly_sum(b);
     };
 
+    // tracing stamps: 0 layer start, 1 norm done, 2 router/shared rows done, 3 logits barrier,
+    // 4 top-8 done, 5 routed gate/up done, 6 activation barrier, 7 activations loaded,
+    // 8 down region landed, 9 down dots done, 10 output stored, 11 output barrier
+    auto stamp = [&](int li, int k) {
+      if (p.timeline != nullptr && c == 0 && ctid == 0)
+        p.timeline[li * kDecodeTraceStamps + k] = global_timer_ns();
+    };
     for (int li = 0; li < p.n_layers; ++li) {
       const bool first = (li == 0);
       const bool last = (li == p.n_layers - 1);
@@ -376,6 +383,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       const __nv_bfloat16* x_src = first ? p.x_in : ((li & 1) ? p.xbuf1 : p.xbuf0);
       __nv_bfloat16* x_dst = last ? p.x_out : ((li & 1) ? p.xbuf0 : p.xbuf1);
 
+      stamp(li, 0);
       // ---- norm: h2 in registers, element k = 256 g + 8 lane + j at xr[8 g + j]
       float xr[64];
       {
@@ -411,6 +419,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         }
       }
 
+      stamp(li, 1);
       // ---- R items ----
       const int n_r_items = 1 + n_shared_pairs + (owns_gate_row ? 1 : 0);
       for (int k = 0; k < n_r_items && alive; ++k) {
@@ -445,8 +454,10 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         }
       }
       seq += n_r_items;
+      stamp(li, 2);
       // (an aborted warp still joins the barriers below; they return false)
       if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
+      stamp(li, 3);
 
       // ---- top-8, ties to the lowest expert id; softmax over the eight ----
       if (warp == 0) {
@@ -507,6 +518,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         }
       }
       consumer_sync();
+      stamp(li, 4);
 
       // ---- phase 1: routed gate/up pairs of the experts held on this GPU ----
       const int n_local = misc->n_local;
@@ -524,13 +536,16 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         if (lane == 0) p.act[pi] = float_to_bf16_bits(__fmul_rn(det_silu(a), b));
       }
       seq += (p1 - p0);
+      stamp(li, 5);
       if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
+      stamp(li, 6);
 
       // ---- phase 2: down products for outputs h0 .. h1-1 ----
       for (int v = ctid; v < kDownRegionRanks * kInter * 2 / 16; v += kDecodeConsumerThreads) {
         reinterpret_cast<uint4*>(act_s)[v] = ld_cg_u4(reinterpret_cast<const uint4*>(p.act) + v);
       }
       consumer_sync();
+      stamp(li, 7);
       if (!mbar_wait_bounded(down_bar, li & 1u, abort_flag)) {
         if (*abort_flag == kStatusTimeoutMbarrier) {
           atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
@@ -538,6 +553,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         }
         alive = false;
       }
+      stamp(li, 8);
       if (alive) {
         const int per_row = n_local + 1;
         const int n_dots = nh * per_row;
@@ -560,6 +576,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         }
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
+      stamp(li, 9);
       if (ctid < nh) {
         const int h = h0 + ctid;
         float acc = 0.0f;
@@ -576,9 +593,11 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         if (p.dbg_routed != nullptr) p.dbg_routed[h] = __float2bfloat16_rn(routed);
         if (p.dbg_shared_scaled != nullptr) p.dbg_shared_scaled[h] = __float2bfloat16_rn(shared_scaled);
       }
+      stamp(li, 10);
       if (!last) {
         if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
       }
+      stamp(li, 11);
     }
     if (c == 0 && ctid == 0 && *abort_flag == 0) {
       *p.bar_base = bar_base + nbar * G;

@@ -15,6 +15,7 @@ constexpr int kDecodeMaxRowsPerBlock = 14;
 constexpr int kDecodeMinBlocks = (kHidden + kDecodeMaxRowsPerBlock - 1) / kDecodeMaxRowsPerBlock;
 constexpr int kDecodeMaxBlocks = kExperts;  // router rows are dealt c, c + grid
 constexpr int kDecodeSmemBytes = 221512;
+constexpr int kDecodeTraceStamps = 12;
 
 struct DecodeParams {
   const LayerPtrs* layers;       // device array indexed by layer
@@ -35,6 +36,9 @@ struct DecodeParams {
   int n_layers;
   int expert_lo;                 // experts [expert_lo, expert_hi) live on this GPU
   int expert_hi;
+  // optional tracing: block 0 stamps %globaltimer at kDecodeTraceStamps points
+  // of every layer into timeline[layer_ordinal * kDecodeTraceStamps + k]
+  unsigned long long* timeline;
   // optional qualification outputs (last processed layer wins)
   __nv_bfloat16* dbg_h2;
   float* dbg_logits;

@@ -190,6 +190,7 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   params.bar_base = reinterpret_cast<unsigned long long*>(scratch + kOffSync + 128);
   params.status = reinterpret_cast<int*>(scratch + kOffStatus);
   params.router_bias = nullptr;
+  params.timeline = nullptr;
   params.quant_eighths = 0;
   params.eps = rms_eps;
   params.first_layer = 0;

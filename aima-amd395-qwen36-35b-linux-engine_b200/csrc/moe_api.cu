@@ -82,6 +82,10 @@ struct aima_moe_handle {
 
   PrefillWorkspace prefill;
 
+  unsigned long long* timeline = nullptr;   // [kMaxLayers * kDecodeTraceStamps], device
+  bool tracing = false;
+  uint32_t traced_layers = 0;
+
   const float* router_bias = nullptr;
   int quant_eighths = 0;
 
@@ -195,6 +199,8 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
   params.n_layers = static_cast<int>(n_layers);
   params.expert_lo = handle->expert_lo;
   params.expert_hi = handle->expert_lo + handle->experts_local;
+  params.timeline = handle->tracing ? handle->timeline : nullptr;
+  if (handle->tracing) handle->traced_layers = n_layers;
   if (debug != nullptr) {
     params.dbg_h2 = static_cast<__nv_bfloat16*>(debug->h2);
     params.dbg_logits = static_cast<float*>(debug->router_logits);
@@ -269,6 +275,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
   handle->expert_lo = handle->experts_local * static_cast<int>(config->rank);
 
   auto cleanup = [&](int code) {
+    if (handle->timeline) cudaFree(handle->timeline);
     if (handle->dev_layers) cudaFree(handle->dev_layers);
     if (handle->decode_scratch) cudaFree(handle->decode_scratch);
     prefill_workspace_free(&handle->prefill);
@@ -281,6 +288,8 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
   error = cudaMemset(handle->dev_layers, 0, sizeof(LayerPtrs) * kMaxLayers);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMemset layer table"));
 
+  error = cudaMalloc(&handle->timeline, sizeof(unsigned long long) * kMaxLayers * kDecodeTraceStamps);
+  if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc decode timeline"));
   handle->decode_scratch_bytes = decode_scratch_size();
   error = cudaMalloc(&handle->decode_scratch, handle->decode_scratch_bytes);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc decode scratch"));
@@ -541,8 +550,34 @@ AIMA_EXPORT int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics*
   return AIMA_MOE_OK;
 }
 
+AIMA_EXPORT int aima_moe_set_tracing(aima_moe_handle* handle, int enabled) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  handle->tracing = enabled != 0;
+  handle->traced_layers = 0;
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t* stamps_ns,
+                                              uint32_t capacity, uint32_t* written) {
+  if (handle == nullptr || stamps_ns == nullptr || written == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "timeline argument is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  const uint32_t available = handle->traced_layers * kDecodeTraceStamps;
+  const uint32_t count = available < capacity ? available : capacity;
+  cudaError_t error = cudaStreamSynchronize(handle->last_stream);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaStreamSynchronize");
+  if (count != 0) {
+    error = cudaMemcpy(stamps_ns, handle->timeline, sizeof(uint64_t) * count, cudaMemcpyDeviceToHost);
+    if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy decode timeline");
+  }
+  *written = count;
+  return AIMA_MOE_OK;
+}
+
 AIMA_EXPORT int aima_moe_release(aima_moe_handle* handle) {
   if (handle == nullptr) return AIMA_MOE_OK;
+  cudaFree(handle->timeline);
   cudaFree(handle->dev_layers);
   cudaFree(handle->decode_scratch);
   prefill_workspace_free(&handle->prefill);

@@ -99,6 +99,9 @@ EXPORTS = [
     ("aima_moe_gemv_bf16_launch", c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
     ("aima_moe_decode_layers_noalloc", c_int,
      [ctypes.POINTER(LayerWeights), c_uint32, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
+    ("aima_moe_set_tracing", c_int, [c_void_p, c_int]),
+    ("aima_moe_read_decode_timeline", c_int,
+     [c_void_p, ctypes.POINTER(c_uint64), c_uint32, ctypes.POINTER(c_uint32)]),
     ("aima_moe_sync_metrics", c_int, [c_void_p, ctypes.POINTER(Metrics)]),
     ("aima_moe_release", c_int, [c_void_p]),
 ]
@@ -323,6 +326,18 @@ class MoeProvider:
         out = torch.empty(m, dtype=torch.bfloat16, device=weight.device)
         self.lib.check(self.lib.aima_moe_gemv_bf16_launch(_ptr(weight), _ptr(x), _ptr(out), m, k, _stream(torch)))
         return out
+
+    def set_tracing(self, enabled: bool) -> None:
+        self.lib.check(self.lib.aima_moe_set_tracing(self.handle, int(enabled)))
+
+    def decode_timeline(self) -> list[list[int]]:
+        """Per layer of the last traced decode launch: 12 GPU nanosecond stamps."""
+        capacity = MAX_LAYERS * 12
+        buffer = (c_uint64 * capacity)()
+        written = c_uint32()
+        self.lib.check(self.lib.aima_moe_read_decode_timeline(self.handle, buffer, capacity, ctypes.byref(written)))
+        values = list(buffer[: written.value])
+        return [values[i:i + 12] for i in range(0, len(values), 12)]
 
     def sync_metrics(self) -> Metrics:
         metrics = Metrics()

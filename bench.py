@@ -257,7 +257,7 @@ def run_ours(args) -> None:
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "decode_b1_stack40 (BASELINE config 1)", "layers": LAYERS,
+            "config": {"workload": f"decode_b1_stack{LAYERS} (BASELINE config 1)", "layers": LAYERS,
                        "hidden": HIDDEN, "experts": 256, "top_k": 8,
                        "l2": "inputs larger than L2 (2.3 GB of weights per step)",
                        "multi_gpu": "independent replicas" if world > 1 else "single GPU"},
@@ -279,15 +279,20 @@ def run_ours(args) -> None:
 
 
 def main() -> None:
+    global LAYERS, BYTES_PER_TOKEN
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=512)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--layers", type=int, default=LAYERS,
+                        help="stack depth; anything but 40 is a profiling aid, not the benchmark config")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    LAYERS = args.layers
+    BYTES_PER_TOKEN = LAYERS * BYTES_PER_LAYER_TOKEN
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -228,6 +228,19 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
  * padded-row counter; returns AIMA_MOE_ERR_TIMEOUT if a bounded wait ran out. */
 int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics* metrics);
 
+/* Tracing, the counterpart of AIMA_NATIVE_PREFILL_TIMELINE
+ * (native/src/native_resident_engine.hip.cpp:105-108, 1226-1259): when enabled,
+ * block 0 of the decode kernel stamps the GPU's nanosecond timer at
+ * AIMA_MOE_DECODE_TRACE_STAMPS points of every layer (layer start, norm done,
+ * router/shared rows done, logits barrier, top-8 done, routed gate/up done,
+ * activation barrier, activations loaded, down region landed, down dots done,
+ * output stored, output barrier).  read_decode_timeline synchronises and copies
+ * layers x AIMA_MOE_DECODE_TRACE_STAMPS stamps of the last decode launch. */
+#define AIMA_MOE_DECODE_TRACE_STAMPS 12
+int aima_moe_set_tracing(aima_moe_handle* handle, int enabled);
+int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t* stamps_ns,
+                                  uint32_t capacity, uint32_t* written);
+
 /* Device bytes prepare() would allocate for this configuration. */
 int aima_moe_query_workspace(const aima_moe_config* config, uint64_t* bytes);
 
