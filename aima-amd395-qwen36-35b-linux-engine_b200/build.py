@@ -15,7 +15,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libaima_moe_b200.so"
 SOURCES = ["moe_api.cu", "decode_kernel.cu", "decode_noalloc.cu", "pointwise.cu", "prefill.cu",
-           "grouped_gemm_simt.cu"]
+           "grouped_gemm_simt.cu", "grouped_gemm_tc.cu"]
 
 
 def nvcc_path() -> str:
@@ -46,7 +46,6 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if verbose:
         command += ["-Xptxas", "-v"]
     command += [str(CSRC / name) for name in SOURCES]
-    command += ["-lcuda"]
     result = subprocess.run(command, capture_output=True, text=True)
     if result.returncode != 0:
         sys.stderr.write(result.stdout + result.stderr)

@@ -27,6 +27,8 @@ enum GemmMode {
   kGemmSharedGateUp = 1,
   kGemmExpertDown = 2,
   kGemmSharedDown = 3,
+  kGemmPlain = 4,     // out = bf16(acc): the contract of Bf16GemmPlan::launch
+                      // (native/src/bf16_gemm.hip.cpp:220-234), dense rows only
 };
 
 struct GroupedGemm {
@@ -49,8 +51,17 @@ struct GroupedGemm {
   const int32_t* sorted_rows;  // flat routed row of each sorted position
 };
 
-cudaError_t launch_grouped_gemm(GemmMode mode, const GroupedGemm& problem,
-                                cudaStream_t stream);
+// What the tensor-core launcher needs beyond the problem itself.
+struct TcExtra {
+  int* status;          // device status word for bounded-wait expiry
+  int sm_count;         // persistent grid size
+  uint64_t a_rows;      // rows of the A allocation (TMA bounds; reads beyond are zero-filled)
+  int experts_in_b;     // experts held in b0 (expert modes), else 1
+};
+
+// tcgen05 / TMEM / TMA implementation (grouped_gemm_tc.cu).
+cudaError_t launch_grouped_gemm_tc(GemmMode mode, const GroupedGemm& problem,
+                                   const TcExtra& extra, cudaStream_t stream);
 
 // CUDA-core implementation kept as an on-device cross-check of the tensor-core
 // kernel (selected per call by the qualification flag).

@@ -107,8 +107,10 @@ grouped_gemm_simt_kernel(const GroupedGemm g) {
         out = __fmul_rn(det_silu(gate), up);
       } else if (MODE == kGemmExpertDown) {
         out = __fmul_rn(acc[i][j], scale);
-      } else {
+      } else if (MODE == kGemmSharedDown) {
         out = __fmul_rn(scale, round_bf16(acc[i][j]));
+      } else {
+        out = acc[i][j];
       }
       g.c[static_cast<size_t>(row) * g.ldc + n] = __float2bfloat16_rn(out);
     }
@@ -125,13 +127,9 @@ cudaError_t launch_grouped_gemm_simt(GemmMode mode, const GroupedGemm& g, cudaSt
     case kGemmSharedGateUp: grouped_gemm_simt_kernel<kGemmSharedGateUp><<<grid, 256, 0, stream>>>(g); break;
     case kGemmExpertDown: grouped_gemm_simt_kernel<kGemmExpertDown><<<grid, 256, 0, stream>>>(g); break;
     case kGemmSharedDown: grouped_gemm_simt_kernel<kGemmSharedDown><<<grid, 256, 0, stream>>>(g); break;
+    case kGemmPlain: grouped_gemm_simt_kernel<kGemmPlain><<<grid, 256, 0, stream>>>(g); break;
   }
   return cudaGetLastError();
-}
-
-// Until the tensor-core kernel lands this is the only implementation.
-cudaError_t launch_grouped_gemm(GemmMode mode, const GroupedGemm& g, cudaStream_t stream) {
-  return launch_grouped_gemm_simt(mode, g, stream);
 }
 
 }  // namespace aima

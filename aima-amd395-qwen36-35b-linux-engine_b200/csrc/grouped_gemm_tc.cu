@@ -1,0 +1,427 @@
+// Grouped BF16 products on the 5th-generation tensor cores (tcgen05 + TMEM),
+// operands staged by TMA, for the prefill expert and shared-expert products.
+//
+// Replaces the two fused_moe_kernel launches of the reference prefill path
+// (native/aot/gfx1151/q8192-output2/manifest.json:1398-1415, 4672-4689; launched
+// at native/src/native_moe_prefill.hip.cpp:862-876), expert_silu_multiply_kernel
+// (:384-402), and the five hipBLASLt plans of the shared expert with their
+// pointwise kernels (:790-826) -- the epilogues are fused.
+//
+// Work unit = one 128-row tile of one expert x one 256-wide slice of the output
+// columns.  D[128, 256] (FP32) lives in tensor memory, two buffers of 256
+// columns, so the epilogue of a unit overlaps the main loop of the next.
+//   warp 0   TMA producer: per 64-wide K block one 128x64 tile of A and two
+//            128x64 tiles of B into a 4-stage shared-memory ring (128-byte swizzle)
+//   warp 1   one thread issues tcgen05.mma (M128 N256 K16, 4 per K block) and
+//            commits to the ring's "empty" barriers / the accumulator's "full" barrier
+//   warp 2   allocates and frees the 512 tensor-memory columns
+//   warps 4-7 epilogue: tcgen05.ld 32 rows x 32 columns per warp, SwiGLU or
+//            scaling, BF16 stores
+// Every mbarrier wait is bounded; on expiry the block sets the status word,
+// stops issuing, waits for its copies in flight, frees tensor memory and returns.
+#include "grouped_gemm.cuh"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace aima {
+namespace {
+
+constexpr int kBM = 128;           // rows per tile (= kTileRows of the plan)
+constexpr int kBN = 256;           // accumulator columns per unit
+constexpr int kBK = 64;            // K elements per stage: 128 bytes = one swizzle row
+constexpr int kStages = 4;
+constexpr int kUmmaK = 16;
+constexpr int kStageABytes = kBM * kBK * 2;        // 16 KB
+constexpr int kStageBBytes = kBN * kBK * 2;        // 32 KB
+constexpr int kStageBytes = kStageABytes + kStageBBytes;
+constexpr int kTcThreads = 256;
+constexpr int kTmemColumns = 512;
+constexpr int kTcSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct TcMaps {
+  CUtensorMap a;    // [rows, k]      box 64 x 128
+  CUtensorMap b0;   // gate half / only weight matrix, [n_rows, k]
+  CUtensorMap b1;   // up half (may equal b0)
+};
+
+struct TcProblem {
+  GroupedGemm g;
+  int n_chunks;           // output column slices of kBN accumulator columns
+  int b_rows_per_expert;  // rows between experts in b0 / b1
+  int up_row_offset;      // row offset of the "up" half inside an expert (gate_up modes)
+  int n_valid;            // valid output columns (plain mode masks beyond)
+  int* status;            // device status word
+};
+
+// ---- PTX wrappers ---------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+               :: "r"(smem_dst), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes
+// (64 BF16) with the 128-byte swizzle TMA applies: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);          // start address
+  desc |= static_cast<uint64_t>(1) << 16;                               // leading byte offset (unused)
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;                       // stride byte offset
+  desc |= static_cast<uint64_t>(1) << 46;                               // descriptor version (sm_100)
+  desc |= static_cast<uint64_t>(2) << 61;                               // SWIZZLE_128B
+  return desc;
+}
+
+// Instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N = 256.
+constexpr uint32_t kInstrDesc =
+    (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kBN >> 3) << 17) |
+    (static_cast<uint32_t>(kBM >> 4) << 24);
+
+__device__ __forceinline__ void pack_store_32(__nv_bfloat16* dst, const float* v) {
+  uint4* out = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 w;
+    w.x = static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 0])) | (static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 1])) << 16);
+    w.y = static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 2])) | (static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 3])) << 16);
+    w.z = static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 4])) | (static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 5])) << 16);
+    w.w = static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 6])) | (static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 7])) << 16);
+    out[i] = w;
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kTcThreads, 1)
+grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) {
+  constexpr bool kDual = (MODE == kGemmExpertGateUp || MODE == kGemmSharedGateUp);
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the swizzled descriptors assume base offset 0
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages * kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * kStageBytes + 8 * (2 * kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 8 * (2 * kStages + 4) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const GroupedGemm& g = pb.g;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 2) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColumns);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_tiles = g.tile_count != nullptr ? *g.tile_count : g.max_tiles;
+  const int total_units = n_tiles * pb.n_chunks;
+  const int k_blocks = g.k / kBK;
+
+  auto unit_tile = [&](int unit, int& tile, int& chunk, int& expert, int& row0, int& rows) {
+    tile = unit / pb.n_chunks;
+    chunk = unit - tile * pb.n_chunks;
+    if (g.tile_expert != nullptr) {
+      expert = g.tile_expert[tile];
+      row0 = g.tile_row0[tile];
+      rows = g.tile_rows[tile];
+    } else {
+      expert = 0;
+      row0 = tile * kBM;
+      rows = min(kBM, g.dense_rows - row0);
+    }
+  };
+  auto timeout = [&]() {
+    atomicCAS(pb.status, 0, kStatusTimeoutMbarrier);
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool alive = true;
+      for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x) {
+        int tile, chunk, expert, row0, rows;
+        unit_tile(unit, tile, chunk, expert, row0, rows);
+        int b0_row, b1_row;
+        if (kDual) {
+          b0_row = expert * pb.b_rows_per_expert + chunk * (kBN / 2);
+          b1_row = expert * pb.b_rows_per_expert + pb.up_row_offset + chunk * (kBN / 2);
+        } else {
+          b0_row = expert * pb.b_rows_per_expert + chunk * kBN;
+          b1_row = b0_row + kBN / 2;
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
+          const uint32_t a_dst = smem_base + stage * kStageBytes;
+          const uint32_t b_dst = a_dst + kStageABytes;
+          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+          tma_load_2d(a_dst, &maps.a, kb * kBK, row0, full_bar(stage));
+          tma_load_2d(b_dst, &maps.b0, kb * kBK, b0_row, full_bar(stage));
+          tma_load_2d(b_dst + kStageBBytes / 2, kDual ? &maps.b1 : &maps.b0, kb * kBK, b1_row, full_bar(stage));
+          ++issued;
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // drain on abort: wait (bounded) for the stages whose copies are still in flight
+      if (*abort_flag != 0) {
+        volatile int ignore = 0;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < min(issued, kStages); ++i) {
+          if (--s < 0) { s = kStages - 1; ph ^= 1u; }
+          mbar_wait_bounded(full_bar(s), ph, &ignore);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool alive = true;
+      for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t use = static_cast<uint32_t>(local >> 1);
+        // the epilogue must have drained this accumulator buffer (first use: free)
+        if (!mbar_wait_bounded(tempty_bar(buf), (use & 1u) ^ 1u, abort_flag)) { alive = false; timeout(); break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kBN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag)) { alive = false; timeout(); break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * kStageBytes;
+          const uint32_t b_addr = a_addr + kStageABytes;
+          const uint64_t adesc = smem_desc_k_major_sw128(a_addr);
+          const uint64_t bdesc = smem_desc_k_major_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // advancing 16 elements (32 bytes) along K inside the swizzled row
+            umma_bf16(tmem_d, adesc + static_cast<uint64_t>(k * 2), bdesc + static_cast<uint64_t>(k * 2),
+                      kInstrDesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));      // frees the stage when the MMAs above retire
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (alive) umma_commit(tfull_bar(buf));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue ----------------------------------
+    const int ew = warp - 4;                       // TMEM lanes 32 ew .. 32 ew + 31
+    int local = 0;
+    bool alive = true;
+    for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x, ++local) {
+      int tile, chunk, expert, row0, rows;
+      unit_tile(unit, tile, chunk, expert, row0, rows);
+      const int buf = local & 1;
+      const uint32_t use = static_cast<uint32_t>(local >> 1);
+      if (!mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_flag)) { alive = false; if (lane == 0) timeout(); break; }
+      tc_fence_after();
+      const int r = ew * 32 + lane;                // row inside the tile
+      const bool row_ok = r < rows;
+      const int row = row0 + r;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(buf * kBN);
+      if (kDual) {
+        // columns [0,128) gate, [128,256) up  ->  128 activations per row
+        __nv_bfloat16* dst = g.c + static_cast<size_t>(row) * g.ldc + chunk * (kBN / 2);
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN / 2; c0 += 32) {
+          uint32_t gr[32], ur[32];
+          tmem_ld32(taddr + c0, gr);
+          tmem_ld32(taddr + kBN / 2 + c0, ur);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float gate = round_bf16(__uint_as_float(gr[j]));
+            const float up = round_bf16(__uint_as_float(ur[j]));
+            const float s = det_silu(gate);
+            v[j] = (MODE == kGemmExpertGateUp) ? __fmul_rn(round_bf16(s), up) : __fmul_rn(s, up);
+          }
+          if (row_ok) pack_store_32(dst + c0, v);
+        }
+      } else {
+        float scale = 1.0f;
+        if (row_ok) {
+          if (MODE == kGemmExpertDown) scale = g.row_scale[g.sorted_rows[row]];
+          if (MODE == kGemmSharedDown) scale = g.row_scale[row];
+        }
+        const int col_base = chunk * kBN;
+        __nv_bfloat16* dst = g.c + static_cast<size_t>(row) * g.ldc + col_base;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN; c0 += 32) {
+          uint32_t ar[32];
+          tmem_ld32(taddr + c0, ar);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float acc = __uint_as_float(ar[j]);
+            if (MODE == kGemmExpertDown) v[j] = __fmul_rn(acc, scale);
+            else if (MODE == kGemmSharedDown) v[j] = __fmul_rn(scale, round_bf16(acc));
+            else v[j] = acc;
+          }
+          if (row_ok && col_base + c0 + 32 <= pb.n_valid) {
+            pack_store_32(dst + c0, v);
+          } else if (row_ok) {
+            for (int j = 0; j < 32; ++j)
+              if (col_base + c0 + j < pb.n_valid) dst[c0 + j] = __float2bfloat16_rn(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, kTmemColumns);
+}
+
+// ---- host side --------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (fn == nullptr) {
+    void* pointer = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pointer, cudaEnableDefault, &query) == cudaSuccess &&
+        query == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(pointer);
+    }
+  }
+  return fn;
+}
+
+// 2-D BF16 tensor [rows, cols] row-major, box 64 columns x 128 rows, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems) {
+  PFN_cuTensorMapEncodeTiled_v12000 encode = encode_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch_elems * 2};
+  const cuuint32_t box[2] = {kBK, kBM};
+  const cuuint32_t elem[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int MODE>
+cudaError_t launch_mode(const TcMaps& maps, const TcProblem& pb, int grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<MODE>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  grouped_gemm_tc_kernel<MODE><<<grid, kTcThreads, kTcSmemBytes, stream>>>(maps, pb);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_grouped_gemm_tc(GemmMode mode, const GroupedGemm& g, const TcExtra& extra,
+                                   cudaStream_t stream) {
+  if (g.max_tiles <= 0) return cudaSuccess;
+  if (g.k % kBK != 0 || extra.status == nullptr) return cudaErrorInvalidValue;
+  TcMaps maps;
+  TcProblem pb{};
+  pb.g = g;
+  pb.status = extra.status;
+  pb.n_valid = g.n;
+  const bool dual = (mode == kGemmExpertGateUp || mode == kGemmSharedGateUp);
+  const uint64_t experts = static_cast<uint64_t>(extra.experts_in_b);
+  bool ok = make_map(&maps.a, g.a, extra.a_rows, static_cast<uint64_t>(g.k), static_cast<uint64_t>(g.lda));
+  if (mode == kGemmExpertGateUp) {
+    pb.n_chunks = g.n / (kBN / 2);
+    pb.b_rows_per_expert = 2 * g.n;
+    pb.up_row_offset = g.n;
+    ok = ok && make_map(&maps.b0, g.b0, experts * 2 * g.n, g.k, g.k);
+    maps.b1 = maps.b0;
+  } else if (mode == kGemmSharedGateUp) {
+    pb.n_chunks = g.n / (kBN / 2);
+    pb.b_rows_per_expert = 0;
+    pb.up_row_offset = 0;
+    ok = ok && make_map(&maps.b0, g.b0, g.n, g.k, g.k) && make_map(&maps.b1, g.b1, g.n, g.k, g.k);
+  } else {
+    pb.n_chunks = (g.n + kBN - 1) / kBN;
+    pb.b_rows_per_expert = (mode == kGemmExpertDown) ? g.n : 0;
+    pb.up_row_offset = 0;
+    ok = ok && make_map(&maps.b0, g.b0, (mode == kGemmExpertDown ? experts : 1) * static_cast<uint64_t>(g.n), g.k, g.k);
+    maps.b1 = maps.b0;
+  }
+  (void)dual;
+  if (!ok) return cudaErrorNotSupported;
+  const int grid = extra.sm_count;
+  switch (mode) {
+    case kGemmExpertGateUp: return launch_mode<kGemmExpertGateUp>(maps, pb, grid, stream);
+    case kGemmSharedGateUp: return launch_mode<kGemmSharedGateUp>(maps, pb, grid, stream);
+    case kGemmExpertDown: return launch_mode<kGemmExpertDown>(maps, pb, grid, stream);
+    case kGemmSharedDown: return launch_mode<kGemmSharedDown>(maps, pb, grid, stream);
+    case kGemmPlain: return launch_mode<kGemmPlain>(maps, pb, grid, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace aima

@@ -8,6 +8,7 @@
 
 #include "decode_kernel.cuh"
 #include "pointwise.cuh"
+#include "grouped_gemm.cuh"
 #include "prefill.cuh"
 
 #include <cstdarg>
@@ -309,6 +310,8 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
     status = prefill_workspace_allocate(&handle->prefill, config->max_prefill_tokens,
                                         handle->sm_count, g_last_error, sizeof g_last_error);
     if (status != AIMA_MOE_OK) return cleanup(status);
+    handle->prefill.status = handle->status;
+    handle->prefill.use_simt_gemm = (config->flags & AIMA_MOE_FLAG_SIMT_PRODUCTS) != 0;
   }
   handle->metrics.struct_bytes = sizeof(aima_moe_metrics);
   handle->metrics.workspace_bytes = handle->decode_scratch_bytes + sizeof(LayerPtrs) * kMaxLayers +
@@ -419,6 +422,7 @@ AIMA_EXPORT int aima_moe_prefill_launch(aima_moe_handle* handle, uint32_t layer,
   call.residual = residual;
   call.out = out;
   call.tokens = static_cast<int>(tokens);
+  call.experts_local = handle->experts_local;
   call.router_bias = handle->router_bias;
   call.quant_eighths = handle->quant_eighths;
   call.debug = debug;
@@ -474,6 +478,7 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
     call.residual = current;
     call.out = target;
     call.tokens = static_cast<int>(tokens);
+    call.experts_local = handle->experts_local;
     call.router_bias = handle->router_bias;
     call.quant_eighths = handle->quant_eighths;
     int launches = 0;
@@ -514,6 +519,30 @@ AIMA_EXPORT int aima_moe_gemv_bf16_launch(const void* weight, const void* x, voi
   const cudaError_t error = launch_gemv_bf16(weight, x, out, static_cast<int>(m),
                                              static_cast<int>(k), static_cast<cudaStream_t>(stream));
   if (error != cudaSuccess) return fail_cuda(error, "launch gemv_bf16_kernel");
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_gemm_bf16_launch(aima_moe_handle* handle, const void* a, const void* b,
+                                          void* d, uint32_t m, uint32_t n, uint32_t k, void* stream) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if (a == nullptr || b == nullptr || d == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "gemm pointer is null");
+  if (m == 0 || n == 0 || k == 0 || k % 64 != 0 || n % 8 != 0)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "gemm needs k a multiple of 64 and n a multiple of 8");
+  GroupedGemm g{};
+  g.max_tiles = static_cast<int>((m + kTileRows - 1) / kTileRows);
+  g.dense_rows = static_cast<int>(m);
+  g.a = static_cast<const __nv_bfloat16*>(a); g.lda = static_cast<int>(k); g.k = static_cast<int>(k);
+  g.b0 = static_cast<const __nv_bfloat16*>(b);
+  g.n = static_cast<int>(n);
+  g.c = static_cast<__nv_bfloat16*>(d); g.ldc = static_cast<int>(n);
+  TcExtra extra{};
+  extra.status = handle->status; extra.sm_count = handle->sm_count; extra.a_rows = m; extra.experts_in_b = 1;
+  const cudaError_t error = launch_grouped_gemm_tc(kGemmPlain, g, extra, static_cast<cudaStream_t>(stream));
+  if (error != cudaSuccess) return fail_cuda(error, "launch grouped_gemm_tc_kernel (plain)");
+  handle->last_stream = static_cast<cudaStream_t>(stream);
+  handle->metrics.kernel_launches += 1;
   return AIMA_MOE_OK;
 }
 

@@ -539,13 +539,20 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   g.b_expert_stride = static_cast<size_t>(2 * kInter) * kHidden;
   g.n = kInter; g.c = ws->expert_act; g.ldc = kInter;
   g.row_scale = nullptr; g.sorted_rows = nullptr;
-  if ((code = launch_grouped_gemm(kGemmExpertGateUp, g, stream)) != cudaSuccess)
+  TcExtra extra{};
+  extra.status = ws->status; extra.sm_count = ws->sm_count;
+  extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK; extra.experts_in_b = call.experts_local;
+  auto product = [&](GemmMode mode, const GroupedGemm& problem, const TcExtra& x) {
+    return ws->use_simt_gemm ? launch_grouped_gemm_simt(mode, problem, stream)
+                             : launch_grouped_gemm_tc(mode, problem, x, stream);
+  };
+  if ((code = product(kGemmExpertGateUp, g, extra)) != cudaSuccess)
     return set_error(error, error_bytes, code, "grouped gemm expert gate_up");
   g.a = ws->expert_act; g.lda = kInter; g.k = kInter;
   g.b0 = call.layer.expert_down; g.b_expert_stride = static_cast<size_t>(kHidden) * kInter;
   g.n = kHidden; g.c = ws->expert_down; g.ldc = kHidden;
   g.row_scale = ws->topk_weights; g.sorted_rows = ws->sorted_rows;
-  if ((code = launch_grouped_gemm(kGemmExpertDown, g, stream)) != cudaSuccess)
+  if ((code = product(kGemmExpertDown, g, extra)) != cudaSuccess)
     return set_error(error, error_bytes, code, "grouped gemm expert down");
   count += 2;
 
@@ -556,13 +563,15 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   s.a = static_cast<const __nv_bfloat16*>(call.h2); s.lda = kHidden; s.k = kHidden;
   s.b0 = call.layer.shared_gate_proj; s.b1 = call.layer.shared_up_proj; s.b_expert_stride = 0;
   s.n = kSharedInter; s.c = ws->shared_act; s.ldc = kSharedInter;
-  if ((code = launch_grouped_gemm(kGemmSharedGateUp, s, stream)) != cudaSuccess)
+  extra.a_rows = static_cast<uint64_t>(T); extra.experts_in_b = 1;
+  if ((code = product(kGemmSharedGateUp, s, extra)) != cudaSuccess)
     return set_error(error, error_bytes, code, "grouped gemm shared gate_up");
   s.a = ws->shared_act; s.lda = kSharedInter; s.k = kSharedInter;
   s.b0 = call.layer.shared_down_proj; s.b1 = nullptr;
   s.n = kHidden; s.c = ws->shared_scaled; s.ldc = kHidden;
   s.row_scale = ws->shared_sigmoid;
-  if ((code = launch_grouped_gemm(kGemmSharedDown, s, stream)) != cudaSuccess)
+  extra.a_rows = static_cast<uint64_t>(ws->capacity);
+  if ((code = product(kGemmSharedDown, s, extra)) != cudaSuccess)
     return set_error(error, error_bytes, code, "grouped gemm shared down");
   count += 2;
 

@@ -14,6 +14,8 @@ struct PrefillWorkspace {
   size_t total_bytes = 0;
   int capacity = 0;
   int sm_count = 0;
+  int* status = nullptr;              // device status word shared with the handle
+  bool use_simt_gemm = false;         // qualification: CUDA-core products instead of tcgen05
   uint8_t* base = nullptr;
   // router outputs
   int32_t* topk_ids = nullptr;        // [T, 8]
@@ -49,6 +51,7 @@ struct PrefillCall {
   const void* residual;
   void* out;
   int tokens;
+  int experts_local;             // experts held in the bound expert tensors
   const float* router_bias;
   int quant_eighths;
   const aima_moe_debug_views* debug;

@@ -97,6 +97,8 @@ EXPORTS = [
     ("aima_moe_rmsnorm_launch", c_int,
      [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_float, c_void_p]),
     ("aima_moe_gemv_bf16_launch", c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
+    ("aima_moe_gemm_bf16_launch", c_int,
+     [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p]),
     ("aima_moe_decode_layers_noalloc", c_int,
      [ctypes.POINTER(LayerWeights), c_uint32, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     ("aima_moe_set_tracing", c_int, [c_void_p, c_int]),
@@ -168,6 +170,7 @@ WEIGHT_KEYS = ("router", "expert_gate_up", "expert_down", "shared_gate", "shared
 
 
 NOALLOC_MAX_LAYERS = 8
+FLAG_SIMT_PRODUCTS = 1
 
 
 def layer_weights_struct(weights: Mapping[str, Any]) -> LayerWeights:
@@ -205,7 +208,7 @@ class MoeProvider:
     """Owns one aima_moe handle on the current CUDA device."""
 
     def __init__(self, layers: int, max_prefill_tokens: int = 0, world: int = 1, rank: int = 0,
-                 rms_eps: float = 1.0e-6, library: MoeLibrary | None = None) -> None:
+                 rms_eps: float = 1.0e-6, library: MoeLibrary | None = None, flags: int = 0) -> None:
         import torch  # device memory and streams only
 
         if not torch.cuda.is_available():
@@ -215,7 +218,7 @@ class MoeProvider:
         self.layers = layers
         self.max_prefill_tokens = max_prefill_tokens
         self.config = Config(ctypes.sizeof(Config), HIDDEN, EXPERTS, TOP_K, EXPERT_INTER, SHARED_INTER,
-                             layers, max_prefill_tokens, world, rank, rms_eps, 0)
+                             layers, max_prefill_tokens, world, rank, rms_eps, flags)
         handle = c_void_p()
         self.lib.check(self.lib.aima_moe_prepare(ctypes.byref(self.config), ctypes.byref(handle)))
         self.handle = handle
@@ -338,6 +341,16 @@ class MoeProvider:
         self.lib.check(self.lib.aima_moe_read_decode_timeline(self.handle, buffer, capacity, ctypes.byref(written)))
         values = list(buffer[: written.value])
         return [values[i:i + 12] for i in range(0, len(values), 12)]
+
+    def gemm(self, a: Any, b: Any) -> Any:
+        """D[m, n] = A[m, k] . B[n, k]^T on the tensor cores (BF16 in/out)."""
+        torch = self._torch
+        m, k = int(a.shape[0]), int(a.shape[1])
+        n = int(b.shape[0])
+        d = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+        self.lib.check(self.lib.aima_moe_gemm_bf16_launch(self.handle, _ptr(a), _ptr(b), _ptr(d), m, n, k,
+                                                          _stream(torch)))
+        return d
 
     def sync_metrics(self) -> Metrics:
         metrics = Metrics()

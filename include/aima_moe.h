@@ -78,6 +78,9 @@ typedef struct aima_moe_config {
 } aima_moe_config;
 
 #define AIMA_MOE_FLAG_NONE 0u
+/* Qualification only: run the prefill products on CUDA cores instead of the
+ * tcgen05 kernel, to cross-check the tensor-core kernel on the device. */
+#define AIMA_MOE_FLAG_SIMT_PRODUCTS 1u
 
 /* One layer's tensors in checkpoint layout
  * (doc/reference/amd395-qwen36-35b-a3b-bf16/qwen36-shape-manifest.json:162-180,
@@ -193,6 +196,12 @@ int aima_moe_rmsnorm_launch(const void* x, const void* residual,
  * contract of launch_bf16_wvsplitk (native/src/bf16_wvsplitk.hip.cpp:337-366). */
 int aima_moe_gemv_bf16_launch(const void* weight, const void* x, void* out,
                               uint32_t m, uint32_t k, void* stream);
+
+/* Dense D[m,n] = A[m,k] . B[n,k]^T, BF16 in/out, FP32 accumulate on the tensor
+ * cores: the contract of Bf16GemmPlan::launch
+ * (native/src/bf16_gemm.hip.cpp:220-234).  k % 64 == 0, n % 8 == 0. */
+int aima_moe_gemm_bf16_launch(aima_moe_handle* handle, const void* a, const void* b,
+                              void* d, uint32_t m, uint32_t n, uint32_t k, void* stream);
 
 /* Decode without any allocation -- this entry point has no counterpart in the
  * reference.  It exists for hosts that must not, or cannot, allocate device

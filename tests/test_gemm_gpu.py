@@ -1,0 +1,84 @@
+"""GPU tests of the tensor-core (tcgen05) product kernel through the C ABI: the reference's
+all-ones known answer, agreement with an FP32 torch reference, and agreement of the whole prefill
+layer with the CUDA-core cross-check kernel at a size the CPU oracle cannot reach."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SEED = 1234
+
+
+@pytest.fixture(scope="module")
+def provider(package, built_library):
+    provider = package.MoeProvider(layers=1, max_prefill_tokens=0)
+    yield provider
+    provider.release()
+
+
+def test_all_ones_gemm_reference_shape(provider):
+    """native/src/bf16_gemm.hip.cpp:281-291: 8192 x 12352 x 2048 all-ones -> every output BF16 0x4500."""
+    device = torch.device("cuda", 0)
+    a = torch.ones(8192, 2048, dtype=torch.bfloat16, device=device)
+    b = torch.ones(12352, 2048, dtype=torch.bfloat16, device=device)
+    d = provider.gemm(a, b)
+    provider.sync_metrics()
+    bits = d.view(torch.int16)
+    assert int((bits != 0x4500).sum()) == 0
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 64), (1, 8, 64), (300, 1000, 512), (1024, 2048, 2048), (77, 264, 192)])
+def test_gemm_matches_fp32_reference(provider, shape):
+    device = torch.device("cuda", 0)
+    m, n, k = shape
+    generator = torch.Generator(device=device).manual_seed(SEED + m + n + k)
+    a = torch.randn(m, k, generator=generator, device=device, dtype=torch.float32).to(torch.bfloat16)
+    b = (torch.randn(n, k, generator=generator, device=device, dtype=torch.float32) * 0.05).to(torch.bfloat16)
+    d = provider.gemm(a, b)
+    provider.sync_metrics()
+    want = (a.float() @ b.float().t())
+    got = d.float()
+    # one BF16 rounding of an FP32-accumulated sum: within 2^-8 relative plus accumulation noise
+    tolerance = want.abs() * 2.0 ** -8 + 1e-3 * (k ** 0.5) * 0.05
+    assert ((got - want).abs() <= tolerance).all()
+    cosine = float((got.double().reshape(-1) @ want.double().reshape(-1)) /
+                   (got.double().norm() * want.double().norm()))
+    assert cosine >= 0.99999
+
+
+def test_prefill_tensor_core_products_match_cuda_core_products(package, gpu_layers, synth):
+    """Whole prefill layer at T = 1024 with skewed routing: tcgen05 products vs the CUDA-core
+    cross-check kernel (same rounding points, different FP32 accumulation order)."""
+    device = torch.device("cuda", 0)
+    tokens = 1024
+    weights = gpu_layers(0)["cuda"]
+    h2 = synth.activations(SEED + 77, tokens, "input", 0).to(device)
+    resid = synth.activations(SEED + 77, tokens, "residual", 0).to(device)
+    bias = synth.zipf_router_bias(SEED).to(device)
+    outputs = []
+    for flags in (0, package.provider.FLAG_SIMT_PRODUCTS):
+        provider = package.MoeProvider(layers=1, max_prefill_tokens=tokens, flags=flags)
+        try:
+            provider.bind_layer(0, weights)
+            provider.set_router_hooks(bias, quantize_eighths=False)
+            views, tensors = provider.make_debug(tokens, prefill=True)
+            out = provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, debug=views)
+            provider.sync_metrics()
+            outputs.append((out.clone(), {k: v.clone() for k, v in tensors.items()}))
+        finally:
+            provider.release()
+    (out_tc, dbg_tc), (out_simt, dbg_simt) = outputs
+    assert torch.equal(dbg_tc["topk_ids"], dbg_simt["topk_ids"])
+    assert torch.equal(dbg_tc["sorted_rows"], dbg_simt["sorted_rows"])
+    counts = dbg_tc["expert_counts"]
+    assert int(counts.max()) > 128 and int((counts == 0).sum()) >= 0      # multi-tile and ragged experts
+    moe_tc = dbg_tc["routed"].float() + dbg_tc["shared_scaled"].float()
+    moe_simt = dbg_simt["routed"].float() + dbg_simt["shared_scaled"].float()
+    assert (moe_tc - moe_simt).abs().max() <= 2.0e-2
+    cosine = float((moe_tc.double().reshape(-1) @ moe_simt.double().reshape(-1)) /
+                   (moe_tc.double().norm() * moe_simt.double().norm()))
+    assert cosine >= 0.9999
+    assert (dbg_tc["routed"] == dbg_simt["routed"]).float().mean() > 0.9
+    assert torch.isfinite(out_tc.float()).all()
