@@ -29,6 +29,7 @@ enum GemmMode {
   kGemmSharedDown = 3,
   kGemmPlain = 4,     // out = bf16(acc): the contract of Bf16GemmPlan::launch
                       // (native/src/bf16_gemm.hip.cpp:220-234), dense rows only
+  kGemmPlainF32 = 5,  // out = acc as FP32 into c_f32 (approximate router logits)
 };
 
 struct GroupedGemm {
@@ -46,6 +47,7 @@ struct GroupedGemm {
   size_t b_expert_stride;      // elements between experts in b0
   int n;                       // output columns
   __nv_bfloat16* c;            // [rows, n]
+  float* c_f32;                // FP32 output of kGemmPlainF32
   int ldc;
   const float* row_scale;      // routing weights [T*8] or sigmoid gate [T]
   const int32_t* sorted_rows;  // flat routed row of each sorted position

@@ -128,6 +128,7 @@ cudaError_t launch_grouped_gemm_simt(GemmMode mode, const GroupedGemm& g, cudaSt
     case kGemmExpertDown: grouped_gemm_simt_kernel<kGemmExpertDown><<<grid, 256, 0, stream>>>(g); break;
     case kGemmSharedDown: grouped_gemm_simt_kernel<kGemmSharedDown><<<grid, 256, 0, stream>>>(g); break;
     case kGemmPlain: grouped_gemm_simt_kernel<kGemmPlain><<<grid, 256, 0, stream>>>(g); break;
+    case kGemmPlainF32: return cudaErrorNotSupported;
   }
   return cudaGetLastError();
 }

@@ -321,7 +321,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
             else if (MODE == kGemmSharedDown) v[j] = __fmul_rn(scale, round_bf16(acc));
             else v[j] = acc;
           }
-          if (row_ok && col_base + c0 + 32 <= pb.n_valid) {
+          if (MODE == kGemmPlainF32) {
+            if (row_ok) {
+              float4* out = reinterpret_cast<float4*>(g.c_f32 + static_cast<size_t>(row) * g.ldc + col_base + c0);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (col_base + c0 + 4 * j + 4 <= pb.n_valid)
+                  out[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              }
+            }
+          } else if (row_ok && col_base + c0 + 32 <= pb.n_valid) {
             pack_store_32(dst + c0, v);
           } else if (row_ok) {
             for (int j = 0; j < 32; ++j)
@@ -420,6 +429,7 @@ cudaError_t launch_grouped_gemm_tc(GemmMode mode, const GroupedGemm& g, const Tc
     case kGemmExpertDown: return launch_mode<kGemmExpertDown>(maps, pb, grid, stream);
     case kGemmSharedDown: return launch_mode<kGemmSharedDown>(maps, pb, grid, stream);
     case kGemmPlain: return launch_mode<kGemmPlain>(maps, pb, grid, stream);
+    case kGemmPlainF32: return launch_mode<kGemmPlainF32>(maps, pb, grid, stream);
   }
   return cudaErrorInvalidValue;
 }

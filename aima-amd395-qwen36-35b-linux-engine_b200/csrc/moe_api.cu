@@ -83,6 +83,7 @@ struct aima_moe_handle {
 
   PrefillWorkspace prefill;
 
+  float* router_row_norms = nullptr;        // [kMaxLayers][256], device, filled by bind_layer
   unsigned long long* timeline = nullptr;   // [kMaxLayers * kDecodeTraceStamps], device
   bool tracing = false;
   uint32_t traced_layers = 0;
@@ -277,6 +278,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
 
   auto cleanup = [&](int code) {
     if (handle->timeline) cudaFree(handle->timeline);
+    if (handle->router_row_norms) cudaFree(handle->router_row_norms);
     if (handle->dev_layers) cudaFree(handle->dev_layers);
     if (handle->decode_scratch) cudaFree(handle->decode_scratch);
     prefill_workspace_free(&handle->prefill);
@@ -291,6 +293,8 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
 
   error = cudaMalloc(&handle->timeline, sizeof(unsigned long long) * kMaxLayers * kDecodeTraceStamps);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc decode timeline"));
+  error = cudaMalloc(&handle->router_row_norms, sizeof(float) * kMaxLayers * kExperts);
+  if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc router row norms"));
   handle->decode_scratch_bytes = decode_scratch_size();
   error = cudaMalloc(&handle->decode_scratch, handle->decode_scratch_bytes);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc decode scratch"));
@@ -312,6 +316,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
     if (status != AIMA_MOE_OK) return cleanup(status);
     handle->prefill.status = handle->status;
     handle->prefill.use_simt_gemm = (config->flags & AIMA_MOE_FLAG_SIMT_PRODUCTS) != 0;
+    handle->prefill.exact_router = (config->flags & AIMA_MOE_FLAG_EXACT_ROUTER) != 0;
   }
   handle->metrics.struct_bytes = sizeof(aima_moe_metrics);
   handle->metrics.workspace_bytes = handle->decode_scratch_bytes + sizeof(LayerPtrs) * kMaxLayers +
@@ -367,9 +372,12 @@ AIMA_EXPORT int aima_moe_bind_layer(aima_moe_handle* handle, uint32_t layer,
   pointers.shared_up_proj = static_cast<const __nv_bfloat16*>(weights->shared_up_proj);
   pointers.shared_down_proj = static_cast<const __nv_bfloat16*>(weights->shared_down_proj);
   pointers.norm_weight = static_cast<const __nv_bfloat16*>(weights->post_attention_norm);
-  const cudaError_t error = cudaMemcpy(handle->dev_layers + layer, &pointers, sizeof pointers,
-                                       cudaMemcpyHostToDevice);
+  cudaError_t error = cudaMemcpy(handle->dev_layers + layer, &pointers, sizeof pointers,
+                                 cudaMemcpyHostToDevice);
   if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy layer table entry");
+  error = launch_router_row_norms(pointers.router, handle->router_row_norms + layer * kExperts, nullptr);
+  if (error == cudaSuccess) error = cudaStreamSynchronize(nullptr);
+  if (error != cudaSuccess) return fail_cuda(error, "router row norms");
   handle->host_layers[layer] = pointers;
   handle->bound[layer] = true;
   return AIMA_MOE_OK;
@@ -423,6 +431,7 @@ AIMA_EXPORT int aima_moe_prefill_launch(aima_moe_handle* handle, uint32_t layer,
   call.out = out;
   call.tokens = static_cast<int>(tokens);
   call.experts_local = handle->experts_local;
+  call.router_row_norms = handle->router_row_norms + layer * kExperts;
   call.router_bias = handle->router_bias;
   call.quant_eighths = handle->quant_eighths;
   call.debug = debug;
@@ -479,6 +488,7 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
     call.out = target;
     call.tokens = static_cast<int>(tokens);
     call.experts_local = handle->experts_local;
+    call.router_row_norms = handle->router_row_norms + layer * kExperts;
     call.router_bias = handle->router_bias;
     call.quant_eighths = handle->quant_eighths;
     int launches = 0;
@@ -560,6 +570,11 @@ AIMA_EXPORT int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics*
     error = cudaMemcpy(&handle->metrics.last_padded_routed_rows, handle->prefill.padded_rows,
                        sizeof(int32_t), cudaMemcpyDeviceToHost);
     if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy padded row count");
+    int32_t stats[2] = {0, 0};
+    error = cudaMemcpy(stats, handle->prefill.router_stats, sizeof stats, cudaMemcpyDeviceToHost);
+    if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy router statistics");
+    handle->metrics.router_candidates = static_cast<uint64_t>(static_cast<uint32_t>(stats[0]));
+    handle->metrics.router_tokens = static_cast<uint64_t>(static_cast<uint32_t>(stats[1]));
   }
   if (metrics != nullptr) {
     if (metrics->struct_bytes != sizeof(aima_moe_metrics))
@@ -607,6 +622,7 @@ AIMA_EXPORT int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t*
 AIMA_EXPORT int aima_moe_release(aima_moe_handle* handle) {
   if (handle == nullptr) return AIMA_MOE_OK;
   cudaFree(handle->timeline);
+  cudaFree(handle->router_row_norms);
   cudaFree(handle->dev_layers);
   cudaFree(handle->decode_scratch);
   prefill_workspace_free(&handle->prefill);

@@ -20,6 +20,126 @@
 namespace aima {
 namespace {
 
+// Monotone map FP32 -> uint32 (larger float <=> larger key), for redux-based maxima.
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// 8th largest of the 256 values a warp holds (8 per lane), counting repeats.
+__device__ __forceinline__ float warp_eighth_largest(const float* v, int lane) {
+  uint32_t k[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) k[q] = order_key(v[q]);
+  uint32_t best = 0;
+#pragma unroll
+  for (int r = 0; r < kTopK; ++r) {
+    uint32_t local = k[0];
+#pragma unroll
+    for (int q = 1; q < 8; ++q) local = max(local, k[q]);
+    best = __reduce_max_sync(0xffffffffu, local);
+    const unsigned owners = __ballot_sync(0xffffffffu, local == best);
+    if (lane == __ffs(owners) - 1) {
+      bool removed = false;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (!removed && k[q] == best) { k[q] = 0u; removed = true; }
+      }
+    }
+  }
+  return key_value(best);
+}
+
+// The reference's prefill selection on the final (BF16-rounded) logits of one
+// token held as v[q] = logit of expert 32 q + lane: threshold, gather in expert
+// order, fixed bitonic network, softmax; lanes 0..7 write slot `lane`.
+__device__ __forceinline__ void route_token(const float* v, int lane, float* sel_v, int* sel_i,
+                                            size_t token, int32_t* __restrict__ ids,
+                                            float* __restrict__ scores, float* __restrict__ weights,
+                                            __nv_bfloat16* __restrict__ dbg_weights) {
+  const float threshold = warp_eighth_largest(v, lane);
+  const unsigned lt_mask = (1u << lane) - 1u;
+  int held = 0;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const bool take = v[q] > threshold;
+    const unsigned m = __ballot_sync(0xffffffffu, take);
+    if (take) {
+      const int pos = held + __popc(m & lt_mask);
+      sel_v[pos] = v[q];
+      sel_i[pos] = 32 * q + lane;
+    }
+    held += __popc(m);
+  }
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const bool take = v[q] == threshold;
+    const unsigned m = __ballot_sync(0xffffffffu, take);
+    if (take) {
+      const int pos = held + __popc(m & lt_mask);
+      if (pos < kTopK) {
+        sel_v[pos] = v[q];
+        sel_i[pos] = 32 * q + lane;
+      }
+    }
+    held += __popc(m);
+  }
+  __syncwarp();
+  float sv[kTopK];
+  int si[kTopK];
+#pragma unroll
+  for (int r = 0; r < kTopK; ++r) { sv[r] = sel_v[r]; si[r] = sel_i[r]; }
+  __syncwarp();
+  // fixed 8-wide bitonic network; a pair is exchanged when
+  // (value[left] > value[right]) equals the "ascending" flag of the left index
+#pragma unroll
+  for (int width = 2; width <= kTopK; width *= 2) {
+#pragma unroll
+    for (int stride = width / 2; stride > 0; stride /= 2) {
+#pragma unroll
+      for (int left = 0; left < kTopK; ++left) {
+        const int right = left ^ stride;
+        if (right > left) {
+          const bool ascending = (left & width) != 0;
+          if ((sv[left] > sv[right]) == ascending) {
+            const float tv = sv[left]; sv[left] = sv[right]; sv[right] = tv;
+            const int ti = si[left]; si[left] = si[right]; si[right] = ti;
+          }
+        }
+      }
+    }
+  }
+  float ex[kTopK];
+  float denom = 0.0f;
+#pragma unroll
+  for (int r = 0; r < kTopK; ++r) {
+    ex[r] = det_expf(__fsub_rn(sv[r], sv[0]));
+    denom = __fadd_rn(denom, ex[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < kTopK; ++r) {
+    if (lane == r) {
+      const size_t o = token * kTopK + r;
+      const uint16_t wb = float_to_bf16_bits(__fdiv_rn(ex[r], denom));
+      ids[o] = si[r];
+      scores[o] = sv[r];
+      weights[o] = bf16_bits_to_float(wb);
+      if (dbg_weights != nullptr) reinterpret_cast<uint16_t*>(dbg_weights)[o] = wb;
+    }
+  }
+}
+
+// logit transform shared by both router kernels: optional harness hooks, then
+// the BF16 rounding the reference's router GEMM applies
+__device__ __forceinline__ float finish_logit(float x, float bias, int quant_eighths) {
+  x = __fadd_rn(x, bias);
+  if (quant_eighths) x = __fmul_rn(rintf(__fmul_rn(x, 8.0f)), 0.125f);
+  return round_bf16(x);
+}
+
 // ---------------------------------------------------------------------------
 // Router: canonical FP32 logits of all 256 experts (+ the shared-expert gate
 // row), BF16 rounding, the reference's selection rule and softmax.
@@ -98,117 +218,125 @@ prefill_router_kernel(const __nv_bfloat16* __restrict__ h2,
   // harness hooks, then the BF16 rounding the reference's router GEMM applies
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
-    float x = v[q];
-    if (bias != nullptr) x = __fadd_rn(x, bias[32 * q + lane]);
-    if (quant_eighths) x = __fmul_rn(rintf(__fmul_rn(x, 8.0f)), 0.125f);
-    v[q] = round_bf16(x);
+    v[q] = finish_logit(v[q], bias != nullptr ? bias[32 * q + lane] : 0.0f, quant_eighths);
     if (dbg_logits != nullptr) dbg_logits[static_cast<size_t>(token) * kExperts + 32 * q + lane] = v[q];
   }
-
-  // threshold = 8th largest value counting repeats
-  float threshold;
-  {
-    float w[8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) w[q] = v[q];
-    float best = 0.0f;
-#pragma unroll
-    for (int r = 0; r < kTopK; ++r) {
-      best = w[0];
-      int best_id = lane;
-#pragma unroll
-      for (int q = 1; q < 8; ++q) {
-        if (w[q] > best) { best = w[q]; best_id = 32 * q + lane; }
-      }
-#pragma unroll
-      for (int s = 16; s >= 1; s >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, s);
-        const int oi = __shfl_xor_sync(0xffffffffu, best_id, s);
-        if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
-      }
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        if (best_id == 32 * q + lane) w[q] = -CUDART_INF_F;
-      }
-    }
-    threshold = best;
-  }
-
-  // values above the threshold in expert order, then threshold ties in expert
-  // order until eight are held
-  float* sel_v = sel_v_s + warp * 8;
-  int* sel_i = sel_i_s + warp * 8;
-  const unsigned lt_mask = (1u << lane) - 1u;
-  int held = 0;
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    const bool take = v[q] > threshold;
-    const unsigned m = __ballot_sync(0xffffffffu, take);
-    if (take) {
-      const int pos = held + __popc(m & lt_mask);
-      sel_v[pos] = v[q];
-      sel_i[pos] = 32 * q + lane;
-    }
-    held += __popc(m);
-  }
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    const bool take = v[q] == threshold;
-    const unsigned m = __ballot_sync(0xffffffffu, take);
-    if (take) {
-      const int pos = held + __popc(m & lt_mask);
-      if (pos < kTopK) {
-        sel_v[pos] = v[q];
-        sel_i[pos] = 32 * q + lane;
-      }
-    }
-    held += __popc(m);
-  }
-  __syncwarp();
-  float sv[kTopK];
-  int si[kTopK];
-#pragma unroll
-  for (int r = 0; r < kTopK; ++r) { sv[r] = sel_v[r]; si[r] = sel_i[r]; }
-  // fixed 8-wide bitonic network; a pair is exchanged when
-  // (value[left] > value[right]) equals the "ascending" flag of the left index
-#pragma unroll
-  for (int width = 2; width <= kTopK; width *= 2) {
-#pragma unroll
-    for (int stride = width / 2; stride > 0; stride /= 2) {
-#pragma unroll
-      for (int left = 0; left < kTopK; ++left) {
-        const int right = left ^ stride;
-        if (right > left) {
-          const bool ascending = (left & width) != 0;
-          if ((sv[left] > sv[right]) == ascending) {
-            const float tv = sv[left]; sv[left] = sv[right]; sv[right] = tv;
-            const int ti = si[left]; si[left] = si[right]; si[right] = ti;
-          }
-        }
-      }
-    }
-  }
-  float ex[kTopK];
-  float denom = 0.0f;
-#pragma unroll
-  for (int r = 0; r < kTopK; ++r) {
-    ex[r] = det_expf(__fsub_rn(sv[r], sv[0]));
-    denom = __fadd_rn(denom, ex[r]);
-  }
-#pragma unroll
-  for (int r = 0; r < kTopK; ++r) {
-    if (lane == r) {
-      const size_t o = static_cast<size_t>(token) * kTopK + r;
-      const uint16_t wb = float_to_bf16_bits(__fdiv_rn(ex[r], denom));
-      ids[o] = si[r];
-      scores[o] = sv[r];
-      weights[o] = bf16_bits_to_float(wb);
-      if (dbg_weights != nullptr) reinterpret_cast<uint16_t*>(dbg_weights)[o] = wb;
-    }
-  }
+  route_token(v, lane, sel_v_s + warp * 8, sel_i_s + warp * 8, static_cast<size_t>(token), ids, scores,
+              weights, dbg_weights);
   if (lane == 0) {
     shared_sigmoid[token] = round_bf16(det_sigmoid(round_bf16(gate_dot)));
   }
+}
+
+// ---------------------------------------------------------------------------
+// Certified router.  All 256 logits come from the tensor cores first (FP32,
+// unknown accumulation order, `approx`).  Their distance to the canonical value
+// is bounded by kappa * |x|_2 * |w_e|_2 (Cauchy-Schwarz on the FP32 rounding
+// error of a 2048-term sum, in the spirit of the reference's certified LM head,
+// native/src/native_lm_head_certificate.hip.cpp:33-39).  Only experts whose
+// upper bound reaches the lower bound of the 8th-largest value can be selected;
+// those few are recomputed with the canonical dot and the reference's rule runs
+// on them alone, so ids, scores and weights stay bit-exact.
+// One warp per token.
+// ---------------------------------------------------------------------------
+constexpr int kCertWarps = 8;
+constexpr float kCertKappa = 6.103515625e-05f;   // 2^-14, ~4x the summed worst-case rounding terms
+
+__global__ void __launch_bounds__(kCertWarps * 32)
+prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
+                                const __nv_bfloat16* __restrict__ router,
+                                const __nv_bfloat16* __restrict__ shared_gate,
+                                const float* __restrict__ approx,
+                                const float* __restrict__ row_norms,
+                                const float* __restrict__ bias, int quant_eighths, int tokens,
+                                int32_t* __restrict__ ids, float* __restrict__ scores,
+                                float* __restrict__ weights, float* __restrict__ shared_sigmoid,
+                                __nv_bfloat16* __restrict__ dbg_weights, int32_t* __restrict__ stats) {
+  __shared__ float sel_v_s[kCertWarps * 8];
+  __shared__ int sel_i_s[kCertWarps * 8];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * kCertWarps + warp;
+  if (token >= tokens) return;
+
+  float xr[64];
+  float sumsq = 0.0f;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    const uint4 v = *(reinterpret_cast<const uint4*>(h2 + static_cast<size_t>(token) * kHidden) + g * 32 + lane);
+    unpack8(v, xr + 8 * g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sumsq = fmaf(xr[8 * g + j], xr[8 * g + j], sumsq);
+  }
+  sumsq = butterfly_sum(sumsq);
+  const float x_norm = sqrtf(sumsq) * 1.0001f;
+
+  float upper[8], lower[8], b[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const int e = 32 * q + lane;
+    b[q] = bias != nullptr ? bias[e] : 0.0f;
+    const float a = approx[static_cast<size_t>(token) * kExperts + e];
+    const float delta = kCertKappa * x_norm * row_norms[e] + 9.5367431640625e-07f * fabsf(a + b[q]);
+    upper[q] = finish_logit(a + delta, b[q], quant_eighths);
+    lower[q] = finish_logit(a - delta, b[q], quant_eighths);
+  }
+  const float floor_value = warp_eighth_largest(lower, lane);
+
+  float v[8];
+  int recomputed = 0;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    unsigned pending = __ballot_sync(0xffffffffu, upper[q] >= floor_value);
+    float mine = -CUDART_INF_F;
+    while (pending != 0u) {
+      const int owner = __ffs(pending) - 1;
+      pending &= pending - 1u;
+      const uint4* row = reinterpret_cast<const uint4*>(router + static_cast<size_t>(32 * q + owner) * kHidden) + lane;
+      float acc = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = fma8(xr + 8 * i, __ldg(row + i * 32), acc);
+      acc = butterfly_sum(acc);
+      if (lane == owner) mine = finish_logit(acc, b[q], quant_eighths);
+      ++recomputed;
+    }
+    v[q] = mine;
+  }
+  route_token(v, lane, sel_v_s + warp * 8, sel_i_s + warp * 8, static_cast<size_t>(token), ids, scores,
+              weights, dbg_weights);
+  {
+    const uint4* row = reinterpret_cast<const uint4*>(shared_gate) + lane;
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc = fma8(xr + 8 * i, __ldg(row + i * 32), acc);
+    acc = butterfly_sum(acc);
+    if (lane == 0) {
+      shared_sigmoid[token] = round_bf16(det_sigmoid(round_bf16(acc)));
+      if (stats != nullptr) {
+        atomicAdd(stats, recomputed);
+        atomicAdd(stats + 1, 1);
+      }
+    }
+  }
+}
+
+// Euclidean norms of the 256 router rows, rounded up a little; one warp per row.
+__global__ void __launch_bounds__(256)
+router_row_norms_kernel(const __nv_bfloat16* __restrict__ router, float* __restrict__ norms) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= kExperts) return;
+  const uint4* src = reinterpret_cast<const uint4*>(router + static_cast<size_t>(row) * kHidden) + lane;
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float w[8];
+    unpack8(__ldg(src + i * 32), w);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum = fmaf(w[j], w[j], sum);
+  }
+  sum = butterfly_sum(sum);
+  if (lane == 0) norms[row] = sqrtf(sum) * 1.0001f;
 }
 
 // ---------------------------------------------------------------------------
@@ -404,7 +532,7 @@ int set_error(char* error, size_t error_bytes, cudaError_t code, const char* wha
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 struct Layout {
-  size_t ids, scores, weights, sigmoid, unit_counts, counts, offsets, sorted, position,
+  size_t ids, scores, weights, sigmoid, approx, stats, unit_counts, counts, offsets, sorted, position,
       tile_expert, tile_row0, tile_rows, tile_count, padded, gathered, act, down, shared_act,
       shared_scaled, x0, x1, h2, total;
 };
@@ -420,6 +548,8 @@ Layout layout_for(size_t T) {
   l.scores = take(rows * 4);
   l.weights = take(rows * 4);
   l.sigmoid = take(T * 4);
+  l.approx = take(T * kExperts * 4);
+  l.stats = take(16);
   l.unit_counts = take(units * kExperts * 4);
   l.counts = take(kExperts * 4);
   l.offsets = take((kExperts + 1) * 4);
@@ -444,6 +574,11 @@ Layout layout_for(size_t T) {
 
 }  // namespace
 
+cudaError_t launch_router_row_norms(const __nv_bfloat16* router, float* norms, cudaStream_t stream) {
+  router_row_norms_kernel<<<kExperts / 8, 256, 0, stream>>>(router, norms);
+  return cudaGetLastError();
+}
+
 size_t prefill_workspace_bytes(uint32_t capacity_tokens) {
   return capacity_tokens == 0 ? 0 : layout_for(capacity_tokens).total;
 }
@@ -463,6 +598,8 @@ int prefill_workspace_allocate(PrefillWorkspace* ws, uint32_t capacity_tokens, i
   ws->topk_scores = reinterpret_cast<float*>(b + l.scores);
   ws->topk_weights = reinterpret_cast<float*>(b + l.weights);
   ws->shared_sigmoid = reinterpret_cast<float*>(b + l.sigmoid);
+  ws->approx_logits = reinterpret_cast<float*>(b + l.approx);
+  ws->router_stats = reinterpret_cast<int32_t*>(b + l.stats);
   ws->unit_counts = reinterpret_cast<int32_t*>(b + l.unit_counts);
   ws->expert_counts = reinterpret_cast<int32_t*>(b + l.counts);
   ws->expert_offsets = reinterpret_cast<int32_t*>(b + l.offsets);
@@ -497,20 +634,42 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   int count = 0;
   cudaError_t code;
 
-  static bool router_configured = false;
-  if (!router_configured) {
-    code = cudaFuncSetAttribute(prefill_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                kRouterSmemBytes);
-    if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaFuncSetAttribute router");
-    router_configured = true;
+  const bool exact_router = ws->exact_router || (dbg != nullptr && dbg->router_logits != nullptr) ||
+                            call.router_row_norms == nullptr;
+  if (exact_router) {
+    static bool router_configured = false;
+    if (!router_configured) {
+      code = cudaFuncSetAttribute(prefill_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kRouterSmemBytes);
+      if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaFuncSetAttribute router");
+      router_configured = true;
+    }
+    prefill_router_kernel<<<(T + kRouterWarps - 1) / kRouterWarps, kRouterWarps * 32, kRouterSmemBytes, stream>>>(
+        static_cast<const __nv_bfloat16*>(call.h2), call.layer.router, call.layer.shared_gate,
+        call.router_bias, call.quant_eighths, T, ws->topk_ids, ws->topk_scores, ws->topk_weights,
+        ws->shared_sigmoid, dbg ? static_cast<float*>(dbg->router_logits) : nullptr,
+        dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr);
+    if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "prefill_router_kernel");
+    ++count;
+  } else {
+    // tensor-core logits for the candidate filter, then exact recomputation of the candidates
+    GroupedGemm r{};
+    r.max_tiles = (T + kTileRows - 1) / kTileRows; r.dense_rows = T;
+    r.a = static_cast<const __nv_bfloat16*>(call.h2); r.lda = kHidden; r.k = kHidden;
+    r.b0 = call.layer.router; r.n = kExperts; r.c_f32 = ws->approx_logits; r.ldc = kExperts;
+    TcExtra rx{};
+    rx.status = ws->status; rx.sm_count = ws->sm_count; rx.a_rows = static_cast<uint64_t>(T); rx.experts_in_b = 1;
+    if ((code = launch_grouped_gemm_tc(kGemmPlainF32, r, rx, stream)) != cudaSuccess)
+      return set_error(error, error_bytes, code, "router logits product");
+    prefill_router_certified_kernel<<<(T + kCertWarps - 1) / kCertWarps, kCertWarps * 32, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(call.h2), call.layer.router, call.layer.shared_gate,
+        ws->approx_logits, call.router_row_norms, call.router_bias, call.quant_eighths, T, ws->topk_ids,
+        ws->topk_scores, ws->topk_weights, ws->shared_sigmoid,
+        dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats);
+    if ((code = cudaGetLastError()) != cudaSuccess)
+      return set_error(error, error_bytes, code, "prefill_router_certified_kernel");
+    count += 2;
   }
-  prefill_router_kernel<<<(T + kRouterWarps - 1) / kRouterWarps, kRouterWarps * 32, kRouterSmemBytes, stream>>>(
-      static_cast<const __nv_bfloat16*>(call.h2), call.layer.router, call.layer.shared_gate,
-      call.router_bias, call.quant_eighths, T, ws->topk_ids, ws->topk_scores, ws->topk_weights,
-      ws->shared_sigmoid, dbg ? static_cast<float*>(dbg->router_logits) : nullptr,
-      dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr);
-  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "prefill_router_kernel");
-  ++count;
 
   const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
   const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;

@@ -16,12 +16,15 @@ struct PrefillWorkspace {
   int sm_count = 0;
   int* status = nullptr;              // device status word shared with the handle
   bool use_simt_gemm = false;         // qualification: CUDA-core products instead of tcgen05
+  bool exact_router = false;          // qualification: all 256 logits with the canonical dot
   uint8_t* base = nullptr;
   // router outputs
   int32_t* topk_ids = nullptr;        // [T, 8]
   float* topk_scores = nullptr;       // [T, 8]
   float* topk_weights = nullptr;      // [T, 8] BF16-rounded, stored as FP32
   float* shared_sigmoid = nullptr;    // [T]    bf16(sigmoid(bf16 gate logit)) as FP32
+  float* approx_logits = nullptr;     // [T, 256] tensor-core router logits (candidate filter only)
+  int32_t* router_stats = nullptr;    // [2] candidates recomputed exactly, tokens routed
   // dispatch plan
   int32_t* unit_counts = nullptr;     // [units, 256] per-warp-unit histogram / prefix
   int32_t* expert_counts = nullptr;   // [256]
@@ -52,6 +55,7 @@ struct PrefillCall {
   void* out;
   int tokens;
   int experts_local;             // experts held in the bound expert tensors
+  const float* router_row_norms; // [256] Euclidean norms of the router rows (certified filter)
   const float* router_bias;
   int quant_eighths;
   const aima_moe_debug_views* debug;
@@ -61,6 +65,9 @@ size_t prefill_workspace_bytes(uint32_t capacity_tokens);
 int prefill_workspace_allocate(PrefillWorkspace* workspace, uint32_t capacity_tokens,
                                int sm_count, char* error, size_t error_bytes);
 void prefill_workspace_free(PrefillWorkspace* workspace);
+
+// Euclidean norm of each of the 256 router rows (FP32), computed once per layer at bind time.
+cudaError_t launch_router_row_norms(const __nv_bfloat16* router, float* norms, cudaStream_t stream);
 
 // Enqueues the whole half-layer on `stream`; `launches` receives the number of
 // kernels enqueued.  Returns an AIMA_MOE_* status.

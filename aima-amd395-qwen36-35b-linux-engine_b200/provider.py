@@ -76,6 +76,7 @@ class Metrics(ctypes.Structure):
         ("prefill_calls", c_uint64), ("decode_calls", c_uint64), ("kernel_launches", c_uint64),
         ("workspace_bytes", c_uint64), ("derived_weight_bytes", c_uint64),
         ("last_padded_routed_rows", c_int32), ("device_status", c_int32),
+        ("router_candidates", c_uint64), ("router_tokens", c_uint64),
     ]
 
 
@@ -171,6 +172,7 @@ WEIGHT_KEYS = ("router", "expert_gate_up", "expert_down", "shared_gate", "shared
 
 NOALLOC_MAX_LAYERS = 8
 FLAG_SIMT_PRODUCTS = 1
+FLAG_EXACT_ROUTER = 2
 
 
 def layer_weights_struct(weights: Mapping[str, Any]) -> LayerWeights:
@@ -248,7 +250,7 @@ class MoeProvider:
         self.lib.check(self.lib.aima_moe_set_router_hooks(self.handle, _ptr(bias), int(quantize_eighths)))
 
     # -- debug views ---------------------------------------------------------
-    def make_debug(self, tokens: int, prefill: bool) -> tuple[DebugViews, dict[str, Any]]:
+    def make_debug(self, tokens: int, prefill: bool, with_logits: bool = True) -> tuple[DebugViews, dict[str, Any]]:
         torch = self._torch
         dev = torch.device("cuda", torch.cuda.current_device())
         t = {
@@ -264,6 +266,8 @@ class MoeProvider:
             t["expert_counts"] = torch.empty(EXPERTS, dtype=torch.int32, device=dev)
             t["expert_offsets"] = torch.empty(EXPERTS + 1, dtype=torch.int32, device=dev)
             t["sorted_rows"] = torch.empty(tokens * TOP_K, dtype=torch.int32, device=dev)
+        if not with_logits:
+            del t["router_logits"]      # prefill then runs the production (certified) router
         views = DebugViews()
         views.struct_bytes = ctypes.sizeof(DebugViews)
         for name, tensor in t.items():

@@ -269,6 +269,8 @@ def run_ours(args) -> None:
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
+        if world == 1 and not args.no_prefill:
+            line["prefill"] = prefill_layer_numbers(package, device, 8192, 20, "zipf", weights=keep[0])
         if world == 1 and not args.no_cpu_baseline:
             baseline = cpu_reference_tokens_per_second(2, 6, os.cpu_count() or 1)
             line["cpu_baseline"] = {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -276,6 +278,76 @@ def run_ours(args) -> None:
     provider.release()
     if distributed:
         dist.destroy_process_group()
+
+
+PREFILL_FLOP_PER_TOKEN = 50_331_648 + 6_295_552 + 1_048_576            # routed, shared, router
+
+
+def measured_tensor_peak() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
+def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing: str, weights=None) -> dict:
+    """Device-timed prefill of ONE MoE layer (BASELINE config 2: T = 8192, Zipf(1.1) router bias)."""
+    import torch
+
+    synth = package.synth
+    provider = package.MoeProvider(layers=1, max_prefill_tokens=tokens)
+    try:
+        if weights is None:
+            weights = synth.layer_weights_cuda_fast(SEED, 0, device)
+        provider.bind_layer(0, weights)
+        if routing == "zipf":
+            provider.set_router_hooks(synth.zipf_router_bias(SEED).to(device), False)
+        generator = torch.Generator(device=device).manual_seed(SEED)
+        h2 = torch.randn(tokens, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
+        resid = torch.randn(tokens, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
+        out = torch.empty_like(resid)
+        before = provider.sync_metrics().kernel_launches
+        for _ in range(3):
+            provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+        per_call = (provider.sync_metrics().kernel_launches - before) // 3
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(iterations):
+            provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+        stop.record()
+        torch.cuda.synchronize()
+        provider.sync_metrics()
+        ms = start.elapsed_time(stop) / iterations
+    finally:
+        provider.release()
+    peak, kind = measured_tensor_peak()
+    tflops = tokens * PREFILL_FLOP_PER_TOKEN / (ms * 1.0e-3) / 1.0e12
+    return {"workload": f"prefill_T{tokens}_1layer_{routing} (BASELINE config 2)", "tokens": tokens,
+            "ms_per_layer": ms, "tokens_per_s": tokens / (ms * 1.0e-3), "achieved_tflops": tflops,
+            "peak_tflops": peak, "peak_source": kind, "frac": tflops / peak, "bound": "tensor",
+            "flop_per_layer": tokens * PREFILL_FLOP_PER_TOKEN, "kernel_launches_per_layer": int(per_call)}
+
+
+def run_prefill(args) -> None:
+    """`--workload prefill`: the one-layer T = 8192 prefill line (profiling aid and second headline)."""
+    import torch
+    from __graft_entry__ import load_package
+
+    package = load_package()
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    numbers = prefill_layer_numbers(package, device, args.tokens, max(args.steps, 1), args.routing)
+    line = {"metric": "moe_prefill_tokens_per_second", "value": numbers["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": numbers["ms_per_layer"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": numbers["workload"], "routing": args.routing},
+            "roofline": {"bound": "tensor", "achieved": numbers["achieved_tflops"], "peak": numbers["peak_tflops"],
+                         "unit": "TFLOP/s", "frac": numbers["frac"], "traffic": None,
+                         "peak_source": numbers["peak_source"]},
+            "gpu_launches": numbers["kernel_launches_per_layer"] * args.steps}
+    print(json.dumps(line))
 
 
 def main() -> None:
@@ -286,8 +358,13 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-prefill", action="store_true", help="skip the one-layer prefill sub-object")
     parser.add_argument("--layers", type=int, default=LAYERS,
                         help="stack depth; anything but 40 is a profiling aid, not the benchmark config")
+    parser.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+                        help="decode = the benchmark line; prefill = one-layer prefill line only")
+    parser.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
+    parser.add_argument("--routing", choices=["zipf", "uniform"], default="zipf")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -295,6 +372,8 @@ def main() -> None:
     BYTES_PER_TOKEN = LAYERS * BYTES_PER_LAYER_TOKEN
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_ours(args)
 

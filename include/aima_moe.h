@@ -81,6 +81,9 @@ typedef struct aima_moe_config {
 /* Qualification only: run the prefill products on CUDA cores instead of the
  * tcgen05 kernel, to cross-check the tensor-core kernel on the device. */
 #define AIMA_MOE_FLAG_SIMT_PRODUCTS 1u
+/* Qualification only: compute all 256 router logits per token with the canonical
+ * FP32 dot instead of filtering candidates with tensor-core logits first. */
+#define AIMA_MOE_FLAG_EXACT_ROUTER 2u
 
 /* One layer's tensors in checkpoint layout
  * (doc/reference/amd395-qwen36-35b-a3b-bf16/qwen36-shape-manifest.json:162-180,
@@ -110,7 +113,8 @@ typedef struct aima_moe_debug_views {
   uint32_t struct_bytes;
   uint32_t reserved;
   void* h2;              /* bf16 [T,2048]  (decode: the norm the kernel formed) */
-  void* router_logits;   /* f32  [T,256]   values the selection rule saw        */
+  void* router_logits;   /* f32  [T,256]   values the selection rule saw; asking for
+                            them makes a prefill call use the exact (all-256) router */
   void* topk_ids;        /* i32  [T,8]                                           */
   void* topk_scores;     /* f32  [T,8]                                           */
   void* topk_weights;    /* bf16 [T,8]                                           */
@@ -134,6 +138,9 @@ typedef struct aima_moe_metrics {
   int32_t last_padded_routed_rows; /* block-32 padded rows of the last prefill
                                       call fetched with aima_moe_sync_metrics */
   int32_t device_status;         /* last device status word read              */
+  uint64_t router_candidates;    /* experts recomputed exactly by the certified
+                                    prefill router since prepare()             */
+  uint64_t router_tokens;        /* tokens it routed                           */
 } aima_moe_metrics;
 
 /* Validates the configuration, selects the current CUDA device, allocates the

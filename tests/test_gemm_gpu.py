@@ -82,3 +82,37 @@ def test_prefill_tensor_core_products_match_cuda_core_products(package, gpu_laye
     assert cosine >= 0.9999
     assert (dbg_tc["routed"] == dbg_simt["routed"]).float().mean() > 0.9
     assert torch.isfinite(out_tc.float()).all()
+
+
+def test_certified_router_equals_exact_router_at_full_size(package, gpu_layers, synth):
+    """T = 8192, three routing regimes: the tensor-core-filtered router and the all-256 canonical
+    router must select identical experts in identical order (size the CPU oracle cannot reach)."""
+    device = torch.device("cuda", 0)
+    tokens = 8192
+    weights = gpu_layers(0)["cuda"]
+    provider = package.MoeProvider(layers=1, max_prefill_tokens=tokens)
+    try:
+        provider.bind_layer(0, weights)
+        for regime in ("uniform", "ties", "zipf"):
+            bias = synth.zipf_router_bias(SEED).to(device) if regime == "zipf" else None
+            provider.set_router_hooks(bias, quantize_eighths=(regime == "ties"))
+            generator = torch.Generator(device=device).manual_seed(SEED + len(regime))
+            h2 = torch.randn(tokens, 2048, generator=generator, device=device).to(torch.bfloat16)
+            resid = torch.randn(tokens, 2048, generator=generator, device=device).to(torch.bfloat16)
+            results = []
+            before = provider.sync_metrics()
+            for with_logits in (False, True):
+                views, tensors = provider.make_debug(tokens, prefill=True, with_logits=with_logits)
+                out = provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0,
+                                                   debug=views)
+                metrics = provider.sync_metrics()
+                results.append((out.clone(), tensors))
+            (out_cert, cert), (out_exact, exact) = results
+            assert torch.equal(cert["topk_ids"], exact["topk_ids"]), regime
+            assert torch.equal(cert["topk_scores"], exact["topk_scores"]), regime
+            assert torch.equal(cert["topk_weights"], exact["topk_weights"]), regime
+            assert torch.equal(out_cert, out_exact), regime
+            per_token = (metrics.router_candidates - before.router_candidates) / tokens
+            assert 8.0 <= per_token <= 48.0, (regime, per_token)
+    finally:
+        provider.release()

@@ -123,6 +123,53 @@ def test_prefill_hot_and_skewed_routing(provider, oracle, gpu_layers, synth):
         provider.set_router_hooks(None, quantize_eighths=False)
 
 
+def _run_production(provider, layer, h2, resid):
+    """Same call without the logits view: the production (certified, tensor-core filtered) router."""
+    device = torch.device("cuda", 0)
+    views, tensors = provider.make_debug(h2.shape[0], prefill=True, with_logits=False)
+    out = provider.launch_selected_moe(post_attention=h2.to(device), residual_hidden=resid.to(device),
+                                       model_layer=layer, debug=views)
+    metrics = provider.sync_metrics()
+    return out.cpu(), {k: v.cpu() for k, v in tensors.items()}, metrics
+
+
+@pytest.mark.parametrize("regime", ["uniform", "ties", "hot", "zipf"])
+def test_certified_router_is_bit_exact(provider, oracle, gpu_layers, synth, regime):
+    """The production router filters candidates with tensor-core logits and recomputes only those
+    with the canonical dot; ids (order included), scores and weights must equal the oracle's."""
+    device = torch.device("cuda", 0)
+    tokens = 700
+    layer = 1
+    bias, quant = None, False
+    if regime == "ties":
+        quant = True
+    elif regime == "hot":
+        bias = synth.hot_expert_bias([5, 6, 7, 64, 65, 128, 200, 255])
+    elif regime == "zipf":
+        bias = synth.zipf_router_bias(SEED + 3)
+    provider.set_router_hooks(None if bias is None else bias.to(device), quantize_eighths=quant)
+    try:
+        h2 = synth.activations(SEED + 950, tokens, "input", layer)
+        resid = synth.activations(SEED + 950, tokens, "residual", layer)
+        before = provider.sync_metrics()
+        out, dbg, metrics = _run_production(provider, layer, h2, resid)
+        view = oracle.OracleLayer(gpu_layers(layer)["cpu"], router_bias=bias, quant_eighths=quant)
+        routing = oracle.router_prefill(h2, view)
+        assert torch.equal(dbg["topk_ids"], routing["ids"])
+        assert torch.equal(dbg["topk_scores"], routing["scores"])
+        assert torch.equal(dbg["topk_weights"], routing["weights"])
+        routed_tokens = metrics.router_tokens - before.router_tokens
+        candidates = metrics.router_candidates - before.router_candidates
+        assert routed_tokens == tokens
+        assert 8 * tokens <= candidates <= 64 * tokens          # a filter, not a full recomputation
+        # and the exact router gives the same layer output bits (same routing, same products)
+        out_exact, dbg_exact, _ = _run(provider, layer, h2, resid)
+        assert torch.equal(out, out_exact)
+        assert torch.equal(dbg["shared_scaled"], dbg_exact["shared_scaled"])
+    finally:
+        provider.set_router_hooks(None, quantize_eighths=False)
+
+
 @pytest.mark.parametrize("tokens", [1, 16])
 def test_prefill_matches_torch_golden(provider, gpu_layers, synth, tokens):
     """BASELINE config 0 against the committed torch-CPU vectors (tests/golden/make_golden.py)."""
