@@ -17,7 +17,8 @@
 //
 //   R   every block: norm of the 2048-vector (per warp, registers), its share
 //       of the 256 router rows and of the 513 shared-expert input pairs
-//   --- grid barrier: all 256 logits known -> top-8 (warp 0 of every block)
+//   --- logits exchange: every logit travels as one 64-bit word {tag, value};
+//       warp 0 of every block polls the 256 words, then takes the top-8
 //   1   routed gate/up rows of the 8 chosen experts (8 KB "pair" items through
 //       a 10-slot ring); meanwhile the block's slice of the down projection
 //       (8 experts + shared, <= 126 KB) is already being copied into a second
@@ -25,7 +26,11 @@
 //   --- grid barrier: all SwiGLU activations known
 //   2   down products for the block's <= 14 output elements, weighted sum,
 //       shared expert, residual add, store
-//   --- grid barrier: next layer's input complete
+//   --- output exchange: the 2048 outputs travel as 32-bit words {tag, bf16};
+//       four warps of every block poll them into shared memory
+// Data that carries its own tag needs no separate barrier and no second round
+// trip through L2; only the activation hand-over is a counter barrier, and it
+// hides behind the arrival of the down-projection rows.
 //
 // Every wait (mbarrier, grid barrier, hand-over of the expert ids to the
 // producer) is bounded; on expiry the block raises a status word, drains its
@@ -54,10 +59,12 @@ constexpr int kOffRing = 0;
 constexpr int kOffDown = kOffRing + kRingSlots * kSlotBytes;                       // 81920
 constexpr int kOffAct = kOffDown + kDownRegionRanks * kDecodeMaxRowsPerBlock * kDownRowBytes;  // +129024
 constexpr int kOffDots = kOffAct + kDownRegionRanks * kInter * 2;                  // +9216
-constexpr int kOffMisc = kOffDots + kDecodeMaxRowsPerBlock * kDotsStride * 4;      // +672
+constexpr int kOffX = kOffDots + kDecodeMaxRowsPerBlock * kDotsStride * 4;         // +672: layer input, packed BF16
+constexpr int kOffNorm = kOffX + kHidden * 2;                                      // +4096: norm weight row
+constexpr int kOffMisc = kOffNorm + kHidden * 2;                                   // +4096
 constexpr int kMiscBytes = 512;
 constexpr int kOffBars = kOffMisc + kMiscBytes;
-constexpr int kBarCount = 2 * kRingSlots + 1;
+constexpr int kBarCount = 2 * kRingSlots + 2;
 constexpr int kSmemTotal = kOffBars + kBarCount * 8;
 static_assert(kSmemTotal <= 227 * 1024, "decode kernel shared memory exceeds 227 KB");
 static_assert(kSmemTotal == kDecodeSmemBytes, "keep decode_kernel.cuh in step");
@@ -143,6 +150,70 @@ __device__ __forceinline__ bool uniform_alive(volatile int* abort_flag,
   return *decision != 0;
 }
 
+// Eight canonical warp reductions at once.  v[d] is this lane's partial of sum d;
+// the result is the butterfly (16, 8, 4, 2, 1) total of sum d(lane), with
+// d(lane) = 4 * bit4 + 2 * bit3 + bit2 of the lane index.  Each level pairs the
+// same lanes as butterfly_sum, so the bits are identical, with 9 shuffles
+// instead of 40.
+__device__ __forceinline__ float warp_reduce8(const float* v, int lane) {
+  const bool b4 = (lane & 16) != 0, b3 = (lane & 8) != 0, b2 = (lane & 4) != 0;
+  float a[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float keep = b4 ? v[j + 4] : v[j];
+    const float send = b4 ? v[j] : v[j + 4];
+    a[j] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+  }
+  float b[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float keep = b3 ? a[j + 2] : a[j];
+    const float send = b3 ? a[j] : a[j + 2];
+    b[j] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+  }
+  const float keep = b2 ? b[1] : b[0];
+  const float send = b2 ? b[0] : b[1];
+  float c = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+  c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, 2));
+  c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, 1));
+  return c;
+}
+__device__ __forceinline__ int reduce8_slot(int lane) {
+  return ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+}
+__device__ __forceinline__ int reduce8_lane(int d) {
+  return ((d >> 2) & 1) * 16 + ((d >> 1) & 1) * 8 + (d & 1) * 4;
+}
+
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// Exchange words are polled while other blocks are still writing them, so both
+// sides use STRONG (relaxed, gpu-scope) accesses: a weak ld.global.cg may keep
+// being served a snapshot of the line taken on the poller's side of the chip.
+__device__ __forceinline__ unsigned long long ld_strong_u64(const void* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_strong_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_strong_u64(void* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_strong_u32(void* p, uint32_t v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+
 // Number of shared-expert input pairs block c owns: i = c, c+G, ... < 512.
 __device__ __forceinline__ int shared_pairs_of(int c, int G) {
   return c < kSharedInter ? (kSharedInter - 1 - c) / G + 1 : 0;
@@ -157,11 +228,14 @@ moe_decode_persistent_kernel(const DecodeParams p) {
   uint8_t* down_region = smem + kOffDown;
   uint16_t* act_s = reinterpret_cast<uint16_t*>(smem + kOffAct);
   float* dots = reinterpret_cast<float*>(smem + kOffDots);
+  uint8_t* x_s = smem + kOffX;
+  uint8_t* norm_s = smem + kOffNorm;
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
   const uint32_t bars = smem_u32(smem + kOffBars);
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (kRingSlots + s); };
   const uint32_t down_bar = bars + 8u * (2 * kRingSlots);
+  const uint32_t norm_bar = bars + 8u * (2 * kRingSlots + 1);
 
   const int G = gridDim.x;
   const int c = blockIdx.x;
@@ -176,6 +250,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(down_bar, 1);
+    mbar_init(norm_bar, 1);
     // every ring slot starts out released: complete phase 0 of its empty barrier
     for (int s = 0; s < kRingSlots; ++s) mbar_arrive(empty_bar(s));
     misc->ids_layer = 0;
@@ -193,6 +268,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
   const int n_shared_pairs = shared_pairs_of(c, G);
   const bool owns_gate_row = (c == G - 1);
   const unsigned long long bar_base = *p.bar_base;
+  const unsigned epoch0 = *p.epoch_base;      // exchange tag of layer ordinal li is epoch0 + li + 1
 
   if (warp == kDecodeConsumerWarps) {
     // ------------------------------ producer ------------------------------
@@ -201,6 +277,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
 #pragma unroll
     for (int s = 0; s < kRingSlots; ++s) issued[s] = 0;
     unsigned down_issued = 0;
+    unsigned norm_issued = 0;
     bool alive = true;
 
     // acquire a ring slot for item `seq`; returns slot index or -1
@@ -221,6 +298,11 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     if (lane == 0) {
       for (int li = 0; li < p.n_layers && alive; ++li) {
         const LayerPtrs L = p.layers[p.first_layer + li];
+        // ---- norm weight row into its own region (its readers finished before the ids of the
+        //      previous layer were published, which this thread has waited for) ----
+        mbar_arrive_expect_tx(norm_bar, kRowBytes);
+        bulk_g2s(smem_u32(norm_s), L.norm_weight, kRowBytes, norm_bar);
+        norm_issued = li + 1;
         // ---- R items: router rows, shared input pairs, shared gate row ----
         {
           const int s = acquire(seq);
@@ -324,6 +406,10 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           volatile int ignore = 0;
           mbar_wait_bounded(down_bar, (down_issued - 1u) & 1u, &ignore);
         }
+        if (norm_issued != 0) {
+          volatile int ignore = 0;
+          mbar_wait_bounded(norm_bar, (norm_issued - 1u) & 1u, &ignore);
+        }
       }
     }
     __syncwarp();
@@ -379,31 +465,80 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     for (int li = 0; li < p.n_layers; ++li) {
       const bool first = (li == 0);
       const bool last = (li == p.n_layers - 1);
-      const LayerPtrs L = p.layers[p.first_layer + li];
-      const __nv_bfloat16* x_src = first ? p.x_in : ((li & 1) ? p.xbuf1 : p.xbuf0);
-      __nv_bfloat16* x_dst = last ? p.x_out : ((li & 1) ? p.xbuf0 : p.xbuf1);
 
       stamp(li, 0);
+      const uint32_t* xw_src = (li & 1) ? p.xbuf1 : p.xbuf0;     // tagged words written by layer li - 1
+      uint32_t* xw_dst = (li & 1) ? p.xbuf0 : p.xbuf1;
+      const unsigned tag_in = (epoch0 + li) & 0xffffu;           // tag of layer li - 1
+      const unsigned tag_out = (epoch0 + li + 1) & 0xffffu;
+      // ---- layer input into shared memory (packed BF16) ----
+      if (first) {
+        if (ctid < kHidden / 8) {
+          reinterpret_cast<uint4*>(x_s)[ctid] = ld_cg_u4(reinterpret_cast<const uint4*>(p.x_in) + ctid);
+        }
+      } else if (warp < 4) {
+        // poll this warp's 512 tagged words until every tag is the previous layer's
+        const uint4* src = reinterpret_cast<const uint4*>(xw_src + (c % kDecodeReplicas) * kHidden) + warp * 128 + lane;
+        uint4 w[4];
+        bool ready = false;
+        const unsigned long long start = global_timer_ns();
+        unsigned spins = 0;
+        while (!ready) {
+          bool mine = true;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            w[i] = ld_strong_u4(src + i * 32);
+            mine = mine && (w[i].x >> 16) == tag_in && (w[i].y >> 16) == tag_in &&
+                   (w[i].z >> 16) == tag_in && (w[i].w >> 16) == tag_in;
+          }
+          ready = __all_sync(0xffffffffu, mine);
+          if (!ready && (++spins & 63u) == 0u) {
+            if (*abort_flag != 0) break;
+            if (global_timer_ns() - start > kWaitBudgetNs) {
+              raise_status(p, abort_flag, kStatusTimeoutPeer);
+              record_site(p, 7, li);
+              break;
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint2 packed;
+          packed.x = (w[i].x & 0xffffu) | (w[i].y << 16);
+          packed.y = (w[i].z & 0xffffu) | (w[i].w << 16);
+          reinterpret_cast<uint2*>(x_s)[warp * 128 + i * 32 + lane] = packed;
+        }
+      }
+      if (!uniform_alive(abort_flag, decision, ctid)) break;
       // ---- norm: h2 in registers, element k = 256 g + 8 lane + j at xr[8 g + j]
       float xr[64];
       {
-        float total = 0.0f;
+        float part[8];
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          const uint4 v = ld_cg_u4(reinterpret_cast<const uint4*>(x_src) + g * 32 + lane);
-          unpack8(v, xr + 8 * g);
-          float part = 0.0f;
+          unpack8(reinterpret_cast<const uint4*>(x_s)[g * 32 + lane], xr + 8 * g);
+          float acc = 0.0f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) part = __fmaf_rn(xr[8 * g + j], xr[8 * g + j], part);
-          part = butterfly_sum(part);
-          total = (g == 0) ? part : __fadd_rn(total, part);
+          for (int j = 0; j < 8; ++j) acc = __fmaf_rn(xr[8 * g + j], xr[8 * g + j], acc);
+          part[g] = acc;
         }
+        const float mine = warp_reduce8(part, lane);
+        float total = __shfl_sync(0xffffffffu, mine, reduce8_lane(0));
+#pragma unroll
+        for (int g = 1; g < 8; ++g) total = __fadd_rn(total, __shfl_sync(0xffffffffu, mine, reduce8_lane(g)));
         const float inv = det_rsqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(kHidden)), p.eps));
+        if (!mbar_wait_bounded(norm_bar, li & 1u, abort_flag)) {
+          if (*abort_flag == kStatusTimeoutMbarrier) {
+            atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+            record_site(p, 8, li);
+          }
+          alive = false;
+        }
+        alive = __all_sync(0xffffffffu, alive);
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          const uint4 wv = __ldg(reinterpret_cast<const uint4*>(L.norm_weight) + g * 32 + lane);
           float wf[8];
-          unpack8(wv, wf);
+          unpack8(reinterpret_cast<const uint4*>(norm_s)[g * 32 + lane], wf);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float scaled = __fmul_rn(xr[8 * g + j], inv);
@@ -426,7 +561,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         const unsigned item = seq + k;
         if (static_cast<int>(item % kRingSlots) != warp) continue;
         const uint8_t* slot = wait_item(item, 2);
-        if (slot == nullptr) { alive = false; break; }
+        if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; break; }
         float a, b;
         pair_dot(slot, xr, a, b);
         release_item(item);
@@ -441,54 +576,103 @@ moe_decode_persistent_kernel(const DecodeParams p) {
               v0 = __fmul_rn(rintf(__fmul_rn(v0, 8.0f)), 0.125f);
               v1 = __fmul_rn(rintf(__fmul_rn(v1, 8.0f)), 0.125f);
             }
-            p.logits[c] = v0;
-            if (eb < kExperts) p.logits[eb] = v1;
+            const unsigned long long tag = static_cast<unsigned long long>(epoch0 + li + 1) << 32;
+#pragma unroll
+            for (int rep = 0; rep < kDecodeReplicas; ++rep) {
+              st_strong_u64(p.logits + rep * kExperts + c, tag | __float_as_uint(v0));
+              if (eb < kExperts) st_strong_u64(p.logits + rep * kExperts + eb, tag | __float_as_uint(v1));
+            }
           } else if (k <= n_shared_pairs) {
             const int i = c + (k - 1) * G;
             const float g = round_bf16(a);
             const float u = round_bf16(b);
-            p.act[kTopK * kInter + i] = float_to_bf16_bits(__fmul_rn(det_silu(g), u));
+            const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(g), u));
+#pragma unroll
+            for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + kTopK * kInter + i] = bits;
           } else {
-            *p.gate_logit = round_bf16(a);
+            const float gate = round_bf16(a);
+#pragma unroll
+            for (int rep = 0; rep < kDecodeReplicas; ++rep)
+              *reinterpret_cast<float*>(p.act + rep * kDecodeActStride + 9 * kInter) = gate;
           }
         }
       }
       seq += n_r_items;
       stamp(li, 2);
-      // (an aborted warp still joins the barriers below; they return false)
-      if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
-      stamp(li, 3);
 
-      // ---- top-8, ties to the lowest expert id; softmax over the eight ----
+      // ---- logits exchange + top-8 (ties to the lowest expert id) + softmax, warp 0 ----
       if (warp == 0) {
-        float v[8];
+        const unsigned tag = epoch0 + li + 1;
+        unsigned long long w[8];
+        bool ready = false;
+        const unsigned long long start = global_timer_ns();
+        unsigned spins = 0;
+        while (!ready) {
+          bool mine = true;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) v[q] = ld_cg_f32(p.logits + 32 * q + lane);
-        if (p.dbg_logits != nullptr && c == 0) {
+          for (int q = 0; q < 8; ++q) {
+            w[q] = ld_strong_u64(p.logits + (c % kDecodeReplicas) * kExperts + 32 * q + lane);
+            mine = mine && static_cast<unsigned>(w[q] >> 32) == tag;
+          }
+          ready = __all_sync(0xffffffffu, mine);
+          if (!ready && (++spins & 63u) == 0u) {
+            if (*abort_flag != 0) break;
+            if (global_timer_ns() - start > kWaitBudgetNs) {
+              raise_status(p, abort_flag, kStatusTimeoutPeer);
+              {
+                // first expert whose word never carried this layer's tag, and what was there instead
+                int bad = 0x7fffffff;
 #pragma unroll
-          for (int q = 0; q < 8; ++q) p.dbg_logits[32 * q + lane] = v[q];
+                for (int q = 7; q >= 0; --q)
+                  if (static_cast<unsigned>(w[q] >> 32) != tag) bad = 32 * q + lane;
+                const int first_bad = __reduce_min_sync(0xffffffffu, bad);
+                int n_bad = 0;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) n_bad += static_cast<unsigned>(w[q] >> 32) != tag ? 1 : 0;
+                n_bad = __reduce_add_sync(0xffffffffu, n_bad);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  const unsigned m = __ballot_sync(0xffffffffu, static_cast<unsigned>(w[q] >> 32) != tag);
+                  if (lane == 0 && p.status[1] == 0) p.status[16 + q] = static_cast<int>(m);
+                }
+                if (bad == first_bad) {
+                  const unsigned long long word = w[(first_bad >> 5) & 7];
+                  unsigned diag[4] = {tag, static_cast<unsigned>(first_bad),
+                                      static_cast<unsigned>(n_bad) | (alive ? 0x10000u : 0u), static_cast<unsigned>(word >> 32)};
+                  record_site(p, 9, li, diag);
+                }
+              }
+              break;
+            }
+          }
+        }
+        stamp(li, 3);
+        uint32_t k[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float value = __uint_as_float(static_cast<uint32_t>(w[q]));
+          k[q] = order_key(value);
+          if (p.dbg_logits != nullptr && c == 0) p.dbg_logits[32 * q + lane] = value;
         }
         float sel_v[kTopK];
         int sel_i[kTopK];
 #pragma unroll
         for (int r = 0; r < kTopK; ++r) {
-          float best = v[0];
-          int best_id = lane;
+          uint32_t local = k[0];
 #pragma unroll
-          for (int q = 1; q < 8; ++q) {
-            if (v[q] > best) { best = v[q]; best_id = 32 * q + lane; }
-          }
+          for (int q = 1; q < 8; ++q) local = max(local, k[q]);
+          const uint32_t best = __reduce_max_sync(0xffffffffu, local);
+          int candidate = 0x7fffffff;
 #pragma unroll
-          for (int s = 16; s >= 1; s >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, s);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_id, s);
-            if (ov > best || (ov == best && oi < best_id)) { best = ov; best_id = oi; }
+          for (int q = 7; q >= 0; --q) {
+            if (k[q] == best) candidate = 32 * q + lane;
           }
-          sel_v[r] = best;
-          sel_i[r] = best_id;
+          const int winner = __reduce_min_sync(0xffffffffu, candidate);
+          sel_v[r] = key_value(best);
+          sel_i[r] = winner;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            if (best_id == 32 * q + lane) v[q] = -CUDART_INF_F;
+            if (winner == 32 * q + lane) k[q] = 0u;
           }
         }
         float ex[kTopK];
@@ -517,7 +701,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           misc->ids_layer = li + 1;
         }
       }
-      consumer_sync();
+      if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 4);
 
       // ---- phase 1: routed gate/up pairs of the experts held on this GPU ----
@@ -529,11 +713,15 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         const unsigned item = seq + (pi - p0);
         if (static_cast<int>(item % kRingSlots) != warp) continue;
         const uint8_t* slot = wait_item(item, 3);
-        if (slot == nullptr) { alive = false; break; }
+        if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; break; }
         float a, b;
         pair_dot(slot, xr, a, b);
         release_item(item);
-        if (lane == 0) p.act[pi] = float_to_bf16_bits(__fmul_rn(det_silu(a), b));
+        if (lane == 0) {
+          const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), b));
+#pragma unroll
+          for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + pi] = bits;
+        }
       }
       seq += (p1 - p0);
       stamp(li, 5);
@@ -542,7 +730,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
 
       // ---- phase 2: down products for outputs h0 .. h1-1 ----
       for (int v = ctid; v < kDownRegionRanks * kInter * 2 / 16; v += kDecodeConsumerThreads) {
-        reinterpret_cast<uint4*>(act_s)[v] = ld_cg_u4(reinterpret_cast<const uint4*>(p.act) + v);
+        reinterpret_cast<uint4*>(act_s)[v] = ld_cg_u4(
+            reinterpret_cast<const uint4*>(p.act + (c % kDecodeReplicas) * kDecodeActStride) + v);
       }
       consumer_sync();
       stamp(li, 7);
@@ -553,26 +742,41 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         }
         alive = false;
       }
+      alive = __all_sync(0xffffffffu, alive);
       stamp(li, 8);
       if (alive) {
+        // dot d = (output row hh, rank slot q); eight dots per warp pass share one reduction
         const int per_row = n_local + 1;
         const int n_dots = nh * per_row;
-        for (int d = warp; d < n_dots; d += kDecodeConsumerWarps) {
-          const int hh = d / per_row;
-          const int q = d - hh * per_row;
-          const int region = (q == n_local) ? kTopK : q;
-          const uint4* wrow = reinterpret_cast<const uint4*>(
-              down_region + (region * kDecodeMaxRowsPerBlock + hh) * kDownRowBytes) + lane;
-          const uint4* arow = reinterpret_cast<const uint4*>(act_s + region * kInter) + lane;
-          float acc = 0.0f;
+        for (int d0 = warp * 8; d0 < n_dots; d0 += kDecodeConsumerWarps * 8) {
+          float part[8];
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            float af[8];
-            unpack8(arow[i * 32], af);
-            acc = fma8(af, wrow[i * 32], acc);
+          for (int u = 0; u < 8; ++u) {
+            const int d = d0 + u;
+            float acc = 0.0f;
+            if (d < n_dots) {
+              const int hh = d / per_row;
+              const int q = d - hh * per_row;
+              const int region = (q == n_local) ? kTopK : q;
+              const uint4* wrow = reinterpret_cast<const uint4*>(
+                  down_region + (region * kDecodeMaxRowsPerBlock + hh) * kDownRowBytes) + lane;
+              const uint4* arow = reinterpret_cast<const uint4*>(act_s + region * kInter) + lane;
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                float af[8];
+                unpack8(arow[i * 32], af);
+                acc = fma8(af, wrow[i * 32], acc);
+              }
+            }
+            part[u] = acc;
           }
-          acc = butterfly_sum(acc);
-          if (lane == 0) dots[hh * kDotsStride + region] = acc;
+          const float total = warp_reduce8(part, lane);
+          const int d = d0 + reduce8_slot(lane);
+          if ((lane & 3) == 0 && d < n_dots) {
+            const int hh = d / per_row;
+            const int q = d - hh * per_row;
+            dots[hh * kDotsStride + ((q == n_local) ? kTopK : q)] = total;
+          }
         }
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
@@ -584,23 +788,28 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           acc = __fmaf_rn(misc->weights[misc->local_rank[q]], dots[ctid * kDotsStride + q], acc);
         }
         const float routed = round_bf16(acc);
-        const float sig = round_bf16(det_sigmoid(ld_cg_f32(p.gate_logit)));
+        const float sig = round_bf16(det_sigmoid(
+            ld_cg_f32(p.act + (c % kDecodeReplicas) * kDecodeActStride + 9 * kInter)));
         const float shared_down = round_bf16(dots[ctid * kDotsStride + kTopK]);
         const float shared_scaled = round_bf16(__fmul_rn(sig, shared_down));
         const float combined = round_bf16(__fadd_rn(routed, shared_scaled));
-        const float resid = bf16_bits_to_float(ld_cg_u16(reinterpret_cast<const uint16_t*>(x_src) + h));
-        x_dst[h] = __float2bfloat16_rn(__fadd_rn(resid, combined));
+        const float resid = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(x_s)[h]);
+        const uint16_t out_bits = float_to_bf16_bits(__fadd_rn(resid, combined));
+        if (last) reinterpret_cast<uint16_t*>(p.x_out)[h] = out_bits;
+        else {
+#pragma unroll
+          for (int rep = 0; rep < kDecodeReplicas; ++rep)
+            st_strong_u32(xw_dst + rep * kHidden + h, (tag_out << 16) | out_bits);
+        }
         if (p.dbg_routed != nullptr) p.dbg_routed[h] = __float2bfloat16_rn(routed);
         if (p.dbg_shared_scaled != nullptr) p.dbg_shared_scaled[h] = __float2bfloat16_rn(shared_scaled);
       }
       stamp(li, 10);
-      if (!last) {
-        if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
-      }
       stamp(li, 11);
     }
     if (c == 0 && ctid == 0 && *abort_flag == 0) {
       *p.bar_base = bar_base + nbar * G;
+      *p.epoch_base = epoch0 + static_cast<unsigned>(p.n_layers);
     }
   }
   __syncthreads();

@@ -14,20 +14,27 @@ constexpr int kDecodeThreads = kDecodeConsumerThreads + 32;  // + producer warp
 constexpr int kDecodeMaxRowsPerBlock = 14;
 constexpr int kDecodeMinBlocks = (kHidden + kDecodeMaxRowsPerBlock - 1) / kDecodeMaxRowsPerBlock;
 constexpr int kDecodeMaxBlocks = kExperts;  // router rows are dealt c, c + grid
-constexpr int kDecodeSmemBytes = 221512;
+constexpr int kDecodeSmemBytes = 229712;
 constexpr int kDecodeTraceStamps = 12;
+// Everything all 148 blocks read back from global memory (router logits, the
+// activation vector, the layer output) is written kDecodeReplicas times, and
+// block c reads copy c % kDecodeReplicas: 148 readers of the same few L2 lines
+// otherwise queue at the L2 slices that own them.
+constexpr int kDecodeReplicas = 8;
+constexpr int kDecodeActStride = 9 * kInter + 64;   // BF16 elements per activation copy; [9*512] = gate logit bits (2 x u16)
 
 struct DecodeParams {
   const LayerPtrs* layers;       // device array indexed by layer
   const __nv_bfloat16* x_in;     // [2048] residual stream entering first_layer
   __nv_bfloat16* x_out;          // [2048] residual stream leaving the last layer
-  __nv_bfloat16* xbuf0;          // [2048] inter-layer ping-pong
-  __nv_bfloat16* xbuf1;
-  float* logits;                 // [256] scratch
-  uint16_t* act;                 // [9 * 512] BF16 activations: 8 ranks + shared
-  float* gate_logit;             // [1] shared-expert gate logit (BF16-rounded)
+  uint32_t* xbuf0;               // [replicas][2048] inter-layer ping-pong, words = tag16 << 16 | bf16
+  uint32_t* xbuf1;
+  unsigned long long* logits;    // [replicas][256] words = tag32 << 32 | FP32 logit bits
+  uint16_t* act;                 // [replicas][kDecodeActStride] BF16 activations: 8 ranks + shared,
+                                 // then the shared-expert gate logit as FP32 bits
   unsigned long long* bar_counter;  // monotonic grid-barrier arrivals
   unsigned long long* bar_base;     // counter value when this launch starts
+  unsigned* epoch_base;             // exchange tags used so far (persists across launches)
   int* status;                   // device status word, 0 = healthy
   const float* router_bias;      // [256] or nullptr
   int quant_eighths;

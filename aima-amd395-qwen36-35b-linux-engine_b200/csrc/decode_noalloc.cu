@@ -29,14 +29,14 @@ constexpr int kNoAllocMaxDevices = 64;
 
 // layout of the static scratch array (bytes)
 constexpr size_t kOffTable = 0;                                   // LayerPtrs[AIMA_MOE_NOALLOC_MAX_LAYERS]
-constexpr size_t kOffX0 = 1024;                                   // inter-layer vector 0, 4096 B
-constexpr size_t kOffX1 = kOffX0 + 4096;                          // inter-layer vector 1
-constexpr size_t kOffLogits = kOffX1 + 4096;                      // 256 FP32 router logits
-constexpr size_t kOffAct = kOffLogits + 1024;                     // 9 x 512 BF16 activations
-constexpr size_t kOffGate = kOffAct + 9 * kInter * 2;             // shared gate logit
-constexpr size_t kOffSync = kOffGate + 256;                       // barrier counter (+0), base (+128)
+constexpr size_t kOffSync = 1024;                                 // barrier counter (+0), base (+128), tag base (+192)
 constexpr size_t kOffStatus = kOffSync + 256;                     // device status words
-constexpr size_t kScratchBytes = kOffStatus + 256;
+constexpr size_t kOffLogits = kOffStatus + 256;                   // replicated tagged 64-bit router logits
+constexpr size_t kOffX0 = kOffLogits + static_cast<size_t>(kDecodeReplicas) * kExperts * 8;   // tagged vector 0
+constexpr size_t kOffX1 = kOffX0 + static_cast<size_t>(kDecodeReplicas) * kHidden * 4;        // tagged vector 1
+constexpr size_t kOffAct = kOffX1 + static_cast<size_t>(kDecodeReplicas) * kHidden * 4;       // activation copies
+constexpr size_t kClearBytes = kOffAct - kOffSync;                // everything that carries a tag or a count
+constexpr size_t kScratchBytes = kOffAct + static_cast<size_t>(kDecodeReplicas) * kDecodeActStride * 2;
 static_assert(sizeof(LayerPtrs) * AIMA_MOE_NOALLOC_MAX_LAYERS <= kOffX0, "layer table overflows its slot");
 static_assert(kScratchBytes <= AIMA_MOE_NOALLOC_SCRATCH_BYTES, "scratch exceeds the stated maximum");
 
@@ -165,9 +165,10 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   if (setup != AIMA_MOE_OK) return setup;
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
 
-  // The array keeps whatever the previous call left: the barrier words and the
-  // status word must start at zero, everything else is written before it is read.
-  cudaError_t error = cudaMemsetAsync(scratch + kOffSync, 0, 512, cuda_stream);
+  // The array keeps whatever the previous call left.  The barrier words, the
+  // status word and every tagged exchange word (their tags restart with each
+  // call) must start at zero; everything else is written before it is read.
+  cudaError_t error = cudaMemsetAsync(scratch + kOffSync, 0, kClearBytes, cuda_stream);
   if (error != cudaSuccess) {
     (void)cudaGetLastError();
     return noalloc_fail(static_cast<int>(error), "cudaMemsetAsync(static scratch sync words) failed");
@@ -181,13 +182,13 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   params.layers = reinterpret_cast<const LayerPtrs*>(scratch + kOffTable);
   params.x_in = static_cast<const __nv_bfloat16*>(x_in);
   params.x_out = static_cast<__nv_bfloat16*>(x_out);
-  params.xbuf0 = reinterpret_cast<__nv_bfloat16*>(scratch + kOffX0);
-  params.xbuf1 = reinterpret_cast<__nv_bfloat16*>(scratch + kOffX1);
-  params.logits = reinterpret_cast<float*>(scratch + kOffLogits);
+  params.xbuf0 = reinterpret_cast<uint32_t*>(scratch + kOffX0);
+  params.xbuf1 = reinterpret_cast<uint32_t*>(scratch + kOffX1);
+  params.logits = reinterpret_cast<unsigned long long*>(scratch + kOffLogits);
   params.act = reinterpret_cast<uint16_t*>(scratch + kOffAct);
-  params.gate_logit = reinterpret_cast<float*>(scratch + kOffGate);
   params.bar_counter = reinterpret_cast<unsigned long long*>(scratch + kOffSync);
   params.bar_base = reinterpret_cast<unsigned long long*>(scratch + kOffSync + 128);
+  params.epoch_base = reinterpret_cast<unsigned*>(scratch + kOffSync + 192);
   params.status = reinterpret_cast<int*>(scratch + kOffStatus);
   params.router_bias = nullptr;
   params.timeline = nullptr;

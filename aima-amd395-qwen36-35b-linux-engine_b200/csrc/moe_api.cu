@@ -72,13 +72,14 @@ struct aima_moe_handle {
   // decode scratch (one allocation)
   uint8_t* decode_scratch = nullptr;
   size_t decode_scratch_bytes = 0;
-  __nv_bfloat16* xbuf0 = nullptr;
-  __nv_bfloat16* xbuf1 = nullptr;
-  float* logits = nullptr;
+  // [exchange area, cleared together: sync words | status | logits | xbuf0 | xbuf1] act | gate
+  uint32_t* xbuf0 = nullptr;
+  uint32_t* xbuf1 = nullptr;
+  unsigned long long* logits = nullptr;
   uint16_t* act = nullptr;
-  float* gate_logit = nullptr;
   unsigned long long* bar_counter = nullptr;
   unsigned long long* bar_base = nullptr;
+  unsigned* epoch_base = nullptr;
   int* status = nullptr;
 
   PrefillWorkspace prefill;
@@ -121,9 +122,13 @@ int validate_config(const aima_moe_config* config) {
   return AIMA_MOE_OK;
 }
 
+// exchange area: sync words 256 B, status 256 B, replicated tagged logits and two replicated tagged vectors
+constexpr size_t kLogitsBytes = static_cast<size_t>(kDecodeReplicas) * kExperts * 8;
+constexpr size_t kXbufBytes = static_cast<size_t>(kDecodeReplicas) * kHidden * 4;
+constexpr size_t kExchangeBytes = 256 + 256 + kLogitsBytes + 2 * kXbufBytes;
+
 size_t decode_scratch_size() {
-  // xbuf0, xbuf1 (4 KB each), logits 1 KB, act 9216 B, gate logit, counters, status
-  return 4096 + 4096 + 1024 + align_up(9 * kInter * 2, 256) + 256 + 256 + 256;
+  return kExchangeBytes + align_up(static_cast<size_t>(kDecodeReplicas) * kDecodeActStride * 2, 256);
 }
 
 int check_device_tensor(const void* pointer, uint64_t bytes, uint64_t expected,
@@ -149,10 +154,9 @@ bool ranges_overlap(const void* a, size_t a_bytes, const void* b, size_t b_bytes
 }
 
 int reset_decode_sync(aima_moe_handle* handle) {
-  cudaError_t error = cudaMemset(handle->bar_counter, 0, 256);
-  if (error == cudaSuccess) error = cudaMemset(handle->bar_base, 0, 256);
-  if (error == cudaSuccess) error = cudaMemset(handle->status, 0, 256);
-  if (error != cudaSuccess) return fail_cuda(error, "cudaMemset decode sync words");
+  // tags restart from zero, so every tagged word must be cleared with the counters
+  const cudaError_t error = cudaMemset(handle->decode_scratch, 0, kExchangeBytes);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaMemset decode exchange area");
   return AIMA_MOE_OK;
 }
 
@@ -190,9 +194,9 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
   params.xbuf1 = handle->xbuf1;
   params.logits = handle->logits;
   params.act = handle->act;
-  params.gate_logit = handle->gate_logit;
   params.bar_counter = handle->bar_counter;
   params.bar_base = handle->bar_base;
+  params.epoch_base = handle->epoch_base;
   params.status = handle->status;
   params.router_bias = handle->router_bias;
   params.quant_eighths = handle->quant_eighths;
@@ -301,14 +305,15 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
   error = cudaMemset(handle->decode_scratch, 0, handle->decode_scratch_bytes);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMemset decode scratch"));
   uint8_t* cursor = handle->decode_scratch;
-  handle->xbuf0 = reinterpret_cast<__nv_bfloat16*>(cursor); cursor += 4096;
-  handle->xbuf1 = reinterpret_cast<__nv_bfloat16*>(cursor); cursor += 4096;
-  handle->logits = reinterpret_cast<float*>(cursor); cursor += 1024;
-  handle->act = reinterpret_cast<uint16_t*>(cursor); cursor += align_up(9 * kInter * 2, 256);
-  handle->gate_logit = reinterpret_cast<float*>(cursor); cursor += 256;
-  handle->bar_counter = reinterpret_cast<unsigned long long*>(cursor); cursor += 128;
-  handle->bar_base = reinterpret_cast<unsigned long long*>(cursor); cursor += 128;
+  handle->bar_counter = reinterpret_cast<unsigned long long*>(cursor);
+  handle->bar_base = reinterpret_cast<unsigned long long*>(cursor + 128);
+  handle->epoch_base = reinterpret_cast<unsigned*>(cursor + 192);
+  cursor += 256;
   handle->status = reinterpret_cast<int*>(cursor); cursor += 256;
+  handle->logits = reinterpret_cast<unsigned long long*>(cursor); cursor += kLogitsBytes;
+  handle->xbuf0 = reinterpret_cast<uint32_t*>(cursor); cursor += kXbufBytes;
+  handle->xbuf1 = reinterpret_cast<uint32_t*>(cursor); cursor += kXbufBytes;
+  handle->act = reinterpret_cast<uint16_t*>(cursor);
 
   if (config->max_prefill_tokens > 0) {
     status = prefill_workspace_allocate(&handle->prefill, config->max_prefill_tokens,
@@ -561,7 +566,7 @@ AIMA_EXPORT int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics*
   std::lock_guard<std::mutex> lock(handle->mutex);
   cudaError_t error = cudaStreamSynchronize(handle->last_stream);
   if (error != cudaSuccess) return fail_cuda(error, "cudaStreamSynchronize");
-  int status_words[12] = {};
+  int status_words[24] = {};
   error = cudaMemcpy(status_words, handle->status, sizeof status_words, cudaMemcpyDeviceToHost);
   if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy status word");
   const int device_status = status_words[0];
