@@ -58,7 +58,8 @@ constexpr int kDotsStride = 12;
 constexpr int kOffRing = 0;
 constexpr int kOffDown = kOffRing + kRingSlots * kSlotBytes;                       // 81920
 constexpr int kOffAct = kOffDown + kDownRegionRanks * kDecodeMaxRowsPerBlock * kDownRowBytes;  // +129024
-constexpr int kOffDots = kOffAct + kDownRegionRanks * kInter * 2;                  // +9216
+constexpr int kActBytes = kDownRegionRanks * kInter * 2 + 16;                      // 9 x 512 BF16 + gate logit
+constexpr int kOffDots = kOffAct + kActBytes;                                      // +9232
 constexpr int kOffX = kOffDots + kDecodeMaxRowsPerBlock * kDotsStride * 4;         // +672: layer input, packed BF16
 constexpr int kOffNorm = kOffX + kHidden * 2;                                      // +4096: norm weight row
 constexpr int kOffMisc = kOffNorm + kHidden * 2;                                   // +4096
@@ -510,22 +511,23 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         }
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
-      // ---- norm: h2 in registers, element k = 256 g + 8 lane + j at xr[8 g + j]
-      float xr[64];
+      // ---- norm, once per block: canonical sum of squares (warp g sums group g), then every
+      //      thread normalises one 8-element chunk into h2_s (the activation region is idle now)
+      uint8_t* h2_s = reinterpret_cast<uint8_t*>(act_s);
+      if (warp < 8) {
+        float xv[8];
+        unpack8(reinterpret_cast<const uint4*>(x_s)[warp * 32 + lane], xv);
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = __fmaf_rn(xv[j], xv[j], acc);
+        acc = butterfly_sum(acc);
+        if (lane == 0) dots[warp] = acc;
+      }
+      consumer_sync();
       {
-        float part[8];
+        float total = dots[0];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          unpack8(reinterpret_cast<const uint4*>(x_s)[g * 32 + lane], xr + 8 * g);
-          float acc = 0.0f;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc = __fmaf_rn(xr[8 * g + j], xr[8 * g + j], acc);
-          part[g] = acc;
-        }
-        const float mine = warp_reduce8(part, lane);
-        float total = __shfl_sync(0xffffffffu, mine, reduce8_lane(0));
-#pragma unroll
-        for (int g = 1; g < 8; ++g) total = __fadd_rn(total, __shfl_sync(0xffffffffu, mine, reduce8_lane(g)));
+        for (int g = 1; g < 8; ++g) total = __fadd_rn(total, dots[g]);
         const float inv = det_rsqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(kHidden)), p.eps));
         if (!mbar_wait_bounded(norm_bar, li & 1u, abort_flag)) {
           if (*abort_flag == kStatusTimeoutMbarrier) {
@@ -535,23 +537,29 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           alive = false;
         }
         alive = __all_sync(0xffffffffu, alive);
+        if (ctid < kHidden / 8) {
+          float xv[8], wf[8];
+          unpack8(reinterpret_cast<const uint4*>(x_s)[ctid], xv);
+          unpack8(reinterpret_cast<const uint4*>(norm_s)[ctid], wf);
+          uint32_t packed[4];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          float wf[8];
-          unpack8(reinterpret_cast<const uint4*>(norm_s)[g * 32 + lane], wf);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float scaled = __fmul_rn(xr[8 * g + j], inv);
-            xr[8 * g + j] = round_bf16(__fmul_rn(scaled, __fadd_rn(wf[j], 1.0f)));
+          for (int j = 0; j < 8; j += 2) {
+            const float a = __fmul_rn(__fmul_rn(xv[j], inv), __fadd_rn(wf[j], 1.0f));
+            const float b = __fmul_rn(__fmul_rn(xv[j + 1], inv), __fadd_rn(wf[j + 1], 1.0f));
+            packed[j / 2] = static_cast<uint32_t>(float_to_bf16_bits(a)) |
+                            (static_cast<uint32_t>(float_to_bf16_bits(b)) << 16);
           }
+          const uint4 out = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          reinterpret_cast<uint4*>(h2_s)[ctid] = out;
+          if (p.dbg_h2 != nullptr && c == 0) reinterpret_cast<uint4*>(p.dbg_h2)[ctid] = out;
         }
-        if (p.dbg_h2 != nullptr && c == 0 && warp == 0) {
+      }
+      consumer_sync();
+      // streaming warps keep h2 in registers: element k = 256 g + 8 lane + j at xr[8 g + j]
+      float xr[64];
+      if (warp < kRingSlots) {
 #pragma unroll
-          for (int g = 0; g < 8; ++g)
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              p.dbg_h2[256 * g + 8 * lane + j] = __float2bfloat16_rn(xr[8 * g + j]);
-        }
+        for (int g = 0; g < 8; ++g) unpack8(reinterpret_cast<const uint4*>(h2_s)[g * 32 + lane], xr + 8 * g);
       }
 
       stamp(li, 1);
@@ -654,9 +662,9 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           k[q] = order_key(value);
           if (p.dbg_logits != nullptr && c == 0) p.dbg_logits[32 * q + lane] = value;
         }
-        float sel_v[kTopK];
-        int sel_i[kTopK];
-#pragma unroll
+        float my_score = 0.0f;      // lane r keeps the r-th selected value
+        int my_id = 0;
+#pragma unroll 1
         for (int r = 0; r < kTopK; ++r) {
           uint32_t local = k[0];
 #pragma unroll
@@ -668,35 +676,34 @@ moe_decode_persistent_kernel(const DecodeParams p) {
             if (k[q] == best) candidate = 32 * q + lane;
           }
           const int winner = __reduce_min_sync(0xffffffffu, candidate);
-          sel_v[r] = key_value(best);
-          sel_i[r] = winner;
+          if (lane == r) { my_score = key_value(best); my_id = winner; }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             if (winner == 32 * q + lane) k[q] = 0u;
           }
         }
-        float ex[kTopK];
+        // softmax over the eight: exp(s_r - s_0) / sum, summed in selection order
+        const float top = __shfl_sync(0xffffffffu, my_score, 0);
+        const float ex = det_expf(__fsub_rn(my_score, top));
         float denom = 0.0f;
 #pragma unroll
-        for (int r = 0; r < kTopK; ++r) {
-          ex[r] = det_expf(__fsub_rn(sel_v[r], sel_v[0]));
-          denom = __fadd_rn(denom, ex[r]);
-        }
-        if (lane == 0) {
-          int n_local = 0;
-#pragma unroll
-          for (int r = 0; r < kTopK; ++r) {
-            const uint16_t wb = float_to_bf16_bits(__fdiv_rn(ex[r], denom));
-            misc->ids[r] = sel_i[r];
-            misc->weights[r] = bf16_bits_to_float(wb);
-            if (sel_i[r] >= p.expert_lo && sel_i[r] < p.expert_hi) misc->local_rank[n_local++] = r;
-            if (c == 0) {
-              if (p.dbg_ids != nullptr) p.dbg_ids[r] = sel_i[r];
-              if (p.dbg_scores != nullptr) p.dbg_scores[r] = sel_v[r];
-              if (p.dbg_weights != nullptr) reinterpret_cast<uint16_t*>(p.dbg_weights)[r] = wb;
-            }
+        for (int r = 0; r < kTopK; ++r) denom = __fadd_rn(denom, __shfl_sync(0xffffffffu, ex, r));
+        const uint16_t wb = float_to_bf16_bits(__fdiv_rn(ex, denom));
+        const bool local_expert = my_id >= p.expert_lo && my_id < p.expert_hi;
+        const unsigned local_mask = __ballot_sync(0xffffffffu, lane < kTopK && local_expert);
+        if (lane < kTopK) {
+          misc->ids[lane] = my_id;
+          misc->weights[lane] = bf16_bits_to_float(wb);
+          if (local_expert) misc->local_rank[__popc(local_mask & ((1u << lane) - 1u))] = lane;
+          if (c == 0) {
+            if (p.dbg_ids != nullptr) p.dbg_ids[lane] = my_id;
+            if (p.dbg_scores != nullptr) p.dbg_scores[lane] = my_score;
+            if (p.dbg_weights != nullptr) reinterpret_cast<uint16_t*>(p.dbg_weights)[lane] = wb;
           }
-          misc->n_local = n_local;
+        }
+        __syncwarp();
+        if (lane == 0) {
+          misc->n_local = __popc(local_mask);
           __threadfence_block();
           misc->ids_layer = li + 1;
         }
@@ -729,7 +736,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       stamp(li, 6);
 
       // ---- phase 2: down products for outputs h0 .. h1-1 ----
-      for (int v = ctid; v < kDownRegionRanks * kInter * 2 / 16; v += kDecodeConsumerThreads) {
+      for (int v = ctid; v < kActBytes / 16; v += kDecodeConsumerThreads) {
         reinterpret_cast<uint4*>(act_s)[v] = ld_cg_u4(
             reinterpret_cast<const uint4*>(p.act + (c % kDecodeReplicas) * kDecodeActStride) + v);
       }
@@ -745,38 +752,37 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       alive = __all_sync(0xffffffffu, alive);
       stamp(li, 8);
       if (alive) {
-        // dot d = (output row hh, rank slot q); eight dots per warp pass share one reduction
-        const int per_row = n_local + 1;
-        const int n_dots = nh * per_row;
-        for (int d0 = warp * 8; d0 < n_dots; d0 += kDecodeConsumerWarps * 8) {
+        // unit = (rank slot q, half of the block's output rows): the activation row is unpacked
+        // once and up to seven dots against it share one eight-way reduction
+        const int half_rows = (nh + 1) / 2;
+        const int n_units = 2 * (n_local + 1);
+        for (int unit = warp; unit < n_units; unit += kDecodeConsumerWarps) {
+          const int q = unit >> 1;
+          const int row_base = (unit & 1) * half_rows;
+          const int region = (q == n_local) ? kTopK : q;
+          float af[16];
+          {
+            const uint4* arow = reinterpret_cast<const uint4*>(act_s + region * kInter) + lane;
+            unpack8(arow[0], af);
+            unpack8(arow[32], af + 8);
+          }
           float part[8];
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            const int d = d0 + u;
+            const int hh = row_base + u;
             float acc = 0.0f;
-            if (d < n_dots) {
-              const int hh = d / per_row;
-              const int q = d - hh * per_row;
-              const int region = (q == n_local) ? kTopK : q;
+            if (u < half_rows && hh < nh) {
               const uint4* wrow = reinterpret_cast<const uint4*>(
                   down_region + (region * kDecodeMaxRowsPerBlock + hh) * kDownRowBytes) + lane;
-              const uint4* arow = reinterpret_cast<const uint4*>(act_s + region * kInter) + lane;
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                float af[8];
-                unpack8(arow[i * 32], af);
-                acc = fma8(af, wrow[i * 32], acc);
-              }
+              acc = fma8(af, wrow[0], acc);
+              acc = fma8(af + 8, wrow[32], acc);
             }
             part[u] = acc;
           }
           const float total = warp_reduce8(part, lane);
-          const int d = d0 + reduce8_slot(lane);
-          if ((lane & 3) == 0 && d < n_dots) {
-            const int hh = d / per_row;
-            const int q = d - hh * per_row;
-            dots[hh * kDotsStride + ((q == n_local) ? kTopK : q)] = total;
-          }
+          const int u = reduce8_slot(lane);
+          const int hh = row_base + u;
+          if ((lane & 3) == 0 && u < half_rows && hh < nh) dots[hh * kDotsStride + region] = total;
         }
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
@@ -788,8 +794,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           acc = __fmaf_rn(misc->weights[misc->local_rank[q]], dots[ctid * kDotsStride + q], acc);
         }
         const float routed = round_bf16(acc);
-        const float sig = round_bf16(det_sigmoid(
-            ld_cg_f32(p.act + (c % kDecodeReplicas) * kDecodeActStride + 9 * kInter)));
+        const float sig = round_bf16(det_sigmoid(*reinterpret_cast<const float*>(act_s + 9 * kInter)));
         const float shared_down = round_bf16(dots[ctid * kDotsStride + kTopK]);
         const float shared_scaled = round_bf16(__fmul_rn(sig, shared_down));
         const float combined = round_bf16(__fadd_rn(routed, shared_scaled));

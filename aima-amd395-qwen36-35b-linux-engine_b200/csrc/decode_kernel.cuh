@@ -14,7 +14,7 @@ constexpr int kDecodeThreads = kDecodeConsumerThreads + 32;  // + producer warp
 constexpr int kDecodeMaxRowsPerBlock = 14;
 constexpr int kDecodeMinBlocks = (kHidden + kDecodeMaxRowsPerBlock - 1) / kDecodeMaxRowsPerBlock;
 constexpr int kDecodeMaxBlocks = kExperts;  // router rows are dealt c, c + grid
-constexpr int kDecodeSmemBytes = 229712;
+constexpr int kDecodeSmemBytes = 229728;
 constexpr int kDecodeTraceStamps = 12;
 // Everything all 148 blocks read back from global memory (router logits, the
 // activation vector, the layer output) is written kDecodeReplicas times, and
