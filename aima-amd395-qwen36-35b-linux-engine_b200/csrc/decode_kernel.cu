@@ -211,6 +211,15 @@ __device__ __forceinline__ uint4 ld_strong_u4(const void* p) {
 __device__ __forceinline__ void st_strong_u64(void* p, unsigned long long v) {
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
 }
+// system scope: the other end is another GPU reached over NVLink
+__device__ __forceinline__ unsigned long long ld_sys_u64(const void* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_sys_u64(void* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ void st_strong_u32(void* p, uint32_t v) {
   asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
@@ -787,11 +796,63 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 9);
+      // ---- expert parallelism: the down products of the rank slots held here go to every peer
+      //      (plain stores over NVLink into its exchange buffer), those held elsewhere are polled
+      //      from this GPU's own buffer; words carry the layer tag, buffers alternate per layer.
+      //      Block c of every GPU owns the same output rows, so a peer can be at most one layer ahead.
+      if (p.world > 1 && alive) {
+        const unsigned long long tag64 = static_cast<unsigned long long>(epoch0 + li + 1) << 32;
+        const size_t parity_base = static_cast<size_t>(li & 1) * kTopK * kHidden;
+        const int sends = n_local * nh * (p.world - 1);
+        for (int s = ctid; s < sends; s += kDecodeConsumerThreads) {
+          const int peer_slot = s / (n_local * nh);
+          const int rest = s - peer_slot * (n_local * nh);
+          const int q = rest / nh;
+          const int hh = rest - q * nh;
+          const int peer = peer_slot + (peer_slot >= p.rank ? 1 : 0);
+          const int slot = misc->local_rank[q];
+          st_sys_u64(p.ep_dots[peer] + parity_base + static_cast<size_t>(slot) * kHidden + h0 + hh,
+                     tag64 | __float_as_uint(dots[hh * kDotsStride + q]));
+        }
+      }
       if (ctid < nh) {
         const int h = h0 + ctid;
         float acc = 0.0f;
-        for (int q = 0; q < n_local; ++q) {
-          acc = __fmaf_rn(misc->weights[misc->local_rank[q]], dots[ctid * kDotsStride + q], acc);
+        if (p.world == 1) {
+          for (int q = 0; q < n_local; ++q) {
+            const float d = dots[ctid * kDotsStride + q];
+            acc = __fmaf_rn(misc->weights[misc->local_rank[q]], d, acc);
+            if (p.dbg_slot_dots != nullptr) p.dbg_slot_dots[misc->local_rank[q] * kHidden + h] = d;
+          }
+        } else {
+          const unsigned tag = epoch0 + li + 1;
+          const unsigned long long* mine = p.ep_dots[p.rank] + static_cast<size_t>(li & 1) * kTopK * kHidden + h;
+          int q = 0;
+          const unsigned long long start = global_timer_ns();
+          for (int r = 0; r < kTopK; ++r) {
+            float d;
+            if (q < n_local && misc->local_rank[q] == r) {
+              d = dots[ctid * kDotsStride + q];
+              ++q;
+            } else {
+              unsigned long long word = ld_sys_u64(mine + static_cast<size_t>(r) * kHidden);
+              unsigned spins = 0;
+              while (static_cast<unsigned>(word >> 32) != tag) {
+                if ((++spins & 63u) == 0u) {
+                  if (*abort_flag != 0) break;
+                  if (global_timer_ns() - start > kWaitBudgetNs) {
+                    raise_status(p, abort_flag, kStatusTimeoutPeer);
+                    record_site(p, 11, li * 16 + r);
+                    break;
+                  }
+                }
+                word = ld_sys_u64(mine + static_cast<size_t>(r) * kHidden);
+              }
+              d = __uint_as_float(static_cast<uint32_t>(word));
+            }
+            acc = __fmaf_rn(misc->weights[r], d, acc);
+            if (p.dbg_slot_dots != nullptr) p.dbg_slot_dots[r * kHidden + h] = d;
+          }
         }
         const float routed = round_bf16(acc);
         const float sig = round_bf16(det_sigmoid(*reinterpret_cast<const float*>(act_s + 9 * kInter)));

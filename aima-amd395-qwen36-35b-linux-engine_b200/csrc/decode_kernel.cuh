@@ -16,6 +16,7 @@ constexpr int kDecodeMinBlocks = (kHidden + kDecodeMaxRowsPerBlock - 1) / kDecod
 constexpr int kDecodeMaxBlocks = kExperts;  // router rows are dealt c, c + grid
 constexpr int kDecodeSmemBytes = 229728;
 constexpr int kDecodeTraceStamps = 12;
+constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU expert-parallel exchange buffer
 // Everything all 148 blocks read back from global memory (router logits, the
 // activation vector, the layer output) is written kDecodeReplicas times, and
 // block c reads copy c % kDecodeReplicas: 148 readers of the same few L2 lines
@@ -43,6 +44,11 @@ struct DecodeParams {
   int n_layers;
   int expert_lo;                 // experts [expert_lo, expert_hi) live on this GPU
   int expert_hi;
+  // expert parallelism: ep_dots[r] is rank r's exchange buffer (own buffer at index `rank`),
+  // laid out [2 layer parities][8 rank slots][2048] 64-bit words = tag32 << 32 | FP32 bits
+  unsigned long long* ep_dots[8];
+  int world;
+  int rank;
   // optional tracing: block 0 stamps %globaltimer at kDecodeTraceStamps points
   // of every layer into timeline[layer_ordinal * kDecodeTraceStamps + k]
   unsigned long long* timeline;
@@ -54,6 +60,7 @@ struct DecodeParams {
   __nv_bfloat16* dbg_weights;
   __nv_bfloat16* dbg_shared_scaled;
   __nv_bfloat16* dbg_routed;
+  float* dbg_slot_dots;          // [8][2048] per-slot down products (FP32) of the locally held experts
 };
 
 cudaError_t launch_moe_decode(const DecodeParams& params, int grid_blocks,

@@ -192,6 +192,8 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   params.status = reinterpret_cast<int*>(scratch + kOffStatus);
   params.router_bias = nullptr;
   params.timeline = nullptr;
+  params.world = 1;
+  params.rank = 0;
   params.quant_eighths = 0;
   params.eps = rms_eps;
   params.first_layer = 0;

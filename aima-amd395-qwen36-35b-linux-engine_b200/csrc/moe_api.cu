@@ -84,6 +84,10 @@ struct aima_moe_handle {
 
   PrefillWorkspace prefill;
 
+  // expert parallelism (world > 1): this GPU's exchange buffer and the peers' mapped buffers
+  unsigned long long* ep_local = nullptr;
+  unsigned long long* ep_peers[8] = {};
+  void* ep_ipc_opened[8] = {};
   float* router_row_norms = nullptr;        // [kMaxLayers][256], device, filled by bind_layer
   unsigned long long* timeline = nullptr;   // [kMaxLayers * kDecodeTraceStamps], device
   bool tracing = false;
@@ -155,7 +159,8 @@ bool ranges_overlap(const void* a, size_t a_bytes, const void* b, size_t b_bytes
 
 int reset_decode_sync(aima_moe_handle* handle) {
   // tags restart from zero, so every tagged word must be cleared with the counters
-  const cudaError_t error = cudaMemset(handle->decode_scratch, 0, kExchangeBytes);
+  cudaError_t error = cudaMemset(handle->decode_scratch, 0, kExchangeBytes);
+  if (error == cudaSuccess && handle->ep_local != nullptr) error = cudaMemset(handle->ep_local, 0, kEpExchangeBytes);
   if (error != cudaSuccess) return fail_cuda(error, "cudaMemset decode exchange area");
   return AIMA_MOE_OK;
 }
@@ -183,8 +188,10 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "decode vectors must be 16-byte aligned");
   if (debug != nullptr && debug->struct_bytes != sizeof(aima_moe_debug_views))
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_debug_views size mismatch");
-  if (handle->config.world != 1)
-    return fail(AIMA_MOE_ERR_UNSUPPORTED, "expert-parallel decode is not built yet");
+  for (uint32_t peer = 0; peer < handle->config.world; ++peer) {
+    if (handle->config.world > 1 && handle->ep_peers[peer] == nullptr)
+      return fail(AIMA_MOE_ERR_NOT_BOUND, "expert-parallel peer %u is not connected (aima_moe_ep_connect)", peer);
+  }
 
   DecodeParams params{};
   params.layers = handle->dev_layers;
@@ -205,6 +212,9 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
   params.n_layers = static_cast<int>(n_layers);
   params.expert_lo = handle->expert_lo;
   params.expert_hi = handle->expert_lo + handle->experts_local;
+  for (int peer = 0; peer < 8; ++peer) params.ep_dots[peer] = handle->ep_peers[peer];
+  params.world = static_cast<int>(handle->config.world);
+  params.rank = static_cast<int>(handle->config.rank);
   params.timeline = handle->tracing ? handle->timeline : nullptr;
   if (handle->tracing) handle->traced_layers = n_layers;
   if (debug != nullptr) {
@@ -215,6 +225,7 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
     params.dbg_weights = static_cast<__nv_bfloat16*>(debug->topk_weights);
     params.dbg_shared_scaled = static_cast<__nv_bfloat16*>(debug->shared_scaled);
     params.dbg_routed = static_cast<__nv_bfloat16*>(debug->routed);
+    params.dbg_slot_dots = static_cast<float*>(debug->slot_dots);
   }
   const cudaError_t error =
       launch_moe_decode(params, handle->decode_grid, static_cast<cudaStream_t>(stream));
@@ -282,6 +293,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
 
   auto cleanup = [&](int code) {
     if (handle->timeline) cudaFree(handle->timeline);
+    if (handle->ep_local) cudaFree(handle->ep_local);
     if (handle->router_row_norms) cudaFree(handle->router_row_norms);
     if (handle->dev_layers) cudaFree(handle->dev_layers);
     if (handle->decode_scratch) cudaFree(handle->decode_scratch);
@@ -297,6 +309,12 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
 
   error = cudaMalloc(&handle->timeline, sizeof(unsigned long long) * kMaxLayers * kDecodeTraceStamps);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc decode timeline"));
+  if (config->world > 1) {
+    error = cudaMalloc(&handle->ep_local, kEpExchangeBytes);
+    if (error == cudaSuccess) error = cudaMemset(handle->ep_local, 0, kEpExchangeBytes);
+    if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc expert-parallel exchange buffer"));
+    handle->ep_peers[config->rank] = handle->ep_local;
+  }
   error = cudaMalloc(&handle->router_row_norms, sizeof(float) * kMaxLayers * kExperts);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc router row norms"));
   handle->decode_scratch_bytes = decode_scratch_size();
@@ -599,6 +617,57 @@ AIMA_EXPORT int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics*
   return AIMA_MOE_OK;
 }
 
+AIMA_EXPORT int aima_moe_ep_local_buffer(aima_moe_handle* handle, void** pointer, uint64_t* bytes) {
+  if (handle == nullptr || pointer == nullptr || bytes == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "expert-parallel buffer argument is null");
+  if (handle->ep_local == nullptr)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "the handle was prepared with world = 1");
+  *pointer = handle->ep_local;
+  *bytes = kEpExchangeBytes;
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_ep_export(aima_moe_handle* handle, void* ipc_handle_64_bytes) {
+  if (handle == nullptr || ipc_handle_64_bytes == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "expert-parallel export argument is null");
+  if (handle->ep_local == nullptr)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "the handle was prepared with world = 1");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t ipc;
+  const cudaError_t error = cudaIpcGetMemHandle(&ipc, handle->ep_local);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaIpcGetMemHandle");
+  std::memcpy(ipc_handle_64_bytes, &ipc, sizeof ipc);
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_ep_connect(aima_moe_handle* handle, uint32_t peer, const void* ipc_handle_64_bytes,
+                                    void* direct_pointer) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if (handle->ep_local == nullptr)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "the handle was prepared with world = 1");
+  if (peer >= handle->config.world)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "peer %u is not a rank of world %u", peer, handle->config.world);
+  if ((ipc_handle_64_bytes == nullptr) == (direct_pointer == nullptr))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "give exactly one of an IPC handle or a direct device pointer");
+  // peer == rank with a direct pointer substitutes this rank's own buffer (hosts that own a
+  // symmetric heap); an IPC handle for oneself makes no sense
+  if (peer == handle->config.rank && direct_pointer == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "the own rank can only be given as a direct pointer");
+  if (direct_pointer != nullptr) {
+    handle->ep_peers[peer] = static_cast<unsigned long long*>(direct_pointer);
+    return AIMA_MOE_OK;
+  }
+  cudaIpcMemHandle_t ipc;
+  std::memcpy(&ipc, ipc_handle_64_bytes, sizeof ipc);
+  void* mapped = nullptr;
+  const cudaError_t error = cudaIpcOpenMemHandle(&mapped, ipc, cudaIpcMemLazyEnablePeerAccess);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaIpcOpenMemHandle");
+  handle->ep_ipc_opened[peer] = mapped;
+  handle->ep_peers[peer] = static_cast<unsigned long long*>(mapped);
+  return AIMA_MOE_OK;
+}
+
 AIMA_EXPORT int aima_moe_set_tracing(aima_moe_handle* handle, int enabled) {
   if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
   std::lock_guard<std::mutex> lock(handle->mutex);
@@ -626,6 +695,10 @@ AIMA_EXPORT int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t*
 
 AIMA_EXPORT int aima_moe_release(aima_moe_handle* handle) {
   if (handle == nullptr) return AIMA_MOE_OK;
+  for (int peer = 0; peer < 8; ++peer) {
+    if (handle->ep_ipc_opened[peer] != nullptr) cudaIpcCloseMemHandle(handle->ep_ipc_opened[peer]);
+  }
+  cudaFree(handle->ep_local);
   cudaFree(handle->timeline);
   cudaFree(handle->router_row_norms);
   cudaFree(handle->dev_layers);

@@ -66,7 +66,7 @@ class DebugViews(ctypes.Structure):
         ("h2", c_void_p), ("router_logits", c_void_p), ("topk_ids", c_void_p),
         ("topk_scores", c_void_p), ("topk_weights", c_void_p), ("shared_scaled", c_void_p),
         ("routed", c_void_p), ("expert_counts", c_void_p), ("expert_offsets", c_void_p),
-        ("sorted_rows", c_void_p),
+        ("sorted_rows", c_void_p), ("slot_dots", c_void_p),
     ]
 
 
@@ -102,6 +102,9 @@ EXPORTS = [
      [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_void_p]),
     ("aima_moe_decode_layers_noalloc", c_int,
      [ctypes.POINTER(LayerWeights), c_uint32, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
+    ("aima_moe_ep_local_buffer", c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_uint64)]),
+    ("aima_moe_ep_export", c_int, [c_void_p, c_void_p]),
+    ("aima_moe_ep_connect", c_int, [c_void_p, c_uint32, c_void_p, c_void_p]),
     ("aima_moe_set_tracing", c_int, [c_void_p, c_int]),
     ("aima_moe_read_decode_timeline", c_int,
      [c_void_p, ctypes.POINTER(c_uint64), c_uint32, ctypes.POINTER(c_uint32)]),
@@ -206,6 +209,22 @@ def decode_layers_noalloc(layer_dicts: list, x_in: Any, x_out: Any, rms_eps: flo
     return x_out
 
 
+def exchange_ipc_handles(mine: bytes, rank: int, world: int, group: Any = None) -> list[bytes]:
+    """All-gathers one 64-byte handle per rank over torch.distributed; returns them by rank."""
+    import torch
+    import torch.distributed as dist
+
+    assert len(mine) == 64
+    backend = dist.get_backend(group)
+    device = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+    local = torch.tensor(list(mine), dtype=torch.uint8, device=device)
+    gathered = [torch.empty(64, dtype=torch.uint8, device=device) for _ in range(world)]
+    dist.all_gather(gathered, local, group=group)
+    handles = [bytes(t.cpu().tolist()) for t in gathered]
+    assert handles[rank] == mine
+    return handles
+
+
 class MoeProvider:
     """Owns one aima_moe handle on the current CUDA device."""
 
@@ -262,6 +281,8 @@ class MoeProvider:
             "shared_scaled": torch.empty(tokens, HIDDEN, dtype=torch.bfloat16, device=dev),
             "routed": torch.empty(tokens, HIDDEN, dtype=torch.bfloat16, device=dev),
         }
+        if not prefill:
+            t["slot_dots"] = torch.zeros(TOP_K, HIDDEN, dtype=torch.float32, device=dev)
         if prefill:
             t["expert_counts"] = torch.empty(EXPERTS, dtype=torch.int32, device=dev)
             t["expert_offsets"] = torch.empty(EXPERTS + 1, dtype=torch.int32, device=dev)
@@ -333,6 +354,31 @@ class MoeProvider:
         out = torch.empty(m, dtype=torch.bfloat16, device=weight.device)
         self.lib.check(self.lib.aima_moe_gemv_bf16_launch(_ptr(weight), _ptr(x), _ptr(out), m, k, _stream(torch)))
         return out
+
+    # -- expert parallelism ---------------------------------------------------
+    def ep_local_buffer(self) -> tuple[int, int]:
+        pointer, size = c_void_p(), c_uint64()
+        self.lib.check(self.lib.aima_moe_ep_local_buffer(self.handle, ctypes.byref(pointer), ctypes.byref(size)))
+        return int(pointer.value), int(size.value)
+
+    def ep_export(self) -> bytes:
+        buffer = ctypes.create_string_buffer(64)
+        self.lib.check(self.lib.aima_moe_ep_export(self.handle, buffer))
+        return buffer.raw
+
+    def ep_connect(self, peer: int, ipc_handle: bytes | None = None, pointer: int | None = None) -> None:
+        handle_buffer = ctypes.create_string_buffer(ipc_handle, 64) if ipc_handle is not None else None
+        self.lib.check(self.lib.aima_moe_ep_connect(
+            self.handle, peer, handle_buffer, c_void_p(pointer) if pointer is not None else None))
+
+    def ep_connect_all(self, group: Any = None) -> None:
+        """One process per GPU: all-gathers the 64-byte IPC handles over torch.distributed
+        (any backend; the payload is a CPU byte tensor for gloo, a CUDA one for nccl) and maps
+        every peer's exchange buffer."""
+        handles = exchange_ipc_handles(self.ep_export(), self.config.rank, self.config.world, group)
+        for peer, handle in enumerate(handles):
+            if peer != self.config.rank:
+                self.ep_connect(peer, ipc_handle=handle)
 
     def set_tracing(self, enabled: bool) -> None:
         self.lib.check(self.lib.aima_moe_set_tracing(self.handle, int(enabled)))

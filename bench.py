@@ -33,6 +33,9 @@ SEED = 1234
 BYTES_PER_LAYER_TOKEN = 1_048_576 + 50_331_648 + 6_295_552 + 4_096       # router, 8 experts, shared, norm
 BYTES_PER_TOKEN = LAYERS * BYTES_PER_LAYER_TOKEN                          # 2 307 194 880
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per layer of the decode kernel, from the ncu capture
+# summarised in profiles/ (2-layer case: 118.9 MB per launch)
+DECODE_TRAFFIC_PER_LAYER = 59_460_000
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -181,14 +184,20 @@ def run_ours(args) -> None:
     if distributed:
         import torch.distributed as dist
 
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
 
-    provider = package.MoeProvider(layers=LAYERS, max_prefill_tokens=0)
+    # expert parallelism: rank r holds experts [r * 256 / W, (r + 1) * 256 / W); router, shared
+    # expert and norms are replicated (same generator stream on every rank)
+    per_rank = 256 // world
+    provider = package.MoeProvider(layers=LAYERS, max_prefill_tokens=0, world=world, rank=rank)
     keep = []
     for layer in range(LAYERS):
-        weights = synth.layer_weights_cuda_fast(SEED, layer, device)
+        weights = synth.layer_weights_cuda_fast(SEED, layer, device, rank * per_rank, (rank + 1) * per_rank)
         provider.bind_layer(layer, weights)
         keep.append(weights)
+    if distributed:
+        provider.ep_connect_all(dist.new_group(backend="gloo"))
     torch.cuda.synchronize()
 
     x0 = synth.activations(SEED, 1, "residual", 0)[0]
@@ -249,21 +258,23 @@ def run_ours(args) -> None:
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
-        tokens = args.steps * world                # replicas: every rank decodes its own token stream
+        tokens = args.steps                        # expert parallel: all ranks work on the same token
         value = tokens / (device_ms / 1000.0)
         achieved = BYTES_PER_TOKEN * args.steps / (device_ms / 1000.0) / 1.0e9
         line = {
             "metric": "moe_decode_b1_tokens_per_second", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": device_ms / args.steps, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"decode_b1_stack{LAYERS} (BASELINE config 1)", "layers": LAYERS,
                        "hidden": HIDDEN, "experts": 256, "top_k": 8,
                        "l2": "inputs larger than L2 (2.3 GB of weights per step)",
-                       "multi_gpu": "independent replicas" if world > 1 else "single GPU"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_kind,
-                         "bytes_per_step": BYTES_PER_TOKEN},
+                       "multi_gpu": (f"expert parallel, {per_rank} experts per GPU, per-slot down products "
+                                     "exchanged by peer stores over NVLink") if world > 1 else "single GPU"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s",
+                         "frac": achieved / (peak * world), "traffic": DECODE_TRAFFIC_PER_LAYER * LAYERS,
+                         "peak_source": peak_kind, "bytes_per_step": BYTES_PER_TOKEN},
             "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s",
                     "h2d_bytes_per_step": HIDDEN * 2, "d2h_bytes_per_step": HIDDEN * 2},
             "gpu_launches": args.steps,

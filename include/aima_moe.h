@@ -123,6 +123,8 @@ typedef struct aima_moe_debug_views {
   void* expert_counts;   /* i32  [256]     prefill only                          */
   void* expert_offsets;  /* i32  [257]     prefill only                          */
   void* sorted_rows;     /* i32  [8T]      prefill only                          */
+  void* slot_dots;       /* f32  [8,2048]  decode only: per rank slot, the down
+                            product act . Wd before the routing weight           */
 } aima_moe_debug_views;
 
 /* Counters in the spirit of NativeMoePrefillMetrics
@@ -243,6 +245,29 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
 /* Synchronises the handle's last stream, reads the device status word and the
  * padded-row counter; returns AIMA_MOE_ERR_TIMEOUT if a bounded wait ran out. */
 int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics* metrics);
+
+/* Expert parallelism over the GPUs of one NVLink / NVSwitch box (no counterpart in
+ * the reference, which is single-GPU; it follows from sharding its contiguous
+ * per-expert tensors).  A handle prepared with world > 1 binds only its slab of
+ * experts and owns one exchange buffer; each rank maps every peer's buffer once:
+ *   same process (one host thread per GPU, peer access enabled by the host):
+ *       aima_moe_ep_local_buffer on the peer's handle, then
+ *       aima_moe_ep_connect(handle, peer, NULL, pointer)
+ *   one process per GPU: aima_moe_ep_export -> 64-byte CUDA IPC handle, carried
+ *       by the host's own bootstrap (MPI, torch.distributed, a socket), then
+ *       aima_moe_ep_connect(handle, peer, ipc_handle, NULL).
+ * Decode: every rank evaluates router and shared expert itself, computes the down
+ * products of the chosen experts it holds, stores them into the peers' buffers
+ * over NVLink and sums all eight in slot order, so every rank ends with the same
+ * bits as a single GPU.  All ranks must launch the same layers in the same order.
+ * A host that owns a symmetric heap may substitute this rank's own buffer with
+ * aima_moe_ep_connect(handle, own rank, NULL, pointer) (AIMA_MOE_EP_BUFFER_BYTES,
+ * zero-filled). */
+#define AIMA_MOE_EP_BUFFER_BYTES 262144
+int aima_moe_ep_local_buffer(aima_moe_handle* handle, void** pointer, uint64_t* bytes);
+int aima_moe_ep_export(aima_moe_handle* handle, void* ipc_handle_64_bytes);
+int aima_moe_ep_connect(aima_moe_handle* handle, uint32_t peer, const void* ipc_handle_64_bytes,
+                        void* direct_pointer);
 
 /* Tracing, the counterpart of AIMA_NATIVE_PREFILL_TIMELINE
  * (native/src/native_resident_engine.hip.cpp:105-108, 1226-1259): when enabled,
