@@ -37,6 +37,7 @@ struct GroupedGemm {
   const int32_t* tile_row0;
   const int32_t* tile_rows;
   const int32_t* tile_count;   // device scalar; nullptr in dense mode
+  int expert_base;             // first expert held in b0 (tile_expert holds global ids)
   int max_tiles;               // launch bound on the tile count
   int dense_rows;
   const __nv_bfloat16* a;      // [rows, k]

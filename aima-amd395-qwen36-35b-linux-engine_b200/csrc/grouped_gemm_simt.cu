@@ -21,7 +21,7 @@ grouped_gemm_simt_kernel(const GroupedGemm g) {
   if (tile >= n_tiles) return;
   int expert = 0, row0, rows;
   if (g.tile_expert != nullptr) {
-    expert = g.tile_expert[tile];
+    expert = g.tile_expert[tile] - g.expert_base;
     row0 = g.tile_row0[tile];
     rows = g.tile_rows[tile];
   } else {

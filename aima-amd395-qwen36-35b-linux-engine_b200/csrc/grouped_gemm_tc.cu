@@ -178,7 +178,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
     tile = unit / pb.n_chunks;
     chunk = unit - tile * pb.n_chunks;
     if (g.tile_expert != nullptr) {
-      expert = g.tile_expert[tile];
+      expert = g.tile_expert[tile] - g.expert_base;
       row0 = g.tile_row0[tile];
       rows = g.tile_rows[tile];
     } else {

@@ -85,7 +85,10 @@ struct aima_moe_handle {
   PrefillWorkspace prefill;
 
   // expert parallelism (world > 1): this GPU's exchange buffer and the peers' mapped buffers
+  // layout of one exchange allocation: [decode slot products kEpExchangeBytes][prefill region]
   unsigned long long* ep_local = nullptr;
+  size_t ep_bytes = 0;
+  EpPrefill ep_prefill;
   unsigned long long* ep_peers[8] = {};
   void* ep_ipc_opened[8] = {};
   float* router_row_norms = nullptr;        // [kMaxLayers][256], device, filled by bind_layer
@@ -160,7 +163,10 @@ bool ranges_overlap(const void* a, size_t a_bytes, const void* b, size_t b_bytes
 int reset_decode_sync(aima_moe_handle* handle) {
   // tags restart from zero, so every tagged word must be cleared with the counters
   cudaError_t error = cudaMemset(handle->decode_scratch, 0, kExchangeBytes);
-  if (error == cudaSuccess && handle->ep_local != nullptr) error = cudaMemset(handle->ep_local, 0, kEpExchangeBytes);
+  if (error == cudaSuccess && handle->ep_local != nullptr) {
+    error = cudaMemset(handle->ep_local, 0, handle->ep_bytes);
+    handle->ep_prefill.epoch = 0;
+  }
   if (error != cudaSuccess) return fail_cuda(error, "cudaMemset decode exchange area");
   return AIMA_MOE_OK;
 }
@@ -310,8 +316,15 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
   error = cudaMalloc(&handle->timeline, sizeof(unsigned long long) * kMaxLayers * kDecodeTraceStamps);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc decode timeline"));
   if (config->world > 1) {
-    error = cudaMalloc(&handle->ep_local, kEpExchangeBytes);
-    if (error == cudaSuccess) error = cudaMemset(handle->ep_local, 0, kEpExchangeBytes);
+    handle->ep_prefill.world = static_cast<int>(config->world);
+    handle->ep_prefill.rank = static_cast<int>(config->rank);
+    handle->ep_bytes = kEpExchangeBytes;
+    if (config->max_prefill_tokens > 0) {
+      handle->ep_bytes += ep_prefill_region_bytes(static_cast<int>(config->max_prefill_tokens),
+                                                  static_cast<int>(config->world), &handle->ep_prefill.layout);
+    }
+    error = cudaMalloc(&handle->ep_local, handle->ep_bytes);
+    if (error == cudaSuccess) error = cudaMemset(handle->ep_local, 0, handle->ep_bytes);
     if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc expert-parallel exchange buffer"));
     handle->ep_peers[config->rank] = handle->ep_local;
   }
@@ -445,8 +458,16 @@ AIMA_EXPORT int aima_moe_prefill_launch(aima_moe_handle* handle, uint32_t layer,
     return fail(AIMA_MOE_ERR_ALIAS, "prefill output aliases an input");
   if (debug != nullptr && debug->struct_bytes != sizeof(aima_moe_debug_views))
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_debug_views size mismatch");
-  if (handle->config.world != 1)
-    return fail(AIMA_MOE_ERR_UNSUPPORTED, "expert-parallel prefill is not built yet");
+  if (handle->config.world > 1) {
+    if (static_cast<uint64_t>(tokens) * handle->config.world > handle->config.max_prefill_tokens)
+      return fail(AIMA_MOE_ERR_CAPACITY, "tokens %u x world %u exceed the prepared global capacity %u", tokens,
+                  handle->config.world, handle->config.max_prefill_tokens);
+    for (uint32_t peer = 0; peer < handle->config.world; ++peer) {
+      if (handle->ep_peers[peer] == nullptr)
+        return fail(AIMA_MOE_ERR_NOT_BOUND, "expert-parallel peer %u is not connected (aima_moe_ep_connect)", peer);
+      handle->ep_prefill.peers[peer] = reinterpret_cast<uint8_t*>(handle->ep_peers[peer]) + kEpExchangeBytes;
+    }
+  }
   PrefillCall call{};
   call.layer = handle->host_layers[layer];
   call.h2 = h2;
@@ -459,8 +480,12 @@ AIMA_EXPORT int aima_moe_prefill_launch(aima_moe_handle* handle, uint32_t layer,
   call.quant_eighths = handle->quant_eighths;
   call.debug = debug;
   int launches = 0;
-  const int status = prefill_layer_launch(&handle->prefill, call, static_cast<cudaStream_t>(stream),
-                                          &launches, g_last_error, sizeof g_last_error);
+  const int status =
+      handle->config.world > 1
+          ? prefill_layer_launch_ep(&handle->prefill, call, &handle->ep_prefill, static_cast<cudaStream_t>(stream),
+                                    &launches, g_last_error, sizeof g_last_error)
+          : prefill_layer_launch(&handle->prefill, call, static_cast<cudaStream_t>(stream), &launches,
+                                 g_last_error, sizeof g_last_error);
   if (status != AIMA_MOE_OK) return status;
   handle->last_stream = static_cast<cudaStream_t>(stream);
   handle->metrics.prefill_calls += 1;
@@ -485,8 +510,15 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
     if (!handle->bound[layer] || handle->host_layers[layer].norm_weight == nullptr)
       return fail(AIMA_MOE_ERR_NOT_BOUND, "layer %u lacks weights or its norm weight", layer);
   }
-  if (handle->config.world != 1)
-    return fail(AIMA_MOE_ERR_UNSUPPORTED, "expert-parallel prefill is not built yet");
+  if (handle->config.world > 1) {
+    if (static_cast<uint64_t>(tokens) * handle->config.world > handle->config.max_prefill_tokens)
+      return fail(AIMA_MOE_ERR_CAPACITY, "tokens x world exceed the prepared global capacity");
+    for (uint32_t peer = 0; peer < handle->config.world; ++peer) {
+      if (handle->ep_peers[peer] == nullptr)
+        return fail(AIMA_MOE_ERR_NOT_BOUND, "expert-parallel peer %u is not connected", peer);
+      handle->ep_prefill.peers[peer] = reinterpret_cast<uint8_t*>(handle->ep_peers[peer]) + kEpExchangeBytes;
+    }
+  }
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
   const size_t bytes = static_cast<size_t>(tokens) * kHidden * 2;
   // x ping-pongs between two workspace buffers; h2 lives in a third.
@@ -515,8 +547,12 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
     call.router_bias = handle->router_bias;
     call.quant_eighths = handle->quant_eighths;
     int launches = 0;
-    const int status = prefill_layer_launch(&handle->prefill, call, cuda_stream, &launches,
-                                            g_last_error, sizeof g_last_error);
+    const int status =
+        handle->config.world > 1
+            ? prefill_layer_launch_ep(&handle->prefill, call, &handle->ep_prefill, cuda_stream, &launches,
+                                      g_last_error, sizeof g_last_error)
+            : prefill_layer_launch(&handle->prefill, call, cuda_stream, &launches, g_last_error,
+                                   sizeof g_last_error);
     if (status != AIMA_MOE_OK) return status;
     handle->metrics.kernel_launches += static_cast<uint64_t>(launches) + 1;
     if (step + 1 == n_layers && target != x_out) {
@@ -623,7 +659,7 @@ AIMA_EXPORT int aima_moe_ep_local_buffer(aima_moe_handle* handle, void** pointer
   if (handle->ep_local == nullptr)
     return fail(AIMA_MOE_ERR_UNSUPPORTED, "the handle was prepared with world = 1");
   *pointer = handle->ep_local;
-  *bytes = kEpExchangeBytes;
+  *bytes = handle->ep_bytes;
   return AIMA_MOE_OK;
 }
 

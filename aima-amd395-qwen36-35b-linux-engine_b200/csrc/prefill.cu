@@ -346,7 +346,7 @@ router_row_norms_kernel(const __nv_bfloat16* __restrict__ router, float* __restr
 constexpr int kPlanWarps = 8;
 
 __global__ void __launch_bounds__(kPlanWarps * 32)
-plan_count_kernel(const int32_t* __restrict__ ids, int routed_rows,
+plan_count_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert_lo, int expert_hi,
                   int32_t* __restrict__ unit_counts) {
   __shared__ int cnt[kPlanWarps][kExperts];
   const int warp = threadIdx.x >> 5;
@@ -358,10 +358,11 @@ plan_count_kernel(const int32_t* __restrict__ ids, int routed_rows,
   if (row0 >= routed_rows) return;
   for (int round = 0; round < kPlanRowsPerWarp / 32; ++round) {
     const int row = row0 + round * 32 + lane;
-    const bool valid = row < routed_rows;
+    // rows routed to experts held by another GPU are not part of this GPU's plan
+    const int e = row < routed_rows ? ids[row] : -1;
+    const bool valid = e >= expert_lo && e < expert_hi;
     const unsigned active = __ballot_sync(0xffffffffu, valid);
     if (valid) {
-      const int e = ids[row];
       const unsigned same = __match_any_sync(active, e);
       if ((same & ((1u << lane) - 1u)) == 0u) cnt[warp][e] += __popc(same);
     }
@@ -422,7 +423,7 @@ plan_scan_kernel(int32_t* __restrict__ unit_counts, int units,
 }
 
 __global__ void __launch_bounds__(kPlanWarps * 32)
-plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows,
+plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert_lo, int expert_hi,
                     const int32_t* __restrict__ unit_prefix,
                     const int32_t* __restrict__ expert_offsets,
                     int32_t* __restrict__ sorted_rows, int32_t* __restrict__ row_position) {
@@ -438,10 +439,10 @@ plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows,
   __syncwarp();
   for (int round = 0; round < kPlanRowsPerWarp / 32; ++round) {
     const int row = row0 + round * 32 + lane;
-    const bool valid = row < routed_rows;
+    const int e = row < routed_rows ? ids[row] : -1;
+    const bool valid = e >= expert_lo && e < expert_hi;
     const unsigned active = __ballot_sync(0xffffffffu, valid);
     if (valid) {
-      const int e = ids[row];
       const unsigned same = __match_any_sync(active, e);
       const int rank = __popc(same & ((1u << lane) - 1u));
       const int pos = next[warp][e] + rank;
@@ -486,7 +487,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
   float slot[kTopK][8];
 #pragma unroll
   for (int s = 0; s < kTopK; ++s) {
-    const int pos = row_position[token * kTopK + s];
+    const int pos = row_position != nullptr ? row_position[token * kTopK + s] : token * kTopK + s;
     unpack8(__ldg(reinterpret_cast<const uint4*>(expert_down + static_cast<size_t>(pos) * kHidden) + t),
             slot[s]);
   }
@@ -520,6 +521,108 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
     reinterpret_cast<uint4*>(dbg_routed + base)[t] =
         make_uint4(packed_routed[0], packed_routed[1], packed_routed[2], packed_routed[3]);
   }
+}
+
+
+// ---------------------------------------------------------------------------
+// Expert-parallel prefill over peer memory (NVLink).  Tokens are sharded T / W
+// per GPU, experts 256 / W per GPU.  Dispatch and combine are the gather and
+// the row return below: plain loads from / stores to the peers' exchange
+// regions; the tensor-core kernels only ever read this GPU's own memory.
+// ---------------------------------------------------------------------------
+struct EpPointers {
+  uint8_t* region[8];
+};
+
+// every rank's routing (ids, weights) into every rank's table, slot `rank`
+__global__ void __launch_bounds__(256)
+ep_publish_routing_kernel(const int32_t* __restrict__ ids, const float* __restrict__ weights, int n,
+                          EpPointers peers, int world, int rank, size_t off_ids, size_t off_weights) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int id = ids[i];
+  const float w = weights[i];
+  for (int q = 0; q < world; ++q) {
+    reinterpret_cast<int32_t*>(peers.region[q] + off_ids)[static_cast<size_t>(rank) * n + i] = id;
+    reinterpret_cast<float*>(peers.region[q] + off_weights)[static_cast<size_t>(rank) * n + i] = w;
+  }
+}
+
+// after the stores of the previous kernel: raise this rank's flag on every GPU
+__global__ void ep_signal_kernel(EpPointers peers, int world, int rank, size_t off_flag, unsigned epoch) {
+  const int q = threadIdx.x;
+  if (q >= world) return;
+  __threadfence_system();
+  unsigned* flag = reinterpret_cast<unsigned*>(peers.region[q] + off_flag) + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flag), "r"(epoch) : "memory");
+}
+
+// bounded wait until every rank's flag in this GPU's region carries `epoch`
+__global__ void ep_wait_kernel(const uint8_t* region, int world, size_t off_flag, unsigned epoch, int* status) {
+  const int q = threadIdx.x;
+  if (q >= world) return;
+  const unsigned* flag = reinterpret_cast<const unsigned*>(region + off_flag) + q;
+  const unsigned long long start = global_timer_ns();
+  unsigned spins = 0;
+  while (true) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v == epoch) break;
+    if ((++spins & 63u) == 0u && global_timer_ns() - start > kWaitBudgetNs) {
+      atomicCAS(status, 0, kStatusTimeoutPeer);
+      break;
+    }
+  }
+}
+
+// dispatch: row `pos` of this GPU's plan <- h2 row of its token, wherever that token lives
+__global__ void __launch_bounds__(256)
+ep_gather_rows_kernel(EpPointers peers, size_t off_h2, int tokens_per_rank,
+                      const int32_t* __restrict__ sorted_rows, const int32_t* __restrict__ expert_offsets,
+                      __nv_bfloat16* __restrict__ gathered) {
+  const int lane = threadIdx.x & 31;
+  const int pos = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (pos >= expert_offsets[kExperts]) return;
+  const int token = sorted_rows[pos] >> 3;
+  const int owner = token / tokens_per_rank;
+  const int local = token - owner * tokens_per_rank;
+  const uint4* src = reinterpret_cast<const uint4*>(peers.region[owner] + off_h2) +
+                     static_cast<size_t>(local) * (kHidden / 8);
+  uint4* dst = reinterpret_cast<uint4*>(gathered + static_cast<size_t>(pos) * kHidden);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i * 32 + lane] = src[i * 32 + lane];
+}
+
+// combine, first half: the weighted expert output of plan row `pos` goes to the GPU that owns
+// its token, at that token's (token, slot) position
+__global__ void __launch_bounds__(256)
+ep_return_rows_kernel(const __nv_bfloat16* __restrict__ expert_down, const int32_t* __restrict__ sorted_rows,
+                      const int32_t* __restrict__ expert_offsets, EpPointers peers, size_t off_return,
+                      int tokens_per_rank) {
+  const int lane = threadIdx.x & 31;
+  const int pos = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (pos >= expert_offsets[kExperts]) return;
+  const int flat = sorted_rows[pos];
+  const int owner = (flat >> 3) / tokens_per_rank;
+  const int local_flat = flat - owner * tokens_per_rank * kTopK;
+  const uint4* src = reinterpret_cast<const uint4*>(expert_down + static_cast<size_t>(pos) * kHidden);
+  uint4* dst = reinterpret_cast<uint4*>(peers.region[owner] + off_return) +
+               static_cast<size_t>(local_flat) * (kHidden / 8);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i * 32 + lane] = src[i * 32 + lane];
+}
+
+// qualification view: weighted expert output rows in flat (token, slot) order
+__global__ void __launch_bounds__(256)
+export_slot_rows_kernel(const __nv_bfloat16* __restrict__ expert_down, const int32_t* __restrict__ row_position,
+                        int routed_rows, __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int flat = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (flat >= routed_rows) return;
+  const uint4* src = reinterpret_cast<const uint4*>(expert_down + static_cast<size_t>(row_position[flat]) * kHidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(flat) * kHidden);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i * 32 + lane] = src[i * 32 + lane];
 }
 
 int set_error(char* error, size_t error_bytes, cudaError_t code, const char* what) {
@@ -673,14 +776,14 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
 
   const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
   const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
-  plan_count_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ws->topk_ids, rows, ws->unit_counts);
+  plan_count_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ws->topk_ids, rows, 0, kExperts, ws->unit_counts);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_count_kernel");
   plan_scan_kernel<<<1, kExperts, 0, stream>>>(ws->unit_counts, units, ws->expert_counts,
                                                ws->expert_offsets, ws->tile_expert, ws->tile_row0,
                                                ws->tile_rows, ws->tile_count, ws->padded_rows);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_scan_kernel");
   plan_scatter_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(
-      ws->topk_ids, rows, ws->unit_counts, ws->expert_offsets, ws->sorted_rows, ws->row_position);
+      ws->topk_ids, rows, 0, kExperts, ws->unit_counts, ws->expert_offsets, ws->sorted_rows, ws->row_position);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_scatter_kernel");
   count += 3;
 
@@ -753,6 +856,165 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
     if (code == cudaSuccess) code = copy(dbg->expert_counts, ws->expert_counts, kExperts * 4);
     if (code == cudaSuccess) code = copy(dbg->expert_offsets, ws->expert_offsets, (kExperts + 1) * 4);
     if (code == cudaSuccess) code = copy(dbg->sorted_rows, ws->sorted_rows, static_cast<size_t>(rows) * 4);
+    if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemcpyAsync debug views");
+    if (dbg->slot_rows != nullptr) {
+      export_slot_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(ws->expert_down, ws->row_position, rows,
+                                                                  static_cast<__nv_bfloat16*>(dbg->slot_rows));
+      if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "export_slot_rows_kernel");
+    }
+  }
+  *launches = count;
+  return AIMA_MOE_OK;
+}
+
+size_t ep_prefill_region_bytes(int capacity_tokens, int world, EpPrefillLayout* layout) {
+  // capacity_tokens = global tokens per call; every rank holds capacity / world of them at most,
+  // but the tables are sized for the global count so that any split fits
+  const size_t rows = static_cast<size_t>(capacity_tokens) * kTopK;
+  size_t cursor = 0;
+  auto take = [&](size_t bytes) { const size_t at = cursor; cursor += (bytes + 255) / 256 * 256; return at; };
+  EpPrefillLayout l{};
+  l.off_flags_routing = take(64);
+  l.off_flags_returned = take(64);
+  l.off_ids = take(rows * 4);
+  l.off_weights = take(rows * 4);
+  l.off_h2 = take(static_cast<size_t>(capacity_tokens) * kHidden * 2);
+  l.off_return = take(rows * kHidden * 2);
+  l.bytes = cursor;
+  (void)world;
+  if (layout != nullptr) *layout = l;
+  return cursor;
+}
+
+int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPrefill* ep,
+                            cudaStream_t stream, int* launches, char* error, size_t error_bytes) {
+  const int T_loc = call.tokens;
+  const int W = ep->world;
+  const int T = T_loc * W;
+  const int rows_loc = T_loc * kTopK;
+  const int rows = T * kTopK;
+  const aima_moe_debug_views* dbg = call.debug;
+  const EpPrefillLayout& L = ep->layout;
+  EpPointers peers{};
+  for (int q = 0; q < W; ++q) peers.region[q] = ep->peers[q];
+  uint8_t* mine = ep->peers[ep->rank];
+  const unsigned epoch = ++ep->epoch;
+  int count = 0;
+  cudaError_t code;
+
+  // 1. route this rank's tokens (certified router) and stage its h2 rows where peers can read them
+  GroupedGemm r{};
+  r.max_tiles = (T_loc + kTileRows - 1) / kTileRows; r.dense_rows = T_loc;
+  r.a = static_cast<const __nv_bfloat16*>(call.h2); r.lda = kHidden; r.k = kHidden;
+  r.b0 = call.layer.router; r.n = kExperts; r.c_f32 = ws->approx_logits; r.ldc = kExperts;
+  TcExtra rx{};
+  rx.status = ws->status; rx.sm_count = ws->sm_count; rx.a_rows = static_cast<uint64_t>(T_loc); rx.experts_in_b = 1;
+  if ((code = launch_grouped_gemm_tc(kGemmPlainF32, r, rx, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "router logits product");
+  prefill_router_certified_kernel<<<(T_loc + kCertWarps - 1) / kCertWarps, kCertWarps * 32, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(call.h2), call.layer.router, call.layer.shared_gate,
+      ws->approx_logits, call.router_row_norms, call.router_bias, call.quant_eighths, T_loc, ws->topk_ids,
+      ws->topk_scores, ws->topk_weights, ws->shared_sigmoid,
+      dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "prefill_router_certified_kernel");
+  count += 2;
+  code = cudaMemcpyAsync(mine + L.off_h2, call.h2, static_cast<size_t>(T_loc) * kHidden * 2,
+                         cudaMemcpyDeviceToDevice, stream);
+  if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemcpyAsync h2 staging");
+
+  // 2. all-gather of the routing tables by peer stores, then flags
+  ep_publish_routing_kernel<<<(rows_loc + 255) / 256, 256, 0, stream>>>(
+      ws->topk_ids, ws->topk_weights, rows_loc, peers, W, ep->rank, L.off_ids, L.off_weights);
+  ep_signal_kernel<<<1, 32, 0, stream>>>(peers, W, ep->rank, L.off_flags_routing, epoch);
+  ep_wait_kernel<<<1, 32, 0, stream>>>(mine, W, L.off_flags_routing, epoch, ws->status);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "routing exchange");
+  count += 3;
+  const int32_t* ids_all = reinterpret_cast<const int32_t*>(mine + L.off_ids);
+  const float* weights_all = reinterpret_cast<const float*>(mine + L.off_weights);
+
+  // 3. plan over the global rows that land on this GPU's experts
+  const int expert_lo = ep->rank * call.experts_local;
+  const int expert_hi = expert_lo + call.experts_local;
+  const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
+  const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
+  plan_count_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ids_all, rows, expert_lo, expert_hi, ws->unit_counts);
+  plan_scan_kernel<<<1, kExperts, 0, stream>>>(ws->unit_counts, units, ws->expert_counts, ws->expert_offsets,
+                                               ws->tile_expert, ws->tile_row0, ws->tile_rows, ws->tile_count,
+                                               ws->padded_rows);
+  plan_scatter_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ids_all, rows, expert_lo, expert_hi,
+                                                                  ws->unit_counts, ws->expert_offsets,
+                                                                  ws->sorted_rows, ws->row_position);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "dispatch plan");
+  count += 3;
+
+  // 4. dispatch: pull the rows over NVLink into expert order
+  ep_gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(peers, L.off_h2, T_loc, ws->sorted_rows,
+                                                            ws->expert_offsets, ws->gathered);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "ep_gather_rows_kernel");
+  ++count;
+
+  // 5. the local experts' products
+  GroupedGemm g{};
+  g.tile_expert = ws->tile_expert; g.tile_row0 = ws->tile_row0; g.tile_rows = ws->tile_rows;
+  g.tile_count = ws->tile_count; g.max_tiles = max_tiles_for(T); g.dense_rows = 0;
+  g.expert_base = expert_lo;
+  g.a = ws->gathered; g.lda = kHidden; g.k = kHidden;
+  g.b0 = call.layer.expert_gate_up; g.b_expert_stride = static_cast<size_t>(2 * kInter) * kHidden;
+  g.n = kInter; g.c = ws->expert_act; g.ldc = kInter;
+  TcExtra extra{};
+  extra.status = ws->status; extra.sm_count = ws->sm_count;
+  extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK; extra.experts_in_b = call.experts_local;
+  if ((code = launch_grouped_gemm_tc(kGemmExpertGateUp, g, extra, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm expert gate_up");
+  g.a = ws->expert_act; g.lda = kInter; g.k = kInter;
+  g.b0 = call.layer.expert_down; g.b_expert_stride = static_cast<size_t>(kHidden) * kInter;
+  g.n = kHidden; g.c = ws->expert_down; g.ldc = kHidden;
+  g.row_scale = weights_all; g.sorted_rows = ws->sorted_rows;
+  if ((code = launch_grouped_gemm_tc(kGemmExpertDown, g, extra, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm expert down");
+  count += 2;
+
+  // 6. combine, first half: rows back to the GPUs that own their tokens, then flags
+  ep_return_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(ws->expert_down, ws->sorted_rows, ws->expert_offsets,
+                                                            peers, L.off_return, T_loc);
+  ep_signal_kernel<<<1, 32, 0, stream>>>(peers, W, ep->rank, L.off_flags_returned, epoch);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "row return");
+  count += 2;
+
+  // 7. shared expert for this rank's tokens (weights are replicated) while rows travel
+  GroupedGemm s{};
+  s.max_tiles = (T_loc + kTileRows - 1) / kTileRows; s.dense_rows = T_loc;
+  s.a = static_cast<const __nv_bfloat16*>(call.h2); s.lda = kHidden; s.k = kHidden;
+  s.b0 = call.layer.shared_gate_proj; s.b1 = call.layer.shared_up_proj;
+  s.n = kSharedInter; s.c = ws->shared_act; s.ldc = kSharedInter;
+  extra.a_rows = static_cast<uint64_t>(T_loc); extra.experts_in_b = 1;
+  if ((code = launch_grouped_gemm_tc(kGemmSharedGateUp, s, extra, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm shared gate_up");
+  s.a = ws->shared_act; s.lda = kSharedInter; s.k = kSharedInter;
+  s.b0 = call.layer.shared_down_proj; s.b1 = nullptr;
+  s.n = kHidden; s.c = ws->shared_scaled; s.ldc = kHidden; s.row_scale = ws->shared_sigmoid;
+  extra.a_rows = static_cast<uint64_t>(ws->capacity);
+  if ((code = launch_grouped_gemm_tc(kGemmSharedDown, s, extra, stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm shared down");
+  count += 2;
+
+  // 8. combine, second half: wait for all eight rows of every local token, sum, add
+  ep_wait_kernel<<<1, 32, 0, stream>>>(mine, W, L.off_flags_returned, epoch, ws->status);
+  combine_kernel<<<T_loc, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(mine + L.off_return), nullptr,
+                                            ws->shared_scaled, static_cast<const __nv_bfloat16*>(call.residual),
+                                            static_cast<__nv_bfloat16*>(call.out),
+                                            dbg ? static_cast<__nv_bfloat16*>(dbg->routed) : nullptr);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "combine_kernel");
+  count += 2;
+  if (dbg != nullptr) {
+    auto copy = [&](void* dst, const void* src, size_t bytes) {
+      if (dst != nullptr) return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream);
+      return cudaSuccess;
+    };
+    code = copy(dbg->topk_ids, ws->topk_ids, static_cast<size_t>(rows_loc) * 4);
+    if (code == cudaSuccess) code = copy(dbg->topk_scores, ws->topk_scores, static_cast<size_t>(rows_loc) * 4);
+    if (code == cudaSuccess) code = copy(dbg->shared_scaled, ws->shared_scaled, static_cast<size_t>(T_loc) * kHidden * 2);
+    if (code == cudaSuccess) code = copy(dbg->expert_counts, ws->expert_counts, kExperts * 4);
     if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemcpyAsync debug views");
   }
   *launches = count;

@@ -48,6 +48,25 @@ struct PrefillWorkspace {
   __nv_bfloat16* stack_h2 = nullptr;
 };
 
+// Exchange region of one GPU for expert-parallel prefill (inside its IPC-shared allocation).
+struct EpPrefillLayout {
+  size_t off_flags_routing;   // u32[8]  rank q has published its routing for epoch e
+  size_t off_flags_returned;  // u32[8]  rank q has returned all rows it computed for epoch e
+  size_t off_ids;             // i32 [T * 8]  routing ids of all ranks, rank-major
+  size_t off_weights;         // f32 [T * 8]
+  size_t off_h2;              // bf16 [T_loc, 2048] this rank's tokens, readable by peers
+  size_t off_return;          // bf16 [T_loc * 8, 2048] weighted expert outputs of this rank's tokens
+  size_t bytes;
+};
+
+struct EpPrefill {
+  int world = 1;
+  int rank = 0;
+  uint8_t* peers[8] = {};     // every rank's region (own included)
+  EpPrefillLayout layout{};
+  unsigned epoch = 0;         // calls so far; all ranks call in lockstep
+};
+
 struct PrefillCall {
   LayerPtrs layer;
   const void* h2;
@@ -74,6 +93,12 @@ cudaError_t launch_router_row_norms(const __nv_bfloat16* router, float* norms, c
 int prefill_layer_launch(PrefillWorkspace* workspace, const PrefillCall& call,
                          cudaStream_t stream, int* launches, char* error,
                          size_t error_bytes);
+
+size_t ep_prefill_region_bytes(int capacity_tokens, int world, EpPrefillLayout* layout);
+
+// Expert-parallel variant: call.tokens = this rank's tokens; all ranks call in lockstep.
+int prefill_layer_launch_ep(PrefillWorkspace* workspace, const PrefillCall& call, EpPrefill* ep,
+                            cudaStream_t stream, int* launches, char* error, size_t error_bytes);
 
 inline int max_tiles_for(int tokens) {
   return tokens * kTopK / kTileRows + kExperts;

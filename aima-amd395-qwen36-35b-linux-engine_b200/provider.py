@@ -66,7 +66,7 @@ class DebugViews(ctypes.Structure):
         ("h2", c_void_p), ("router_logits", c_void_p), ("topk_ids", c_void_p),
         ("topk_scores", c_void_p), ("topk_weights", c_void_p), ("shared_scaled", c_void_p),
         ("routed", c_void_p), ("expert_counts", c_void_p), ("expert_offsets", c_void_p),
-        ("sorted_rows", c_void_p), ("slot_dots", c_void_p),
+        ("sorted_rows", c_void_p), ("slot_dots", c_void_p), ("slot_rows", c_void_p),
     ]
 
 
@@ -269,7 +269,8 @@ class MoeProvider:
         self.lib.check(self.lib.aima_moe_set_router_hooks(self.handle, _ptr(bias), int(quantize_eighths)))
 
     # -- debug views ---------------------------------------------------------
-    def make_debug(self, tokens: int, prefill: bool, with_logits: bool = True) -> tuple[DebugViews, dict[str, Any]]:
+    def make_debug(self, tokens: int, prefill: bool, with_logits: bool = True,
+                   with_slot_rows: bool = False) -> tuple[DebugViews, dict[str, Any]]:
         torch = self._torch
         dev = torch.device("cuda", torch.cuda.current_device())
         t = {
@@ -287,6 +288,8 @@ class MoeProvider:
             t["expert_counts"] = torch.empty(EXPERTS, dtype=torch.int32, device=dev)
             t["expert_offsets"] = torch.empty(EXPERTS + 1, dtype=torch.int32, device=dev)
             t["sorted_rows"] = torch.empty(tokens * TOP_K, dtype=torch.int32, device=dev)
+        if prefill and with_slot_rows:
+            t["slot_rows"] = torch.empty(tokens * TOP_K, HIDDEN, dtype=torch.bfloat16, device=dev)
         if not with_logits:
             del t["router_logits"]      # prefill then runs the production (certified) router
         views = DebugViews()

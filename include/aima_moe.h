@@ -125,6 +125,8 @@ typedef struct aima_moe_debug_views {
   void* sorted_rows;     /* i32  [8T]      prefill only                          */
   void* slot_dots;       /* f32  [8,2048]  decode only: per rank slot, the down
                             product act . Wd before the routing weight           */
+  void* slot_rows;       /* bf16 [8T,2048] prefill only (single GPU): weighted expert
+                            outputs in (token, slot) order                       */
 } aima_moe_debug_views;
 
 /* Counters in the spirit of NativeMoePrefillMetrics
@@ -260,10 +262,15 @@ int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics* metrics);
  * products of the chosen experts it holds, stores them into the peers' buffers
  * over NVLink and sums all eight in slot order, so every rank ends with the same
  * bits as a single GPU.  All ranks must launch the same layers in the same order.
+ * Prefill: tokens are sharded over the ranks (aima_moe_prefill_launch takes this
+ * rank's tokens; `max_prefill_tokens` is the GLOBAL capacity, tokens x world must
+ * fit).  Each rank routes its tokens, the routing tables are all-gathered by peer
+ * stores, every rank plans the rows that land on its experts, pulls their
+ * activations from the owners (dispatch), runs its experts, and stores the
+ * weighted rows back to the owners (combine).
  * A host that owns a symmetric heap may substitute this rank's own buffer with
- * aima_moe_ep_connect(handle, own rank, NULL, pointer) (AIMA_MOE_EP_BUFFER_BYTES,
- * zero-filled). */
-#define AIMA_MOE_EP_BUFFER_BYTES 262144
+ * aima_moe_ep_connect(handle, own rank, NULL, pointer); it must be zero-filled and
+ * as large as aima_moe_ep_local_buffer reports. */
 int aima_moe_ep_local_buffer(aima_moe_handle* handle, void** pointer, uint64_t* bytes);
 int aima_moe_ep_export(aima_moe_handle* handle, void* ipc_handle_64_bytes);
 int aima_moe_ep_connect(aima_moe_handle* handle, uint32_t peer, const void* ipc_handle_64_bytes,

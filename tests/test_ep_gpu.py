@@ -81,6 +81,90 @@ def test_expert_parallel_rank_alone_matches_single_gpu(package, gpu_layers, synt
             provider.release()
 
 
+def test_expert_parallel_prefill_rank_alone_matches_single_gpu(package, gpu_layers, synth):
+    """World of two on one GPU, one rank at a time: the peer's routing table, its staged
+    activations, its flags and the rows it would return are written beforehand from a single-GPU
+    run; the rank's output rows and the rows it returns must equal the single-GPU bits."""
+    import ctypes
+
+    device = torch.device("cuda", 0)
+    weights = gpu_layers(0)["cuda"]
+    total, per_rank = 192, 96
+    h2 = synth.activations(SEED + 61, total, "input", 0).to(device)
+    resid = synth.activations(SEED + 61, total, "residual", 0).to(device)
+
+    single = package.MoeProvider(layers=1, max_prefill_tokens=total)
+    try:
+        single.bind_layer(0, weights)
+        views, ref = single.make_debug(total, prefill=True, with_logits=False, with_slot_rows=True)
+        want = single.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, debug=views)
+        single.sync_metrics()
+        want = want.clone()
+        ref = {k: v.clone() for k, v in ref.items()}
+    finally:
+        single.release()
+    ids_all = ref["topk_ids"].reshape(-1)                       # [total * 8]
+    weights_all = ref["topk_weights"].float().reshape(-1)
+
+    for rank in (0, 1):
+        lo, hi = rank * 128, rank * 128 + 128
+        t0, t1 = rank * per_rank, (rank + 1) * per_rank
+        other = 1 - rank
+        o0, o1 = other * per_rank, (other + 1) * per_rank
+        provider = package.MoeProvider(layers=1, max_prefill_tokens=total, world=2, rank=rank)
+        try:
+            slab = dict(weights)
+            slab["expert_gate_up"] = weights["expert_gate_up"][lo:hi].contiguous()
+            slab["expert_down"] = weights["expert_down"][lo:hi].contiguous()
+            provider.bind_layer(0, slab)
+            _, region_bytes = provider.ep_local_buffer()
+            own = torch.zeros(region_bytes, dtype=torch.uint8, device=device)
+            peer = torch.zeros(region_bytes, dtype=torch.uint8, device=device)
+            # region layout (bytes after the 262144-byte decode part): flags 256 + 256,
+            # ids [total*8] i32, weights [total*8] f32, h2 [total, 2048] bf16, return rows [total*8, 2048] bf16
+            base = 262144
+            rows = total * 8
+            def span(n):
+                nonlocal cursor
+                at = cursor
+                cursor += (n + 255) // 256 * 256
+                return at
+            cursor = base
+            off_flag_routing, off_flag_returned = span(64), span(64)
+            off_ids, off_w = span(rows * 4), span(rows * 4)
+            off_h2, off_ret = span(total * H * 2), span(rows * H * 2)
+            assert cursor == region_bytes
+            def view(buf, off, count, dtype):
+                return buf[off:off + count * torch.empty((), dtype=dtype).element_size()].view(dtype)
+            # what the peer would have left in this rank's region before its flags went up
+            view(own, off_flag_routing, 8, torch.int32)[other] = 1
+            view(own, off_flag_returned, 8, torch.int32)[other] = 1
+            view(own, off_ids, rows, torch.int32)[other * per_rank * 8:(other + 1) * per_rank * 8] = ids_all[o0 * 8:o1 * 8]
+            view(own, off_w, rows, torch.float32)[other * per_rank * 8:(other + 1) * per_rank * 8] = weights_all[o0 * 8:o1 * 8]
+            ret = view(own, off_ret, per_rank * 8 * H, torch.bfloat16).view(per_rank * 8, H)
+            mine_ids = ids_all[t0 * 8:t1 * 8]
+            remote = (mine_ids < lo) | (mine_ids >= hi)
+            ret[remote] = ref["slot_rows"][t0 * 8:t1 * 8][remote]
+            # the peer's staged activations, which this rank's dispatch reads
+            view(peer, off_h2, per_rank * H, torch.bfloat16).view(per_rank, H).copy_(h2[o0:o1])
+            provider.ep_connect(rank, pointer=own.data_ptr())
+            provider.ep_connect(other, pointer=peer.data_ptr())
+            out = provider.launch_selected_moe(post_attention=h2[t0:t1].contiguous(),
+                                               residual_hidden=resid[t0:t1].contiguous(), model_layer=0)
+            provider.sync_metrics()
+            assert torch.equal(out, want[t0:t1]), f"rank {rank}"
+            # rows this rank computed for the peer's tokens, as left in the peer's return area
+            sent = view(peer, off_ret, per_rank * 8 * H, torch.bfloat16).view(per_rank * 8, H)
+            peer_ids = ids_all[o0 * 8:o1 * 8]
+            local = (peer_ids >= lo) & (peer_ids < hi)
+            assert torch.equal(sent[local], ref["slot_rows"][o0 * 8:o1 * 8][local]), f"rank {rank} returned rows"
+            assert int(view(peer, off_flag_routing, 8, torch.int32)[rank]) == 1
+            assert int(view(peer, off_flag_returned, 8, torch.int32)[rank]) == 1
+        finally:
+            provider.release()
+    del ctypes
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -120,6 +204,20 @@ def _rank_main(rank: int, world: int, port: int, results) -> None:
             x, y = y, x
         dist.barrier()
         provider.release()
+        # prefill: 128 tokens per rank through layer 0
+        prefill = package.MoeProvider(layers=1, max_prefill_tokens=128 * world, world=world, rank=rank)
+        prefill.bind_layer(0, keep[0])
+        prefill.ep_connect_all()
+        h2_all = synth.activations(SEED + 77, 128 * world, "input", 0)
+        resid_all = synth.activations(SEED + 77, 128 * world, "residual", 0)
+        dist.barrier()
+        out = prefill.launch_selected_moe(post_attention=h2_all[rank * 128:(rank + 1) * 128].to(device),
+                                          residual_hidden=resid_all[rank * 128:(rank + 1) * 128].to(device),
+                                          model_layer=0)
+        prefill.sync_metrics()
+        dist.barrier()
+        outputs.append(out.cpu().clone())
+        prefill.release()
         results.put((rank, outputs))
     finally:
         dist.destroy_process_group()
@@ -147,3 +245,11 @@ def test_expert_parallel_two_gpus_match_the_oracle(oracle, synth):
             expected = oracle.decode_layer(expected, layer)["out"]
         assert torch.equal(got[0][step], expected), f"rank 0 step {step}"
         assert torch.equal(got[1][step], expected), f"rank 1 step {step}"
+    # prefill rows of both ranks against the oracle (same tolerance as the single-GPU prefill tests)
+    h2_all = synth.activations(SEED + 77, 128 * world, "input", 0)
+    resid_all = synth.activations(SEED + 77, 128 * world, "residual", 0)
+    select = [0, 5, 127, 128, 200, 255]
+    want = oracle.prefill_layer(h2_all, resid_all, layers[0], select=select)
+    both = torch.cat([got[0][3], got[1][3]])
+    ulp = want["out"].float().abs() * 2.0 ** -7
+    assert ((both[select].float() - want["out"].float()).abs() <= ulp + 2.0e-2).all()
