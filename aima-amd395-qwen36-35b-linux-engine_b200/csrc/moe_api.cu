@@ -709,6 +709,13 @@ AIMA_EXPORT int aima_moe_set_tracing(aima_moe_handle* handle, int enabled) {
   std::lock_guard<std::mutex> lock(handle->mutex);
   handle->tracing = enabled != 0;
   handle->traced_layers = 0;
+  handle->ep_prefill.trace = handle->tracing;
+  if (handle->tracing && handle->config.world > 1 && handle->ep_prefill.stage_events[0] == nullptr) {
+    for (int i = 0; i <= kEpPrefillStages; ++i) {
+      const cudaError_t error = cudaEventCreate(&handle->ep_prefill.stage_events[i]);
+      if (error != cudaSuccess) return fail_cuda(error, "cudaEventCreate prefill stage event");
+    }
+  }
   return AIMA_MOE_OK;
 }
 
@@ -729,8 +736,30 @@ AIMA_EXPORT int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t*
   return AIMA_MOE_OK;
 }
 
+AIMA_EXPORT int aima_moe_read_ep_prefill_stages(aima_moe_handle* handle, float* stage_ms, uint32_t capacity,
+                                                uint32_t* written) {
+  if (handle == nullptr || stage_ms == nullptr || written == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "stage timing argument is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  *written = 0;
+  if (!handle->ep_prefill.trace || handle->ep_prefill.stage_events[0] == nullptr || handle->ep_prefill.epoch == 0)
+    return AIMA_MOE_OK;
+  cudaError_t error = cudaStreamSynchronize(handle->last_stream);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaStreamSynchronize");
+  for (uint32_t i = 0; i < static_cast<uint32_t>(kEpPrefillStages) && i < capacity; ++i) {
+    error = cudaEventElapsedTime(stage_ms + i, handle->ep_prefill.stage_events[i],
+                                 handle->ep_prefill.stage_events[i + 1]);
+    if (error != cudaSuccess) return fail_cuda(error, "cudaEventElapsedTime prefill stage");
+    *written = i + 1;
+  }
+  return AIMA_MOE_OK;
+}
+
 AIMA_EXPORT int aima_moe_release(aima_moe_handle* handle) {
   if (handle == nullptr) return AIMA_MOE_OK;
+  for (int i = 0; i < 8; ++i) {
+    if (handle->ep_prefill.stage_events[i] != nullptr) cudaEventDestroy(handle->ep_prefill.stage_events[i]);
+  }
   for (int peer = 0; peer < 8; ++peer) {
     if (handle->ep_ipc_opened[peer] != nullptr) cudaIpcCloseMemHandle(handle->ep_ipc_opened[peer]);
   }

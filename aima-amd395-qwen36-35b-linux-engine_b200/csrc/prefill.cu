@@ -901,6 +901,12 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   const unsigned epoch = ++ep->epoch;
   int count = 0;
   cudaError_t code;
+  int mark_index = 0;
+  auto mark = [&]() {
+    if (ep->trace && ep->stage_events[mark_index] != nullptr) cudaEventRecord(ep->stage_events[mark_index], stream);
+    ++mark_index;
+  };
+  mark();
 
   // 1. route this rank's tokens (certified router) and stage its h2 rows where peers can read them
   GroupedGemm r{};
@@ -922,6 +928,7 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
                          cudaMemcpyDeviceToDevice, stream);
   if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemcpyAsync h2 staging");
 
+  mark();
   // 2. all-gather of the routing tables by peer stores, then flags
   ep_publish_routing_kernel<<<(rows_loc + 255) / 256, 256, 0, stream>>>(
       ws->topk_ids, ws->topk_weights, rows_loc, peers, W, ep->rank, L.off_ids, L.off_weights);
@@ -932,6 +939,7 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   const int32_t* ids_all = reinterpret_cast<const int32_t*>(mine + L.off_ids);
   const float* weights_all = reinterpret_cast<const float*>(mine + L.off_weights);
 
+  mark();
   // 3. plan over the global rows that land on this GPU's experts
   const int expert_lo = ep->rank * call.experts_local;
   const int expert_hi = expert_lo + call.experts_local;
@@ -947,12 +955,14 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "dispatch plan");
   count += 3;
 
+  mark();
   // 4. dispatch: pull the rows over NVLink into expert order
   ep_gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(peers, L.off_h2, T_loc, ws->sorted_rows,
                                                             ws->expert_offsets, ws->gathered);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "ep_gather_rows_kernel");
   ++count;
 
+  mark();
   // 5. the local experts' products
   GroupedGemm g{};
   g.tile_expert = ws->tile_expert; g.tile_row0 = ws->tile_row0; g.tile_rows = ws->tile_rows;
@@ -974,6 +984,7 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
     return set_error(error, error_bytes, code, "grouped gemm expert down");
   count += 2;
 
+  mark();
   // 6. combine, first half: rows back to the GPUs that own their tokens, then flags
   ep_return_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(ws->expert_down, ws->sorted_rows, ws->expert_offsets,
                                                             peers, L.off_return, T_loc);
@@ -981,6 +992,7 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "row return");
   count += 2;
 
+  mark();
   // 7. shared expert for this rank's tokens (weights are replicated) while rows travel
   GroupedGemm s{};
   s.max_tiles = (T_loc + kTileRows - 1) / kTileRows; s.dense_rows = T_loc;
@@ -1006,6 +1018,7 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
                                             dbg ? static_cast<__nv_bfloat16*>(dbg->routed) : nullptr);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "combine_kernel");
   count += 2;
+  mark();
   if (dbg != nullptr) {
     auto copy = [&](void* dst, const void* src, size_t bytes) {
       if (dst != nullptr) return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream);

@@ -65,7 +65,11 @@ struct EpPrefill {
   uint8_t* peers[8] = {};     // every rank's region (own included)
   EpPrefillLayout layout{};
   unsigned epoch = 0;         // calls so far; all ranks call in lockstep
+  // optional stage timing (tracing): events at the 8 stage boundaries of the last call
+  cudaEvent_t stage_events[8] = {};
+  bool trace = false;
 };
+constexpr int kEpPrefillStages = 7;   // route, routing exchange, plan, dispatch, experts, return, shared+wait+combine
 
 struct PrefillCall {
   LayerPtrs layer;

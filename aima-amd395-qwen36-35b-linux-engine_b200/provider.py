@@ -105,6 +105,8 @@ EXPORTS = [
     ("aima_moe_ep_local_buffer", c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_uint64)]),
     ("aima_moe_ep_export", c_int, [c_void_p, c_void_p]),
     ("aima_moe_ep_connect", c_int, [c_void_p, c_uint32, c_void_p, c_void_p]),
+    ("aima_moe_read_ep_prefill_stages", c_int,
+     [c_void_p, ctypes.POINTER(c_float), c_uint32, ctypes.POINTER(c_uint32)]),
     ("aima_moe_set_tracing", c_int, [c_void_p, c_int]),
     ("aima_moe_read_decode_timeline", c_int,
      [c_void_p, ctypes.POINTER(c_uint64), c_uint32, ctypes.POINTER(c_uint32)]),
@@ -404,6 +406,16 @@ class MoeProvider:
         self.lib.check(self.lib.aima_moe_gemm_bf16_launch(self.handle, _ptr(a), _ptr(b), _ptr(d), m, n, k,
                                                           _stream(torch)))
         return d
+
+    EP_PREFILL_STAGES = ("route", "routing_exchange", "plan", "dispatch", "experts", "row_return",
+                         "shared_wait_combine")
+
+    def ep_prefill_stages(self) -> dict[str, float]:
+        """Milliseconds per stage of the last traced expert-parallel prefill call."""
+        buffer = (c_float * 7)()
+        written = c_uint32()
+        self.lib.check(self.lib.aima_moe_read_ep_prefill_stages(self.handle, buffer, 7, ctypes.byref(written)))
+        return {name: float(buffer[i]) for i, name in enumerate(self.EP_PREFILL_STAGES[: written.value])}
 
     def sync_metrics(self) -> Metrics:
         metrics = Metrics()

@@ -341,11 +341,81 @@ def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing
             "flop_per_layer": tokens * PREFILL_FLOP_PER_TOKEN, "kernel_launches_per_layer": int(per_call)}
 
 
+def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) -> None:
+    """One prefill layer with tokens sharded over `world` GPUs (BASELINE config 3 per bucket)."""
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+
+    package = load_package()
+    synth = package.synth
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=device)
+    per_rank_experts = 256 // world
+    tokens_local = args.tokens // world
+    provider = package.MoeProvider(layers=1, max_prefill_tokens=args.tokens, world=world, rank=rank)
+    weights = synth.layer_weights_cuda_fast(SEED, 0, device, rank * per_rank_experts, (rank + 1) * per_rank_experts)
+    provider.bind_layer(0, weights)
+    provider.ep_connect_all(dist.new_group(backend="gloo"))
+    if args.routing == "zipf":
+        provider.set_router_hooks(synth.zipf_router_bias(SEED).to(device), False)
+    generator = torch.Generator(device=device).manual_seed(SEED + rank)
+    h2 = torch.randn(tokens_local, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
+    resid = torch.randn(tokens_local, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
+    out = torch.empty_like(resid)
+    steps = max(args.steps, 1)
+    for _ in range(3):
+        provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+    provider.sync_metrics()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+    stop.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    provider.sync_metrics()
+    ms = start.elapsed_time(stop) / steps
+    provider.set_tracing(True)
+    provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+    stages = provider.ep_prefill_stages()
+    times = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms = float(times.item())
+    if rank == 0:
+        peak, kind = measured_tensor_peak()
+        tflops = args.tokens * PREFILL_FLOP_PER_TOKEN / (ms * 1.0e-3) / 1.0e12
+        exposed = sum(stages.get(name, 0.0) for name in ("routing_exchange", "dispatch", "row_return"))
+        print(json.dumps({
+            "metric": "moe_prefill_tokens_per_second", "value": args.tokens / (ms * 1.0e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"prefill_T{args.tokens}_1layer_{args.routing} (BASELINE config 3 bucket)",
+                       "routing": args.routing, "tokens_per_gpu": tokens_local,
+                       "multi_gpu": f"expert parallel, {per_rank_experts} experts per GPU, dispatch by peer loads, "
+                                    "combine by peer stores over NVLink"},
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak * world, "unit": "TFLOP/s",
+                         "frac": tflops / (peak * world), "traffic": None, "peak_source": kind},
+            "stage_ms_rank0": stages, "exposed_communication_ms_rank0": exposed,
+        }))
+    provider.release()
+    dist.destroy_process_group()
+
+
 def run_prefill(args) -> None:
     """`--workload prefill`: the one-layer T = 8192 prefill line (profiling aid and second headline)."""
     import torch
     from __graft_entry__ import load_package
 
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        run_prefill_expert_parallel(args, world, int(os.environ.get("RANK", "0")),
+                                    int(os.environ.get("LOCAL_RANK", "0")))
+        return
     package = load_package()
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)

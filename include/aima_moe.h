@@ -289,6 +289,14 @@ int aima_moe_set_tracing(aima_moe_handle* handle, int enabled);
 int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t* stamps_ns,
                                   uint32_t capacity, uint32_t* written);
 
+/* With tracing on and world > 1: milliseconds of the AIMA_MOE_EP_PREFILL_STAGES
+ * stages of the last expert-parallel prefill call on this rank (route, routing
+ * exchange, plan, dispatch, expert products, row return, shared expert + wait +
+ * combine), from CUDA events on the call's stream. */
+#define AIMA_MOE_EP_PREFILL_STAGES 7
+int aima_moe_read_ep_prefill_stages(aima_moe_handle* handle, float* stage_ms, uint32_t capacity,
+                                    uint32_t* written);
+
 /* Device bytes prepare() would allocate for this configuration. */
 int aima_moe_query_workspace(const aima_moe_config* config, uint64_t* bytes);
 
