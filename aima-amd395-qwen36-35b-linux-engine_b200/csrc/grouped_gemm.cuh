@@ -42,6 +42,10 @@ struct GroupedGemm {
   int dense_rows;
   const __nv_bfloat16* a;      // [rows, k]
   int lda;
+  // kGemmExpertGateUp on the tensor cores only: when non-null, tile row r is row
+  // (sorted_rows[row] >> 3) of this [tokens, k] matrix, gathered straight into shared memory
+  // (no materialised copy of the routed rows); `a` is then unused
+  const __nv_bfloat16* gather_src;
   int k;
   const __nv_bfloat16* b0;     // gate (or only) weight matrix / expert slab
   const __nv_bfloat16* b1;     // separate "up" matrix (shared expert) or nullptr

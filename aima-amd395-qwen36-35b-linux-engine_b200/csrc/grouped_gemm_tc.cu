@@ -15,6 +15,8 @@
 //   warp 1   one thread issues tcgen05.mma (M128 N256 K16, 4 per K block) and
 //            commits to the ring's "empty" barriers / the accumulator's "full" barrier
 //   warp 2   allocates and frees the 512 tensor-memory columns
+//   warps 2-3 (gate_up with fused dispatch only) gather the tile's 128 activation rows by token
+//            index with 16-byte cp.async copies, writing the 128-byte swizzle pattern themselves
 //   warps 4-7 epilogue: tcgen05.ld 32 rows x 32 columns per warp, SwiGLU or
 //            scaling, BF16 stores
 // Every mbarrier wait is bounded; on expiry the block sets the status word,
@@ -132,7 +134,17 @@ __device__ __forceinline__ void pack_store_32(__nv_bfloat16* dst, const float* v
   }
 }
 
-template <int MODE>
+constexpr int kGatherThreads = 64;     // warps 2 and 3
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <int MODE, bool kGather = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) {
   constexpr bool kDual = (MODE == kGemmExpertGateUp || MODE == kGemmSharedGateUp);
@@ -154,7 +166,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), kGather ? 1 + kGatherThreads : 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -213,8 +225,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kStageABytes;
-          mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-          tma_load_2d(a_dst, &maps.a, kb * kBK, row0, full_bar(stage));
+          mbar_arrive_expect_tx(full_bar(stage), kGather ? kStageBBytes : kStageBytes);
+          if (!kGather) tma_load_2d(a_dst, &maps.a, kb * kBK, row0, full_bar(stage));
           tma_load_2d(b_dst, &maps.b0, kb * kBK, b0_row, full_bar(stage));
           tma_load_2d(b_dst + kStageBBytes / 2, kDual ? &maps.b1 : &maps.b0, kb * kBK, b1_row, full_bar(stage));
           ++issued;
@@ -232,6 +244,49 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
         }
       }
     }
+  } else if (kGather && (warp == 2 || warp == 3)) {
+    // ------------------------------ A-row gather -------------------------------
+    // thread t copies rows t and t + 64 of the tile: 8 chunks of 16 bytes per row and K block,
+    // chunk c of row r lands at chunk position c ^ (r & 7) of the row (the 128-byte swizzle)
+    const int lt = (warp - 2) * 32 + lane;
+    int stage = 0;
+    uint32_t phase = 0;
+    int committed = 0;             // groups committed so far
+    int arrive_stage = 0;          // stage of the oldest group not yet signalled
+    bool alive = true;
+    auto signal_oldest = [&]() {
+      fence_async_proxy();
+      mbar_arrive(full_bar(arrive_stage));
+      if (++arrive_stage == kStages) arrive_stage = 0;
+    };
+    for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x) {
+      int tile, chunk, expert, row0, rows;
+      unit_tile(unit, tile, chunk, expert, row0, rows);
+      const int r0 = lt, r1 = lt + kGatherThreads;
+      const int t0 = g.sorted_rows[row0 + min(r0, rows - 1)] >> 3;
+      const int t1 = g.sorted_rows[row0 + min(r1, rows - 1)] >> 3;
+      const __nv_bfloat16* src0 = g.gather_src + static_cast<size_t>(t0) * g.lda;
+      const __nv_bfloat16* src1 = g.gather_src + static_cast<size_t>(t1) * g.lda;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
+        const uint32_t base = smem_base + stage * kStageBytes;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          cp_async_16(base + r0 * 128 + ((c ^ (r0 & 7)) << 4), src0 + kb * kBK + c * 8);
+          cp_async_16(base + r1 * 128 + ((c ^ (r1 & 7)) << 4), src1 + kb * kBK + c * 8);
+        }
+        cp_async_commit();
+        ++committed;
+        if (committed >= 3) {        // at most two groups stay in flight
+          cp_async_wait<2>();
+          signal_oldest();
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    // drain the last (up to two) groups
+    if (committed >= 2) { cp_async_wait<1>(); signal_oldest(); }
+    if (committed >= 1) { cp_async_wait<0>(); signal_oldest(); }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
@@ -375,16 +430,16 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MODE>
+template <int MODE, bool kGather = false>
 cudaError_t launch_mode(const TcMaps& maps, const TcProblem& pb, int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<MODE>,
+    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<MODE, kGather>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  grouped_gemm_tc_kernel<MODE><<<grid, kTcThreads, kTcSmemBytes, stream>>>(maps, pb);
+  grouped_gemm_tc_kernel<MODE, kGather><<<grid, kTcThreads, kTcSmemBytes, stream>>>(maps, pb);
   return cudaGetLastError();
 }
 
@@ -401,7 +456,10 @@ cudaError_t launch_grouped_gemm_tc(GemmMode mode, const GroupedGemm& g, const Tc
   pb.n_valid = g.n;
   const bool dual = (mode == kGemmExpertGateUp || mode == kGemmSharedGateUp);
   const uint64_t experts = static_cast<uint64_t>(extra.experts_in_b);
-  bool ok = make_map(&maps.a, g.a, extra.a_rows, static_cast<uint64_t>(g.k), static_cast<uint64_t>(g.lda));
+  const bool gather = (mode == kGemmExpertGateUp && g.gather_src != nullptr);
+  if (gather && g.sorted_rows == nullptr) return cudaErrorInvalidValue;
+  bool ok = make_map(&maps.a, gather ? g.gather_src : g.a, extra.a_rows, static_cast<uint64_t>(g.k),
+                     static_cast<uint64_t>(g.lda));
   if (mode == kGemmExpertGateUp) {
     pb.n_chunks = g.n / (kBN / 2);
     pb.b_rows_per_expert = 2 * g.n;
@@ -424,7 +482,9 @@ cudaError_t launch_grouped_gemm_tc(GemmMode mode, const GroupedGemm& g, const Tc
   if (!ok) return cudaErrorNotSupported;
   const int grid = extra.sm_count;
   switch (mode) {
-    case kGemmExpertGateUp: return launch_mode<kGemmExpertGateUp>(maps, pb, grid, stream);
+    case kGemmExpertGateUp:
+      return gather ? launch_mode<kGemmExpertGateUp, true>(maps, pb, grid, stream)
+                    : launch_mode<kGemmExpertGateUp>(maps, pb, grid, stream);
     case kGemmSharedGateUp: return launch_mode<kGemmSharedGateUp>(maps, pb, grid, stream);
     case kGemmExpertDown: return launch_mode<kGemmExpertDown>(maps, pb, grid, stream);
     case kGemmSharedDown: return launch_mode<kGemmSharedDown>(maps, pb, grid, stream);

@@ -787,10 +787,17 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_scatter_kernel");
   count += 3;
 
-  gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(call.h2), ws->sorted_rows, rows, ws->gathered);
-  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "gather_rows_kernel");
-  ++count;
+  // Routed rows are materialised in expert order and read by TMA.  The alternative -- the gate_up
+  // kernel gathering its rows itself with cp.async (fused_dispatch) -- saves 0.5 GB of traffic per
+  // T = 8192 layer but measured slower (1.08 vs 0.83 ms): 64 gather threads with three copy groups
+  // in flight cannot keep the 4-stage ring fed.
+  const bool fused_dispatch = ws->fused_dispatch && !ws->use_simt_gemm;
+  if (!fused_dispatch) {
+    gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(call.h2), ws->sorted_rows, rows, ws->gathered);
+    if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "gather_rows_kernel");
+    ++count;
+  }
 
   // routed experts: gate_up + SwiGLU, then down x routing weight
   GroupedGemm g{};
@@ -800,16 +807,24 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   g.b0 = call.layer.expert_gate_up; g.b1 = nullptr;
   g.b_expert_stride = static_cast<size_t>(2 * kInter) * kHidden;
   g.n = kInter; g.c = ws->expert_act; g.ldc = kInter;
-  g.row_scale = nullptr; g.sorted_rows = nullptr;
+  g.row_scale = nullptr; g.sorted_rows = ws->sorted_rows;
   TcExtra extra{};
   extra.status = ws->status; extra.sm_count = ws->sm_count;
-  extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK; extra.experts_in_b = call.experts_local;
+  extra.experts_in_b = call.experts_local;
+  if (fused_dispatch) {
+    g.gather_src = static_cast<const __nv_bfloat16*>(call.h2);
+    extra.a_rows = static_cast<uint64_t>(T);
+  } else {
+    extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK;
+  }
   auto product = [&](GemmMode mode, const GroupedGemm& problem, const TcExtra& x) {
     return ws->use_simt_gemm ? launch_grouped_gemm_simt(mode, problem, stream)
                              : launch_grouped_gemm_tc(mode, problem, x, stream);
   };
   if ((code = product(kGemmExpertGateUp, g, extra)) != cudaSuccess)
     return set_error(error, error_bytes, code, "grouped gemm expert gate_up");
+  g.gather_src = nullptr;
+  extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK;
   g.a = ws->expert_act; g.lda = kInter; g.k = kInter;
   g.b0 = call.layer.expert_down; g.b_expert_stride = static_cast<size_t>(kHidden) * kInter;
   g.n = kHidden; g.c = ws->expert_down; g.ldc = kHidden;

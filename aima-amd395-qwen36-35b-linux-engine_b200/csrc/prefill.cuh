@@ -17,6 +17,7 @@ struct PrefillWorkspace {
   int* status = nullptr;              // device status word shared with the handle
   bool use_simt_gemm = false;         // qualification: CUDA-core products instead of tcgen05
   bool exact_router = false;          // qualification: all 256 logits with the canonical dot
+  bool fused_dispatch = false;        // gate_up kernel gathers its rows itself (no materialised copy)
   uint8_t* base = nullptr;
   // router outputs
   int32_t* topk_ids = nullptr;        // [T, 8]

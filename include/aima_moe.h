@@ -84,6 +84,10 @@ typedef struct aima_moe_config {
 /* Qualification only: compute all 256 router logits per token with the canonical
  * FP32 dot instead of filtering candidates with tensor-core logits first. */
 #define AIMA_MOE_FLAG_EXACT_ROUTER 2u
+/* Prefill: let the gate_up tensor-core kernel gather its activation rows by token index itself
+ * (cp.async, hand-written swizzle) instead of reading a materialised copy by TMA.  Same bits;
+ * currently slower, kept for measurement. */
+#define AIMA_MOE_FLAG_FUSED_DISPATCH 8u
 
 /* One layer's tensors in checkpoint layout
  * (doc/reference/amd395-qwen36-35b-a3b-bf16/qwen36-shape-manifest.json:162-180,
