@@ -15,8 +15,9 @@
 //   warp 1   one thread issues tcgen05.mma (M128 N256 K16, 4 per K block) and
 //            commits to the ring's "empty" barriers / the accumulator's "full" barrier
 //   warp 2   allocates and frees the 512 tensor-memory columns
-//   warps 2-3 (gate_up with fused dispatch only) gather the tile's 128 activation rows by token
-//            index with 16-byte cp.async copies, writing the 128-byte swizzle pattern themselves
+//            with fused dispatch (gate_up only) all 32 lanes of warp 0 take part: lane l fetches
+//            rows 4l .. 4l+3 of the A tile BY TOKEN INDEX with one TMA gather4 copy per K block
+//            (rows beyond the tile's last valid row get an out-of-range index and arrive as zeros)
 //   warps 4-7 epilogue: tcgen05.ld 32 rows x 32 columns per warp, SwiGLU or
 //            scaling, BF16 stores
 // Every mbarrier wait is bounded; on expiry the block sets the status word,
@@ -53,6 +54,7 @@ struct TcProblem {
   int b_rows_per_expert;  // rows between experts in b0 / b1
   int up_row_offset;      // row offset of the "up" half inside an expert (gate_up modes)
   int n_valid;            // valid output columns (plain mode masks beyond)
+  int a_rows;             // rows of the A tensor (fused dispatch: first out-of-range row index)
   int* status;            // device status word
 };
 
@@ -63,6 +65,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%2, %3}], [%4];"
       :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// Four rows of a 2-D tensor, picked by row index, into four consecutive 128-byte rows of a
+// swizzled tile.  The tensor map has a box of 64 columns x 1 row.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int x,
+                                            int y0, int y1, int y2, int y3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      :: "r"(dst), "l"(map), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t columns) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -134,16 +145,6 @@ __device__ __forceinline__ void pack_store_32(__nv_bfloat16* dst, const float* v
   }
 }
 
-constexpr int kGatherThreads = 64;     // warps 2 and 3
-
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
-__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
 template <int MODE, bool kGather = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) {
@@ -166,7 +167,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), kGather ? 1 + kGatherThreads : 1);
+      mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -205,7 +206,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    if (kGather || lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
@@ -221,20 +222,39 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
           b0_row = expert * pb.b_rows_per_expert + chunk * kBN;
           b1_row = b0_row + kBN / 2;
         }
+        int token[4] = {0, 0, 0, 0};
+        if (kGather) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int r = 4 * lane + j;
+            token[j] = r < rows ? (g.sorted_rows[row0 + r] >> 3) : pb.a_rows;   // a_rows: out of range, reads zeros
+          }
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kStageABytes;
-          mbar_arrive_expect_tx(full_bar(stage), kGather ? kStageBBytes : kStageBytes);
-          if (!kGather) tma_load_2d(a_dst, &maps.a, kb * kBK, row0, full_bar(stage));
-          tma_load_2d(b_dst, &maps.b0, kb * kBK, b0_row, full_bar(stage));
-          tma_load_2d(b_dst + kStageBBytes / 2, kDual ? &maps.b1 : &maps.b0, kb * kBK, b1_row, full_bar(stage));
+          if (lane == 0) {
+            if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); }
+            if (alive) {
+              mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
+              if (!kGather) tma_load_2d(a_dst, &maps.a, kb * kBK, row0, full_bar(stage));
+              tma_load_2d(b_dst, &maps.b0, kb * kBK, b0_row, full_bar(stage));
+              tma_load_2d(b_dst + kStageBBytes / 2, kDual ? &maps.b1 : &maps.b0, kb * kBK, b1_row, full_bar(stage));
+            }
+          }
+          if (kGather) {
+            alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+            if (alive)
+              tma_gather4(a_dst + lane * 512, &maps.a, kb * kBK, token[0], token[1], token[2], token[3],
+                          full_bar(stage));
+          }
+          if (!alive) break;
           ++issued;
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
       // drain on abort: wait (bounded) for the stages whose copies are still in flight
-      if (*abort_flag != 0) {
+      if (lane == 0 && *abort_flag != 0) {
         volatile int ignore = 0;
         int s = stage;
         uint32_t ph = phase;
@@ -244,49 +264,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
         }
       }
     }
-  } else if (kGather && (warp == 2 || warp == 3)) {
-    // ------------------------------ A-row gather -------------------------------
-    // thread t copies rows t and t + 64 of the tile: 8 chunks of 16 bytes per row and K block,
-    // chunk c of row r lands at chunk position c ^ (r & 7) of the row (the 128-byte swizzle)
-    const int lt = (warp - 2) * 32 + lane;
-    int stage = 0;
-    uint32_t phase = 0;
-    int committed = 0;             // groups committed so far
-    int arrive_stage = 0;          // stage of the oldest group not yet signalled
-    bool alive = true;
-    auto signal_oldest = [&]() {
-      fence_async_proxy();
-      mbar_arrive(full_bar(arrive_stage));
-      if (++arrive_stage == kStages) arrive_stage = 0;
-    };
-    for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x) {
-      int tile, chunk, expert, row0, rows;
-      unit_tile(unit, tile, chunk, expert, row0, rows);
-      const int r0 = lt, r1 = lt + kGatherThreads;
-      const int t0 = g.sorted_rows[row0 + min(r0, rows - 1)] >> 3;
-      const int t1 = g.sorted_rows[row0 + min(r1, rows - 1)] >> 3;
-      const __nv_bfloat16* src0 = g.gather_src + static_cast<size_t>(t0) * g.lda;
-      const __nv_bfloat16* src1 = g.gather_src + static_cast<size_t>(t1) * g.lda;
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
-        const uint32_t base = smem_base + stage * kStageBytes;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          cp_async_16(base + r0 * 128 + ((c ^ (r0 & 7)) << 4), src0 + kb * kBK + c * 8);
-          cp_async_16(base + r1 * 128 + ((c ^ (r1 & 7)) << 4), src1 + kb * kBK + c * 8);
-        }
-        cp_async_commit();
-        ++committed;
-        if (committed >= 3) {        // at most two groups stay in flight
-          cp_async_wait<2>();
-          signal_oldest();
-        }
-        if (++stage == kStages) { stage = 0; phase ^= 1u; }
-      }
-    }
-    // drain the last (up to two) groups
-    if (committed >= 2) { cp_async_wait<1>(); signal_oldest(); }
-    if (committed >= 1) { cp_async_wait<0>(); signal_oldest(); }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
@@ -417,13 +394,15 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
   return fn;
 }
 
-// 2-D BF16 tensor [rows, cols] row-major, box 64 columns x 128 rows, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems) {
+// 2-D BF16 tensor [rows, cols] row-major, box 64 columns x box_rows rows (128 for tile loads,
+// 1 for gather4 loads), 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+              uint32_t box_rows = kBM) {
   PFN_cuTensorMapEncodeTiled_v12000 encode = encode_fn();
   if (encode == nullptr) return false;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {pitch_elems * 2};
-  const cuuint32_t box[2] = {kBK, kBM};
+  const cuuint32_t box[2] = {kBK, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -459,7 +438,8 @@ cudaError_t launch_grouped_gemm_tc(GemmMode mode, const GroupedGemm& g, const Tc
   const bool gather = (mode == kGemmExpertGateUp && g.gather_src != nullptr);
   if (gather && g.sorted_rows == nullptr) return cudaErrorInvalidValue;
   bool ok = make_map(&maps.a, gather ? g.gather_src : g.a, extra.a_rows, static_cast<uint64_t>(g.k),
-                     static_cast<uint64_t>(g.lda));
+                     static_cast<uint64_t>(g.lda), gather ? 1u : static_cast<uint32_t>(kBM));
+  pb.a_rows = static_cast<int>(extra.a_rows);
   if (mode == kGemmExpertGateUp) {
     pb.n_chunks = g.n / (kBN / 2);
     pb.b_rows_per_expert = 2 * g.n;

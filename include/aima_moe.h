@@ -85,8 +85,9 @@ typedef struct aima_moe_config {
  * FP32 dot instead of filtering candidates with tensor-core logits first. */
 #define AIMA_MOE_FLAG_EXACT_ROUTER 2u
 /* Prefill: let the gate_up tensor-core kernel gather its activation rows by token index itself
- * (cp.async, hand-written swizzle) instead of reading a materialised copy by TMA.  Same bits;
- * currently slower, kept for measurement. */
+ * (TMA gather4, four rows per copy) instead of reading a materialised copy with one tiled TMA
+ * load per stage.  Same bits; slower on B200 (128 one-row boxes per stage instead of one box),
+ * kept for measurement. */
 #define AIMA_MOE_FLAG_FUSED_DISPATCH 8u
 
 /* One layer's tensors in checkpoint layout
