@@ -787,10 +787,9 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_scatter_kernel");
   count += 3;
 
-  // Routed rows are materialised in expert order and read by TMA.  The alternative -- the gate_up
-  // kernel gathering its rows itself with cp.async (fused_dispatch) -- saves 0.5 GB of traffic per
-  // T = 8192 layer but measured slower (1.08 vs 0.83 ms): 64 gather threads with three copy groups
-  // in flight cannot keep the 4-stage ring fed.
+  // Routed rows are materialised in expert order and read by one tiled TMA load per stage.  The
+  // alternative (fused_dispatch: the gate_up kernel fetches its rows by token index with TMA
+  // gather4) saves 0.5 GB of traffic per T = 8192 layer but measured slower, 1.20 vs 0.83 ms.
   const bool fused_dispatch = ws->fused_dispatch && !ws->use_simt_gemm;
   if (!fused_dispatch) {
     gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(

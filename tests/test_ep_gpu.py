@@ -171,6 +171,15 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+def _bits(tensor):
+    """BF16 tensor as a numpy uint16 array: pickled by value, so the queue needs no shared file descriptors."""
+    return tensor.detach().cpu().contiguous().view(torch.int16).numpy().copy()
+
+
+def _from_bits(array):
+    return torch.from_numpy(array).view(torch.bfloat16)
+
+
 def _rank_main(rank: int, world: int, port: int, results) -> None:
     import torch.distributed as dist
     import conftest
@@ -200,7 +209,7 @@ def _rank_main(rank: int, world: int, port: int, results) -> None:
             dist.barrier()
             provider.decode_stack(x, y, 0, 3)
             provider.sync_metrics()
-            outputs.append(y.cpu().clone())
+            outputs.append(_bits(y))
             x, y = y, x
         dist.barrier()
         provider.release()
@@ -216,18 +225,19 @@ def _rank_main(rank: int, world: int, port: int, results) -> None:
                                           model_layer=0)
         prefill.sync_metrics()
         dist.barrier()
-        outputs.append(out.cpu().clone())
+        outputs.append(_bits(out))
         prefill.release()
         results.put((rank, outputs))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_two_gpus_match_the_oracle(oracle, synth):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_ranks_match_the_oracle(oracle, synth, world):
     import torch.multiprocessing as mp
 
-    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     context = mp.get_context("spawn")
     results = context.Queue()
     port = _free_port()
@@ -235,6 +245,7 @@ def test_expert_parallel_two_gpus_match_the_oracle(oracle, synth):
     for process in processes:
         process.start()
     got = dict(results.get(timeout=600) for _ in range(world))
+    got = {rank: [_from_bits(a) for a in arrays] for rank, arrays in got.items()}
     for process in processes:
         process.join(timeout=120)
         assert process.exitcode == 0
@@ -243,13 +254,13 @@ def test_expert_parallel_two_gpus_match_the_oracle(oracle, synth):
     for step in range(3):
         for layer in layers:
             expected = oracle.decode_layer(expected, layer)["out"]
-        assert torch.equal(got[0][step], expected), f"rank 0 step {step}"
-        assert torch.equal(got[1][step], expected), f"rank 1 step {step}"
-    # prefill rows of both ranks against the oracle (same tolerance as the single-GPU prefill tests)
+        for rank in range(world):
+            assert torch.equal(got[rank][step], expected), f"rank {rank} step {step}"
+    # prefill rows of all ranks against the oracle (same tolerance as the single-GPU prefill tests)
     h2_all = synth.activations(SEED + 77, 128 * world, "input", 0)
     resid_all = synth.activations(SEED + 77, 128 * world, "residual", 0)
-    select = [0, 5, 127, 128, 200, 255]
+    select = sorted({0, 5, 127, 128, 200, 255, 128 * world - 1})
     want = oracle.prefill_layer(h2_all, resid_all, layers[0], select=select)
-    both = torch.cat([got[0][3], got[1][3]])
+    everyone = torch.cat([got[rank][3] for rank in range(world)])
     ulp = want["out"].float().abs() * 2.0 ** -7
-    assert ((both[select].float() - want["out"].float()).abs() <= ulp + 2.0e-2).all()
+    assert ((everyone[select].float() - want["out"].float()).abs() <= ulp + 2.0e-2).all()
