@@ -693,6 +693,11 @@ int prefill_workspace_allocate(PrefillWorkspace* ws, uint32_t capacity_tokens, i
   if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMalloc prefill workspace");
   code = cudaMemset(ws->base, 0, l.total);
   if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemset prefill workspace");
+  code = cudaStreamCreateWithFlags(&ws->side_stream, cudaStreamNonBlocking);
+  if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->fork_event, cudaEventDisableTiming);
+  if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->router_event, cudaEventDisableTiming);
+  if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->join_event, cudaEventDisableTiming);
+  if (code != cudaSuccess) return set_error(error, error_bytes, code, "side stream / events of the prefill workspace");
   ws->total_bytes = l.total;
   ws->capacity = static_cast<int>(capacity_tokens);
   ws->sm_count = sm_count;
@@ -726,6 +731,10 @@ int prefill_workspace_allocate(PrefillWorkspace* ws, uint32_t capacity_tokens, i
 
 void prefill_workspace_free(PrefillWorkspace* ws) {
   if (ws->base != nullptr) cudaFree(ws->base);
+  if (ws->fork_event != nullptr) cudaEventDestroy(ws->fork_event);
+  if (ws->router_event != nullptr) cudaEventDestroy(ws->router_event);
+  if (ws->join_event != nullptr) cudaEventDestroy(ws->join_event);
+  if (ws->side_stream != nullptr) cudaStreamDestroy(ws->side_stream);
   *ws = PrefillWorkspace{};
 }
 
@@ -736,6 +745,28 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   const aima_moe_debug_views* dbg = call.debug;
   int count = 0;
   cudaError_t code;
+
+  // fork: the shared gate/up product needs only h2
+  cudaStream_t side = ws->side_stream;
+  if ((code = cudaEventRecord(ws->fork_event, stream)) != cudaSuccess ||
+      (code = cudaStreamWaitEvent(side, ws->fork_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "fork of the shared-expert stream");
+  auto product = [&](GemmMode mode, const GroupedGemm& problem, const TcExtra& x, cudaStream_t on) {
+    return ws->use_simt_gemm ? launch_grouped_gemm_simt(mode, problem, on)
+                             : launch_grouped_gemm_tc(mode, problem, x, on);
+  };
+  GroupedGemm s{};
+  TcExtra shared_extra{};
+  shared_extra.status = ws->status; shared_extra.sm_count = ws->sm_count;
+  s.tile_expert = nullptr; s.tile_row0 = nullptr; s.tile_rows = nullptr; s.tile_count = nullptr;
+  s.max_tiles = (T + kTileRows - 1) / kTileRows; s.dense_rows = T;
+  s.a = static_cast<const __nv_bfloat16*>(call.h2); s.lda = kHidden; s.k = kHidden;
+  s.b0 = call.layer.shared_gate_proj; s.b1 = call.layer.shared_up_proj; s.b_expert_stride = 0;
+  s.n = kSharedInter; s.c = ws->shared_act; s.ldc = kSharedInter;
+  shared_extra.a_rows = static_cast<uint64_t>(T); shared_extra.experts_in_b = 1;
+  if ((code = product(kGemmSharedGateUp, s, shared_extra, side)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm shared gate_up");
+  ++count;
 
   const bool exact_router = ws->exact_router || (dbg != nullptr && dbg->router_logits != nullptr) ||
                             call.router_row_norms == nullptr;
@@ -773,6 +804,21 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
       return set_error(error, error_bytes, code, "prefill_router_certified_kernel");
     count += 2;
   }
+
+  // the shared down product scales by the sigmoid the router kernel wrote
+  if ((code = cudaEventRecord(ws->router_event, stream)) != cudaSuccess ||
+      (code = cudaStreamWaitEvent(side, ws->router_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "router event of the shared-expert stream");
+  s.a = ws->shared_act; s.lda = kSharedInter; s.k = kSharedInter;
+  s.b0 = call.layer.shared_down_proj; s.b1 = nullptr;
+  s.n = kHidden; s.c = ws->shared_scaled; s.ldc = kHidden;
+  s.row_scale = ws->shared_sigmoid;
+  shared_extra.a_rows = static_cast<uint64_t>(ws->capacity);
+  if ((code = product(kGemmSharedDown, s, shared_extra, side)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm shared down");
+  ++count;
+  if ((code = cudaEventRecord(ws->join_event, side)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "join event of the shared-expert stream");
 
   const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
   const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
@@ -816,11 +862,7 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   } else {
     extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK;
   }
-  auto product = [&](GemmMode mode, const GroupedGemm& problem, const TcExtra& x) {
-    return ws->use_simt_gemm ? launch_grouped_gemm_simt(mode, problem, stream)
-                             : launch_grouped_gemm_tc(mode, problem, x, stream);
-  };
-  if ((code = product(kGemmExpertGateUp, g, extra)) != cudaSuccess)
+  if ((code = product(kGemmExpertGateUp, g, extra, stream)) != cudaSuccess)
     return set_error(error, error_bytes, code, "grouped gemm expert gate_up");
   g.gather_src = nullptr;
   extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK;
@@ -828,29 +870,13 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   g.b0 = call.layer.expert_down; g.b_expert_stride = static_cast<size_t>(kHidden) * kInter;
   g.n = kHidden; g.c = ws->expert_down; g.ldc = kHidden;
   g.row_scale = ws->topk_weights; g.sorted_rows = ws->sorted_rows;
-  if ((code = product(kGemmExpertDown, g, extra)) != cudaSuccess)
+  if ((code = product(kGemmExpertDown, g, extra, stream)) != cudaSuccess)
     return set_error(error, error_bytes, code, "grouped gemm expert down");
   count += 2;
 
-  // shared expert as dense products over all tokens
-  GroupedGemm s{};
-  s.tile_expert = nullptr; s.tile_row0 = nullptr; s.tile_rows = nullptr; s.tile_count = nullptr;
-  s.max_tiles = (T + kTileRows - 1) / kTileRows; s.dense_rows = T;
-  s.a = static_cast<const __nv_bfloat16*>(call.h2); s.lda = kHidden; s.k = kHidden;
-  s.b0 = call.layer.shared_gate_proj; s.b1 = call.layer.shared_up_proj; s.b_expert_stride = 0;
-  s.n = kSharedInter; s.c = ws->shared_act; s.ldc = kSharedInter;
-  extra.a_rows = static_cast<uint64_t>(T); extra.experts_in_b = 1;
-  if ((code = product(kGemmSharedGateUp, s, extra)) != cudaSuccess)
-    return set_error(error, error_bytes, code, "grouped gemm shared gate_up");
-  s.a = ws->shared_act; s.lda = kSharedInter; s.k = kSharedInter;
-  s.b0 = call.layer.shared_down_proj; s.b1 = nullptr;
-  s.n = kHidden; s.c = ws->shared_scaled; s.ldc = kHidden;
-  s.row_scale = ws->shared_sigmoid;
-  extra.a_rows = static_cast<uint64_t>(ws->capacity);
-  if ((code = product(kGemmSharedDown, s, extra)) != cudaSuccess)
-    return set_error(error, error_bytes, code, "grouped gemm shared down");
-  count += 2;
-
+  // join: the combine needs the shared expert's output
+  if ((code = cudaStreamWaitEvent(stream, ws->join_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "join of the shared-expert stream");
   combine_kernel<<<T, 256, 0, stream>>>(ws->expert_down, ws->row_position, ws->shared_scaled,
                                         static_cast<const __nv_bfloat16*>(call.residual),
                                         static_cast<__nv_bfloat16*>(call.out),

@@ -19,6 +19,12 @@ struct PrefillWorkspace {
   bool exact_router = false;          // qualification: all 256 logits with the canonical dot
   bool fused_dispatch = false;        // gate_up kernel gathers its rows itself (no materialised copy)
   uint8_t* base = nullptr;
+  // The shared expert does not depend on the routing: it runs on a second stream, forked from and
+  // joined to the caller's stream with events, next to the router, the plan and the row gather.
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t fork_event = nullptr;     // caller's stream: inputs of this call are ready
+  cudaEvent_t router_event = nullptr;   // caller's stream: sigmoid of the shared gate is written
+  cudaEvent_t join_event = nullptr;     // side stream: shared expert output is written
   // router outputs
   int32_t* topk_ids = nullptr;        // [T, 8]
   float* topk_scores = nullptr;       // [T, 8]
