@@ -373,68 +373,101 @@ plan_count_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert_l
   }
 }
 
-// One block of 256 threads: per-expert totals, exclusive offsets, per-unit
-// exclusive prefixes (in place), the tile list and the reference's block-32
-// padded row count.
-__global__ void __launch_bounds__(kExperts)
-plan_scan_kernel(int32_t* __restrict__ unit_counts, int units,
-                 int32_t* __restrict__ expert_counts, int32_t* __restrict__ expert_offsets,
-                 int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row0,
-                 int32_t* __restrict__ tile_rows, int32_t* __restrict__ tile_count,
-                 int32_t* __restrict__ padded_rows) {
-  __shared__ int counts[kExperts];
-  __shared__ int offsets[kExperts + 1];
-  __shared__ int tile_base[kExperts + 1];
-  const int e = threadIdx.x;
+// One warp per expert: exclusive prefix of that expert's counts over the units (in place) and the
+// expert's total.  Grid = 256 / kPlanWarps blocks.
+__global__ void __launch_bounds__(kPlanWarps * 32)
+plan_scan_kernel(int32_t* __restrict__ unit_counts, int units, int32_t* __restrict__ expert_counts) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * kPlanWarps + (threadIdx.x >> 5);
   int running = 0;
-  for (int u = 0; u < units; ++u) {
+  for (int u0 = 0; u0 < units; u0 += 32) {
+    const int u = u0 + lane;
     const size_t index = static_cast<size_t>(u) * kExperts + e;
-    const int c = unit_counts[index];
-    unit_counts[index] = running;
-    running += c;
-  }
-  counts[e] = running;
-  __syncthreads();
-  if (e == 0) {
-    int offset = 0, tiles = 0, padded = 0;
-    for (int i = 0; i < kExperts; ++i) {
-      offsets[i] = offset;
-      tile_base[i] = tiles;
-      offset += counts[i];
-      tiles += (counts[i] + kTileRows - 1) / kTileRows;
-      padded += (counts[i] + 31) / 32 * 32;
+    const int c = u < units ? unit_counts[index] : 0;
+    int inclusive = c;
+#pragma unroll
+    for (int d = 1; d < 32; d *= 2) {
+      const int up = __shfl_up_sync(0xffffffffu, inclusive, d);
+      if (lane >= d) inclusive += up;
     }
-    offsets[kExperts] = offset;
-    tile_base[kExperts] = tiles;
-    *tile_count = tiles;
-    *padded_rows = padded;
+    if (u < units) unit_counts[index] = running + inclusive - c;
+    running += __shfl_sync(0xffffffffu, inclusive, 31);
   }
-  __syncthreads();
-  expert_counts[e] = counts[e];
-  expert_offsets[e] = offsets[e];
-  if (e == 0) expert_offsets[kExperts] = offsets[kExperts];
-  const int n_tiles = tile_base[e + 1] - tile_base[e];
-  for (int t = 0; t < n_tiles; ++t) {
-    const int index = tile_base[e] + t;
-    tile_expert[index] = e;
-    tile_row0[index] = offsets[e] + t * kTileRows;
-    tile_rows[index] = min(kTileRows, counts[e] - t * kTileRows);
-  }
+  if (lane == 0) expert_counts[e] = running;
 }
 
+// Exclusive offsets of the 256 experts from their counts, in shared memory (all 256 threads of a
+// block take part); thread 0 .. 255 returns with offsets[0 .. 256] and tile_base[0 .. 256] filled.
+__device__ __forceinline__ int expert_offsets_in_block(const int32_t* __restrict__ expert_counts,
+                                                       int* offsets, int* tile_base, int* warp_sums) {
+  const int e = threadIdx.x;
+  const int lane = e & 31, warp = e >> 5;
+  const int count = expert_counts[e];
+  int v0 = count, v1 = (count + kTileRows - 1) / kTileRows, v2 = (count + 31) / 32 * 32;
+  const int mine0 = v0, mine1 = v1;
+#pragma unroll
+  for (int d = 1; d < 32; d *= 2) {
+    const int a0 = __shfl_up_sync(0xffffffffu, v0, d);
+    const int a1 = __shfl_up_sync(0xffffffffu, v1, d);
+    const int a2 = __shfl_up_sync(0xffffffffu, v2, d);
+    if (lane >= d) { v0 += a0; v1 += a1; v2 += a2; }
+  }
+  if (lane == 31) { warp_sums[warp] = v0; warp_sums[8 + warp] = v1; warp_sums[16 + warp] = v2; }
+  __syncthreads();
+  int b0 = 0, b1 = 0, padded = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    if (w < warp) { b0 += warp_sums[w]; b1 += warp_sums[8 + w]; }
+    padded += warp_sums[16 + w];
+  }
+  offsets[e] = b0 + v0 - mine0;
+  tile_base[e] = b1 + v1 - mine1;
+  if (e == kExperts - 1) { offsets[kExperts] = b0 + v0; tile_base[kExperts] = b1 + v1; }
+  __syncthreads();
+  return padded;
+}
+
+// Stable scatter.  Every block first derives the expert offsets from the counts; block 0 also
+// publishes them together with the tile list and the reference's block-32 padded row count.
 __global__ void __launch_bounds__(kPlanWarps * 32)
 plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert_lo, int expert_hi,
                     const int32_t* __restrict__ unit_prefix,
-                    const int32_t* __restrict__ expert_offsets,
+                    const int32_t* __restrict__ expert_counts,
+                    int32_t* __restrict__ expert_offsets,
+                    int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row0,
+                    int32_t* __restrict__ tile_rows, int32_t* __restrict__ tile_count,
+                    int32_t* __restrict__ padded_rows,
                     int32_t* __restrict__ sorted_rows, int32_t* __restrict__ row_position) {
+  static_assert(kPlanWarps * 32 == kExperts, "one thread per expert in the prologue");
   __shared__ int next[kPlanWarps][kExperts];
+  __shared__ int offsets[kExperts + 1];
+  __shared__ int tile_base[kExperts + 1];
+  __shared__ int warp_sums[24];
+  const int padded = expert_offsets_in_block(expert_counts, offsets, tile_base, warp_sums);
+  if (blockIdx.x == 0) {
+    const int e = threadIdx.x;
+    const int count = offsets[e + 1] - offsets[e];
+    expert_offsets[e] = offsets[e];
+    if (e == 0) {
+      expert_offsets[kExperts] = offsets[kExperts];
+      *tile_count = tile_base[kExperts];
+      *padded_rows = padded;
+    }
+    const int n_tiles = tile_base[e + 1] - tile_base[e];
+    for (int t = 0; t < n_tiles; ++t) {
+      const int index = tile_base[e] + t;
+      tile_expert[index] = e;
+      tile_row0[index] = offsets[e] + t * kTileRows;
+      tile_rows[index] = min(kTileRows, count - t * kTileRows);
+    }
+  }
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int unit = blockIdx.x * kPlanWarps + warp;
   const int row0 = unit * kPlanRowsPerWarp;
   if (row0 >= routed_rows) return;
   for (int e = lane; e < kExperts; e += 32) {
-    next[warp][e] = expert_offsets[e] + unit_prefix[static_cast<size_t>(unit) * kExperts + e];
+    next[warp][e] = offsets[e] + unit_prefix[static_cast<size_t>(unit) * kExperts + e];
   }
   __syncwarp();
   for (int round = 0; round < kPlanRowsPerWarp / 32; ++round) {
@@ -453,6 +486,20 @@ plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert
     }
     __syncwarp();
   }
+}
+
+// Enqueues the dispatch plan for `rows` routed rows whose expert ids are `ids`.
+cudaError_t launch_plan(PrefillWorkspace* ws, const int32_t* ids, int rows, int expert_lo, int expert_hi,
+                        cudaStream_t stream, int* launches) {
+  const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
+  const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
+  plan_count_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ids, rows, expert_lo, expert_hi, ws->unit_counts);
+  plan_scan_kernel<<<kExperts / kPlanWarps, kPlanWarps * 32, 0, stream>>>(ws->unit_counts, units, ws->expert_counts);
+  plan_scatter_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(
+      ids, rows, expert_lo, expert_hi, ws->unit_counts, ws->expert_counts, ws->expert_offsets, ws->tile_expert,
+      ws->tile_row0, ws->tile_rows, ws->tile_count, ws->padded_rows, ws->sorted_rows, ws->row_position);
+  *launches += 3;
+  return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------
@@ -820,18 +867,8 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   if ((code = cudaEventRecord(ws->join_event, side)) != cudaSuccess)
     return set_error(error, error_bytes, code, "join event of the shared-expert stream");
 
-  const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
-  const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
-  plan_count_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ws->topk_ids, rows, 0, kExperts, ws->unit_counts);
-  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_count_kernel");
-  plan_scan_kernel<<<1, kExperts, 0, stream>>>(ws->unit_counts, units, ws->expert_counts,
-                                               ws->expert_offsets, ws->tile_expert, ws->tile_row0,
-                                               ws->tile_rows, ws->tile_count, ws->padded_rows);
-  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_scan_kernel");
-  plan_scatter_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(
-      ws->topk_ids, rows, 0, kExperts, ws->unit_counts, ws->expert_offsets, ws->sorted_rows, ws->row_position);
-  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "plan_scatter_kernel");
-  count += 3;
+  if ((code = launch_plan(ws, ws->topk_ids, rows, 0, kExperts, stream, &count)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "dispatch plan");
 
   // Routed rows are materialised in expert order and read by one tiled TMA load per stage.  The
   // alternative (fused_dispatch: the gate_up kernel fetches its rows by token index with TMA
@@ -983,17 +1020,8 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   // 3. plan over the global rows that land on this GPU's experts
   const int expert_lo = ep->rank * call.experts_local;
   const int expert_hi = expert_lo + call.experts_local;
-  const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
-  const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
-  plan_count_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ids_all, rows, expert_lo, expert_hi, ws->unit_counts);
-  plan_scan_kernel<<<1, kExperts, 0, stream>>>(ws->unit_counts, units, ws->expert_counts, ws->expert_offsets,
-                                               ws->tile_expert, ws->tile_row0, ws->tile_rows, ws->tile_count,
-                                               ws->padded_rows);
-  plan_scatter_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ids_all, rows, expert_lo, expert_hi,
-                                                                  ws->unit_counts, ws->expert_offsets,
-                                                                  ws->sorted_rows, ws->row_position);
-  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "dispatch plan");
-  count += 3;
+  if ((code = launch_plan(ws, ids_all, rows, expert_lo, expert_hi, stream, &count)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "dispatch plan");
 
   mark();
   // 4. dispatch: pull the rows over NVLink into expert order
