@@ -532,11 +532,16 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
       // final layer would write over its own residual input: stage through a buffer
       target = (step & 1u) ? handle->prefill.stack_x1 : handle->prefill.stack_x0;
     }
-    cudaError_t error = launch_rmsnorm_rows(current, nullptr, handle->host_layers[layer].norm_weight,
-                                            nullptr, handle->prefill.stack_h2,
-                                            static_cast<int>(tokens), handle->config.rms_eps,
-                                            cuda_stream);
-    if (error != cudaSuccess) return fail_cuda(error, "launch rmsnorm_rows_kernel");
+    // the first layer's h2 comes from the norm kernel; every later layer's h2 was written by the
+    // previous layer's combine kernel (fused exit norm)
+    cudaError_t error = cudaSuccess;
+    if (step == 0) {
+      error = launch_rmsnorm_rows(current, nullptr, handle->host_layers[layer].norm_weight, nullptr,
+                                  handle->prefill.stack_h2, static_cast<int>(tokens), handle->config.rms_eps,
+                                  cuda_stream);
+      if (error != cudaSuccess) return fail_cuda(error, "launch rmsnorm_rows_kernel");
+      handle->metrics.kernel_launches += 1;
+    }
     PrefillCall call{};
     call.layer = handle->host_layers[layer];
     call.h2 = handle->prefill.stack_h2;
@@ -547,6 +552,11 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
     call.router_row_norms = handle->router_row_norms + layer * kExperts;
     call.router_bias = handle->router_bias;
     call.quant_eighths = handle->quant_eighths;
+    call.eps = handle->config.rms_eps;
+    if (step + 1 < n_layers) {
+      call.next_norm_weight = handle->host_layers[layer + 1].norm_weight;
+      call.next_norm_out = handle->prefill.stack_h2;
+    }
     int launches = 0;
     const int status =
         handle->config.world > 1
@@ -555,7 +565,7 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
             : prefill_layer_launch(&handle->prefill, call, cuda_stream, &launches, g_last_error,
                                    sizeof g_last_error);
     if (status != AIMA_MOE_OK) return status;
-    handle->metrics.kernel_launches += static_cast<uint64_t>(launches) + 1;
+    handle->metrics.kernel_launches += static_cast<uint64_t>(launches);
     if (step + 1 == n_layers && target != x_out) {
       error = cudaMemcpyAsync(x_out, target, bytes, cudaMemcpyDeviceToDevice, cuda_stream);
       if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpyAsync prefill stack output");
@@ -564,6 +574,61 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
   }
   handle->last_stream = cuda_stream;
   handle->metrics.prefill_calls += n_layers;
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_prefill_fused_launch(aima_moe_handle* handle, uint32_t layer, const void* attn_out,
+                                              const void* residual_in, const void* next_norm_weight,
+                                              void* layer_out, void* next_norm_out, uint32_t tokens,
+                                              void* stream) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if (attn_out == nullptr || residual_in == nullptr || layer_out == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "fused prefill input/output is null");
+  if ((next_norm_weight == nullptr) != (next_norm_out == nullptr))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "next_norm_weight and next_norm_out go together");
+  if (tokens == 0 || tokens > handle->config.max_prefill_tokens)
+    return fail(AIMA_MOE_ERR_CAPACITY, "tokens %u outside prepared capacity %u", tokens,
+                handle->config.max_prefill_tokens);
+  if (layer >= handle->config.layers || !handle->bound[layer] ||
+      handle->host_layers[layer].norm_weight == nullptr)
+    return fail(AIMA_MOE_ERR_NOT_BOUND, "layer %u lacks weights or its post-attention norm weight", layer);
+  if (handle->config.world > 1)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "the fused boundary is built for world = 1");
+  const size_t bytes = static_cast<size_t>(tokens) * kHidden * 2;
+  if (next_norm_out != nullptr && ranges_overlap(next_norm_out, bytes, layer_out, bytes))
+    return fail(AIMA_MOE_ERR_ALIAS, "next_norm_out aliases layer_out");
+  for (const void* pointer : {attn_out, residual_in, static_cast<const void*>(layer_out),
+                              static_cast<const void*>(next_norm_out), next_norm_weight}) {
+    if (reinterpret_cast<uintptr_t>(pointer) % 16 != 0)
+      return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "fused prefill pointers must be 16-byte aligned");
+  }
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  // entry: after_attn = bf16(attn_out + residual_in) and h2 = RMSNorm(after_attn) into the workspace
+  cudaError_t error = launch_rmsnorm_rows(attn_out, residual_in, handle->host_layers[layer].norm_weight,
+                                          handle->prefill.stack_x0, handle->prefill.stack_h2,
+                                          static_cast<int>(tokens), handle->config.rms_eps, cuda_stream);
+  if (error != cudaSuccess) return fail_cuda(error, "launch rmsnorm_rows_kernel");
+  PrefillCall call{};
+  call.layer = handle->host_layers[layer];
+  call.h2 = handle->prefill.stack_h2;
+  call.residual = handle->prefill.stack_x0;
+  call.out = layer_out;
+  call.tokens = static_cast<int>(tokens);
+  call.experts_local = handle->experts_local;
+  call.router_row_norms = handle->router_row_norms + layer * kExperts;
+  call.router_bias = handle->router_bias;
+  call.quant_eighths = handle->quant_eighths;
+  call.eps = handle->config.rms_eps;
+  call.next_norm_weight = next_norm_weight;
+  call.next_norm_out = next_norm_out;
+  int launches = 0;
+  const int status = prefill_layer_launch(&handle->prefill, call, cuda_stream, &launches, g_last_error,
+                                          sizeof g_last_error);
+  if (status != AIMA_MOE_OK) return status;
+  handle->last_stream = cuda_stream;
+  handle->metrics.prefill_calls += 1;
+  handle->metrics.kernel_launches += static_cast<uint64_t>(launches) + 1;
   return AIMA_MOE_OK;
 }
 

@@ -528,7 +528,10 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
                const int32_t* __restrict__ row_position,
                const __nv_bfloat16* __restrict__ shared_scaled,
                const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
-               __nv_bfloat16* __restrict__ dbg_routed) {
+               __nv_bfloat16* __restrict__ dbg_routed,
+               const __nv_bfloat16* __restrict__ next_norm_weight,
+               __nv_bfloat16* __restrict__ next_norm_out, float eps) {
+  __shared__ float group_sums[8];
   const int token = blockIdx.x;
   const int t = threadIdx.x;
   float slot[kTopK][8];
@@ -543,6 +546,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
   unpack8(__ldg(reinterpret_cast<const uint4*>(shared_scaled + base) + t), sh);
   unpack8(__ldg(reinterpret_cast<const uint4*>(residual + base) + t), rs);
   uint32_t packed[4], packed_routed[4];
+  float o8[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float s04 = __fadd_rn(slot[0][j], slot[4][j]);
@@ -555,6 +559,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
     const uint16_t routed_bits = float_to_bf16_bits(sum);
     const float combined = round_bf16(__fadd_rn(bf16_bits_to_float(routed_bits), sh[j]));
     const uint16_t o = float_to_bf16_bits(__fadd_rn(rs[j], combined));
+    o8[j] = bf16_bits_to_float(o);
     if (j & 1) {
       packed[j / 2] |= static_cast<uint32_t>(o) << 16;
       packed_routed[j / 2] |= static_cast<uint32_t>(routed_bits) << 16;
@@ -567,6 +572,32 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
   if (dbg_routed != nullptr) {
     reinterpret_cast<uint4*>(dbg_routed + base)[t] =
         make_uint4(packed_routed[0], packed_routed[1], packed_routed[2], packed_routed[3]);
+  }
+  // Optional exit: RMSNorm of the row just produced (the next layer's input norm), with the
+  // arithmetic of rmsnorm_rows_kernel -- thread t owns the eight elements 8t .. 8t+7, i.e. lane
+  // t % 32 of group t / 32, so the warp butterflies are the canonical group sums.
+  if (next_norm_out != nullptr) {
+    float part = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) part = __fmaf_rn(o8[j], o8[j], part);
+    part = butterfly_sum(part);
+    if ((t & 31) == 0) group_sums[t >> 5] = part;
+    __syncthreads();
+    float total = group_sums[0];
+#pragma unroll
+    for (int g = 1; g < 8; ++g) total = __fadd_rn(total, group_sums[g]);
+    const float inv = det_rsqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(kHidden)), eps));
+    float w[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(next_norm_weight) + t), w);
+    uint32_t normed[4];
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      const float a = __fmul_rn(__fmul_rn(o8[j], inv), __fadd_rn(w[j], 1.0f));
+      const float b = __fmul_rn(__fmul_rn(o8[j + 1], inv), __fadd_rn(w[j + 1], 1.0f));
+      normed[j / 2] = static_cast<uint32_t>(float_to_bf16_bits(a)) |
+                      (static_cast<uint32_t>(float_to_bf16_bits(b)) << 16);
+    }
+    reinterpret_cast<uint4*>(next_norm_out + base)[t] = make_uint4(normed[0], normed[1], normed[2], normed[3]);
   }
 }
 
@@ -917,7 +948,9 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   combine_kernel<<<T, 256, 0, stream>>>(ws->expert_down, ws->row_position, ws->shared_scaled,
                                         static_cast<const __nv_bfloat16*>(call.residual),
                                         static_cast<__nv_bfloat16*>(call.out),
-                                        dbg ? static_cast<__nv_bfloat16*>(dbg->routed) : nullptr);
+                                        dbg ? static_cast<__nv_bfloat16*>(dbg->routed) : nullptr,
+                                        static_cast<const __nv_bfloat16*>(call.next_norm_weight),
+                                        static_cast<__nv_bfloat16*>(call.next_norm_out), call.eps);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "combine_kernel");
   ++count;
 
@@ -1083,7 +1116,9 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   combine_kernel<<<T_loc, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(mine + L.off_return), nullptr,
                                             ws->shared_scaled, static_cast<const __nv_bfloat16*>(call.residual),
                                             static_cast<__nv_bfloat16*>(call.out),
-                                            dbg ? static_cast<__nv_bfloat16*>(dbg->routed) : nullptr);
+                                            dbg ? static_cast<__nv_bfloat16*>(dbg->routed) : nullptr,
+                                            static_cast<const __nv_bfloat16*>(call.next_norm_weight),
+                                            static_cast<__nv_bfloat16*>(call.next_norm_out), call.eps);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "combine_kernel");
   count += 2;
   mark();

@@ -89,6 +89,10 @@ struct PrefillCall {
   const float* router_bias;
   int quant_eighths;
   const aima_moe_debug_views* debug;
+  // optional fused exit: RMSNorm of the layer output with this weight (the next layer's input norm)
+  const void* next_norm_weight = nullptr;
+  void* next_norm_out = nullptr;
+  float eps = 1.0e-6f;
 };
 
 size_t prefill_workspace_bytes(uint32_t capacity_tokens);

@@ -95,6 +95,8 @@ EXPORTS = [
     ("aima_moe_decode_stack_launch", c_int, [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_void_p]),
     ("aima_moe_prefill_stack_launch", c_int,
      [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, c_uint32, c_void_p]),
+    ("aima_moe_prefill_fused_launch", c_int,
+     [c_void_p, c_uint32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_void_p]),
     ("aima_moe_rmsnorm_launch", c_int,
      [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_float, c_void_p]),
     ("aima_moe_gemv_bf16_launch", c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_void_p]),
@@ -343,6 +345,17 @@ class MoeProvider:
         self.lib.check(self.lib.aima_moe_prefill_stack_launch(
             self.handle, first_layer, n, _ptr(x_in), _ptr(x_out), int(x_in.shape[0]), _stream(torch)))
         return x_out
+
+    def prefill_fused(self, attn_out: Any, residual_in: Any, model_layer: int,
+                      next_norm_weight: Any = None) -> tuple[Any, Any]:
+        """add + RMSNorm -> MoE half -> (optional) next layer's input norm; returns (layer_out, next_norm_out)."""
+        torch = self._torch
+        layer_out = torch.empty_like(residual_in)
+        next_norm_out = torch.empty_like(residual_in) if next_norm_weight is not None else None
+        self.lib.check(self.lib.aima_moe_prefill_fused_launch(
+            self.handle, model_layer, _ptr(attn_out), _ptr(residual_in), _ptr(next_norm_weight),
+            _ptr(layer_out), _ptr(next_norm_out), int(attn_out.shape[0]), _stream(torch)))
+        return layer_out, next_norm_out
 
     def rmsnorm(self, x: Any, weight: Any, residual: Any = None, eps: float = 1.0e-6) -> tuple[Any, Any]:
         torch = self._torch

@@ -200,6 +200,20 @@ int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t first_layer,
                                   uint32_t n_layers, const void* x_in,
                                   void* x_out, uint32_t tokens, void* stream);
 
+/* One prefill layer with the norms on either side of the MoE half fused in, so the host hands
+ * over what the attention half produced rather than h2:
+ *   after_attn = bf16(attn_out + residual_in); h2 = RMSNorm(after_attn) with the layer's bound
+ *   post-attention norm weight     (prefill_add_rmsnorm_2048_kernel, native_pointwise.hip.cpp:144-182;
+ *                                   call site four_layer_mini_engine.py:8481-8489)
+ *   layer_out = bf16(after_attn + bf16(routed + shared))                    (as aima_moe_prefill_launch)
+ *   next_norm_out = RMSNorm(layer_out) with next_norm_weight, written by the combine kernel itself
+ *                                   (the next layer's input norm, native_pointwise.hip.cpp:109-142)
+ * next_norm_weight / next_norm_out may both be NULL.  All tensors bf16 [tokens,2048]; layer_out
+ * may alias residual_in.  World = 1 only. */
+int aima_moe_prefill_fused_launch(aima_moe_handle* handle, uint32_t layer, const void* attn_out,
+                                  const void* residual_in, const void* next_norm_weight,
+                                  void* layer_out, void* next_norm_out, uint32_t tokens, void* stream);
+
 /* Residual add + RMSNorm with the (weight + 1) rule
  * (native/src/native_pointwise.hip.cpp:109-182).  residual may be NULL (plain
  * norm); residual_out may be NULL. */

@@ -212,6 +212,34 @@ def test_prefill_stack_matches_chained_layers(provider, oracle, gpu_layers, synt
     assert torch.equal(h2.cpu(), h2_cpu)
 
 
+def test_fused_boundary_equals_the_separate_calls(provider, oracle, gpu_layers, synth):
+    """attn_out + residual -> norm -> MoE -> next layer's norm in one call: same bits as the three calls."""
+    device = torch.device("cuda", 0)
+    tokens = 96
+    attn_out = synth.activations(SEED + 910, tokens, "input", 0).to(device)
+    residual_in = synth.activations(SEED + 910, tokens, "residual", 0).to(device)
+    norm0 = gpu_layers(0)["cuda"]["post_attention_layernorm"]
+    norm1 = gpu_layers(1)["cuda"]["post_attention_layernorm"]
+    layer_out, next_norm = provider.prefill_fused(attn_out, residual_in, 0, next_norm_weight=norm1)
+    after_attn, h2 = provider.rmsnorm(attn_out, norm0, residual=residual_in)
+    want = provider.launch_selected_moe(post_attention=h2, residual_hidden=after_attn, model_layer=0)
+    _, want_next = provider.rmsnorm(want, norm1)
+    provider.sync_metrics()
+    assert torch.equal(layer_out, want)
+    assert torch.equal(next_norm, want_next)
+    # the fused exit norm against the CPU oracle's norm of the same rows
+    _, oracle_next = oracle.rmsnorm(layer_out.cpu(), gpu_layers(1)["cpu"]["post_attention_layernorm"])
+    assert torch.equal(next_norm.cpu(), oracle_next)
+    # and the entry (add + norm) against the oracle
+    oracle_after, oracle_h2 = oracle.rmsnorm(attn_out.cpu(), gpu_layers(0)["cpu"]["post_attention_layernorm"],
+                                             residual=residual_in.cpu())
+    assert torch.equal(after_attn.cpu(), oracle_after)
+    assert torch.equal(h2.cpu(), oracle_h2)
+    only_out, none = provider.prefill_fused(attn_out, residual_in, 0)
+    provider.sync_metrics()
+    assert none is None and torch.equal(only_out, want)
+
+
 def test_prefill_argument_checks(provider, package, synth):
     device = torch.device("cuda", 0)
     h2 = synth.activations(1, 4).to(device)
