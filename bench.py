@@ -33,6 +33,8 @@ SEED = 1234
 BYTES_PER_LAYER_TOKEN = 1_048_576 + 50_331_648 + 6_295_552 + 4_096       # router, 8 experts, shared, norm
 BYTES_PER_TOKEN = LAYERS * BYTES_PER_LAYER_TOKEN                          # 2 307 194 880
 FALLBACK_HBM_GBS = 6650.0
+# all weights of one layer: router, 256 experts (gate_up + down), shared expert, shared gate, norm
+BYTES_PER_LAYER_WEIGHTS = 1_048_576 + 256 * 6_291_456 + 6_291_456 + 4_096 + 4_096
 # dram__bytes_read.sum + dram__bytes_write.sum per layer of the decode kernel, from the ncu capture
 # summarised in profiles/ (2-layer case: 118.9 MB per launch)
 DECODE_TRAFFIC_PER_LAYER = 59_460_000
@@ -341,6 +343,52 @@ def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing
             "flop_per_layer": tokens * PREFILL_FLOP_PER_TOKEN, "kernel_launches_per_layer": int(per_call)}
 
 
+def prefill_stack_numbers(package, device, tokens: int, layers: int, iterations: int, routing: str) -> dict:
+    """Device-timed prefill through `layers` MoE layers (BASELINE config 3: T x 40 layers, norm between
+    layers fused into the previous layer's combine kernel), every layer with its own weights."""
+    import torch
+
+    synth = package.synth
+    provider = package.MoeProvider(layers=layers, max_prefill_tokens=tokens)
+    try:
+        keep = []
+        for layer in range(layers):
+            weights = synth.layer_weights_cuda_fast(SEED, layer, device)
+            provider.bind_layer(layer, weights)
+            keep.append(weights)
+        if routing == "zipf":
+            provider.set_router_hooks(synth.zipf_router_bias(SEED).to(device), False)
+        generator = torch.Generator(device=device).manual_seed(SEED)
+        x = torch.randn(tokens, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
+        y = torch.empty_like(x)
+        before = provider.sync_metrics().kernel_launches
+        for _ in range(3):
+            provider.prefill_stack(x, y, 0, layers)
+        per_pass = (provider.sync_metrics().kernel_launches - before) // 3
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(iterations):
+            provider.prefill_stack(x, y, 0, layers)
+        stop.record()
+        torch.cuda.synchronize()
+        provider.sync_metrics()
+        ms = start.elapsed_time(stop) / iterations
+    finally:
+        provider.release()
+    tensor_peak, kind = measured_tensor_peak()
+    hbm_peak, _ = measured_peaks()
+    tflops = tokens * PREFILL_FLOP_PER_TOKEN * layers / (ms * 1.0e-3) / 1.0e12
+    # algorithmic bytes per layer: every weight once + h2, residual, output rows
+    layer_bytes = BYTES_PER_LAYER_WEIGHTS + tokens * HIDDEN * 2 * 3
+    gbs = layer_bytes * layers / (ms * 1.0e-3) / 1.0e9
+    return {"workload": f"prefill_T{tokens}_stack{layers}_{routing} (BASELINE config 3)", "tokens": tokens,
+            "layers": layers, "ms_per_pass": ms, "ms_per_layer": ms / layers, "tokens_per_s": tokens / (ms * 1.0e-3),
+            "achieved_tflops": tflops, "tensor_frac": tflops / tensor_peak, "achieved_gbs": gbs,
+            "hbm_frac": gbs / hbm_peak, "peak_tflops": tensor_peak, "peak_gbs": hbm_peak, "peak_source": kind,
+            "kernel_launches_per_pass": int(per_pass)}
+
+
 def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) -> None:
     """One prefill layer with tokens sharded over `world` GPUs (BASELINE config 3 per bucket)."""
     import torch
@@ -419,6 +467,26 @@ def run_prefill(args) -> None:
     package = load_package()
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
+    if args.stack_layers > 1:
+        numbers = prefill_stack_numbers(package, device, args.tokens, args.stack_layers, max(args.steps, 1),
+                                        args.routing)
+        tensor_bound = args.tokens >= 8192
+        print(json.dumps({
+            "metric": "moe_prefill_tokens_per_second", "value": numbers["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": numbers["ms_per_pass"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": numbers["workload"], "routing": args.routing, "layers": args.stack_layers,
+                       "l2": "inputs larger than L2 (1.6 GB of weights per layer)"},
+            "roofline": {"bound": "tensor" if tensor_bound else "hbm",
+                         "achieved": numbers["achieved_tflops"] if tensor_bound else numbers["achieved_gbs"],
+                         "peak": numbers["peak_tflops"] if tensor_bound else numbers["peak_gbs"],
+                         "unit": "TFLOP/s" if tensor_bound else "GB/s",
+                         "frac": numbers["tensor_frac"] if tensor_bound else numbers["hbm_frac"],
+                         "traffic": None, "peak_source": numbers["peak_source"]},
+            "ms_per_layer": numbers["ms_per_layer"], "tensor_frac": numbers["tensor_frac"],
+            "hbm_frac": numbers["hbm_frac"],
+            "gpu_launches": numbers["kernel_launches_per_pass"] * args.steps}))
+        return
     numbers = prefill_layer_numbers(package, device, args.tokens, max(args.steps, 1), args.routing)
     line = {"metric": "moe_prefill_tokens_per_second", "value": numbers["tokens_per_s"], "unit": "tokens/s",
             "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": numbers["ms_per_layer"],
@@ -446,6 +514,8 @@ def main() -> None:
                         help="decode = the benchmark line; prefill = one-layer prefill line only")
     parser.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
     parser.add_argument("--routing", choices=["zipf", "uniform"], default="zipf")
+    parser.add_argument("--stack-layers", type=int, default=1,
+                        help="--workload prefill: run this many layers through the stack entry point (config 3: 40)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
