@@ -1018,6 +1018,25 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   };
   mark();
 
+  // The shared expert (weights replicated, this rank's tokens) runs on the side stream: its gate/up
+  // product starts at once, its down product once the router kernel has written the sigmoid; it
+  // fills the SMs while the main stream waits for peers and for rows crossing NVLink.
+  cudaStream_t side = ws->side_stream;
+  if ((code = cudaEventRecord(ws->fork_event, stream)) != cudaSuccess ||
+      (code = cudaStreamWaitEvent(side, ws->fork_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "fork of the shared-expert stream");
+  GroupedGemm s{};
+  TcExtra shared_extra{};
+  shared_extra.status = ws->status; shared_extra.sm_count = ws->sm_count;
+  s.max_tiles = (T_loc + kTileRows - 1) / kTileRows; s.dense_rows = T_loc;
+  s.a = static_cast<const __nv_bfloat16*>(call.h2); s.lda = kHidden; s.k = kHidden;
+  s.b0 = call.layer.shared_gate_proj; s.b1 = call.layer.shared_up_proj;
+  s.n = kSharedInter; s.c = ws->shared_act; s.ldc = kSharedInter;
+  shared_extra.a_rows = static_cast<uint64_t>(T_loc); shared_extra.experts_in_b = 1;
+  if ((code = launch_grouped_gemm_tc(kGemmSharedGateUp, s, shared_extra, side)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm shared gate_up");
+  ++count;
+
   // 1. route this rank's tokens (certified router) and stage its h2 rows where peers can read them
   GroupedGemm r{};
   r.max_tiles = (T_loc + kTileRows - 1) / kTileRows; r.dense_rows = T_loc;
@@ -1034,6 +1053,18 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
       dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "prefill_router_certified_kernel");
   count += 2;
+  if ((code = cudaEventRecord(ws->router_event, stream)) != cudaSuccess ||
+      (code = cudaStreamWaitEvent(side, ws->router_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "router event of the shared-expert stream");
+  s.a = ws->shared_act; s.lda = kSharedInter; s.k = kSharedInter;
+  s.b0 = call.layer.shared_down_proj; s.b1 = nullptr;
+  s.n = kHidden; s.c = ws->shared_scaled; s.ldc = kHidden; s.row_scale = ws->shared_sigmoid;
+  shared_extra.a_rows = static_cast<uint64_t>(ws->capacity);
+  if ((code = launch_grouped_gemm_tc(kGemmSharedDown, s, shared_extra, side)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "grouped gemm shared down");
+  ++count;
+  if ((code = cudaEventRecord(ws->join_event, side)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "join event of the shared-expert stream");
   code = cudaMemcpyAsync(mine + L.off_h2, call.h2, static_cast<size_t>(T_loc) * kHidden * 2,
                          cudaMemcpyDeviceToDevice, stream);
   if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemcpyAsync h2 staging");
@@ -1094,22 +1125,9 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   count += 2;
 
   mark();
-  // 7. shared expert for this rank's tokens (weights are replicated) while rows travel
-  GroupedGemm s{};
-  s.max_tiles = (T_loc + kTileRows - 1) / kTileRows; s.dense_rows = T_loc;
-  s.a = static_cast<const __nv_bfloat16*>(call.h2); s.lda = kHidden; s.k = kHidden;
-  s.b0 = call.layer.shared_gate_proj; s.b1 = call.layer.shared_up_proj;
-  s.n = kSharedInter; s.c = ws->shared_act; s.ldc = kSharedInter;
-  extra.a_rows = static_cast<uint64_t>(T_loc); extra.experts_in_b = 1;
-  if ((code = launch_grouped_gemm_tc(kGemmSharedGateUp, s, extra, stream)) != cudaSuccess)
-    return set_error(error, error_bytes, code, "grouped gemm shared gate_up");
-  s.a = ws->shared_act; s.lda = kSharedInter; s.k = kSharedInter;
-  s.b0 = call.layer.shared_down_proj; s.b1 = nullptr;
-  s.n = kHidden; s.c = ws->shared_scaled; s.ldc = kHidden; s.row_scale = ws->shared_sigmoid;
-  extra.a_rows = static_cast<uint64_t>(ws->capacity);
-  if ((code = launch_grouped_gemm_tc(kGemmSharedDown, s, extra, stream)) != cudaSuccess)
-    return set_error(error, error_bytes, code, "grouped gemm shared down");
-  count += 2;
+  // 7. the shared expert's output is needed from here on
+  if ((code = cudaStreamWaitEvent(stream, ws->join_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "join of the shared-expert stream");
 
   // 8. combine, second half: wait for all eight rows of every local token, sum, add
   ep_wait_kernel<<<1, 32, 0, stream>>>(mine, W, L.off_flags_returned, epoch, ws->status);

@@ -310,7 +310,7 @@ int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t* stamps_ns,
 
 /* With tracing on and world > 1: milliseconds of the AIMA_MOE_EP_PREFILL_STAGES
  * stages of the last expert-parallel prefill call on this rank (route, routing
- * exchange, plan, dispatch, expert products, row return, shared expert + wait +
+ * exchange, plan, dispatch, expert products, row return, join of the shared expert + wait +
  * combine), from CUDA events on the call's stream. */
 #define AIMA_MOE_EP_PREFILL_STAGES 7
 int aima_moe_read_ep_prefill_stages(aima_moe_handle* handle, float* stage_ms, uint32_t capacity,
