@@ -56,6 +56,10 @@ struct GroupedGemm {
   int ldc;
   const float* row_scale;      // routing weights [T*8] or sigmoid gate [T]
   const int32_t* sorted_rows;  // flat routed row of each sorted position
+  // tensor-core kernel only: this launch covers tiles [n * part / parts, n * (part + 1) / parts) of the
+  // n tiles of the plan (parts <= 1: all of them), so that copies for one part overlap products of another
+  int part;
+  int parts;
 };
 
 // What the tensor-core launcher needs beyond the problem itself.

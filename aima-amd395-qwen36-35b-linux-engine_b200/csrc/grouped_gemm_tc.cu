@@ -183,13 +183,17 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int n_tiles = g.tile_count != nullptr ? *g.tile_count : g.max_tiles;
-  const int total_units = n_tiles * pb.n_chunks;
+  const int n_tiles_all = g.tile_count != nullptr ? *g.tile_count : g.max_tiles;
+  const int parts = g.parts > 1 ? g.parts : 1;
+  const int tile_lo = static_cast<int>(static_cast<long long>(n_tiles_all) * g.part / parts);
+  const int tile_hi = static_cast<int>(static_cast<long long>(n_tiles_all) * (g.part + 1) / parts);
+  const int total_units = (tile_hi - tile_lo) * pb.n_chunks;
   const int k_blocks = g.k / kBK;
 
   auto unit_tile = [&](int unit, int& tile, int& chunk, int& expert, int& row0, int& rows) {
     tile = unit / pb.n_chunks;
     chunk = unit - tile * pb.n_chunks;
+    tile += tile_lo;
     if (g.tile_expert != nullptr) {
       expert = g.tile_expert[tile] - g.expert_base;
       row0 = g.tile_row0[tile];

@@ -354,6 +354,9 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
     handle->prefill.use_simt_gemm = (config->flags & AIMA_MOE_FLAG_SIMT_PRODUCTS) != 0;
     handle->prefill.exact_router = (config->flags & AIMA_MOE_FLAG_EXACT_ROUTER) != 0;
     handle->prefill.fused_dispatch = (config->flags & AIMA_MOE_FLAG_FUSED_DISPATCH) != 0;
+    handle->prefill.ep_parts = (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_4)   ? 4
+                               : (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_2) ? 2
+                                                                               : 1;
   }
   handle->metrics.struct_bytes = sizeof(aima_moe_metrics);
   handle->metrics.workspace_bytes = handle->decode_scratch_bytes + sizeof(LayerPtrs) * kMaxLayers +

@@ -653,41 +653,69 @@ __global__ void ep_wait_kernel(const uint8_t* region, int world, size_t off_flag
   }
 }
 
+// Sorted-row range of part `part` of `parts` of the plan's tiles (the same split the product kernel
+// makes): tiles follow the sorted order, so a range of tiles is a range of rows.
+__device__ __forceinline__ void part_rows(const int32_t* __restrict__ expert_offsets,
+                                          const int32_t* __restrict__ tile_row0,
+                                          const int32_t* __restrict__ tile_count, int part, int parts,
+                                          int& row_lo, int& row_hi) {
+  const int total = expert_offsets[kExperts];
+  const int n_tiles = *tile_count;
+  const int tile_lo = static_cast<int>(static_cast<long long>(n_tiles) * part / parts);
+  const int tile_hi = static_cast<int>(static_cast<long long>(n_tiles) * (part + 1) / parts);
+  row_lo = tile_lo < n_tiles ? tile_row0[tile_lo] : total;
+  row_hi = tile_hi < n_tiles ? tile_row0[tile_hi] : total;
+}
+
 // dispatch: row `pos` of this GPU's plan <- h2 row of its token, wherever that token lives
 __global__ void __launch_bounds__(256)
 ep_gather_rows_kernel(EpPointers peers, size_t off_h2, int tokens_per_rank,
                       const int32_t* __restrict__ sorted_rows, const int32_t* __restrict__ expert_offsets,
-                      __nv_bfloat16* __restrict__ gathered) {
+                      const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ tile_count,
+                      int part, int parts, __nv_bfloat16* __restrict__ gathered) {
   const int lane = threadIdx.x & 31;
-  const int pos = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (pos >= expert_offsets[kExperts]) return;
-  const int token = sorted_rows[pos] >> 3;
-  const int owner = token / tokens_per_rank;
-  const int local = token - owner * tokens_per_rank;
-  const uint4* src = reinterpret_cast<const uint4*>(peers.region[owner] + off_h2) +
-                     static_cast<size_t>(local) * (kHidden / 8);
-  uint4* dst = reinterpret_cast<uint4*>(gathered + static_cast<size_t>(pos) * kHidden);
+  int row_lo, row_hi;
+  part_rows(expert_offsets, tile_row0, tile_count, part, parts, row_lo, row_hi);
+  // a small grid that loops: the copy kernels share the SMs with the product kernels of another
+  // part, whose one-block-per-SM grid must find room at once
+  for (int pos = row_lo + blockIdx.x * 8 + (threadIdx.x >> 5); pos < row_hi; pos += gridDim.x * 8) {
+    const int token = sorted_rows[pos] >> 3;
+    const int owner = token / tokens_per_rank;
+    const int local = token - owner * tokens_per_rank;
+    const uint4* src = reinterpret_cast<const uint4*>(peers.region[owner] + off_h2) +
+                       static_cast<size_t>(local) * (kHidden / 8);
+    uint4* dst = reinterpret_cast<uint4*>(gathered + static_cast<size_t>(pos) * kHidden);
+    uint4 v[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) dst[i * 32 + lane] = src[i * 32 + lane];
+    for (int i = 0; i < 8; ++i) v[i] = src[i * 32 + lane];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dst[i * 32 + lane] = v[i];
+  }
 }
 
 // combine, first half: the weighted expert output of plan row `pos` goes to the GPU that owns
 // its token, at that token's (token, slot) position
 __global__ void __launch_bounds__(256)
 ep_return_rows_kernel(const __nv_bfloat16* __restrict__ expert_down, const int32_t* __restrict__ sorted_rows,
-                      const int32_t* __restrict__ expert_offsets, EpPointers peers, size_t off_return,
-                      int tokens_per_rank) {
+                      const int32_t* __restrict__ expert_offsets,
+                      const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ tile_count,
+                      int part, int parts, EpPointers peers, size_t off_return, int tokens_per_rank) {
   const int lane = threadIdx.x & 31;
-  const int pos = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (pos >= expert_offsets[kExperts]) return;
-  const int flat = sorted_rows[pos];
-  const int owner = (flat >> 3) / tokens_per_rank;
-  const int local_flat = flat - owner * tokens_per_rank * kTopK;
-  const uint4* src = reinterpret_cast<const uint4*>(expert_down + static_cast<size_t>(pos) * kHidden);
-  uint4* dst = reinterpret_cast<uint4*>(peers.region[owner] + off_return) +
-               static_cast<size_t>(local_flat) * (kHidden / 8);
+  int row_lo, row_hi;
+  part_rows(expert_offsets, tile_row0, tile_count, part, parts, row_lo, row_hi);
+  for (int pos = row_lo + blockIdx.x * 8 + (threadIdx.x >> 5); pos < row_hi; pos += gridDim.x * 8) {
+    const int flat = sorted_rows[pos];
+    const int owner = (flat >> 3) / tokens_per_rank;
+    const int local_flat = flat - owner * tokens_per_rank * kTopK;
+    const uint4* src = reinterpret_cast<const uint4*>(expert_down + static_cast<size_t>(pos) * kHidden);
+    uint4* dst = reinterpret_cast<uint4*>(peers.region[owner] + off_return) +
+                 static_cast<size_t>(local_flat) * (kHidden / 8);
+    uint4 v[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) dst[i * 32 + lane] = src[i * 32 + lane];
+    for (int i = 0; i < 8; ++i) v[i] = src[i * 32 + lane];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dst[i * 32 + lane] = v[i];
+  }
 }
 
 // qualification view: weighted expert output rows in flat (token, slot) order
@@ -775,6 +803,14 @@ int prefill_workspace_allocate(PrefillWorkspace* ws, uint32_t capacity_tokens, i
   if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->fork_event, cudaEventDisableTiming);
   if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->router_event, cudaEventDisableTiming);
   if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->join_event, cudaEventDisableTiming);
+  if (code == cudaSuccess) code = cudaStreamCreateWithFlags(&ws->inbound_stream, cudaStreamNonBlocking);
+  if (code == cudaSuccess) code = cudaStreamCreateWithFlags(&ws->outbound_stream, cudaStreamNonBlocking);
+  if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->plan_event, cudaEventDisableTiming);
+  if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->returned_event, cudaEventDisableTiming);
+  for (int k = 0; k < PrefillWorkspace::kMaxParts && code == cudaSuccess; ++k) {
+    code = cudaEventCreateWithFlags(&ws->gathered_event[k], cudaEventDisableTiming);
+    if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->computed_event[k], cudaEventDisableTiming);
+  }
   if (code != cudaSuccess) return set_error(error, error_bytes, code, "side stream / events of the prefill workspace");
   ws->total_bytes = l.total;
   ws->capacity = static_cast<int>(capacity_tokens);
@@ -813,6 +849,14 @@ void prefill_workspace_free(PrefillWorkspace* ws) {
   if (ws->router_event != nullptr) cudaEventDestroy(ws->router_event);
   if (ws->join_event != nullptr) cudaEventDestroy(ws->join_event);
   if (ws->side_stream != nullptr) cudaStreamDestroy(ws->side_stream);
+  if (ws->plan_event != nullptr) cudaEventDestroy(ws->plan_event);
+  if (ws->returned_event != nullptr) cudaEventDestroy(ws->returned_event);
+  for (int k = 0; k < PrefillWorkspace::kMaxParts; ++k) {
+    if (ws->gathered_event[k] != nullptr) cudaEventDestroy(ws->gathered_event[k]);
+    if (ws->computed_event[k] != nullptr) cudaEventDestroy(ws->computed_event[k]);
+  }
+  if (ws->inbound_stream != nullptr) cudaStreamDestroy(ws->inbound_stream);
+  if (ws->outbound_stream != nullptr) cudaStreamDestroy(ws->outbound_stream);
   *ws = PrefillWorkspace{};
 }
 
@@ -1088,41 +1132,69 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
     return set_error(error, error_bytes, code, "dispatch plan");
 
   mark();
-  // 4. dispatch: pull the rows over NVLink into expert order
-  ep_gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(peers, L.off_h2, T_loc, ws->sorted_rows,
-                                                            ws->expert_offsets, ws->gathered);
-  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "ep_gather_rows_kernel");
-  ++count;
-
-  mark();
-  // 5. the local experts' products
+  // 4.-6. dispatch, products and row return, pipelined over `parts` ranges of the plan's tiles:
+  //   inbound stream   rows of part k pulled over NVLink into expert order
+  //   caller's stream  gate_up and down products of part k once its rows are here
+  //   outbound stream  weighted rows of part k stored to the GPUs that own their tokens
+  const int parts = ws->ep_parts >= 1 && ws->ep_parts <= PrefillWorkspace::kMaxParts ? ws->ep_parts : 1;
+  const int part_blocks = min(((max_tiles_for(T) / parts + 1) * kTileRows + 7) / 8, 2 * ws->sm_count);
+  cudaStream_t inbound = ws->inbound_stream, outbound = ws->outbound_stream;
+  if ((code = cudaEventRecord(ws->plan_event, stream)) != cudaSuccess ||
+      (code = cudaStreamWaitEvent(inbound, ws->plan_event, 0)) != cudaSuccess ||
+      (code = cudaStreamWaitEvent(outbound, ws->plan_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "fork of the dispatch / return streams");
+  for (int k = 0; k < parts; ++k) {
+    ep_gather_rows_kernel<<<part_blocks, 256, 0, inbound>>>(peers, L.off_h2, T_loc, ws->sorted_rows,
+                                                            ws->expert_offsets, ws->tile_row0, ws->tile_count,
+                                                            k, parts, ws->gathered);
+    if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "ep_gather_rows_kernel");
+    if ((code = cudaEventRecord(ws->gathered_event[k], inbound)) != cudaSuccess)
+      return set_error(error, error_bytes, code, "gathered event");
+    ++count;
+  }
   GroupedGemm g{};
   g.tile_expert = ws->tile_expert; g.tile_row0 = ws->tile_row0; g.tile_rows = ws->tile_rows;
   g.tile_count = ws->tile_count; g.max_tiles = max_tiles_for(T); g.dense_rows = 0;
   g.expert_base = expert_lo;
-  g.a = ws->gathered; g.lda = kHidden; g.k = kHidden;
-  g.b0 = call.layer.expert_gate_up; g.b_expert_stride = static_cast<size_t>(2 * kInter) * kHidden;
-  g.n = kInter; g.c = ws->expert_act; g.ldc = kInter;
+  g.parts = parts;
   TcExtra extra{};
   extra.status = ws->status; extra.sm_count = ws->sm_count;
   extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK; extra.experts_in_b = call.experts_local;
-  if ((code = launch_grouped_gemm_tc(kGemmExpertGateUp, g, extra, stream)) != cudaSuccess)
-    return set_error(error, error_bytes, code, "grouped gemm expert gate_up");
-  g.a = ws->expert_act; g.lda = kInter; g.k = kInter;
-  g.b0 = call.layer.expert_down; g.b_expert_stride = static_cast<size_t>(kHidden) * kInter;
-  g.n = kHidden; g.c = ws->expert_down; g.ldc = kHidden;
-  g.row_scale = weights_all; g.sorted_rows = ws->sorted_rows;
-  if ((code = launch_grouped_gemm_tc(kGemmExpertDown, g, extra, stream)) != cudaSuccess)
-    return set_error(error, error_bytes, code, "grouped gemm expert down");
-  count += 2;
-
+  for (int k = 0; k < parts; ++k) {
+    if ((code = cudaStreamWaitEvent(stream, ws->gathered_event[k], 0)) != cudaSuccess)
+      return set_error(error, error_bytes, code, "wait for gathered rows");
+    if (k == 0) mark();
+    g.part = k;
+    g.a = ws->gathered; g.lda = kHidden; g.k = kHidden;
+    g.b0 = call.layer.expert_gate_up; g.b_expert_stride = static_cast<size_t>(2 * kInter) * kHidden;
+    g.n = kInter; g.c = ws->expert_act; g.ldc = kInter;
+    g.row_scale = nullptr; g.sorted_rows = ws->sorted_rows;
+    if ((code = launch_grouped_gemm_tc(kGemmExpertGateUp, g, extra, stream)) != cudaSuccess)
+      return set_error(error, error_bytes, code, "grouped gemm expert gate_up");
+    g.a = ws->expert_act; g.lda = kInter; g.k = kInter;
+    g.b0 = call.layer.expert_down; g.b_expert_stride = static_cast<size_t>(kHidden) * kInter;
+    g.n = kHidden; g.c = ws->expert_down; g.ldc = kHidden;
+    g.row_scale = weights_all;
+    if ((code = launch_grouped_gemm_tc(kGemmExpertDown, g, extra, stream)) != cudaSuccess)
+      return set_error(error, error_bytes, code, "grouped gemm expert down");
+    count += 2;
+    if ((code = cudaEventRecord(ws->computed_event[k], stream)) != cudaSuccess ||
+        (code = cudaStreamWaitEvent(outbound, ws->computed_event[k], 0)) != cudaSuccess)
+      return set_error(error, error_bytes, code, "computed event");
+    ep_return_rows_kernel<<<part_blocks, 256, 0, outbound>>>(ws->expert_down, ws->sorted_rows, ws->expert_offsets,
+                                                             ws->tile_row0, ws->tile_count, k, parts, peers,
+                                                             L.off_return, T_loc);
+    if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "ep_return_rows_kernel");
+    ++count;
+  }
   mark();
-  // 6. combine, first half: rows back to the GPUs that own their tokens, then flags
-  ep_return_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(ws->expert_down, ws->sorted_rows, ws->expert_offsets,
-                                                            peers, L.off_return, T_loc);
-  ep_signal_kernel<<<1, 32, 0, stream>>>(peers, W, ep->rank, L.off_flags_returned, epoch);
+  // all rows stored: raise this rank's flag on every GPU, then rejoin the caller's stream
+  ep_signal_kernel<<<1, 32, 0, outbound>>>(peers, W, ep->rank, L.off_flags_returned, epoch);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "row return");
-  count += 2;
+  ++count;
+  if ((code = cudaEventRecord(ws->returned_event, outbound)) != cudaSuccess ||
+      (code = cudaStreamWaitEvent(stream, ws->returned_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "join of the return stream");
 
   mark();
   // 7. the shared expert's output is needed from here on

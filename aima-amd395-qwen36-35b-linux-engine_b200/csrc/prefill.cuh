@@ -25,6 +25,16 @@ struct PrefillWorkspace {
   cudaEvent_t fork_event = nullptr;     // caller's stream: inputs of this call are ready
   cudaEvent_t router_event = nullptr;   // caller's stream: sigmoid of the shared gate is written
   cudaEvent_t join_event = nullptr;     // side stream: shared expert output is written
+  // Expert parallelism: rows arrive (dispatch) and leave (row return) on two more streams, part by
+  // part, while the products of another part run on the caller's stream.
+  static constexpr int kMaxParts = 8;
+  int ep_parts = 1;                               // 1: dispatch, products and return run one after the other
+  cudaStream_t inbound_stream = nullptr;
+  cudaStream_t outbound_stream = nullptr;
+  cudaEvent_t plan_event = nullptr;               // caller's stream: the plan is written
+  cudaEvent_t gathered_event[kMaxParts] = {};     // inbound stream: rows of part k are here
+  cudaEvent_t computed_event[kMaxParts] = {};     // caller's stream: products of part k are written
+  cudaEvent_t returned_event = nullptr;           // outbound stream: all rows are stored and flagged
   // router outputs
   int32_t* topk_ids = nullptr;        // [T, 8]
   float* topk_scores = nullptr;       // [T, 8]

@@ -181,6 +181,8 @@ NOALLOC_MAX_LAYERS = 8
 FLAG_SIMT_PRODUCTS = 1
 FLAG_EXACT_ROUTER = 2
 FLAG_FUSED_DISPATCH = 8
+FLAG_EP_PIPELINE_2 = 32
+FLAG_EP_PIPELINE_4 = 64
 
 
 def layer_weights_struct(weights: Mapping[str, Any]) -> LayerWeights:

@@ -403,7 +403,8 @@ def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) ->
     dist.init_process_group("nccl", device_id=device)
     per_rank_experts = 256 // world
     tokens_local = args.tokens // world
-    provider = package.MoeProvider(layers=1, max_prefill_tokens=args.tokens, world=world, rank=rank)
+    flags = {1: 0, 2: package.provider.FLAG_EP_PIPELINE_2, 4: package.provider.FLAG_EP_PIPELINE_4}[args.ep_pipeline]
+    provider = package.MoeProvider(layers=1, max_prefill_tokens=args.tokens, world=world, rank=rank, flags=flags)
     weights = synth.layer_weights_cuda_fast(SEED, 0, device, rank * per_rank_experts, (rank + 1) * per_rank_experts)
     provider.bind_layer(0, weights)
     provider.ep_connect_all(dist.new_group(backend="gloo"))
@@ -443,7 +444,7 @@ def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) ->
             "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"prefill_T{args.tokens}_1layer_{args.routing} (BASELINE config 3 bucket)",
-                       "routing": args.routing, "tokens_per_gpu": tokens_local,
+                       "routing": args.routing, "tokens_per_gpu": tokens_local, "pipeline_parts": args.ep_pipeline,
                        "multi_gpu": f"expert parallel, {per_rank_experts} experts per GPU, dispatch by peer loads, "
                                     "combine by peer stores over NVLink"},
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak * world, "unit": "TFLOP/s",
@@ -514,6 +515,8 @@ def main() -> None:
                         help="decode = the benchmark line; prefill = one-layer prefill line only")
     parser.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
     parser.add_argument("--routing", choices=["zipf", "uniform"], default="zipf")
+    parser.add_argument("--ep-pipeline", type=int, choices=[1, 2, 4], default=1,
+                        help="--workload prefill on N > 1 GPUs: parts of the dispatch / products / return pipeline")
     parser.add_argument("--stack-layers", type=int, default=1,
                         help="--workload prefill: run this many layers through the stack entry point (config 3: 40)")
     args = parser.parse_args()

@@ -89,6 +89,12 @@ typedef struct aima_moe_config {
  * load per stage.  Same bits; slower on B200 (128 one-row boxes per stage instead of one box),
  * kept for measurement. */
 #define AIMA_MOE_FLAG_FUSED_DISPATCH 8u
+/* Expert-parallel prefill: split the plan's tiles into 2 (or 4) parts and pull the rows of one part
+ * over NVLink / store the results of another back while the products of a third run, on three
+ * streams.  Same bits.  On 2 GPUs it measured no faster than running the three steps one after
+ * the other (the copies and the HBM-bound products slow each other down), so it is off by default. */
+#define AIMA_MOE_FLAG_EP_PIPELINE_2 32u
+#define AIMA_MOE_FLAG_EP_PIPELINE_4 64u
 
 /* One layer's tensors in checkpoint layout
  * (doc/reference/amd395-qwen36-35b-a3b-bf16/qwen36-shape-manifest.json:162-180,

@@ -227,6 +227,20 @@ def _rank_main(rank: int, world: int, port: int, results) -> None:
         dist.barrier()
         outputs.append(_bits(out))
         prefill.release()
+        # the pipelined variant (dispatch / products / return in two parts on three streams): same bits
+        piped = package.MoeProvider(layers=1, max_prefill_tokens=128 * world, world=world, rank=rank,
+                                    flags=package.provider.FLAG_EP_PIPELINE_2)
+        piped.bind_layer(0, keep[0])
+        piped.ep_connect_all()
+        dist.barrier()
+        again = piped.launch_selected_moe(post_attention=h2_all[rank * 128:(rank + 1) * 128].to(device),
+                                          residual_hidden=resid_all[rank * 128:(rank + 1) * 128].to(device),
+                                          model_layer=0)
+        piped.sync_metrics()
+        dist.barrier()
+        if not torch.equal(again, out):
+            raise AssertionError(f"rank {rank}: pipelined expert-parallel prefill differs from the plain one")
+        piped.release()
         results.put((rank, outputs))
     finally:
         dist.destroy_process_group()
