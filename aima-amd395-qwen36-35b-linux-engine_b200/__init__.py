@@ -8,10 +8,11 @@ parent on ``sys.path`` and import it through ``importlib.import_module``.
 from .provider import (  # noqa: F401
     AimaMoeError,
     MoeLibrary,
+    LmHead,
     MoeProvider,
     library_path,
     load_library,
 )
 from . import synth  # noqa: F401
 
-__all__ = ["AimaMoeError", "MoeLibrary", "MoeProvider", "library_path", "load_library", "synth"]
+__all__ = ["AimaMoeError", "LmHead", "MoeLibrary", "MoeProvider", "library_path", "load_library", "synth"]

@@ -1,0 +1,287 @@
+// LM head with a certified top-1: a row-wise int8 copy of the vocabulary matrix is scanned for
+// every token (one byte per weight instead of two), Cauchy-Schwarz bounds around the approximate
+// logits decide which rows can still win, and only those are evaluated exactly in BF16.
+//
+// Follows NativeLmHeadStore::build / quantize_lm_head_rowwise_kernel
+// (native/src/native_lm_head.hip.cpp:53-115, 126-176), the row-wise int8 GEMV of
+// benchmarks/shape-lab/four_layer_mini_engine.py:1223-1258 and launch_native_lm_head_certificate
+// (native/src/native_lm_head_certificate.hip.cpp:44-275): same bounds, same outward rounding,
+// same capacity of 1024 candidates, same tie rule (equal logits -> lowest token id).
+// The scan is the bandwidth-bound kernel: rows x 2048 bytes per token.
+#include "lm_head.cuh"
+
+#include <math_constants.h>
+
+namespace aima {
+namespace {
+
+constexpr int kLmThreads = 256;
+constexpr int kLmBoundBlocks = 256;
+constexpr int kResidualSafetyUlps = 8;
+constexpr int kHiddenSafetyUlps = 4;
+
+// ---------------------------------------------------------------------------
+// Build: q = clamp(rint(w / scale)), scale = max|w| * fl(1/127), residual_l2 = ||w - q * scale||_2
+// rounded up by 8 ULPs.  One block per row; thread t takes columns t, t + 256, ...; sums are
+// FP64, added pairwise in shared memory (offset 128, 64, ... 1) -- the order the CPU oracle uses.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kLmThreads)
+lm_head_quantize_kernel(const __nv_bfloat16* __restrict__ source, int8_t* __restrict__ q_weight,
+                        float* __restrict__ scales, float* __restrict__ residual_l2) {
+  __shared__ float reduction[kLmThreads];
+  __shared__ double squared[kLmThreads];
+  const size_t base = static_cast<size_t>(blockIdx.x) * kHidden;
+  const int t = threadIdx.x;
+  float local_max = 0.0f;
+  for (int column = t; column < kHidden; column += kLmThreads)
+    local_max = fmaxf(local_max, fabsf(__bfloat162float(source[base + column])));
+  reduction[t] = local_max;
+  __syncthreads();
+  for (int offset = kLmThreads / 2; offset > 0; offset >>= 1) {
+    if (t < offset) reduction[t] = fmaxf(reduction[t], reduction[t + offset]);
+    __syncthreads();
+  }
+  const float maximum = fmaxf(reduction[0], 1.0e-12f);
+  const float scale = __fmul_rn(maximum, 1.0f / 127.0f);   // multiplication by the rounded reciprocal
+  if (t == 0) scales[blockIdx.x] = scale;
+  double local_squared = 0.0;
+  for (int column = t; column < kHidden; column += kLmThreads) {
+    const float value = __bfloat162float(source[base + column]);
+    const float rounded = rintf(__fdiv_rn(value, scale));
+    const int quantized = static_cast<int>(fminf(127.0f, fmaxf(-127.0f, rounded)));
+    q_weight[base + column] = static_cast<int8_t>(quantized);
+    const float reconstructed = __fmul_rn(static_cast<float>(quantized), scale);
+    const double residual = static_cast<double>(__fsub_rn(value, reconstructed));
+    local_squared = __dadd_rn(local_squared, __dmul_rn(residual, residual));
+  }
+  squared[t] = local_squared;
+  __syncthreads();
+  for (int offset = kLmThreads / 2; offset > 0; offset >>= 1) {
+    if (t < offset) squared[t] = __dadd_rn(squared[t], squared[t + offset]);
+    __syncthreads();
+  }
+  if (t == 0) {
+    float norm = static_cast<float>(sqrt(squared[0]));
+    for (int step = 0; step < kResidualSafetyUlps; ++step) norm = nextafterf(norm, CUDART_INF_F);
+    residual_l2[blockIdx.x] = norm;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Scan: approximate[row] = scale[row] * sum_c q[row, c] * hidden[c], FP32.
+// One warp per row at a time; lane l owns the 16-byte pieces l, l + 32, l + 64, l + 96 of the
+// row (64 weights), multiplies them in ascending order into one accumulator, then the warp
+// butterfly (16, 8, 4, 2, 1).  The lane's 64 hidden values stay in registers for all its rows.
+// int8 -> FP32 without the conversion pipe: the byte, biased by 128, is placed in the mantissa
+// of 2^23 and 2^23 + 128 is subtracted -- exact.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float byte_to_float(uint32_t biased_word, uint32_t selector) {
+  return __fsub_rn(__uint_as_float(__byte_perm(biased_word, 0x4B000000u, selector)), 8388736.0f);
+}
+
+__device__ __forceinline__ float fma_word(uint32_t word, const float* x, float acc) {
+  const uint32_t biased = word ^ 0x80808080u;
+  acc = __fmaf_rn(byte_to_float(biased, 0x7540u), x[0], acc);
+  acc = __fmaf_rn(byte_to_float(biased, 0x7541u), x[1], acc);
+  acc = __fmaf_rn(byte_to_float(biased, 0x7542u), x[2], acc);
+  acc = __fmaf_rn(byte_to_float(biased, 0x7543u), x[3], acc);
+  return acc;
+}
+
+constexpr int kScanWarps = 8;
+
+__global__ void __launch_bounds__(kScanWarps * 32)
+lm_head_scan_kernel(const int8_t* __restrict__ q_weight, const float* __restrict__ scales,
+                    const __nv_bfloat16* __restrict__ hidden, float* __restrict__ logits, int rows) {
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * kScanWarps + (threadIdx.x >> 5);
+  const int warps_total = gridDim.x * kScanWarps;
+  float x[64];
+#pragma unroll
+  for (int piece = 0; piece < 4; ++piece) {
+    // 16 weights of piece (32 piece + lane): hidden elements 16 (32 piece + lane) .. + 15
+    const uint4* src = reinterpret_cast<const uint4*>(hidden) + 2 * (32 * piece + lane);
+    unpack8(__ldg(src), x + 16 * piece);
+    unpack8(__ldg(src + 1), x + 16 * piece + 8);
+  }
+  for (int row = warp_global; row < rows; row += warps_total) {
+    const uint4* qrow = reinterpret_cast<const uint4*>(q_weight + static_cast<size_t>(row) * kHidden) + lane;
+    uint4 w[4];
+#pragma unroll
+    for (int piece = 0; piece < 4; ++piece) w[piece] = __ldcs(qrow + 32 * piece);
+    float acc = 0.0f;
+#pragma unroll
+    for (int piece = 0; piece < 4; ++piece) {
+      acc = fma_word(w[piece].x, x + 16 * piece, acc);
+      acc = fma_word(w[piece].y, x + 16 * piece + 4, acc);
+      acc = fma_word(w[piece].z, x + 16 * piece + 8, acc);
+      acc = fma_word(w[piece].w, x + 16 * piece + 12, acc);
+    }
+    acc = butterfly_sum(acc);
+    if (lane == 0) logits[row] = __fmul_rn(acc, scales[row]);
+  }
+}
+
+// ||hidden||_2 in FP64 (thread-strided partials, pairwise tree), rounded to FP32 and up 4 ULPs.
+__global__ void __launch_bounds__(kLmThreads)
+lm_head_hidden_norm_kernel(const __nv_bfloat16* __restrict__ hidden, aima_moe_lm_head_result* wire) {
+  __shared__ double reduction[kLmThreads];
+  const int t = threadIdx.x;
+  double local = 0.0;
+  for (int index = t; index < kHidden; index += kLmThreads) {
+    const double value = static_cast<double>(__bfloat162float(hidden[index]));
+    local = __dadd_rn(local, __dmul_rn(value, value));
+  }
+  reduction[t] = local;
+  __syncthreads();
+  for (int stride = kLmThreads / 2; stride != 0; stride >>= 1) {
+    if (t < stride) reduction[t] = __dadd_rn(reduction[t], reduction[t + stride]);
+    __syncthreads();
+  }
+  if (t == 0) {
+    float norm = static_cast<float>(sqrt(reduction[0]));
+    for (int step = 0; step < kHiddenSafetyUlps; ++step) norm = nextafterf(norm, CUDART_INF_F);
+    wire->hidden_l2 = norm;
+  }
+}
+
+__device__ __forceinline__ float row_error(float residual, float hidden_l2) {
+  return nextafterf(__fmul_rn(residual, hidden_l2), CUDART_INF_F);
+}
+
+// largest lower bound over all rows, first per block ...
+__global__ void __launch_bounds__(kLmThreads)
+lm_head_bound_kernel(const float* __restrict__ logits, const float* __restrict__ residual_l2,
+                     const aima_moe_lm_head_result* __restrict__ wire, float* __restrict__ partial, int rows) {
+  __shared__ float reduction[kLmThreads];
+  const float hidden_l2 = wire->hidden_l2;
+  float local_max = -CUDART_INF_F;
+  for (int row = blockIdx.x * kLmThreads + threadIdx.x; row < rows; row += gridDim.x * kLmThreads) {
+    const float lower = nextafterf(__fsub_rn(logits[row], row_error(residual_l2[row], hidden_l2)), -CUDART_INF_F);
+    local_max = fmaxf(local_max, lower);
+  }
+  reduction[threadIdx.x] = local_max;
+  __syncthreads();
+  for (int stride = kLmThreads / 2; stride != 0; stride >>= 1) {
+    if (threadIdx.x < stride) reduction[threadIdx.x] = fmaxf(reduction[threadIdx.x], reduction[threadIdx.x + stride]);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[blockIdx.x] = reduction[0];
+}
+
+// ... then over the blocks; also resets the candidate list
+__global__ void __launch_bounds__(kLmBoundBlocks)
+lm_head_reduce_kernel(const float* __restrict__ partial, aima_moe_lm_head_result* wire) {
+  __shared__ float reduction[kLmBoundBlocks];
+  reduction[threadIdx.x] = partial[threadIdx.x];
+  __syncthreads();
+  for (int stride = kLmBoundBlocks / 2; stride != 0; stride >>= 1) {
+    if (threadIdx.x < stride) reduction[threadIdx.x] = fmaxf(reduction[threadIdx.x], reduction[threadIdx.x + stride]);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    wire->maximum_lower_bound = reduction[0];
+    wire->candidate_count = 0;
+    wire->overflow = 0;
+  }
+}
+
+// every row whose upper bound reaches the largest lower bound is a candidate
+__global__ void __launch_bounds__(kLmThreads)
+lm_head_collect_kernel(const float* __restrict__ logits, const float* __restrict__ residual_l2,
+                       aima_moe_lm_head_result* wire, uint32_t* __restrict__ candidate_ids, int rows) {
+  const int row = blockIdx.x * kLmThreads + threadIdx.x;
+  if (row >= rows) return;
+  const float upper = nextafterf(__fadd_rn(logits[row], row_error(residual_l2[row], wire->hidden_l2)), CUDART_INF_F);
+  if (upper < wire->maximum_lower_bound) return;
+  const uint32_t slot = atomicAdd(&wire->candidate_count, 1u);
+  if (slot < AIMA_MOE_LM_HEAD_CANDIDATES) candidate_ids[slot] = static_cast<uint32_t>(row);
+  else wire->overflow = 1;
+}
+
+// exact BF16 logit of every candidate straight from the raw matrix (no gathered copy): the
+// canonical warp dot, rounded to BF16 like the reference's N = 1 GEMV provider
+constexpr int kExactWarps = 8;
+__global__ void __launch_bounds__(kExactWarps * 32)
+lm_head_exact_kernel(const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ hidden,
+                     const aima_moe_lm_head_result* __restrict__ wire, const uint32_t* __restrict__ candidate_ids,
+                     __nv_bfloat16* __restrict__ candidate_logits) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t candidate = blockIdx.x * kExactWarps + (threadIdx.x >> 5);
+  const uint32_t count = min(wire->candidate_count, static_cast<uint32_t>(AIMA_MOE_LM_HEAD_CANDIDATES));
+  if (candidate >= count) return;
+  const uint4* wrow = reinterpret_cast<const uint4*>(weight + static_cast<size_t>(candidate_ids[candidate]) * kHidden) + lane;
+  const uint4* xrow = reinterpret_cast<const uint4*>(hidden) + lane;
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kHidden / 256; ++i) {
+    float xf[8];
+    unpack8(__ldg(xrow + i * 32), xf);
+    acc = fma8(xf, __ldg(wrow + i * 32), acc);
+  }
+  acc = butterfly_sum(acc);
+  if (lane == 0) candidate_logits[candidate] = __float2bfloat16_rn(acc);
+}
+
+__device__ __forceinline__ bool better(float value, uint32_t index, float current, uint32_t current_index) {
+  return value > current || (value == current && index < current_index);
+}
+
+// exact top-1 over the candidates; their exact logits replace the approximate ones in `logits`
+__global__ void __launch_bounds__(kLmThreads)
+lm_head_argmax_kernel(const __nv_bfloat16* __restrict__ candidate_logits, aima_moe_lm_head_result* wire,
+                      const uint32_t* __restrict__ candidate_ids, float* __restrict__ logits) {
+  __shared__ float values[kLmThreads];
+  __shared__ uint32_t indices[kLmThreads];
+  const uint32_t count = min(wire->candidate_count, static_cast<uint32_t>(AIMA_MOE_LM_HEAD_CANDIDATES));
+  float local_value = -CUDART_INF_F;
+  uint32_t local_index = 0;
+  for (uint32_t candidate = threadIdx.x; candidate < count; candidate += kLmThreads) {
+    const float value = __bfloat162float(candidate_logits[candidate]);
+    const uint32_t token = candidate_ids[candidate];
+    logits[token] = value;
+    if (better(value, token, local_value, local_index)) { local_value = value; local_index = token; }
+  }
+  values[threadIdx.x] = local_value;
+  indices[threadIdx.x] = local_index;
+  __syncthreads();
+  for (int stride = kLmThreads / 2; stride != 0; stride >>= 1) {
+    if (threadIdx.x < stride &&
+        better(values[threadIdx.x + stride], indices[threadIdx.x + stride], values[threadIdx.x], indices[threadIdx.x])) {
+      values[threadIdx.x] = values[threadIdx.x + stride];
+      indices[threadIdx.x] = indices[threadIdx.x + stride];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    wire->exact_top1_logit = values[0];
+    wire->exact_top1_token_id = indices[0];
+  }
+}
+
+}  // namespace
+
+cudaError_t lm_head_quantize(const void* weight, int rows, int8_t* q_weight, float* scales, float* residual_l2,
+                             cudaStream_t stream) {
+  lm_head_quantize_kernel<<<rows, kLmThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(weight), q_weight,
+                                                           scales, residual_l2);
+  return cudaGetLastError();
+}
+
+cudaError_t lm_head_certify(const LmHeadBuffers& b, const void* weight, const void* hidden, float* logits,
+                            int rows, int sm_count, cudaStream_t stream, int* launches) {
+  const __nv_bfloat16* h = static_cast<const __nv_bfloat16*>(hidden);
+  lm_head_scan_kernel<<<sm_count * 8, kScanWarps * 32, 0, stream>>>(b.q_weight, b.scales, h, logits, rows);
+  lm_head_hidden_norm_kernel<<<1, kLmThreads, 0, stream>>>(h, b.wire);
+  lm_head_bound_kernel<<<kLmBoundBlocks, kLmThreads, 0, stream>>>(logits, b.residual_l2, b.wire, b.partial, rows);
+  lm_head_reduce_kernel<<<1, kLmBoundBlocks, 0, stream>>>(b.partial, b.wire);
+  lm_head_collect_kernel<<<(rows + kLmThreads - 1) / kLmThreads, kLmThreads, 0, stream>>>(
+      logits, b.residual_l2, b.wire, b.candidate_ids, rows);
+  lm_head_exact_kernel<<<AIMA_MOE_LM_HEAD_CANDIDATES / kExactWarps, kExactWarps * 32, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(weight), h, b.wire, b.candidate_ids, b.candidate_logits);
+  lm_head_argmax_kernel<<<1, kLmThreads, 0, stream>>>(b.candidate_logits, b.wire, b.candidate_ids, logits);
+  *launches = 7;
+  return cudaGetLastError();
+}
+
+}  // namespace aima

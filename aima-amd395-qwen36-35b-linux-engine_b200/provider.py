@@ -80,6 +80,13 @@ class Metrics(ctypes.Structure):
     ]
 
 
+class LmHeadResult(ctypes.Structure):
+    _fields_ = [
+        ("hidden_l2", c_float), ("maximum_lower_bound", c_float), ("exact_top1_logit", c_float),
+        ("exact_top1_token_id", c_uint32), ("candidate_count", c_uint32), ("overflow", c_uint32),
+    ]
+
+
 # every symbol include/aima_moe.h declares: (name, restype, argtypes)
 EXPORTS = [
     ("aima_moe_abi_version", c_uint32, []),
@@ -112,6 +119,12 @@ EXPORTS = [
     ("aima_moe_set_tracing", c_int, [c_void_p, c_int]),
     ("aima_moe_read_decode_timeline", c_int,
      [c_void_p, ctypes.POINTER(c_uint64), c_uint32, ctypes.POINTER(c_uint32)]),
+    ("aima_moe_lm_head_build", c_int, [c_void_p, c_uint32, ctypes.POINTER(c_void_p), c_void_p]),
+    ("aima_moe_lm_head_views", c_int,
+     [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)]),
+    ("aima_moe_lm_head_launch", c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    ("aima_moe_lm_head_read_result", c_int, [c_void_p, ctypes.POINTER(LmHeadResult)]),
+    ("aima_moe_lm_head_release", c_int, [c_void_p]),
     ("aima_moe_sync_metrics", c_int, [c_void_p, ctypes.POINTER(Metrics)]),
     ("aima_moe_release", c_int, [c_void_p]),
 ]
@@ -454,3 +467,57 @@ class MoeProvider:
             self.release()
         except Exception:
             pass
+
+
+class LmHead:
+    """LM head with a certified top-1 over a raw [rows, 2048] BF16 matrix on the device: the binding of
+    aima_moe_lm_head_* (the reference's int8_certified_global_tie variant,
+    benchmarks/shape-lab/four_layer_mini_engine.py:8656-8678)."""
+
+    def __init__(self, weight: Any, library: MoeLibrary | None = None) -> None:
+        import torch
+
+        if not torch.cuda.is_available():
+            raise RuntimeError("aima_moe needs a CUDA device (sm_100a); there is no CPU fallback")
+        self._torch = torch
+        self.lib = library or load_library()
+        self.weight = weight                      # kept alive: the exact candidate logits read it
+        self.rows = int(weight.shape[0])
+        handle = c_void_p()
+        self.lib.check(self.lib.aima_moe_lm_head_build(_ptr(weight), self.rows, ctypes.byref(handle), _stream(torch)))
+        self.handle = handle
+
+    def views(self) -> tuple[Any, Any, Any]:
+        """(q_weight int8 [rows, 2048], scales f32 [rows], residual_l2 f32 [rows]) copied to host tensors."""
+        torch = self._torch
+        q, s, r = c_void_p(), c_void_p(), c_void_p()
+        self.lib.check(self.lib.aima_moe_lm_head_views(self.handle, ctypes.byref(q), ctypes.byref(s), ctypes.byref(r)))
+        torch.cuda.synchronize()
+
+        class _DeviceArray:  # zero-copy view of library-owned device memory
+            def __init__(self, pointer: int, shape: tuple, typestr: str) -> None:
+                self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (pointer, False),
+                                                 "version": 2}
+
+        device = self.weight.device
+        out_q = torch.as_tensor(_DeviceArray(q.value, (self.rows, HIDDEN), "|i1"), device=device).cpu()
+        out_s = torch.as_tensor(_DeviceArray(s.value, (self.rows,), "<f4"), device=device).cpu()
+        out_r = torch.as_tensor(_DeviceArray(r.value, (self.rows,), "<f4"), device=device).cpu()
+        return out_q, out_s, out_r
+
+    def launch(self, hidden: Any, logits: Any | None = None) -> Any:
+        torch = self._torch
+        if logits is None:
+            logits = torch.empty(self.rows, dtype=torch.float32, device=hidden.device)
+        self.lib.check(self.lib.aima_moe_lm_head_launch(self.handle, _ptr(hidden), _ptr(logits), _stream(torch)))
+        return logits
+
+    def result(self) -> LmHeadResult:
+        result = LmHeadResult()
+        self.lib.check(self.lib.aima_moe_lm_head_read_result(self.handle, ctypes.byref(result)))
+        return result
+
+    def release(self) -> None:
+        if self.handle is not None and self.handle.value:
+            self.lib.aima_moe_lm_head_release(self.handle)
+            self.handle = c_void_p()

@@ -333,6 +333,43 @@ const char* aima_moe_last_error_string(void);
 /* ABI version of this header: major << 16 | minor. */
 uint32_t aima_moe_abi_version(void);
 
+/* ---------------------------------------------------------------------------
+ * LM head with a certified top-1 (the reference's "int8_certified_global_tie" variant).
+ * Replaces NativeLmHeadStore::build (native/src/native_lm_head.hip.cpp:126-176: row-wise int8
+ * copy, scales and outward-rounded residual norms of lm_head.weight), the row-wise int8 GEMV
+ * (benchmarks/shape-lab/four_layer_mini_engine.py:1223-1258, launched at :3570-3590) and
+ * launch_native_lm_head_certificate (native/src/native_lm_head_certificate.hip.cpp:213-275,
+ * result struct native/include/aima/native_lm_head_certificate.h:21-28).
+ *
+ * build: weight_bf16 is the raw [rows, 2048] BF16 matrix on the device (248 320 rows in the
+ * reference; any row count here).  The library allocates rows x 2048 int8 + 2 x rows floats and
+ * quantises on `stream`; the raw matrix stays caller-owned and must outlive the handle (the exact
+ * candidate logits are read from it).
+ * launch: hidden_bf16 [2048] (the final-norm output), logits_f32 [rows].  Enqueues seven kernels:
+ * the int8 scan writes approximate logits; rows whose upper bound reaches the largest lower bound
+ * become candidates (at most AIMA_MOE_LM_HEAD_CANDIDATES); their exact BF16 logits overwrite the
+ * approximate ones in logits_f32; the exact top-1 (equal logits -> lowest token id) goes to the
+ * result.  Asynchronous and allocation-free.
+ * read_result: synchronises the last stream and copies the result; returns AIMA_MOE_ERR_CAPACITY
+ * when more than 1024 rows were candidates (top-1 not certified), as the reference's assert does. */
+#define AIMA_MOE_LM_HEAD_CANDIDATES 1024
+typedef struct aima_moe_lm_head aima_moe_lm_head;
+typedef struct aima_moe_lm_head_result {
+  float hidden_l2;             /* ||hidden||_2, rounded up */
+  float maximum_lower_bound;   /* largest lower bound over all rows */
+  float exact_top1_logit;      /* BF16 value as FP32 */
+  uint32_t exact_top1_token_id;
+  uint32_t candidate_count;    /* may exceed the capacity; then overflow = 1 */
+  uint32_t overflow;
+} aima_moe_lm_head_result;
+
+int aima_moe_lm_head_build(const void* weight_bf16, uint32_t rows, aima_moe_lm_head** out, void* stream);
+int aima_moe_lm_head_views(aima_moe_lm_head* handle, void** q_weight, void** scales, void** residual_l2);
+int aima_moe_lm_head_launch(aima_moe_lm_head* handle, const void* hidden_bf16, void* logits_f32,
+                            void* stream);
+int aima_moe_lm_head_read_result(aima_moe_lm_head* handle, aima_moe_lm_head_result* result);
+int aima_moe_lm_head_release(aima_moe_lm_head* handle);
+
 #ifdef __cplusplus
 }
 #endif

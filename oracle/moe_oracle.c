@@ -542,6 +542,143 @@ void aima_or_compare_bf16(const uint16_t* expected, const uint16_t* actual,
   result[4] = finite;
 }
 
+
+/* ---------------------------------------------------------------------------
+ * LM head with a certified top-1.
+ * Quantisation: quantize_lm_head_rowwise_kernel (native/src/native_lm_head.hip.cpp:53-115):
+ * scale = max(max|w|, 1e-12) * fl(1/127); q = clamp(nearbyint(w / scale), -127, 127);
+ * residual_l2 = fl32(sqrt(sum (w - q*scale)^2 in FP64)) moved up 8 ULPs.  The FP64 sum runs as
+ * that kernel runs it: 256 partials (columns t, t+256, ...) added pairwise, offset 128 .. 1.
+ * Certificate: native/src/native_lm_head_certificate.hip.cpp:44-211.
+ * Scan order (this build's statement of the row-wise int8 GEMV, four_layer_mini_engine.py:1223-1258,
+ * whose own FP32 order is Triton's): lane l of 32 owns the 16-byte pieces l, l+32, l+64, l+96 of a
+ * row, one FP32 fma chain over its 64 weights in ascending order, lanes joined by the butterfly
+ * 16, 8, 4, 2, 1; the sum is multiplied by the row's scale.
+ * --------------------------------------------------------------------------- */
+typedef struct aima_or_lm_head_result {
+  float hidden_l2;
+  float maximum_lower_bound;
+  float exact_top1_logit;
+  uint32_t exact_top1_token_id;
+  uint32_t candidate_count;
+  uint32_t overflow;
+} aima_or_lm_head_result;
+
+static double tree256(double* v) {
+  for (int offset = 128; offset > 0; offset >>= 1)
+    for (int t = 0; t < offset; ++t) v[t] = v[t] + v[t + offset];
+  return v[0];
+}
+
+void aima_or_lm_head_quantize(const uint16_t* weight, int rows, int8_t* q, float* scales,
+                              float* residual_l2) {
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < rows; ++row) {
+    const uint16_t* w = weight + (size_t)row * 2048;
+    float maximum = 0.0f;
+    for (int c = 0; c < 2048; ++c) maximum = fmaxf(maximum, fabsf(bf2f(w[c])));
+    maximum = fmaxf(maximum, 1.0e-12f);
+    const float inverse127 = 1.0f / 127.0f;
+    const float scale = maximum * inverse127;
+    scales[row] = scale;
+    double partial[256];
+    for (int t = 0; t < 256; ++t) {
+      double local = 0.0;
+      for (int c = t; c < 2048; c += 256) {
+        const float value = bf2f(w[c]);
+        const float rounded = nearbyintf(value / scale);
+        const int quantized = (int)fminf(127.0f, fmaxf(-127.0f, rounded));
+        q[(size_t)row * 2048 + c] = (int8_t)quantized;
+        const float reconstructed = (float)quantized * scale;
+        const float residual = value - reconstructed;
+        const double product = (double)residual * (double)residual;
+        local = local + product;
+      }
+      partial[t] = local;
+    }
+    float norm = (float)sqrt(tree256(partial));
+    for (int step = 0; step < 8; ++step) norm = nextafterf(norm, INFINITY);
+    residual_l2[row] = norm;
+  }
+}
+
+static float int8_dot_2048(const int8_t* q, const float* x) {
+  float lane_acc[32];
+  for (int lane = 0; lane < 32; ++lane) {
+    float acc = 0.0f;
+    for (int piece = 0; piece < 4; ++piece) {
+      const int base = 16 * (32 * piece + lane);
+      for (int j = 0; j < 16; ++j) acc = fmaf((float)q[base + j], x[base + j], acc);
+    }
+    lane_acc[lane] = acc;
+  }
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    float next[32];
+    for (int lane = 0; lane < 32; ++lane) next[lane] = lane_acc[lane] + lane_acc[lane ^ offset];
+    for (int lane = 0; lane < 32; ++lane) lane_acc[lane] = next[lane];
+  }
+  return lane_acc[0];
+}
+
+static int lm_better(float value, uint32_t index, float current, uint32_t current_index) {
+  return value > current || (value == current && index < current_index);
+}
+
+/* logits [rows]: approximate everywhere, exact (BF16 value) at the candidates.  candidate_ids
+ * (capacity 1024) receives the candidates in ascending row order.  Returns 0, or -8 when more
+ * than 1024 rows are candidates. */
+int aima_or_lm_head_certify(const uint16_t* weight, const int8_t* q, const float* scales,
+                            const float* residual_l2, const uint16_t* hidden, int rows,
+                            float* logits, aima_or_lm_head_result* result, uint32_t* candidate_ids) {
+  float x[2048];
+  for (int c = 0; c < 2048; ++c) x[c] = bf2f(hidden[c]);
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < rows; ++row)
+    logits[row] = int8_dot_2048(q + (size_t)row * 2048, x) * scales[row];
+  double partial[256];
+  for (int t = 0; t < 256; ++t) {
+    double local = 0.0;
+    for (int c = t; c < 2048; c += 256) {
+      const double value = (double)x[c];
+      const double product = value * value;
+      local = local + product;
+    }
+    partial[t] = local;
+  }
+  float hidden_l2 = (float)sqrt(tree256(partial));
+  for (int step = 0; step < 4; ++step) hidden_l2 = nextafterf(hidden_l2, INFINITY);
+  float maximum_lower = -INFINITY;
+  for (int row = 0; row < rows; ++row) {
+    const float error = nextafterf(residual_l2[row] * hidden_l2, INFINITY);
+    const float lower = nextafterf(logits[row] - error, -INFINITY);
+    maximum_lower = fmaxf(maximum_lower, lower);
+  }
+  uint32_t count = 0;
+  for (int row = 0; row < rows; ++row) {
+    const float error = nextafterf(residual_l2[row] * hidden_l2, INFINITY);
+    const float upper = nextafterf(logits[row] + error, INFINITY);
+    if (upper < maximum_lower) continue;
+    if (count < 1024) candidate_ids[count] = (uint32_t)row;
+    ++count;
+  }
+  result->hidden_l2 = hidden_l2;
+  result->maximum_lower_bound = maximum_lower;
+  result->candidate_count = count;
+  result->overflow = count > 1024 ? 1u : 0u;
+  const uint32_t bounded = count < 1024 ? count : 1024;
+  float best = -INFINITY;
+  uint32_t best_index = 0;
+  for (uint32_t c = 0; c < bounded; ++c) {
+    const uint32_t token = candidate_ids[c];
+    const float value = bf2f(f2bf(aima_or_dot(hidden, weight + (size_t)token * 2048, 2048)));
+    logits[token] = value;
+    if (lm_better(value, token, best, best_index)) { best = value; best_index = token; }
+  }
+  result->exact_top1_logit = best;
+  result->exact_top1_token_id = best_index;
+  return count > 1024 ? -8 : 0;
+}
+
 #ifdef __cplusplus
 }
 #endif

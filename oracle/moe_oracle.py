@@ -45,6 +45,12 @@ def build(force: bool = False) -> Path:
 _LIB = None
 
 
+class LmHeadResult(ctypes.Structure):
+    _fields_ = [("hidden_l2", c_float), ("maximum_lower_bound", c_float), ("exact_top1_logit", c_float),
+                ("exact_top1_token_id", ctypes.c_uint32), ("candidate_count", ctypes.c_uint32),
+                ("overflow", ctypes.c_uint32)]
+
+
 def lib() -> ctypes.CDLL:
     global _LIB
     if _LIB is None:
@@ -73,6 +79,11 @@ def lib() -> ctypes.CDLL:
         _LIB.aima_or_gemv.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int]
         _LIB.aima_or_compare_bf16.restype = None
         _LIB.aima_or_compare_bf16.argtypes = [c_void_p, c_void_p, c_size_t, POINTER(c_double)]
+        _LIB.aima_or_lm_head_quantize.restype = None
+        _LIB.aima_or_lm_head_quantize.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+        _LIB.aima_or_lm_head_certify.restype = c_int
+        _LIB.aima_or_lm_head_certify.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_void_p, POINTER(LmHeadResult), c_void_p]
     return _LIB
 
 
@@ -272,6 +283,37 @@ def gemv(weight: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     out = torch.zeros(m, dtype=torch.bfloat16)
     lib().aima_or_gemv(_bf16_ptr(weight), _bf16_ptr(x.contiguous()), _bf16_ptr(out), m, k)
     return out
+
+
+def lm_head_quantize(weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Row-wise int8 copy, scales and outward-rounded residual norms of a [rows, 2048] BF16 matrix."""
+    weight = weight.contiguous()
+    rows = weight.shape[0]
+    q = torch.zeros(rows, H, dtype=torch.int8)
+    scales = torch.zeros(rows, dtype=torch.float32)
+    residual = torch.zeros(rows, dtype=torch.float32)
+    lib().aima_or_lm_head_quantize(_bf16_ptr(weight), rows, c_void_p(q.data_ptr()), c_void_p(scales.data_ptr()),
+                                   c_void_p(residual.data_ptr()))
+    return q, scales, residual
+
+
+def lm_head_certify(weight: torch.Tensor, q: torch.Tensor, scales: torch.Tensor, residual: torch.Tensor,
+                    hidden: torch.Tensor) -> dict[str, Any]:
+    """Certified top-1: approximate logits (exact at the candidates), candidates in row order, result fields."""
+    weight = weight.contiguous()
+    rows = weight.shape[0]
+    logits = torch.zeros(rows, dtype=torch.float32)
+    candidates = torch.zeros(1024, dtype=torch.int32)
+    result = LmHeadResult()
+    status = lib().aima_or_lm_head_certify(
+        _bf16_ptr(weight), c_void_p(q.contiguous().data_ptr()), c_void_p(scales.contiguous().data_ptr()),
+        c_void_p(residual.contiguous().data_ptr()), _bf16_ptr(hidden.contiguous()), rows,
+        c_void_p(logits.data_ptr()), ctypes.byref(result), c_void_p(candidates.data_ptr()))
+    count = min(int(result.candidate_count), 1024)
+    return {"status": status, "logits": logits, "candidates": candidates[:count].clone(),
+            "hidden_l2": float(result.hidden_l2), "maximum_lower_bound": float(result.maximum_lower_bound),
+            "top1_logit": float(result.exact_top1_logit), "top1_token": int(result.exact_top1_token_id),
+            "candidate_count": int(result.candidate_count), "overflow": int(result.overflow)}
 
 
 def compare_bf16(expected: torch.Tensor, actual: torch.Tensor) -> dict[str, float]:
