@@ -104,28 +104,42 @@ lm_head_scan_kernel(const int8_t* __restrict__ q_weight, const float* __restrict
     unpack8(__ldg(src), x + 16 * piece);
     unpack8(__ldg(src + 1), x + 16 * piece + 8);
   }
-  for (int row = warp_global; row < rows; row += warps_total) {
-    const uint4* qrow = reinterpret_cast<const uint4*>(q_weight + static_cast<size_t>(row) * kHidden) + lane;
-    uint4 w[4];
+  // two rows per trip: eight 16-byte loads per lane in flight
+  for (int row = warp_global; row < rows; row += 2 * warps_total) {
+    const int row_b = row + warps_total;
+    const bool has_b = row_b < rows;
+    const uint4* qrow_a = reinterpret_cast<const uint4*>(q_weight + static_cast<size_t>(row) * kHidden) + lane;
+    const uint4* qrow_b = reinterpret_cast<const uint4*>(q_weight + static_cast<size_t>(has_b ? row_b : row) * kHidden) + lane;
+    uint4 wa[4], wb[4];
 #pragma unroll
-    for (int piece = 0; piece < 4; ++piece) w[piece] = __ldcs(qrow + 32 * piece);
-    float acc = 0.0f;
+    for (int piece = 0; piece < 4; ++piece) wa[piece] = __ldcs(qrow_a + 32 * piece);
+#pragma unroll
+    for (int piece = 0; piece < 4; ++piece) wb[piece] = __ldcs(qrow_b + 32 * piece);
+    float acc_a = 0.0f, acc_b = 0.0f;
 #pragma unroll
     for (int piece = 0; piece < 4; ++piece) {
-      acc = fma_word(w[piece].x, x + 16 * piece, acc);
-      acc = fma_word(w[piece].y, x + 16 * piece + 4, acc);
-      acc = fma_word(w[piece].z, x + 16 * piece + 8, acc);
-      acc = fma_word(w[piece].w, x + 16 * piece + 12, acc);
+      acc_a = fma_word(wa[piece].x, x + 16 * piece, acc_a);
+      acc_a = fma_word(wa[piece].y, x + 16 * piece + 4, acc_a);
+      acc_a = fma_word(wa[piece].z, x + 16 * piece + 8, acc_a);
+      acc_a = fma_word(wa[piece].w, x + 16 * piece + 12, acc_a);
+      acc_b = fma_word(wb[piece].x, x + 16 * piece, acc_b);
+      acc_b = fma_word(wb[piece].y, x + 16 * piece + 4, acc_b);
+      acc_b = fma_word(wb[piece].z, x + 16 * piece + 8, acc_b);
+      acc_b = fma_word(wb[piece].w, x + 16 * piece + 12, acc_b);
     }
-    acc = butterfly_sum(acc);
-    if (lane == 0) logits[row] = __fmul_rn(acc, scales[row]);
+    acc_a = butterfly_sum(acc_a);
+    acc_b = butterfly_sum(acc_b);
+    if (lane == 0) {
+      logits[row] = __fmul_rn(acc_a, scales[row]);
+      if (has_b) logits[row_b] = __fmul_rn(acc_b, scales[row_b]);
+    }
   }
 }
 
 // ||hidden||_2 in FP64 (thread-strided partials, pairwise tree), rounded to FP32 and up 4 ULPs.
-__global__ void __launch_bounds__(kLmThreads)
-lm_head_hidden_norm_kernel(const __nv_bfloat16* __restrict__ hidden, aima_moe_lm_head_result* wire) {
-  __shared__ double reduction[kLmThreads];
+// Every block of the bound kernel evaluates it for itself (2048 values) rather than waiting for
+// a kernel of its own.
+__device__ __forceinline__ float hidden_norm_in_block(const __nv_bfloat16* __restrict__ hidden, double* reduction) {
   const int t = threadIdx.x;
   double local = 0.0;
   for (int index = t; index < kHidden; index += kLmThreads) {
@@ -138,23 +152,24 @@ lm_head_hidden_norm_kernel(const __nv_bfloat16* __restrict__ hidden, aima_moe_lm
     if (t < stride) reduction[t] = __dadd_rn(reduction[t], reduction[t + stride]);
     __syncthreads();
   }
-  if (t == 0) {
-    float norm = static_cast<float>(sqrt(reduction[0]));
-    for (int step = 0; step < kHiddenSafetyUlps; ++step) norm = nextafterf(norm, CUDART_INF_F);
-    wire->hidden_l2 = norm;
-  }
+  float norm = static_cast<float>(sqrt(reduction[0]));
+  for (int step = 0; step < kHiddenSafetyUlps; ++step) norm = nextafterf(norm, CUDART_INF_F);
+  return norm;
 }
 
 __device__ __forceinline__ float row_error(float residual, float hidden_l2) {
   return nextafterf(__fmul_rn(residual, hidden_l2), CUDART_INF_F);
 }
 
-// largest lower bound over all rows, first per block ...
+// largest lower bound over all rows, per block; block 0 also publishes the hidden norm and empties
+// the candidate list
 __global__ void __launch_bounds__(kLmThreads)
 lm_head_bound_kernel(const float* __restrict__ logits, const float* __restrict__ residual_l2,
-                     const aima_moe_lm_head_result* __restrict__ wire, float* __restrict__ partial, int rows) {
+                     const __nv_bfloat16* __restrict__ hidden, aima_moe_lm_head_result* wire,
+                     float* __restrict__ partial, int rows) {
+  __shared__ double norm_reduction[kLmThreads];
   __shared__ float reduction[kLmThreads];
-  const float hidden_l2 = wire->hidden_l2;
+  const float hidden_l2 = hidden_norm_in_block(hidden, norm_reduction);
   float local_max = -CUDART_INF_F;
   for (int row = blockIdx.x * kLmThreads + threadIdx.x; row < rows; row += gridDim.x * kLmThreads) {
     const float lower = nextafterf(__fsub_rn(logits[row], row_error(residual_l2[row], hidden_l2)), -CUDART_INF_F);
@@ -166,12 +181,23 @@ lm_head_bound_kernel(const float* __restrict__ logits, const float* __restrict__
     if (threadIdx.x < stride) reduction[threadIdx.x] = fmaxf(reduction[threadIdx.x], reduction[threadIdx.x + stride]);
     __syncthreads();
   }
-  if (threadIdx.x == 0) partial[blockIdx.x] = reduction[0];
+  if (threadIdx.x == 0) {
+    partial[blockIdx.x] = reduction[0];
+    if (blockIdx.x == 0) {
+      wire->hidden_l2 = hidden_l2;
+      wire->candidate_count = 0;
+      wire->overflow = 0;
+    }
+  }
 }
 
-// ... then over the blocks; also resets the candidate list
-__global__ void __launch_bounds__(kLmBoundBlocks)
-lm_head_reduce_kernel(const float* __restrict__ partial, aima_moe_lm_head_result* wire) {
+// every row whose upper bound reaches the largest lower bound is a candidate; each block first
+// reduces the 256 per-block maxima of the previous kernel
+__global__ void __launch_bounds__(kLmThreads)
+lm_head_collect_kernel(const float* __restrict__ logits, const float* __restrict__ residual_l2,
+                       const float* __restrict__ partial, aima_moe_lm_head_result* wire,
+                       uint32_t* __restrict__ candidate_ids, int rows) {
+  static_assert(kLmThreads == kLmBoundBlocks, "one thread per partial maximum");
   __shared__ float reduction[kLmBoundBlocks];
   reduction[threadIdx.x] = partial[threadIdx.x];
   __syncthreads();
@@ -179,83 +205,67 @@ lm_head_reduce_kernel(const float* __restrict__ partial, aima_moe_lm_head_result
     if (threadIdx.x < stride) reduction[threadIdx.x] = fmaxf(reduction[threadIdx.x], reduction[threadIdx.x + stride]);
     __syncthreads();
   }
-  if (threadIdx.x == 0) {
-    wire->maximum_lower_bound = reduction[0];
-    wire->candidate_count = 0;
-    wire->overflow = 0;
-  }
-}
-
-// every row whose upper bound reaches the largest lower bound is a candidate
-__global__ void __launch_bounds__(kLmThreads)
-lm_head_collect_kernel(const float* __restrict__ logits, const float* __restrict__ residual_l2,
-                       aima_moe_lm_head_result* wire, uint32_t* __restrict__ candidate_ids, int rows) {
+  const float maximum_lower_bound = reduction[0];
+  if (blockIdx.x == 0 && threadIdx.x == 0) wire->maximum_lower_bound = maximum_lower_bound;
   const int row = blockIdx.x * kLmThreads + threadIdx.x;
   if (row >= rows) return;
   const float upper = nextafterf(__fadd_rn(logits[row], row_error(residual_l2[row], wire->hidden_l2)), CUDART_INF_F);
-  if (upper < wire->maximum_lower_bound) return;
+  if (upper < maximum_lower_bound) return;
   const uint32_t slot = atomicAdd(&wire->candidate_count, 1u);
   if (slot < AIMA_MOE_LM_HEAD_CANDIDATES) candidate_ids[slot] = static_cast<uint32_t>(row);
   else wire->overflow = 1;
-}
-
-// exact BF16 logit of every candidate straight from the raw matrix (no gathered copy): the
-// canonical warp dot, rounded to BF16 like the reference's N = 1 GEMV provider
-constexpr int kExactWarps = 8;
-__global__ void __launch_bounds__(kExactWarps * 32)
-lm_head_exact_kernel(const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ hidden,
-                     const aima_moe_lm_head_result* __restrict__ wire, const uint32_t* __restrict__ candidate_ids,
-                     __nv_bfloat16* __restrict__ candidate_logits) {
-  const int lane = threadIdx.x & 31;
-  const uint32_t candidate = blockIdx.x * kExactWarps + (threadIdx.x >> 5);
-  const uint32_t count = min(wire->candidate_count, static_cast<uint32_t>(AIMA_MOE_LM_HEAD_CANDIDATES));
-  if (candidate >= count) return;
-  const uint4* wrow = reinterpret_cast<const uint4*>(weight + static_cast<size_t>(candidate_ids[candidate]) * kHidden) + lane;
-  const uint4* xrow = reinterpret_cast<const uint4*>(hidden) + lane;
-  float acc = 0.0f;
-#pragma unroll
-  for (int i = 0; i < kHidden / 256; ++i) {
-    float xf[8];
-    unpack8(__ldg(xrow + i * 32), xf);
-    acc = fma8(xf, __ldg(wrow + i * 32), acc);
-  }
-  acc = butterfly_sum(acc);
-  if (lane == 0) candidate_logits[candidate] = __float2bfloat16_rn(acc);
 }
 
 __device__ __forceinline__ bool better(float value, uint32_t index, float current, uint32_t current_index) {
   return value > current || (value == current && index < current_index);
 }
 
-// exact top-1 over the candidates; their exact logits replace the approximate ones in `logits`
-__global__ void __launch_bounds__(kLmThreads)
-lm_head_argmax_kernel(const __nv_bfloat16* __restrict__ candidate_logits, aima_moe_lm_head_result* wire,
-                      const uint32_t* __restrict__ candidate_ids, float* __restrict__ logits) {
-  __shared__ float values[kLmThreads];
-  __shared__ uint32_t indices[kLmThreads];
+// One block: the exact BF16 logit of every candidate straight from the raw matrix (no gathered
+// copy) -- the canonical warp dot, rounded to BF16 like the reference's N = 1 GEMV provider -- then
+// the exact top-1 over them.  The exact logits replace the approximate ones in `logits`.
+constexpr int kExactWarps = 32;
+__global__ void __launch_bounds__(kExactWarps * 32)
+lm_head_exact_kernel(const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ hidden,
+                     aima_moe_lm_head_result* wire, const uint32_t* __restrict__ candidate_ids,
+                     float* __restrict__ logits) {
+  __shared__ float values[kExactWarps];
+  __shared__ uint32_t indices[kExactWarps];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
   const uint32_t count = min(wire->candidate_count, static_cast<uint32_t>(AIMA_MOE_LM_HEAD_CANDIDATES));
+  const uint4* xrow = reinterpret_cast<const uint4*>(hidden) + lane;
   float local_value = -CUDART_INF_F;
   uint32_t local_index = 0;
-  for (uint32_t candidate = threadIdx.x; candidate < count; candidate += kLmThreads) {
-    const float value = __bfloat162float(candidate_logits[candidate]);
+  for (uint32_t candidate = warp; candidate < count; candidate += kExactWarps) {
     const uint32_t token = candidate_ids[candidate];
-    logits[token] = value;
+    const uint4* wrow = reinterpret_cast<const uint4*>(weight + static_cast<size_t>(token) * kHidden) + lane;
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kHidden / 256; ++i) {
+      float xf[8];
+      unpack8(__ldg(xrow + i * 32), xf);
+      acc = fma8(xf, __ldg(wrow + i * 32), acc);
+    }
+    acc = butterfly_sum(acc);
+    const float value = round_bf16(acc);
+    if (lane == 0) logits[token] = value;
     if (better(value, token, local_value, local_index)) { local_value = value; local_index = token; }
   }
-  values[threadIdx.x] = local_value;
-  indices[threadIdx.x] = local_index;
+  if (lane == 0) { values[warp] = local_value; indices[warp] = local_index; }
   __syncthreads();
-  for (int stride = kLmThreads / 2; stride != 0; stride >>= 1) {
-    if (threadIdx.x < stride &&
-        better(values[threadIdx.x + stride], indices[threadIdx.x + stride], values[threadIdx.x], indices[threadIdx.x])) {
-      values[threadIdx.x] = values[threadIdx.x + stride];
-      indices[threadIdx.x] = indices[threadIdx.x + stride];
+  if (warp == 0) {
+    float value = values[lane];
+    uint32_t index = indices[lane];
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other_value = __shfl_xor_sync(0xffffffffu, value, offset);
+      const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+      if (better(other_value, other_index, value, index)) { value = other_value; index = other_index; }
     }
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) {
-    wire->exact_top1_logit = values[0];
-    wire->exact_top1_token_id = indices[0];
+    if (lane == 0) {
+      wire->exact_top1_logit = value;
+      wire->exact_top1_token_id = index;
+    }
   }
 }
 
@@ -272,15 +282,12 @@ cudaError_t lm_head_certify(const LmHeadBuffers& b, const void* weight, const vo
                             int rows, int sm_count, cudaStream_t stream, int* launches) {
   const __nv_bfloat16* h = static_cast<const __nv_bfloat16*>(hidden);
   lm_head_scan_kernel<<<sm_count * 8, kScanWarps * 32, 0, stream>>>(b.q_weight, b.scales, h, logits, rows);
-  lm_head_hidden_norm_kernel<<<1, kLmThreads, 0, stream>>>(h, b.wire);
-  lm_head_bound_kernel<<<kLmBoundBlocks, kLmThreads, 0, stream>>>(logits, b.residual_l2, b.wire, b.partial, rows);
-  lm_head_reduce_kernel<<<1, kLmBoundBlocks, 0, stream>>>(b.partial, b.wire);
+  lm_head_bound_kernel<<<kLmBoundBlocks, kLmThreads, 0, stream>>>(logits, b.residual_l2, h, b.wire, b.partial, rows);
   lm_head_collect_kernel<<<(rows + kLmThreads - 1) / kLmThreads, kLmThreads, 0, stream>>>(
-      logits, b.residual_l2, b.wire, b.candidate_ids, rows);
-  lm_head_exact_kernel<<<AIMA_MOE_LM_HEAD_CANDIDATES / kExactWarps, kExactWarps * 32, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(weight), h, b.wire, b.candidate_ids, b.candidate_logits);
-  lm_head_argmax_kernel<<<1, kLmThreads, 0, stream>>>(b.candidate_logits, b.wire, b.candidate_ids, logits);
-  *launches = 7;
+      logits, b.residual_l2, b.partial, b.wire, b.candidate_ids, rows);
+  lm_head_exact_kernel<<<1, kExactWarps * 32, 0, stream>>>(static_cast<const __nv_bfloat16*>(weight), h, b.wire,
+                                                           b.candidate_ids, logits);
+  *launches = 4;
   return cudaGetLastError();
 }
 

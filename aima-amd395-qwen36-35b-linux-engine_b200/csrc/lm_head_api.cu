@@ -11,7 +11,7 @@ struct aima_moe_lm_head {
   int sm_count = 0;
   uint32_t rows = 0;
   const void* weight = nullptr;      // caller-owned raw BF16 matrix [rows, 2048]
-  void* allocation = nullptr;        // q | scales | residual_l2 | wire | partial | candidate ids | candidate logits
+  void* allocation = nullptr;        // q | scales | residual_l2 | wire | partial | candidate ids
   aima::LmHeadBuffers buffers{};
   cudaStream_t last_stream = nullptr;
   uint64_t launches = 0;
@@ -78,8 +78,7 @@ AIMA_EXPORT int aima_moe_lm_head_build(const void* weight_bf16, uint32_t rows, a
   const size_t q_bytes = align256(static_cast<size_t>(rows) * aima::kHidden);
   const size_t row_bytes = align256(static_cast<size_t>(rows) * sizeof(float));
   const size_t total = q_bytes + 2 * row_bytes + 256 + 1024 +
-                       align256(AIMA_MOE_LM_HEAD_CANDIDATES * sizeof(uint32_t)) +
-                       align256(AIMA_MOE_LM_HEAD_CANDIDATES * sizeof(uint16_t));
+                       align256(AIMA_MOE_LM_HEAD_CANDIDATES * sizeof(uint32_t));
   error = cudaMalloc(&handle->allocation, total);
   if (error != cudaSuccess) {
     delete handle;
@@ -92,8 +91,6 @@ AIMA_EXPORT int aima_moe_lm_head_build(const void* weight_bf16, uint32_t rows, a
   handle->buffers.wire = reinterpret_cast<aima_moe_lm_head_result*>(cursor); cursor += 256;
   handle->buffers.partial = reinterpret_cast<float*>(cursor); cursor += 1024;
   handle->buffers.candidate_ids = reinterpret_cast<uint32_t*>(cursor);
-  cursor += align256(AIMA_MOE_LM_HEAD_CANDIDATES * sizeof(uint32_t));
-  handle->buffers.candidate_logits = reinterpret_cast<__nv_bfloat16*>(cursor);
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
   error = cudaMemsetAsync(handle->buffers.wire, 0, 256, cuda_stream);
   if (error == cudaSuccess)

@@ -455,6 +455,87 @@ def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) ->
     dist.destroy_process_group()
 
 
+def run_lm_head(args) -> None:
+    """`--workload lm_head`: certified top-1 over the reference's 248 320 x 2048 vocabulary matrix, one
+    token per step.  Algorithmic bytes per step: the int8 copy once (rows x 2048) + scales, residual
+    norms and logits (rows x 4 B each, logits written then read twice) + the candidates' BF16 rows."""
+    import time
+
+    import torch
+    from __graft_entry__ import load_package
+
+    package = load_package()
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    rows = 248320
+    generator = torch.Generator(device=device).manual_seed(SEED)
+    weight = (torch.randn(rows, HIDDEN, generator=generator, device=device) * 0.02).to(torch.bfloat16)
+    hiddens = [torch.randn(HIDDEN, generator=generator, device=device).to(torch.bfloat16) for _ in range(8)]
+    head = package.LmHead(weight)
+    logits = torch.empty(rows, dtype=torch.float32, device=device)
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    for i in range(warmup):
+        head.launch(hiddens[i % 8], logits)
+    candidates = head.result().candidate_count
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(steps):
+        head.launch(hiddens[i % 8], logits)
+    stop.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = start.elapsed_time(stop) / steps
+    result = head.result()
+    # end to end: hidden from pinned host memory, the 24-byte result read back every step
+    pinned = [h.cpu().pin_memory() for h in hiddens]
+    staging = torch.empty(HIDDEN, dtype=torch.bfloat16, device=device)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        staging.copy_(pinned[i % 8], non_blocking=True)
+        head.launch(staging, logits)
+        head.result()
+    e2e_ms = (time.perf_counter() - t0) * 1.0e3 / steps
+    baseline = None
+    if not args.no_cpu_baseline:
+        # the CPU restatement (oracle/, plain C + OpenMP) on the first tenth of the rows, scaled by ten
+        sys.path.insert(0, str(ROOT / "oracle"))
+        import moe_oracle
+
+        sample = rows // 10
+        q_all, scales_all, residual_all = head.views()
+        w_cpu = weight[:sample].cpu()
+        q_cpu, s_cpu, r_cpu = q_all[:sample].contiguous(), scales_all[:sample].contiguous(), residual_all[:sample].contiguous()
+        h_cpu = hiddens[0].cpu()
+        moe_oracle.lm_head_certify(w_cpu, q_cpu, s_cpu, r_cpu, h_cpu)
+        t0 = time.perf_counter()
+        repeats = 5
+        for _ in range(repeats):
+            moe_oracle.lm_head_certify(w_cpu, q_cpu, s_cpu, r_cpu, h_cpu)
+        seconds = (time.perf_counter() - t0) / repeats * (rows / sample)
+        baseline = {"value": 1.0 / seconds, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                    "sample": f"{sample} of {rows} rows x {repeats} repeats, scaled to the full vocabulary"}
+    head.release()
+    step_bytes = rows * HIDDEN + rows * 4 * 5 + int(candidates) * HIDDEN * 2
+    peak, kind = measured_peaks()
+    gbs = step_bytes / (ms * 1.0e-3) / 1.0e9
+    print(json.dumps({
+        "metric": "lm_head_certified_top1_tokens_per_second", "value": 1.0e3 / ms, "unit": "tokens/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 scan + bf16 candidates", "data": "synthetic",
+        "config": {"workload": "lm_head_certified_top1 (248320 x 2048, one token per step)",
+                   "l2": "inputs larger than L2 (509 MB int8 matrix per step)"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                     "traffic": None, "peak_source": kind, "bytes_per_step": step_bytes},
+        "e2e": {"value": 1.0e3 / e2e_ms, "unit": "tokens/s", "h2d_bytes_per_step": HIDDEN * 2,
+                "d2h_bytes_per_step": 24},
+        "candidates_last_step": int(result.candidate_count), "gpu_launches": 4 * steps, "clocks": clocks,
+        **({"cpu_baseline": baseline} if baseline is not None else {})}))
+
+
 def run_prefill(args) -> None:
     """`--workload prefill`: the one-layer T = 8192 prefill line (profiling aid and second headline)."""
     import torch
@@ -511,7 +592,7 @@ def main() -> None:
     parser.add_argument("--no-prefill", action="store_true", help="skip the one-layer prefill sub-object")
     parser.add_argument("--layers", type=int, default=LAYERS,
                         help="stack depth; anything but 40 is a profiling aid, not the benchmark config")
-    parser.add_argument("--workload", choices=["decode", "prefill"], default="decode",
+    parser.add_argument("--workload", choices=["decode", "prefill", "lm_head"], default="decode",
                         help="decode = the benchmark line; prefill = one-layer prefill line only")
     parser.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
     parser.add_argument("--routing", choices=["zipf", "uniform"], default="zipf")
@@ -528,6 +609,8 @@ def main() -> None:
         run_reference(args)
     elif args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "lm_head":
+        run_lm_head(args)
     else:
         run_ours(args)
 

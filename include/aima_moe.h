@@ -345,7 +345,7 @@ uint32_t aima_moe_abi_version(void);
  * reference; any row count here).  The library allocates rows x 2048 int8 + 2 x rows floats and
  * quantises on `stream`; the raw matrix stays caller-owned and must outlive the handle (the exact
  * candidate logits are read from it).
- * launch: hidden_bf16 [2048] (the final-norm output), logits_f32 [rows].  Enqueues seven kernels:
+ * launch: hidden_bf16 [2048] (the final-norm output), logits_f32 [rows].  Enqueues four kernels:
  * the int8 scan writes approximate logits; rows whose upper bound reaches the largest lower bound
  * become candidates (at most AIMA_MOE_LM_HEAD_CANDIDATES); their exact BF16 logits overwrite the
  * approximate ones in logits_f32; the exact top-1 (equal logits -> lowest token id) goes to the
