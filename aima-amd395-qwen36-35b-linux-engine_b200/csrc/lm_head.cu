@@ -88,7 +88,7 @@ __device__ __forceinline__ float fma_word(uint32_t word, const float* x, float a
   return acc;
 }
 
-constexpr int kScanWarps = 8;
+constexpr int kScanWarps = 4;
 
 __global__ void __launch_bounds__(kScanWarps * 32)
 lm_head_scan_kernel(const int8_t* __restrict__ q_weight, const float* __restrict__ scales,
@@ -104,17 +104,24 @@ lm_head_scan_kernel(const int8_t* __restrict__ q_weight, const float* __restrict
     unpack8(__ldg(src), x + 16 * piece);
     unpack8(__ldg(src + 1), x + 16 * piece + 8);
   }
-  // two rows per trip: eight 16-byte loads per lane in flight
-  for (int row = warp_global; row < rows; row += 2 * warps_total) {
+  // Two rows per trip, and the loads of the next trip are issued before the arithmetic of this one:
+  // eight to sixteen 16-byte loads per lane stay in flight.
+  auto load_pair = [&](int row, uint4* wa, uint4* wb) {
     const int row_b = row + warps_total;
-    const bool has_b = row_b < rows;
     const uint4* qrow_a = reinterpret_cast<const uint4*>(q_weight + static_cast<size_t>(row) * kHidden) + lane;
-    const uint4* qrow_b = reinterpret_cast<const uint4*>(q_weight + static_cast<size_t>(has_b ? row_b : row) * kHidden) + lane;
-    uint4 wa[4], wb[4];
+    const uint4* qrow_b = reinterpret_cast<const uint4*>(q_weight + static_cast<size_t>(row_b < rows ? row_b : row) * kHidden) + lane;
 #pragma unroll
     for (int piece = 0; piece < 4; ++piece) wa[piece] = __ldcs(qrow_a + 32 * piece);
 #pragma unroll
     for (int piece = 0; piece < 4; ++piece) wb[piece] = __ldcs(qrow_b + 32 * piece);
+  };
+  uint4 wa[4], wb[4];
+  if (warp_global < rows) load_pair(warp_global, wa, wb);
+  for (int row = warp_global; row < rows; row += 2 * warps_total) {
+    const int row_b = row + warps_total;
+    const int next = row + 2 * warps_total;
+    uint4 na[4], nb[4];
+    if (next < rows) load_pair(next, na, nb);
     float acc_a = 0.0f, acc_b = 0.0f;
 #pragma unroll
     for (int piece = 0; piece < 4; ++piece) {
@@ -131,7 +138,11 @@ lm_head_scan_kernel(const int8_t* __restrict__ q_weight, const float* __restrict
     acc_b = butterfly_sum(acc_b);
     if (lane == 0) {
       logits[row] = __fmul_rn(acc_a, scales[row]);
-      if (has_b) logits[row_b] = __fmul_rn(acc_b, scales[row_b]);
+      if (row_b < rows) logits[row_b] = __fmul_rn(acc_b, scales[row_b]);
+    }
+    if (next < rows) {
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) { wa[piece] = na[piece]; wb[piece] = nb[piece]; }
     }
   }
 }
@@ -281,7 +292,7 @@ cudaError_t lm_head_quantize(const void* weight, int rows, int8_t* q_weight, flo
 cudaError_t lm_head_certify(const LmHeadBuffers& b, const void* weight, const void* hidden, float* logits,
                             int rows, int sm_count, cudaStream_t stream, int* launches) {
   const __nv_bfloat16* h = static_cast<const __nv_bfloat16*>(hidden);
-  lm_head_scan_kernel<<<sm_count * 8, kScanWarps * 32, 0, stream>>>(b.q_weight, b.scales, h, logits, rows);
+  lm_head_scan_kernel<<<sm_count * 16, kScanWarps * 32, 0, stream>>>(b.q_weight, b.scales, h, logits, rows);
   lm_head_bound_kernel<<<kLmBoundBlocks, kLmThreads, 0, stream>>>(logits, b.residual_l2, h, b.wire, b.partial, rows);
   lm_head_collect_kernel<<<(rows + kLmThreads - 1) / kLmThreads, kLmThreads, 0, stream>>>(
       logits, b.residual_l2, b.partial, b.wire, b.candidate_ids, rows);
