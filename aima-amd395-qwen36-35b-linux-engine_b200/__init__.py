@@ -10,9 +10,10 @@ from .provider import (  # noqa: F401
     MoeLibrary,
     LmHead,
     MoeProvider,
+    StripedImage,
     library_path,
     load_library,
 )
 from . import synth  # noqa: F401
 
-__all__ = ["AimaMoeError", "LmHead", "MoeLibrary", "MoeProvider", "library_path", "load_library", "synth"]
+__all__ = ["AimaMoeError", "LmHead", "MoeLibrary", "MoeProvider", "StripedImage", "library_path", "load_library", "synth"]

@@ -15,7 +15,8 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libaima_moe_b200.so"
 SOURCES = ["moe_api.cu", "decode_kernel.cu", "decode_noalloc.cu", "pointwise.cu", "prefill.cu",
-           "grouped_gemm_simt.cu", "grouped_gemm_tc.cu", "lm_head.cu", "lm_head_api.cu"]
+           "grouped_gemm_simt.cu", "grouped_gemm_tc.cu", "lm_head.cu", "lm_head_api.cu",
+           "image_loader.cu"]
 
 
 def nvcc_path() -> str:

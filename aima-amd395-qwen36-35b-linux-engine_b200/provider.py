@@ -80,6 +80,13 @@ class Metrics(ctypes.Structure):
     ]
 
 
+class ImageIngestResult(ctypes.Structure):
+    _fields_ = [
+        ("bytes", c_uint64), ("read_ms", ctypes.c_double), ("checksum_ms", c_float), ("direct_io", c_uint32),
+        ("xor_value", c_uint64), ("sum_value", c_uint64),
+    ]
+
+
 class LmHeadResult(ctypes.Structure):
     _fields_ = [
         ("hidden_l2", c_float), ("maximum_lower_bound", c_float), ("exact_top1_logit", c_float),
@@ -125,6 +132,17 @@ EXPORTS = [
     ("aima_moe_lm_head_launch", c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
     ("aima_moe_lm_head_read_result", c_int, [c_void_p, ctypes.POINTER(LmHeadResult)]),
     ("aima_moe_lm_head_release", c_int, [c_void_p]),
+    ("aima_moe_image_plan", c_int,
+     [ctypes.POINTER(c_uint64), ctypes.POINTER(ctypes.c_char_p), c_uint64, ctypes.POINTER(c_uint32),
+      ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64)]),
+    ("aima_moe_image_checksum_host", c_int, [c_void_p, c_uint64, ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64)]),
+    ("aima_moe_image_build", c_int,
+     [ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint32),
+      ctypes.POINTER(c_uint64), c_uint64, ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64),
+      ctypes.POINTER(c_uint64)]),
+    ("aima_moe_image_scatter_ingest", c_int,
+     [ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64),
+      c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_uint64, c_uint64, ctypes.POINTER(ImageIngestResult)]),
     ("aima_moe_sync_metrics", c_int, [c_void_p, ctypes.POINTER(Metrics)]),
     ("aima_moe_release", c_int, [c_void_p]),
 ]
@@ -521,3 +539,57 @@ class LmHead:
         if self.handle is not None and self.handle.value:
             self.lib.aima_moe_lm_head_release(self.handle)
             self.handle = c_void_p()
+
+
+class StripedImage:
+    """Binding of aima_moe_image_*: the two-lane striped weight image (layout plan, builder, scatter ingest with
+    the device checksum).  `tensors` maps names to contiguous CPU tensors whose byte size is a multiple of 8."""
+
+    def __init__(self, library: MoeLibrary | None = None) -> None:
+        self.lib = library or load_library()
+
+    def plan(self, names: list[str], payload_bytes: list[int]) -> dict:
+        count = len(names)
+        sizes = (c_uint64 * count)(*payload_bytes)
+        c_names = (ctypes.c_char_p * count)(*[name.encode() for name in names])
+        lane = (c_uint32 * count)()
+        lane_offset = (c_uint64 * count)()
+        aggregate = (c_uint64 * count)()
+        lane_bytes = (c_uint64 * 2)()
+        self.lib.check(self.lib.aima_moe_image_plan(sizes, c_names, count, lane, lane_offset, aggregate, lane_bytes))
+        return {"lane": list(lane), "lane_offset": list(lane_offset), "aggregate_offset": list(aggregate),
+                "lane_bytes": list(lane_bytes)}
+
+    def checksum(self, tensor: Any, start: tuple[int, int] = (0, 0)) -> tuple[int, int]:
+        xor_value, sum_value = c_uint64(start[0]), c_uint64(start[1])
+        nbytes = tensor.numel() * tensor.element_size()
+        self.lib.check(self.lib.aima_moe_image_checksum_host(
+            c_void_p(tensor.data_ptr()), nbytes, ctypes.byref(xor_value), ctypes.byref(sum_value)))
+        return int(xor_value.value), int(sum_value.value)
+
+    def build(self, lane0_path: str, lane1_path: str, names: list[str], tensors: dict) -> dict:
+        sizes = [tensors[name].numel() * tensors[name].element_size() for name in names]
+        plan = self.plan(names, sizes)
+        count = len(names)
+        pointers = (c_void_p * count)(*[tensors[name].data_ptr() for name in names])
+        xor_value, sum_value = c_uint64(), c_uint64()
+        self.lib.check(self.lib.aima_moe_image_build(
+            str(lane0_path).encode(), str(lane1_path).encode(), pointers, (c_uint64 * count)(*sizes),
+            (c_uint32 * count)(*plan["lane"]), (c_uint64 * count)(*plan["lane_offset"]), count,
+            (c_uint64 * 2)(*plan["lane_bytes"]), ctypes.byref(xor_value), ctypes.byref(sum_value)))
+        plan.update({"payload_bytes": sizes, "xor": int(xor_value.value), "sum": int(sum_value.value),
+                     "names": list(names)})
+        return plan
+
+    def scatter_ingest(self, lane0_path: str, lane1_path: str, ranges: list[tuple[int, int]], destinations: list,
+                       lane_bytes: list[int], chunk_bytes: int = 8 << 20,
+                       expected: tuple[int, int] | None = None) -> ImageIngestResult:
+        """ranges: (aggregate offset, bytes) per destination tensor (device, contiguous)."""
+        count = len(ranges)
+        result = ImageIngestResult()
+        self.lib.check(self.lib.aima_moe_image_scatter_ingest(
+            str(lane0_path).encode(), str(lane1_path).encode(), (c_uint64 * count)(*[r[0] for r in ranges]),
+            (c_uint64 * count)(*[r[1] for r in ranges]), (c_uint64 * count)(*[t.data_ptr() for t in destinations]),
+            count, lane_bytes[0], lane_bytes[1], chunk_bytes, 0 if expected is None else 1,
+            0 if expected is None else expected[0], 0 if expected is None else expected[1], ctypes.byref(result)))
+        return result

@@ -370,6 +370,49 @@ int aima_moe_lm_head_launch(aima_moe_lm_head* handle, const void* hidden_bf16, v
 int aima_moe_lm_head_read_result(aima_moe_lm_head* handle, aima_moe_lm_head_result* result);
 int aima_moe_lm_head_release(aima_moe_lm_head* handle);
 
+/* ---------------------------------------------------------------------------
+ * Striped weight image: the on-disk format that feeds the expert tensors.  Two lane files
+ * (lane0.bin, lane1.bin, meant for two physical drives); every tensor is one extent aligned to 4096
+ * bytes in one lane; the aggregate address space is lane 0 followed by lane 1
+ * (engine/production-striped-image-manifest.json).
+ *
+ * image_plan: the reference's layout rule -- sort by descending aligned bytes, then name; give
+ *   each tensor to the lane with the smaller total, lane 0 on ties -- reproduces the manifest's
+ *   lane / lane_offset / aggregate_offset of all 693 tensors from names and sizes.
+ * image_checksum_host: XOR and wrapping SUM over 64-bit words, accumulated into the two outputs
+ *   (benchmarks/shape-lab/native/src/striped_image_builder.cpp:137-147).
+ * image_build: writes the lane files from host tensors at the planned offsets (zero padding).
+ * image_scatter_ingest: the C ABI shape of torch_owned_striped_tensor_scatter_ingest
+ *   (benchmarks/shape-lab/native/src/torch_owned_striped_image_loader.hip.cpp:127-135): byte
+ *   ranges [aggregate_offsets[i], + payload_bytes[i]) go to the device pointers
+ *   destination_ptrs[i]; one reader per lane with two pinned buffers of chunk_bytes and two
+ *   streams, O_DIRECT where the file system allows it; then the XOR / SUM checksum of everything
+ *   written is evaluated ON THE DEVICE and, if check_expected != 0, compared.  A range need not be
+ *   a whole tensor: rank r of W loads the byte range of experts [r*256/W, (r+1)*256/W) of an expert
+ *   tensor (offsets stay multiples of 4096).  Synchronous; allocates only its staging buffers. */
+typedef struct aima_moe_image_ingest_result {
+  uint64_t bytes;         /* payload bytes moved to the device */
+  double read_ms;         /* wall time of reads + copies */
+  float checksum_ms;      /* device time of the checksum kernel */
+  uint32_t direct_io;     /* bit l set: lane l was read with O_DIRECT */
+  uint64_t xor_value;
+  uint64_t sum_value;
+} aima_moe_image_ingest_result;
+
+int aima_moe_image_plan(const uint64_t* payload_bytes, const char* const* names, uint64_t count,
+                        uint32_t* lane, uint64_t* lane_offset, uint64_t* aggregate_offset,
+                        uint64_t* lane_bytes /* [2] */);
+int aima_moe_image_checksum_host(const void* data, uint64_t bytes, uint64_t* xor_value, uint64_t* sum_value);
+int aima_moe_image_build(const char* lane0_path, const char* lane1_path, const void* const* host_tensors,
+                         const uint64_t* payload_bytes, const uint32_t* lane, const uint64_t* lane_offset,
+                         uint64_t count, const uint64_t* lane_bytes, uint64_t* xor_value, uint64_t* sum_value);
+int aima_moe_image_scatter_ingest(const char* lane0_path, const char* lane1_path,
+                                  const uint64_t* aggregate_offsets, const uint64_t* payload_bytes,
+                                  const uint64_t* destination_ptrs, uint64_t tensor_count,
+                                  uint64_t lane0_bytes, uint64_t lane1_bytes, uint64_t chunk_bytes,
+                                  int check_expected, uint64_t expected_xor, uint64_t expected_sum,
+                                  aima_moe_image_ingest_result* result);
+
 #ifdef __cplusplus
 }
 #endif
