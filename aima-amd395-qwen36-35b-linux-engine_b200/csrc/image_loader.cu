@@ -47,28 +47,45 @@ int image_fail(int status, const std::string& message) {
   return status;
 }
 
-// block b folds words b, b + grid, ... of a task; XOR and wrapping SUM are order-free
+// XOR and wrapping SUM are order-free: every range is cut into pieces of at most kChecksumPieceWords
+// words, one block per piece, 16-byte loads, four in flight per thread; block results join by atomics.
 struct ChecksumTask {
-  const uint64_t* data;
+  const uint64_t* data;     // 16-byte aligned
   uint64_t words;
 };
+constexpr uint64_t kChecksumPieceWords = (2u << 20) / 8;
 
 __global__ void __launch_bounds__(kChecksumThreads)
-image_checksum_kernel(const ChecksumTask* __restrict__ tasks, int blocks_per_task,
+image_checksum_kernel(const ChecksumTask* __restrict__ tasks,
                       unsigned long long* __restrict__ xor_out, unsigned long long* __restrict__ sum_out) {
   __shared__ unsigned long long xor_values[kChecksumThreads];
   __shared__ unsigned long long sum_values[kChecksumThreads];
-  const ChecksumTask task = tasks[blockIdx.x / blocks_per_task];
-  const int part = blockIdx.x % blocks_per_task;
-  unsigned long long local_xor = 0, local_sum = 0;
-  for (uint64_t index = static_cast<uint64_t>(part) * kChecksumThreads + threadIdx.x; index < task.words;
-       index += static_cast<uint64_t>(blocks_per_task) * kChecksumThreads) {
-    const unsigned long long value = __ldcs(reinterpret_cast<const unsigned long long*>(task.data) + index);
-    local_xor ^= value;
-    local_sum += value;
+  const ChecksumTask task = tasks[blockIdx.x];
+  const ulonglong2* pairs = reinterpret_cast<const ulonglong2*>(task.data);
+  const uint64_t n_pairs = task.words / 2;
+  unsigned long long x0 = 0, x1 = 0, s0 = 0, s1 = 0;
+  uint64_t index = threadIdx.x;
+  for (; index + 3 * kChecksumThreads < n_pairs; index += 4 * kChecksumThreads) {
+    const ulonglong2 a = __ldcs(pairs + index);
+    const ulonglong2 b = __ldcs(pairs + index + kChecksumThreads);
+    const ulonglong2 c = __ldcs(pairs + index + 2 * kChecksumThreads);
+    const ulonglong2 d = __ldcs(pairs + index + 3 * kChecksumThreads);
+    x0 ^= a.x ^ b.x ^ c.x ^ d.x;
+    x1 ^= a.y ^ b.y ^ c.y ^ d.y;
+    s0 += a.x + b.x + c.x + d.x;
+    s1 += a.y + b.y + c.y + d.y;
   }
-  xor_values[threadIdx.x] = local_xor;
-  sum_values[threadIdx.x] = local_sum;
+  for (; index < n_pairs; index += kChecksumThreads) {
+    const ulonglong2 a = __ldcs(pairs + index);
+    x0 ^= a.x; x1 ^= a.y; s0 += a.x; s1 += a.y;
+  }
+  if ((task.words & 1u) != 0 && threadIdx.x == 0) {
+    const unsigned long long last = task.data[task.words - 1];
+    x0 ^= last;
+    s0 += last;
+  }
+  xor_values[threadIdx.x] = x0 ^ x1;
+  sum_values[threadIdx.x] = s0 + s1;
   __syncthreads();
   for (int offset = kChecksumThreads / 2; offset > 0; offset >>= 1) {
     if (threadIdx.x < offset) {
@@ -277,7 +294,7 @@ AIMA_EXPORT int aima_moe_image_scatter_ingest(const char* lane0_path, const char
   readers[0].path = lane0_path;
   readers[1].path = lane1_path;
   uint64_t total = 0;
-  std::vector<ChecksumTask> tasks(tensor_count);
+  std::vector<ChecksumTask> tasks;
   for (uint64_t i = 0; i < tensor_count; ++i) {
     const uint64_t offset = aggregate_offsets[i], bytes = payload_bytes[i];
     if (destination_ptrs[i] == 0 || offset % kImageAlignment != 0 || bytes == 0 || bytes % 8 != 0 ||
@@ -295,7 +312,9 @@ AIMA_EXPORT int aima_moe_image_scatter_ingest(const char* lane0_path, const char
       return image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "image ingest: destination " + std::to_string(i) + " is not device memory");
     }
     readers[l].jobs.push_back({in_lane, bytes, reinterpret_cast<uint8_t*>(destination_ptrs[i])});
-    tasks[i] = {reinterpret_cast<const uint64_t*>(destination_ptrs[i]), bytes / 8};
+    for (uint64_t word = 0; word < bytes / 8; word += kChecksumPieceWords)
+      tasks.push_back({reinterpret_cast<const uint64_t*>(destination_ptrs[i]) + word,
+                       std::min<uint64_t>(kChecksumPieceWords, bytes / 8 - word)});
     total += bytes;
   }
   for (LaneReader& reader : readers) { reader.chunk_bytes = chunk_bytes; reader.device = device; }
@@ -310,20 +329,19 @@ AIMA_EXPORT int aima_moe_image_scatter_ingest(const char* lane0_path, const char
   // device checksum over everything that was written
   ChecksumTask* device_tasks = nullptr;
   unsigned long long* device_words = nullptr;
-  cudaError_t error = cudaMalloc(&device_tasks, sizeof(ChecksumTask) * tensor_count);
+  cudaError_t error = cudaMalloc(&device_tasks, sizeof(ChecksumTask) * tasks.size());
   if (error == cudaSuccess) error = cudaMalloc(&device_words, 16);
   if (error == cudaSuccess) error = cudaMemset(device_words, 0, 16);
   if (error == cudaSuccess)
-    error = cudaMemcpy(device_tasks, tasks.data(), sizeof(ChecksumTask) * tensor_count, cudaMemcpyHostToDevice);
+    error = cudaMemcpy(device_tasks, tasks.data(), sizeof(ChecksumTask) * tasks.size(), cudaMemcpyHostToDevice);
   cudaEvent_t begin = nullptr, end = nullptr;
   float checksum_ms = 0.0f;
   if (error == cudaSuccess) error = cudaEventCreate(&begin);
   if (error == cudaSuccess) error = cudaEventCreate(&end);
   if (error == cudaSuccess) {
-    const int blocks_per_task = 64;
     cudaEventRecord(begin, nullptr);
-    image_checksum_kernel<<<static_cast<unsigned>(tensor_count) * blocks_per_task, kChecksumThreads>>>(
-        device_tasks, blocks_per_task, device_words, device_words + 1);
+    image_checksum_kernel<<<static_cast<unsigned>(tasks.size()), kChecksumThreads>>>(device_tasks, device_words,
+                                                                                   device_words + 1);
     cudaEventRecord(end, nullptr);
     error = cudaGetLastError();
     if (error == cudaSuccess) error = cudaEventSynchronize(end);

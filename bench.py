@@ -536,6 +536,56 @@ def run_lm_head(args) -> None:
         **({"cpu_baseline": baseline} if baseline is not None else {})}))
 
 
+def run_ingest(args) -> None:
+    """`--workload ingest`: one layer's expert tensors (1.5 GiB) written as a two-lane striped image, then
+    loaded with aima_moe_image_scatter_ingest; a step is one full ingest.  The roofline line is the device
+    checksum kernel (reads every loaded byte once); read_gbs is file -> pinned buffer -> device."""
+    import tempfile
+
+    import torch
+    from __graft_entry__ import load_package
+
+    package = load_package()
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    image = package.StripedImage()
+    generator = torch.Generator().manual_seed(SEED)
+    tensors = {
+        "model.language_model.layers.0.mlp.experts.gate_up_proj":
+            torch.randint(-2**15, 2**15 - 1, (256, 1024, 2048), generator=generator, dtype=torch.int16),
+        "model.language_model.layers.0.mlp.experts.down_proj":
+            torch.randint(-2**15, 2**15 - 1, (256, 2048, 512), generator=generator, dtype=torch.int16),
+    }
+    names = sorted(tensors)
+    steps, warmup = max(min(args.steps, 20), 1), 1
+    with tempfile.TemporaryDirectory(dir=os.environ.get("AIMA_IMAGE_DIR")) as folder:
+        paths = (os.path.join(folder, "lane0.bin"), os.path.join(folder, "lane1.bin"))
+        plan = image.build(*paths, names, tensors)
+        destinations = [torch.empty_like(tensors[name], device=device) for name in names]
+        ranges = [(plan["aggregate_offset"][i], plan["payload_bytes"][i]) for i in range(len(names))]
+        results = []
+        for _ in range(warmup + steps):
+            results.append(image.scatter_ingest(*paths, ranges, destinations, plan["lane_bytes"], chunk_bytes=32 << 20,
+                                                expected=(plan["xor"], plan["sum"])))
+        results = results[warmup:]
+    total = results[0].bytes
+    read_ms = sum(r.read_ms for r in results) / len(results)
+    checksum_ms = sum(r.checksum_ms for r in results) / len(results)
+    peak, kind = measured_peaks()
+    gbs = total / (checksum_ms * 1.0e-3) / 1.0e9
+    print(json.dumps({
+        "metric": "striped_image_ingest_gigabytes_per_second", "value": total / (read_ms * 1.0e-3) / 1.0e9,
+        "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": read_ms + checksum_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "config": {"workload": "striped_image_ingest (one layer's expert tensors, 1.5 GiB, two lanes)",
+                   "direct_io_lanes": int(results[0].direct_io), "chunk_bytes": 32 << 20,
+                   "l2": "inputs larger than L2 (1.6 GB per step)"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                     "traffic": None, "peak_source": kind, "kernel": "image_checksum_kernel",
+                     "bytes_per_step": int(total)},
+        "read_ms": read_ms, "checksum_ms": checksum_ms, "gpu_launches": steps}))
+
+
 def run_prefill(args) -> None:
     """`--workload prefill`: the one-layer T = 8192 prefill line (profiling aid and second headline)."""
     import torch
@@ -592,7 +642,7 @@ def main() -> None:
     parser.add_argument("--no-prefill", action="store_true", help="skip the one-layer prefill sub-object")
     parser.add_argument("--layers", type=int, default=LAYERS,
                         help="stack depth; anything but 40 is a profiling aid, not the benchmark config")
-    parser.add_argument("--workload", choices=["decode", "prefill", "lm_head"], default="decode",
+    parser.add_argument("--workload", choices=["decode", "prefill", "lm_head", "ingest"], default="decode",
                         help="decode = the benchmark line; prefill = one-layer prefill line only")
     parser.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
     parser.add_argument("--routing", choices=["zipf", "uniform"], default="zipf")
@@ -611,6 +661,8 @@ def main() -> None:
         run_prefill(args)
     elif args.workload == "lm_head":
         run_lm_head(args)
+    elif args.workload == "ingest":
+        run_ingest(args)
     else:
         run_ours(args)
 
