@@ -369,3 +369,219 @@ AIMA_EXPORT int aima_moe_image_scatter_ingest(const char* lane0_path, const char
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Safetensors shards as the source of an image: header index and a builder that copies extents
+// from source files.  Format: 8-byte little-endian header length N, N bytes of JSON
+// {"tensor": {"dtype": "BF16", "shape": [..], "data_offsets": [begin, end]}, ..., "__metadata__": {..}},
+// then the data section; data_offsets are relative to its start.  The reference's manifest records
+// the same two numbers per tensor (source_data_offset_bytes = 8 + N, source_offset_bytes =
+// source_data_offset_bytes + begin; engine/production-striped-image-manifest.json entries[*]) and its
+// builder copies [source offset, + payload) to the planned extent
+// (benchmarks/shape-lab/native/src/striped_image_builder.cpp:97-135, 149-200).
+// ---------------------------------------------------------------------------
+namespace {
+
+struct JsonCursor {
+  const char* p;
+  const char* end;
+  bool ok = true;
+  void skip_ws() { while (p < end && (*p == ' ' || *p == '\n' || *p == '\r' || *p == '\t')) ++p; }
+  bool eat(char c) { skip_ws(); if (p < end && *p == c) { ++p; return true; } return false; }
+  bool peek(char c) { skip_ws(); return p < end && *p == c; }
+  std::string string() {
+    std::string out;
+    skip_ws();
+    if (p >= end || *p != '"') { ok = false; return out; }
+    ++p;
+    while (p < end && *p != '"') {
+      if (*p == '\\' && p + 1 < end) {
+        ++p;
+        switch (*p) {
+          case 'n': out.push_back('\n'); break;
+          case 't': out.push_back('\t'); break;
+          case 'r': out.push_back('\r'); break;
+          case 'b': out.push_back('\b'); break;
+          case 'f': out.push_back('\f'); break;
+          case 'u': out.push_back('?'); p += (p + 4 < end) ? 4 : 0; break;   // names are ASCII in practice
+          default: out.push_back(*p); break;
+        }
+        ++p;
+      } else {
+        out.push_back(*p++);
+      }
+    }
+    if (p >= end) { ok = false; return out; }
+    ++p;
+    return out;
+  }
+  uint64_t number() {
+    skip_ws();
+    uint64_t value = 0;
+    bool any = false;
+    while (p < end && *p >= '0' && *p <= '9') { value = value * 10 + static_cast<uint64_t>(*p - '0'); ++p; any = true; }
+    if (!any) ok = false;
+    return value;
+  }
+  void skip_value() {   // any JSON value
+    skip_ws();
+    if (p >= end) { ok = false; return; }
+    if (*p == '"') { (void)string(); return; }
+    if (*p == '{' || *p == '[') {
+      const char open = *p, close = (*p == '{') ? '}' : ']';
+      ++p;
+      if (eat(close)) return;
+      do {
+        if (open == '{') { (void)string(); if (!eat(':')) { ok = false; return; } }
+        skip_value();
+        if (!ok) return;
+      } while (eat(','));
+      if (!eat(close)) ok = false;
+      return;
+    }
+    while (p < end && *p != ',' && *p != '}' && *p != ']') ++p;   // number, true, false, null
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+AIMA_EXPORT int aima_moe_safetensors_index(const char* path, aima_moe_safetensors_entry* entries,
+                                           uint64_t capacity, uint64_t* count) {
+  if (path == nullptr || count == nullptr || (entries == nullptr && capacity != 0))
+    return image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "safetensors index: null argument");
+  *count = 0;
+  const int descriptor = open(path, O_RDONLY);
+  if (descriptor < 0) return image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, std::string("safetensors index: cannot open ") + path);
+  uint64_t header_bytes = 0;
+  const off_t file_bytes = lseek(descriptor, 0, SEEK_END);
+  if (pread(descriptor, &header_bytes, 8, 0) != 8 || header_bytes == 0 || header_bytes > (1ull << 30) ||
+      static_cast<uint64_t>(file_bytes) < 8 + header_bytes) {
+    close(descriptor);
+    return image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, std::string("safetensors index: bad header length in ") + path);
+  }
+  std::string header(header_bytes, '\0');
+  uint64_t got = 0;
+  while (got < header_bytes) {
+    const ssize_t n = pread(descriptor, &header[got], header_bytes - got, static_cast<off_t>(8 + got));
+    if (n <= 0) break;
+    got += static_cast<uint64_t>(n);
+  }
+  close(descriptor);
+  if (got < header_bytes) return image_fail(AIMA_MOE_ERR_INTERNAL, "safetensors index: short read of the header");
+  const uint64_t data_start = 8 + header_bytes;
+  JsonCursor json{header.data(), header.data() + header.size()};
+  if (!json.eat('{')) return image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "safetensors index: header is not a JSON object");
+  uint64_t found = 0;
+  if (!json.peek('}')) {
+    do {
+      const std::string name = json.string();
+      if (!json.ok || !json.eat(':')) { json.ok = false; break; }
+      if (name == "__metadata__") { json.skip_value(); continue; }
+      aima_moe_safetensors_entry entry{};
+      bool have_offsets = false;
+      if (!json.eat('{')) { json.ok = false; break; }
+      do {
+        const std::string key = json.string();
+        if (!json.ok || !json.eat(':')) { json.ok = false; break; }
+        if (key == "dtype") {
+          const std::string dtype = json.string();
+          std::snprintf(entry.dtype, sizeof entry.dtype, "%s", dtype.c_str());
+        } else if (key == "shape") {
+          if (!json.eat('[')) { json.ok = false; break; }
+          if (!json.peek(']')) {
+            do {
+              const uint64_t extent = json.number();
+              if (entry.rank < 4) entry.shape[entry.rank] = extent;
+              ++entry.rank;
+            } while (json.ok && json.eat(','));
+          }
+          if (!json.eat(']')) json.ok = false;
+        } else if (key == "data_offsets") {
+          if (!json.eat('[')) { json.ok = false; break; }
+          entry.data_begin = data_start + json.number();
+          if (!json.eat(',')) json.ok = false;
+          entry.data_end = data_start + json.number();
+          if (!json.eat(']')) json.ok = false;
+          have_offsets = true;
+        } else {
+          json.skip_value();
+        }
+      } while (json.ok && json.eat(','));
+      if (!json.ok || !json.eat('}')) { json.ok = false; break; }
+      if (!have_offsets || entry.rank > 4 || entry.data_end < entry.data_begin ||
+          entry.data_end > static_cast<uint64_t>(file_bytes) || name.size() >= sizeof entry.name)
+        return image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "safetensors index: tensor " + name + " has a bad entry");
+      std::snprintf(entry.name, sizeof entry.name, "%s", name.c_str());
+      if (found < capacity) entries[found] = entry;
+      ++found;
+    } while (json.ok && json.eat(','));
+  }
+  if (!json.ok || !json.eat('}'))
+    return image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, std::string("safetensors index: malformed header in ") + path);
+  *count = found;
+  if (found > capacity && capacity != 0)
+    return image_fail(AIMA_MOE_ERR_CAPACITY, "safetensors index: more tensors than the entry array holds");
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_image_build_from_files(const char* lane0_path, const char* lane1_path,
+                                                const char* const* source_paths, const uint64_t* source_offsets,
+                                                const uint64_t* payload_bytes, const uint32_t* lane,
+                                                const uint64_t* lane_offset, uint64_t count,
+                                                const uint64_t* lane_bytes, uint64_t* xor_value, uint64_t* sum_value) {
+  if (lane0_path == nullptr || lane1_path == nullptr || source_paths == nullptr || source_offsets == nullptr ||
+      payload_bytes == nullptr || lane == nullptr || lane_offset == nullptr || lane_bytes == nullptr || count == 0)
+    return image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "image build: null argument");
+  const char* paths[kLanes] = {lane0_path, lane1_path};
+  int descriptors[kLanes] = {-1, -1};
+  int status = AIMA_MOE_OK;
+  for (int l = 0; l < kLanes && status == AIMA_MOE_OK; ++l) {
+    descriptors[l] = open(paths[l], O_WRONLY | O_CREAT | O_TRUNC, 0644);
+    if (descriptors[l] < 0 || ftruncate(descriptors[l], static_cast<off_t>(lane_bytes[l])) != 0)
+      status = image_fail(AIMA_MOE_ERR_INTERNAL, std::string("image build: cannot create ") + paths[l]);
+  }
+  std::vector<uint8_t> buffer(16u << 20);
+  uint64_t x = 0, s = 0;
+  for (uint64_t i = 0; i < count && status == AIMA_MOE_OK; ++i) {
+    if (source_paths[i] == nullptr || lane[i] >= kLanes || lane_offset[i] % kImageAlignment != 0 ||
+        payload_bytes[i] == 0 || payload_bytes[i] % 8 != 0 || lane_offset[i] + payload_bytes[i] > lane_bytes[lane[i]]) {
+      status = image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "image build: extent " + std::to_string(i) + " is misaligned or outside its lane");
+      break;
+    }
+    const int source = open(source_paths[i], O_RDONLY);
+    if (source < 0) { status = image_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, std::string("image build: cannot open ") + source_paths[i]); break; }
+    uint64_t done = 0;
+    while (done < payload_bytes[i] && status == AIMA_MOE_OK) {
+      const uint64_t want = std::min<uint64_t>(buffer.size(), payload_bytes[i] - done);
+      uint64_t got = 0;
+      while (got < want) {
+        const ssize_t n = pread(source, buffer.data() + got, want - got, static_cast<off_t>(source_offsets[i] + done + got));
+        if (n <= 0) break;
+        got += static_cast<uint64_t>(n);
+      }
+      if (got < want) { status = image_fail(AIMA_MOE_ERR_INTERNAL, std::string("image build: short read from ") + source_paths[i]); break; }
+      uint64_t put = 0;
+      while (put < want) {
+        const ssize_t n = pwrite(descriptors[lane[i]], buffer.data() + put, want - put, static_cast<off_t>(lane_offset[i] + done + put));
+        if (n <= 0) break;
+        put += static_cast<uint64_t>(n);
+      }
+      if (put < want) { status = image_fail(AIMA_MOE_ERR_INTERNAL, "image build: short write"); break; }
+      aima_moe_image_checksum_host(buffer.data(), want, &x, &s);
+      done += want;
+    }
+    close(source);
+  }
+  for (int l = 0; l < kLanes; ++l) {
+    if (descriptors[l] >= 0) { fsync(descriptors[l]); close(descriptors[l]); }
+  }
+  if (status == AIMA_MOE_OK) {
+    if (xor_value != nullptr) *xor_value = x;
+    if (sum_value != nullptr) *sum_value = s;
+  }
+  return status;
+}
+
+}  // extern "C"

@@ -80,6 +80,13 @@ class Metrics(ctypes.Structure):
     ]
 
 
+class SafetensorsEntry(ctypes.Structure):
+    _fields_ = [
+        ("name", ctypes.c_char * 200), ("dtype", ctypes.c_char * 8), ("rank", c_uint32), ("reserved", c_uint32),
+        ("shape", c_uint64 * 4), ("data_begin", c_uint64), ("data_end", c_uint64),
+    ]
+
+
 class ImageIngestResult(ctypes.Structure):
     _fields_ = [
         ("bytes", c_uint64), ("read_ms", ctypes.c_double), ("checksum_ms", c_float), ("direct_io", c_uint32),
@@ -132,6 +139,12 @@ EXPORTS = [
     ("aima_moe_lm_head_launch", c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
     ("aima_moe_lm_head_read_result", c_int, [c_void_p, ctypes.POINTER(LmHeadResult)]),
     ("aima_moe_lm_head_release", c_int, [c_void_p]),
+    ("aima_moe_safetensors_index", c_int,
+     [ctypes.c_char_p, ctypes.POINTER(SafetensorsEntry), c_uint64, ctypes.POINTER(c_uint64)]),
+    ("aima_moe_image_build_from_files", c_int,
+     [ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(c_uint64),
+      ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint32), ctypes.POINTER(c_uint64), c_uint64,
+      ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64)]),
     ("aima_moe_image_plan", c_int,
      [ctypes.POINTER(c_uint64), ctypes.POINTER(ctypes.c_char_p), c_uint64, ctypes.POINTER(c_uint32),
       ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64), ctypes.POINTER(c_uint64)]),
@@ -579,6 +592,31 @@ class StripedImage:
             (c_uint64 * 2)(*plan["lane_bytes"]), ctypes.byref(xor_value), ctypes.byref(sum_value)))
         plan.update({"payload_bytes": sizes, "xor": int(xor_value.value), "sum": int(sum_value.value),
                      "names": list(names)})
+        return plan
+
+    def safetensors_index(self, path: str) -> list[dict]:
+        """Tensors of one safetensors shard: name, dtype, shape and absolute byte range in the file."""
+        count = c_uint64()
+        self.lib.check(self.lib.aima_moe_safetensors_index(str(path).encode(), None, 0, ctypes.byref(count)))
+        entries = (SafetensorsEntry * max(count.value, 1))()
+        self.lib.check(self.lib.aima_moe_safetensors_index(str(path).encode(), entries, count.value, ctypes.byref(count)))
+        return [{"name": e.name.decode(), "dtype": e.dtype.decode(), "shape": list(e.shape[:e.rank]),
+                 "begin": int(e.data_begin), "end": int(e.data_end)} for e in entries[:count.value]]
+
+    def build_from_files(self, lane0_path: str, lane1_path: str, sources: list[dict]) -> dict:
+        """sources: dicts with name, path, begin, end (e.g. from safetensors_index plus the shard's path)."""
+        names = [entry["name"] for entry in sources]
+        sizes = [entry["end"] - entry["begin"] for entry in sources]
+        plan = self.plan(names, sizes)
+        count = len(sources)
+        xor_value, sum_value = c_uint64(), c_uint64()
+        self.lib.check(self.lib.aima_moe_image_build_from_files(
+            str(lane0_path).encode(), str(lane1_path).encode(),
+            (ctypes.c_char_p * count)(*[str(entry["path"]).encode() for entry in sources]),
+            (c_uint64 * count)(*[entry["begin"] for entry in sources]), (c_uint64 * count)(*sizes),
+            (c_uint32 * count)(*plan["lane"]), (c_uint64 * count)(*plan["lane_offset"]), count,
+            (c_uint64 * 2)(*plan["lane_bytes"]), ctypes.byref(xor_value), ctypes.byref(sum_value)))
+        plan.update({"payload_bytes": sizes, "xor": int(xor_value.value), "sum": int(sum_value.value), "names": names})
         return plan
 
     def scatter_ingest(self, lane0_path: str, lane1_path: str, ranges: list[tuple[int, int]], destinations: list,

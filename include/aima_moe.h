@@ -399,6 +399,27 @@ typedef struct aima_moe_image_ingest_result {
   uint64_t sum_value;
 } aima_moe_image_ingest_result;
 
+/* Safetensors shards as the source: safetensors_index lists the tensors of one shard (absolute file
+ * offsets: 8 + header length + data_offsets, the manifest's source_offset_bytes); image_build_from_files
+ * copies [source_offsets[i], + payload_bytes[i]) of source_paths[i] to the planned extents, as the
+ * reference's builder does from its plan rows (striped_image_builder.cpp:97-135).  Pass capacity 0 and
+ * entries NULL to count the tensors first. */
+typedef struct aima_moe_safetensors_entry {
+  char name[200];
+  char dtype[8];
+  uint32_t rank;
+  uint32_t reserved;
+  uint64_t shape[4];
+  uint64_t data_begin;    /* absolute offset of the first payload byte in the file */
+  uint64_t data_end;
+} aima_moe_safetensors_entry;
+int aima_moe_safetensors_index(const char* path, aima_moe_safetensors_entry* entries, uint64_t capacity,
+                               uint64_t* count);
+int aima_moe_image_build_from_files(const char* lane0_path, const char* lane1_path,
+                                    const char* const* source_paths, const uint64_t* source_offsets,
+                                    const uint64_t* payload_bytes, const uint32_t* lane,
+                                    const uint64_t* lane_offset, uint64_t count, const uint64_t* lane_bytes,
+                                    uint64_t* xor_value, uint64_t* sum_value);
 int aima_moe_image_plan(const uint64_t* payload_bytes, const char* const* names, uint64_t count,
                         uint32_t* lane, uint64_t* lane_offset, uint64_t* aggregate_offset,
                         uint64_t* lane_bytes /* [2] */);

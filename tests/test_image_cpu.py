@@ -71,3 +71,63 @@ def test_builder_writes_the_planned_bytes(package, built_library, tmp_path):
     for lane in range(2):
         assert not files[lane][~covered[lane]].any()            # padding is zero
     assert (plan["xor"], plan["sum"]) == image_oracle.checksum([tensors[n].view(torch.int16).numpy() for n in names])
+
+
+def _write_safetensors(path, tensors: dict, metadata: dict | None = None) -> dict:
+    """Writes the safetensors container by hand (8-byte header length, JSON header, data section)."""
+    import struct
+
+    header, blobs, cursor = {}, [], 0
+    if metadata is not None:
+        header["__metadata__"] = metadata
+    for name, tensor in tensors.items():
+        raw = tensor.contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(tensor.shape), "data_offsets": [cursor, cursor + len(raw)]}
+        blobs.append(raw)
+        cursor += len(raw)
+    text = json.dumps(header, separators=(",", ":")).encode()
+    text += b" " * ((8 - len(text) % 8) % 8)
+    with open(path, "wb") as handle:
+        handle.write(struct.pack("<Q", len(text)))
+        handle.write(text)
+        for raw in blobs:
+            handle.write(raw)
+    return {name: (8 + len(text) + spec["data_offsets"][0], 8 + len(text) + spec["data_offsets"][1])
+            for name, spec in header.items() if name != "__metadata__"}
+
+
+def test_safetensors_index_and_build_from_shards(package, built_library, tmp_path):
+    image = package.StripedImage()
+    generator = torch.Generator().manual_seed(13)
+    shard_a = {
+        "model.language_model.layers.0.mlp.experts.gate_up_proj": torch.randn(4, 64, 128, generator=generator).to(torch.bfloat16),
+        "model.language_model.layers.0.mlp.gate.weight": torch.randn(256, 128, generator=generator).to(torch.bfloat16),
+    }
+    shard_b = {
+        "model.language_model.layers.0.mlp.experts.down_proj": torch.randn(4, 128, 32, generator=generator).to(torch.bfloat16),
+        'odd "name"\\with escapes': torch.randn(3, 5, 8, generator=generator).to(torch.bfloat16),
+    }
+    want_a = _write_safetensors(tmp_path / "a.safetensors", shard_a, {"format": "pt", "nested": {"k": [1, 2, {"x": None}]}})
+    want_b = _write_safetensors(tmp_path / "b.safetensors", shard_b)
+    sources, truth = [], {}
+    for path, tensors, want in ((tmp_path / "a.safetensors", shard_a, want_a), (tmp_path / "b.safetensors", shard_b, want_b)):
+        index = image.safetensors_index(path)
+        assert sorted(e["name"] for e in index) == sorted(tensors)
+        for entry in index:
+            assert entry["dtype"] == "BF16" and entry["shape"] == list(tensors[entry["name"]].shape)
+            assert (entry["begin"], entry["end"]) == want[entry["name"]]
+            sources.append({**entry, "path": path})
+            truth[entry["name"]] = tensors[entry["name"]]
+    plan = image.build_from_files(tmp_path / "lane0.bin", tmp_path / "lane1.bin", sources)
+    files = [np.fromfile(tmp_path / "lane0.bin", dtype=np.uint8), np.fromfile(tmp_path / "lane1.bin", dtype=np.uint8)]
+    for i, name in enumerate(plan["names"]):
+        raw = truth[name].contiguous().view(torch.int16).numpy().tobytes()
+        offset = plan["lane_offset"][i]
+        assert files[plan["lane"][i]][offset:offset + len(raw)].tobytes() == raw
+    assert (plan["xor"], plan["sum"]) == image_oracle.checksum(
+        [truth[name].contiguous().view(torch.int16).numpy() for name in plan["names"]])
+    # a truncated file and a malformed header fail closed
+    (tmp_path / "bad.safetensors").write_bytes(b"\x10\x00\x00\x00\x00\x00\x00\x00{\"a\":")
+    import pytest
+    with pytest.raises(package.AimaMoeError):
+        image.safetensors_index(tmp_path / "bad.safetensors")
