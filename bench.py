@@ -304,6 +304,17 @@ def measured_tensor_peak() -> tuple[float, str]:
         return 1590.0, "fallback"
 
 
+def apply_routing(provider, synth, device, routing: str) -> None:
+    """Router hooks of the benchmark regimes: uniform (none), zipf (config 2), hot (+20 on eight fixed experts,
+    config 4b), ties (logits rounded to multiples of 1/8, config 4c)."""
+    if routing == "zipf":
+        provider.set_router_hooks(synth.zipf_router_bias(SEED).to(device), False)
+    elif routing == "hot":
+        provider.set_router_hooks(synth.hot_expert_bias(range(3, 256, 32)).to(device), False)
+    elif routing == "ties":
+        provider.set_router_hooks(None, True)
+
+
 def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing: str, weights=None) -> dict:
     """Device-timed prefill of ONE MoE layer (BASELINE config 2: T = 8192, Zipf(1.1) router bias)."""
     import torch
@@ -314,8 +325,7 @@ def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing
         if weights is None:
             weights = synth.layer_weights_cuda_fast(SEED, 0, device)
         provider.bind_layer(0, weights)
-        if routing == "zipf":
-            provider.set_router_hooks(synth.zipf_router_bias(SEED).to(device), False)
+        apply_routing(provider, synth, device, routing)
         generator = torch.Generator(device=device).manual_seed(SEED)
         h2 = torch.randn(tokens, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
         resid = torch.randn(tokens, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
@@ -356,8 +366,7 @@ def prefill_stack_numbers(package, device, tokens: int, layers: int, iterations:
             weights = synth.layer_weights_cuda_fast(SEED, layer, device)
             provider.bind_layer(layer, weights)
             keep.append(weights)
-        if routing == "zipf":
-            provider.set_router_hooks(synth.zipf_router_bias(SEED).to(device), False)
+        apply_routing(provider, synth, device, routing)
         generator = torch.Generator(device=device).manual_seed(SEED)
         x = torch.randn(tokens, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
         y = torch.empty_like(x)
@@ -404,26 +413,37 @@ def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) ->
     per_rank_experts = 256 // world
     tokens_local = args.tokens // world
     flags = {1: 0, 2: package.provider.FLAG_EP_PIPELINE_2, 4: package.provider.FLAG_EP_PIPELINE_4}[args.ep_pipeline]
-    provider = package.MoeProvider(layers=1, max_prefill_tokens=args.tokens, world=world, rank=rank, flags=flags)
-    weights = synth.layer_weights_cuda_fast(SEED, 0, device, rank * per_rank_experts, (rank + 1) * per_rank_experts)
-    provider.bind_layer(0, weights)
+    n_layers = max(args.stack_layers, 1)
+    provider = package.MoeProvider(layers=n_layers, max_prefill_tokens=args.tokens, world=world, rank=rank, flags=flags)
+    keep = []
+    for layer in range(n_layers):
+        weights = synth.layer_weights_cuda_fast(SEED, layer, device, rank * per_rank_experts,
+                                                (rank + 1) * per_rank_experts)
+        provider.bind_layer(layer, weights)
+        keep.append(weights)
     provider.ep_connect_all(dist.new_group(backend="gloo"))
-    if args.routing == "zipf":
-        provider.set_router_hooks(synth.zipf_router_bias(SEED).to(device), False)
+    apply_routing(provider, synth, device, args.routing)
     generator = torch.Generator(device=device).manual_seed(SEED + rank)
     h2 = torch.randn(tokens_local, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
     resid = torch.randn(tokens_local, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
     out = torch.empty_like(resid)
     steps = max(args.steps, 1)
+
+    def one_step() -> None:
+        if n_layers > 1:
+            provider.prefill_stack(resid, out, 0, n_layers)          # norm + MoE half per layer (config 3 / 4)
+        else:
+            provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+
     for _ in range(3):
-        provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+        one_step()
     provider.sync_metrics()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dist.barrier()
     torch.cuda.synchronize()
     start.record()
     for _ in range(steps):
-        provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+        one_step()
     stop.record()
     dist.barrier()
     torch.cuda.synchronize()
@@ -437,13 +457,14 @@ def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) ->
     ms = float(times.item())
     if rank == 0:
         peak, kind = measured_tensor_peak()
-        tflops = args.tokens * PREFILL_FLOP_PER_TOKEN / (ms * 1.0e-3) / 1.0e12
+        tflops = args.tokens * PREFILL_FLOP_PER_TOKEN * n_layers / (ms * 1.0e-3) / 1.0e12
         exposed = sum(stages.get(name, 0.0) for name in ("routing_exchange", "dispatch", "row_return"))
         print(json.dumps({
             "metric": "moe_prefill_tokens_per_second", "value": args.tokens / (ms * 1.0e-3), "unit": "tokens/s",
             "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"prefill_T{args.tokens}_1layer_{args.routing} (BASELINE config 3 bucket)",
+            "config": {"workload": f"prefill_T{args.tokens}_{n_layers}layer_{args.routing} (BASELINE config 3 / 4 bucket)",
+                       "layers": n_layers, "ms_per_layer": ms / n_layers,
                        "routing": args.routing, "tokens_per_gpu": tokens_local, "pipeline_parts": args.ep_pipeline,
                        "multi_gpu": f"expert parallel, {per_rank_experts} experts per GPU, dispatch by peer loads, "
                                     "combine by peer stores over NVLink"},
@@ -645,7 +666,7 @@ def main() -> None:
     parser.add_argument("--workload", choices=["decode", "prefill", "lm_head", "ingest"], default="decode",
                         help="decode = the benchmark line; prefill = one-layer prefill line only")
     parser.add_argument("--tokens", type=int, default=8192, help="prefill tokens (--workload prefill)")
-    parser.add_argument("--routing", choices=["zipf", "uniform"], default="zipf")
+    parser.add_argument("--routing", choices=["zipf", "uniform", "hot", "ties"], default="zipf")
     parser.add_argument("--ep-pipeline", type=int, choices=[1, 2, 4], default=1,
                         help="--workload prefill on N > 1 GPUs: parts of the dispatch / products / return pipeline")
     parser.add_argument("--stack-layers", type=int, default=1,
