@@ -82,3 +82,20 @@ def test_synthetic_layers_are_reproducible(synth):
     assert bias.shape == (256,) and abs(float(bias.mean())) < 1e-6
     x = synth.activations(1, 64)
     assert abs(float(x.float().std()) - 1.0) < 0.02
+
+
+def test_lm_head_and_image_argument_checks_need_no_device(package, built_library):
+    lib = package.load_library()
+    handle = ctypes.c_void_p()
+    assert lib.aima_moe_lm_head_build(None, 10, ctypes.byref(handle), None) == -1 and not handle.value
+    assert lib.aima_moe_lm_head_launch(None, None, None, None) == -1
+    assert lib.aima_moe_lm_head_release(None) == 0
+    count = ctypes.c_uint64(7)
+    assert lib.aima_moe_safetensors_index(b"/nonexistent/file.safetensors", None, 0, ctypes.byref(count)) == -1
+    assert count.value == 0 and b"cannot open" in lib.aima_moe_last_error_string()
+    assert lib.aima_moe_image_plan(None, None, 0, None, None, None, None) == -1
+    x, s = ctypes.c_uint64(0), ctypes.c_uint64(0)
+    assert lib.aima_moe_image_checksum_host(ctypes.c_char_p(b"1234567"), 7, ctypes.byref(x), ctypes.byref(s)) == -1
+    p = package.provider
+    assert ctypes.sizeof(p.LmHeadResult) == 24 and ctypes.sizeof(p.ImageIngestResult) == 40
+    assert ctypes.sizeof(p.SafetensorsEntry) == 200 + 8 + 8 + 32 + 16
