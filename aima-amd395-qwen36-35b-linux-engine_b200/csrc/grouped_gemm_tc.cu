@@ -19,7 +19,9 @@
 //            rows 4l .. 4l+3 of the A tile BY TOKEN INDEX with one TMA gather4 copy per K block
 //            (rows beyond the tile's last valid row get an out-of-range index and arrive as zeros)
 //   warps 4-7 epilogue: tcgen05.ld 32 rows x 32 columns per warp, SwiGLU or
-//            scaling, BF16 stores
+//            scaling; the BF16 results of 64 output columns are turned in shared memory so that
+//            every store instruction writes whole 128-byte pieces of four rows (a thread storing
+//            its own row would touch 32 different lines per instruction)
 // Every mbarrier wait is bounded; on expiry the block sets the status word,
 // stops issuing, waits for its copies in flight, frees tensor memory and returns.
 #include "grouped_gemm.cuh"
@@ -40,7 +42,9 @@ constexpr int kStageBBytes = kBN * kBK * 2;        // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;
 constexpr int kTcThreads = 256;
 constexpr int kTmemColumns = 512;
-constexpr int kTcSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kStoreStageBytes = 32 * 128;          // per epilogue warp: 32 rows x 64 BF16 outputs
+constexpr int kTcSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+                             4 * kStoreStageBytes;
 
 struct TcMaps {
   CUtensorMap a;    // [rows, k]      box 64 x 128
@@ -132,8 +136,9 @@ constexpr uint32_t kInstrDesc =
     (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kBN >> 3) << 17) |
     (static_cast<uint32_t>(kBM >> 4) << 24);
 
-__device__ __forceinline__ void pack_store_32(__nv_bfloat16* dst, const float* v) {
-  uint4* out = reinterpret_cast<uint4*>(dst);
+// 32 results of this thread's row into half `half` (0/1) of the warp's 32 x 128-byte staging
+// tile; 16-byte pieces are XOR-swizzled by the row so that neither side has bank conflicts.
+__device__ __forceinline__ void stage_32(uint8_t* stage, int lane, int half, const float* v) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     uint4 w;
@@ -141,9 +146,28 @@ __device__ __forceinline__ void pack_store_32(__nv_bfloat16* dst, const float* v
     w.y = static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 2])) | (static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 3])) << 16);
     w.z = static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 4])) | (static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 5])) << 16);
     w.w = static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 6])) | (static_cast<uint32_t>(float_to_bf16_bits(v[8 * i + 7])) << 16);
-    out[i] = w;
+    const int piece = (4 * half + i) ^ (lane & 7);
+    *reinterpret_cast<uint4*>(stage + lane * 128 + piece * 16) = w;
   }
 }
+
+// The staged 32 x 64 tile to global memory: instruction i writes rows 4i .. 4i+3, eight lanes per
+// row.  dst = first row of the warp's 32, first of the 64 columns; rows_ok = valid rows of the 32;
+// cols_ok = valid columns of the 64 (a multiple of 8).
+__device__ __forceinline__ void store_staged(const uint8_t* stage, int lane, __nv_bfloat16* dst, size_t ldc,
+                                             int rows_ok, int cols_ok) {
+  __syncwarp();
+  const int piece = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = 4 * i + (lane >> 3);
+    const uint4 w = *reinterpret_cast<const uint4*>(stage + row * 128 + ((piece ^ (row & 7)) * 16));
+    if (row < rows_ok && piece * 8 < cols_ok)
+      *reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * ldc + piece * 8) = w;
+  }
+  __syncwarp();
+}
+
 
 template <int MODE, bool kGather = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -317,60 +341,75 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
       const bool row_ok = r < rows;
       const int row = row0 + r;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(buf * kBN);
+      uint8_t* stage = smem_gen + kStages * kStageBytes + 256 + ew * kStoreStageBytes;
+      const int rows_ok = min(32, rows - ew * 32);           // valid rows among this warp's 32 (may be <= 0)
       if (kDual) {
-        // columns [0,128) gate, [128,256) up  ->  128 activations per row
-        __nv_bfloat16* dst = g.c + static_cast<size_t>(row) * g.ldc + chunk * (kBN / 2);
+        // columns [0,128) gate, [128,256) up  ->  128 activations per row, stored 64 at a time
+        __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + chunk * (kBN / 2);
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN / 2; c0 += 32) {
-          uint32_t gr[32], ur[32];
-          tmem_ld32(taddr + c0, gr);
-          tmem_ld32(taddr + kBN / 2 + c0, ur);
-          tmem_ld_wait();
-          float v[32];
+        for (int c0 = 0; c0 < kBN / 2; c0 += 64) {
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            uint32_t gr[32], ur[32];
+            tmem_ld32(taddr + c0 + 32 * half, gr);
+            tmem_ld32(taddr + kBN / 2 + c0 + 32 * half, ur);
+            tmem_ld_wait();
+            float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float gate = round_bf16(__uint_as_float(gr[j]));
-            const float up = round_bf16(__uint_as_float(ur[j]));
-            const float s = det_silu(gate);
-            v[j] = (MODE == kGemmExpertGateUp) ? __fmul_rn(round_bf16(s), up) : __fmul_rn(s, up);
+            for (int j = 0; j < 32; ++j) {
+              const float gate = round_bf16(__uint_as_float(gr[j]));
+              const float up = round_bf16(__uint_as_float(ur[j]));
+              const float s = det_silu(gate);
+              v[j] = (MODE == kGemmExpertGateUp) ? __fmul_rn(round_bf16(s), up) : __fmul_rn(s, up);
+            }
+            stage_32(stage, lane, half, v);
           }
-          if (row_ok) pack_store_32(dst + c0, v);
+          store_staged(stage, lane, dst + c0, static_cast<size_t>(g.ldc), rows_ok, 64);
         }
-      } else {
+      } else if (MODE != kGemmPlainF32) {
         float scale = 1.0f;
         if (row_ok) {
           if (MODE == kGemmExpertDown) scale = g.row_scale[g.sorted_rows[row]];
           if (MODE == kGemmSharedDown) scale = g.row_scale[row];
         }
         const int col_base = chunk * kBN;
-        __nv_bfloat16* dst = g.c + static_cast<size_t>(row) * g.ldc + col_base;
+        __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + col_base;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN; c0 += 64) {
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            uint32_t ar[32];
+            tmem_ld32(taddr + c0 + 32 * half, ar);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float acc = __uint_as_float(ar[j]);
+              if (MODE == kGemmExpertDown) v[j] = __fmul_rn(acc, scale);
+              else if (MODE == kGemmSharedDown) v[j] = __fmul_rn(scale, round_bf16(acc));
+              else v[j] = acc;
+            }
+            stage_32(stage, lane, half, v);
+          }
+          store_staged(stage, lane, dst + c0, static_cast<size_t>(g.ldc), rows_ok,
+                       max(0, min(64, pb.n_valid - col_base - c0)));
+        }
+      } else {
+        // FP32 output (approximate router logits): every thread stores its own row
+        const int col_base = chunk * kBN;
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN; c0 += 32) {
           uint32_t ar[32];
           tmem_ld32(taddr + c0, ar);
           tmem_ld_wait();
-          float v[32];
+          if (row_ok) {
+            float4* out = reinterpret_cast<float4*>(g.c_f32 + static_cast<size_t>(row) * g.ldc + col_base + c0);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float acc = __uint_as_float(ar[j]);
-            if (MODE == kGemmExpertDown) v[j] = __fmul_rn(acc, scale);
-            else if (MODE == kGemmSharedDown) v[j] = __fmul_rn(scale, round_bf16(acc));
-            else v[j] = acc;
-          }
-          if (MODE == kGemmPlainF32) {
-            if (row_ok) {
-              float4* out = reinterpret_cast<float4*>(g.c_f32 + static_cast<size_t>(row) * g.ldc + col_base + c0);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (col_base + c0 + 4 * j + 4 <= pb.n_valid)
-                  out[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              }
+            for (int j = 0; j < 8; ++j) {
+              if (col_base + c0 + 4 * j + 4 <= pb.n_valid)
+                out[j] = make_float4(__uint_as_float(ar[4 * j]), __uint_as_float(ar[4 * j + 1]),
+                                     __uint_as_float(ar[4 * j + 2]), __uint_as_float(ar[4 * j + 3]));
             }
-          } else if (row_ok && col_base + c0 + 32 <= pb.n_valid) {
-            pack_store_32(dst + c0, v);
-          } else if (row_ok) {
-            for (int j = 0; j < 32; ++j)
-              if (col_base + c0 + j < pb.n_valid) dst[c0 + j] = __float2bfloat16_rn(v[j]);
           }
         }
       }
