@@ -15,9 +15,8 @@
 //   warp 1   one thread issues tcgen05.mma (M128 N256 K16, 4 per K block) and
 //            commits to the ring's "empty" barriers / the accumulator's "full" barrier
 //   warp 2   allocates and frees the 512 tensor-memory columns
-//            with fused dispatch (gate_up only) all 32 lanes of warp 0 take part: lane l fetches
-//            rows 4l .. 4l+3 of the A tile BY TOKEN INDEX with one TMA gather4 copy per K block
-//            (rows beyond the tile's last valid row get an out-of-range index and arrive as zeros)
+//   warps 2-3 with fused dispatch (gate_up only): gather the tile's 128 activation rows BY TOKEN
+//            INDEX with 16-byte cp.async copies that arrive on the stage's barrier when complete
 //   warps 4-7 epilogue: tcgen05.ld 32 rows x 32 columns per warp, SwiGLU or
 //            scaling; the BF16 results of 64 output columns are turned in shared memory so that
 //            every store instruction writes whole 128-byte pieces of four rows (a thread storing
@@ -70,15 +69,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "[%0], [%1, {%2, %3}], [%4];"
       :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
-// Four rows of a 2-D tensor, picked by row index, into four consecutive 128-byte rows of a
-// swizzled tile.  The tensor map has a box of 64 columns x 1 row.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int x,
-                                            int y0, int y1, int y2, int y3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-      :: "r"(dst), "l"(map), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(bar) : "memory");
+constexpr int kGatherThreads = 64;     // warps 2 and 3
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
 }
+// the barrier receives one arrival (already part of its expected count) once all cp.async copies this
+// thread has issued so far are complete
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t columns) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                :: "r"(smem_dst), "r"(columns) : "memory");
@@ -191,7 +192,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), kGather ? 1 + kGatherThreads : 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -234,7 +235,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (kGather || lane == 0) {
+    if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
@@ -250,39 +251,20 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
           b0_row = expert * pb.b_rows_per_expert + chunk * kBN;
           b1_row = b0_row + kBN / 2;
         }
-        int token[4] = {0, 0, 0, 0};
-        if (kGather) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int r = 4 * lane + j;
-            token[j] = r < rows ? (g.sorted_rows[row0 + r] >> 3) : pb.a_rows;   // a_rows: out of range, reads zeros
-          }
-        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kStageABytes;
-          if (lane == 0) {
-            if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); }
-            if (alive) {
-              mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-              if (!kGather) tma_load_2d(a_dst, &maps.a, kb * kBK, row0, full_bar(stage));
-              tma_load_2d(b_dst, &maps.b0, kb * kBK, b0_row, full_bar(stage));
-              tma_load_2d(b_dst + kStageBBytes / 2, kDual ? &maps.b1 : &maps.b0, kb * kBK, b1_row, full_bar(stage));
-            }
-          }
-          if (kGather) {
-            alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
-            if (alive)
-              tma_gather4(a_dst + lane * 512, &maps.a, kb * kBK, token[0], token[1], token[2], token[3],
-                          full_bar(stage));
-          }
-          if (!alive) break;
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
+          mbar_arrive_expect_tx(full_bar(stage), kGather ? kStageBBytes : kStageBytes);
+          if (!kGather) tma_load_2d(a_dst, &maps.a, kb * kBK, row0, full_bar(stage));
+          tma_load_2d(b_dst, &maps.b0, kb * kBK, b0_row, full_bar(stage));
+          tma_load_2d(b_dst + kStageBBytes / 2, kDual ? &maps.b1 : &maps.b0, kb * kBK, b1_row, full_bar(stage));
           ++issued;
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
       // drain on abort: wait (bounded) for the stages whose copies are still in flight
-      if (lane == 0 && *abort_flag != 0) {
+      if (*abort_flag != 0) {
         volatile int ignore = 0;
         int s = stage;
         uint32_t ph = phase;
@@ -292,6 +274,43 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
         }
       }
     }
+  } else if (kGather && (warp == 2 || warp == 3)) {
+    // ------------------------------ A-row gather -------------------------------
+    // Eight neighbouring threads copy the eight 16-byte pieces of one row per K block (a warp
+    // instruction then touches four 128-byte lines, not 32): thread t owns piece t % 8 of rows
+    // t / 8 + 8 j, j = 0 .. 15, fetched by token index; piece c of row r goes to piece position
+    // c ^ (r & 7) (the 128-byte swizzle).  The copies are asynchronous and the thread never waits for
+    // them: an arrive-on-completion on the stage's "full" barrier (already counted in the barrier's
+    // arrival count) follows each batch, so the only wait is for a free stage and up to kStages
+    // batches per thread stay in flight.
+    const int lt = (warp - 2) * 32 + lane;
+    const int piece = lt & 7;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x) {
+      int tile, chunk, expert, row0, rows;
+      unit_tile(unit, tile, chunk, expert, row0, rows);
+      int source[16];            // element offset of this thread's piece in each of its 16 rows
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int r = (lt >> 3) + 8 * j;
+        const int token = g.sorted_rows[row0 + min(r, rows - 1)] >> 3;   // rows past the tile's end repeat its last row
+        source[j] = token * g.lda + piece * 8;
+      }
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
+        const uint32_t base = smem_base + stage * kStageBytes;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int r = (lt >> 3) + 8 * j;
+          cp_async_16(base + r * 128 + ((piece ^ (r & 7)) << 4), g.gather_src + source[j] + kb * kBK);
+        }
+        cp_async_arrive_noinc(full_bar(stage));
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    cp_async_wait_all();     // nothing of this thread's may be in flight when the block exits
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
@@ -308,6 +327,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kBN);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag)) { alive = false; timeout(); break; }
+          if (kGather) fence_async_proxy();     // rows written by cp.async are read through the async proxy
           tc_fence_after();
           const uint32_t a_addr = smem_base + stage * kStageBytes;
           const uint32_t b_addr = a_addr + kStageABytes;

@@ -353,7 +353,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
     handle->prefill.status = handle->status;
     handle->prefill.use_simt_gemm = (config->flags & AIMA_MOE_FLAG_SIMT_PRODUCTS) != 0;
     handle->prefill.exact_router = (config->flags & AIMA_MOE_FLAG_EXACT_ROUTER) != 0;
-    handle->prefill.fused_dispatch = (config->flags & AIMA_MOE_FLAG_FUSED_DISPATCH) != 0;
+    handle->prefill.fused_dispatch = (config->flags & AIMA_MOE_FLAG_MATERIALIZED_DISPATCH) == 0;
     handle->prefill.ep_parts = (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_4)   ? 4
                                : (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_2) ? 2
                                                                                : 1;

@@ -17,7 +17,7 @@ struct PrefillWorkspace {
   int* status = nullptr;              // device status word shared with the handle
   bool use_simt_gemm = false;         // qualification: CUDA-core products instead of tcgen05
   bool exact_router = false;          // qualification: all 256 logits with the canonical dot
-  bool fused_dispatch = false;        // gate_up kernel gathers its rows itself (no materialised copy)
+  bool fused_dispatch = true;         // gate_up kernel gathers its rows itself (no materialised copy)
   uint8_t* base = nullptr;
   // The shared expert does not depend on the routing: it runs on a second stream, forked from and
   // joined to the caller's stream with events, next to the router, the plan and the row gather.

@@ -224,7 +224,7 @@ WEIGHT_KEYS = ("router", "expert_gate_up", "expert_down", "shared_gate", "shared
 NOALLOC_MAX_LAYERS = 8
 FLAG_SIMT_PRODUCTS = 1
 FLAG_EXACT_ROUTER = 2
-FLAG_FUSED_DISPATCH = 8
+FLAG_MATERIALIZED_DISPATCH = 8
 FLAG_EP_PIPELINE_2 = 32
 FLAG_EP_PIPELINE_4 = 64
 
