@@ -17,7 +17,7 @@
 //   warp 2   allocates and frees the 512 tensor-memory columns
 //   warps 2-3 with fused dispatch (gate_up only): gather the tile's 128 activation rows BY TOKEN
 //            INDEX with 16-byte cp.async copies that arrive on the stage's barrier when complete
-//   warps 4-7 epilogue: tcgen05.ld 32 rows x 32 columns per warp, SwiGLU or
+//   warps 4-11 epilogue (two per quarter of the TMEM lanes, half of the columns each): tcgen05.ld 32 rows x 32 columns per warp, SwiGLU or
 //            scaling; the BF16 results of 64 output columns are turned in shared memory so that
 //            every store instruction writes whole 128-byte pieces of four rows (a thread storing
 //            its own row would touch 32 different lines per instruction)
@@ -39,11 +39,12 @@ constexpr int kUmmaK = 16;
 constexpr int kStageABytes = kBM * kBK * 2;        // 16 KB
 constexpr int kStageBBytes = kBN * kBK * 2;        // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;
-constexpr int kTcThreads = 256;
+constexpr int kEpilogueWarps = 8;   // two per quarter of the 128 TMEM lanes, each taking half of the columns
+constexpr int kTcThreads = (4 + kEpilogueWarps) * 32;
 constexpr int kTmemColumns = 512;
 constexpr int kStoreStageBytes = 32 * 128;          // per epilogue warp: 32 rows x 64 BF16 outputs
 constexpr int kTcSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
-                             4 * kStoreStageBytes;
+                             kEpilogueWarps * kStoreStageBytes;
 
 struct TcMaps {
   CUtensorMap a;    // [rows, k]      box 64 x 128
@@ -197,7 +198,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);
+      mbar_init(tempty_bar(b), kEpilogueWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -347,7 +348,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
     }
   } else if (warp >= 4) {
     // ------------------------------ epilogue ----------------------------------
-    const int ew = warp - 4;                       // TMEM lanes 32 ew .. 32 ew + 31
+    const int ew = (warp - 4) & 3;                 // TMEM lanes 32 ew .. 32 ew + 31 (a warp reaches the quarter warp % 4)
+    const int eh = (warp - 4) >> 2;                // which half of the unit's columns this warp drains
     int local = 0;
     bool alive = true;
     for (int unit = blockIdx.x; unit < total_units && alive; unit += gridDim.x, ++local) {
@@ -361,13 +363,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
       const bool row_ok = r < rows;
       const int row = row0 + r;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(buf * kBN);
-      uint8_t* stage = smem_gen + kStages * kStageBytes + 256 + ew * kStoreStageBytes;
+      uint8_t* stage = smem_gen + kStages * kStageBytes + 256 + (warp - 4) * kStoreStageBytes;
       const int rows_ok = min(32, rows - ew * 32);           // valid rows among this warp's 32 (may be <= 0)
       if (kDual) {
         // columns [0,128) gate, [128,256) up  ->  128 activations per row, stored 64 at a time
         __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + chunk * (kBN / 2);
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN / 2; c0 += 64) {
+        for (int c0 = eh * (kBN / 4); c0 < (eh + 1) * (kBN / 4); c0 += 64) {
 #pragma unroll 1
           for (int half = 0; half < 2; ++half) {
             uint32_t gr[32], ur[32];
@@ -395,7 +397,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
         const int col_base = chunk * kBN;
         __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + col_base;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN; c0 += 64) {
+        for (int c0 = eh * (kBN / 2); c0 < (eh + 1) * (kBN / 2); c0 += 64) {
 #pragma unroll 1
           for (int half = 0; half < 2; ++half) {
             uint32_t ar[32];
@@ -418,7 +420,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
         // FP32 output (approximate router logits): every thread stores its own row
         const int col_base = chunk * kBN;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN; c0 += 32) {
+        for (int c0 = eh * (kBN / 2); c0 < (eh + 1) * (kBN / 2); c0 += 32) {
           uint32_t ar[32];
           tmem_ld32(taddr + c0, ar);
           tmem_ld_wait();
