@@ -242,7 +242,23 @@ prefill_router_kernel(const __nv_bfloat16* __restrict__ h2,
 constexpr int kCertWarps = 8;
 constexpr float kCertKappa = 6.103515625e-05f;   // 2^-14, ~4x the summed worst-case rounding terms
 
-__global__ void __launch_bounds__(kCertWarps * 32)
+// canonical 8-element step of the warp dot with BOTH operands still packed (same FMA order as fma8)
+__device__ __forceinline__ float fma8_packed(const uint4& x, const uint4& w, float acc) {
+  acc = __fmaf_rn(bf16_lo(x.x), bf16_lo(w.x), acc);
+  acc = __fmaf_rn(bf16_hi(x.x), bf16_hi(w.x), acc);
+  acc = __fmaf_rn(bf16_lo(x.y), bf16_lo(w.y), acc);
+  acc = __fmaf_rn(bf16_hi(x.y), bf16_hi(w.y), acc);
+  acc = __fmaf_rn(bf16_lo(x.z), bf16_lo(w.z), acc);
+  acc = __fmaf_rn(bf16_hi(x.z), bf16_hi(w.z), acc);
+  acc = __fmaf_rn(bf16_lo(x.w), bf16_lo(w.w), acc);
+  acc = __fmaf_rn(bf16_hi(x.w), bf16_hi(w.w), acc);
+  return acc;
+}
+
+// The token's row stays packed in registers, and the candidates are recomputed two at a time: the
+// kernel is bound by the latency of the candidates' router rows coming from L2, so two rows are
+// requested before either is used.
+__global__ void __launch_bounds__(kCertWarps * 32, 2)
 prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
                                 const __nv_bfloat16* __restrict__ router,
                                 const __nv_bfloat16* __restrict__ shared_gate,
@@ -259,14 +275,15 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
   const int token = blockIdx.x * kCertWarps + warp;
   if (token >= tokens) return;
 
-  float xr[64];
+  uint4 xp[8];
   float sumsq = 0.0f;
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
-    const uint4 v = *(reinterpret_cast<const uint4*>(h2 + static_cast<size_t>(token) * kHidden) + g * 32 + lane);
-    unpack8(v, xr + 8 * g);
+    xp[g] = *(reinterpret_cast<const uint4*>(h2 + static_cast<size_t>(token) * kHidden) + g * 32 + lane);
+    float x8[8];
+    unpack8(xp[g], x8);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sumsq = fmaf(xr[8 * g + j], xr[8 * g + j], sumsq);
+    for (int j = 0; j < 8; ++j) sumsq = fmaf(x8[j], x8[j], sumsq);
   }
   sumsq = butterfly_sum(sumsq);
   const float x_norm = sqrtf(sumsq) * 1.0001f;
@@ -283,24 +300,54 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
   }
   const float floor_value = warp_eighth_largest(lower, lane);
 
-  float v[8];
-  int recomputed = 0;
+  // lane q (q < 8) keeps the candidate mask of experts 32 q .. 32 q + 31; the warp walks all masks
+  // and takes two candidates per trip
+  unsigned my_mask = 0u;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
-    unsigned pending = __ballot_sync(0xffffffffu, upper[q] >= floor_value);
-    float mine = -CUDART_INF_F;
-    while (pending != 0u) {
-      const int owner = __ffs(pending) - 1;
-      pending &= pending - 1u;
-      const uint4* row = reinterpret_cast<const uint4*>(router + static_cast<size_t>(32 * q + owner) * kHidden) + lane;
-      float acc = 0.0f;
+    const unsigned m = __ballot_sync(0xffffffffu, upper[q] >= floor_value);
+    if (lane == q) my_mask = m;
+  }
+  float v[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc = fma8(xr + 8 * i, __ldg(row + i * 32), acc);
-      acc = butterfly_sum(acc);
-      if (lane == owner) mine = finish_logit(acc, b[q], quant_eighths);
-      ++recomputed;
+  for (int q = 0; q < 8; ++q) v[q] = -CUDART_INF_F;
+  int recomputed = 0;
+  int group = 0;
+  unsigned pending = __shfl_sync(0xffffffffu, my_mask, 0);
+  auto pop = [&]() -> int {
+    while (pending == 0u) {
+      if (++group >= 8) return -1;
+      pending = __shfl_sync(0xffffffffu, my_mask, group);
     }
-    v[q] = mine;
+    const int owner = __ffs(pending) - 1;
+    pending &= pending - 1u;
+    return 32 * group + owner;
+  };
+  while (true) {
+    const int e0 = pop();
+    if (e0 < 0) break;
+    const int e1 = pop();
+    const uint4* row0 = reinterpret_cast<const uint4*>(router + static_cast<size_t>(e0) * kHidden) + lane;
+    const uint4* row1 = reinterpret_cast<const uint4*>(router + static_cast<size_t>(e1 >= 0 ? e1 : e0) * kHidden) + lane;
+    uint4 w0[8], w1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w0[i] = __ldg(row0 + i * 32);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w1[i] = __ldg(row1 + i * 32);
+    float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      acc0 = fma8_packed(xp[i], w0[i], acc0);
+      acc1 = fma8_packed(xp[i], w1[i], acc1);
+    }
+    acc0 = butterfly_sum(acc0);
+    acc1 = butterfly_sum(acc1);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (e0 == 32 * q + lane) v[q] = finish_logit(acc0, b[q], quant_eighths);
+      if (e1 == 32 * q + lane) v[q] = finish_logit(acc1, b[q], quant_eighths);
+    }
+    recomputed += e1 >= 0 ? 2 : 1;
   }
   route_token(v, lane, sel_v_s + warp * 8, sel_i_s + warp * 8, static_cast<size_t>(token), ids, scores,
               weights, dbg_weights);
@@ -308,7 +355,7 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
     const uint4* row = reinterpret_cast<const uint4*>(shared_gate) + lane;
     float acc = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fma8(xr + 8 * i, __ldg(row + i * 32), acc);
+    for (int i = 0; i < 8; ++i) acc = fma8_packed(xp[i], __ldg(row + i * 32), acc);
     acc = butterfly_sum(acc);
     if (lane == 0) {
       shared_sigmoid[token] = round_bf16(det_sigmoid(round_bf16(acc)));
