@@ -369,23 +369,18 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         const int n_pairs = n_local * kInter;
         const int p0 = static_cast<int>((static_cast<long long>(c) * n_pairs) / G);
         const int p1 = static_cast<int>((static_cast<long long>(c + 1) * n_pairs) / G);
-        const int burst = min(p1 - p0, kRingSlots - 2);
-        auto issue_down = [&]() {
-          const uint32_t rank_bytes = nh * kDownRowBytes;
-          mbar_arrive_expect_tx(down_bar, rank_bytes * (n_local + 1));
-          for (int q = 0; q < n_local; ++q) {
-            const int e_local = misc->ids[misc->local_rank[q]] - p.expert_lo;
-            const __nv_bfloat16* src = L.expert_down +
-                (static_cast<size_t>(e_local) * kHidden + h0) * kInter;
-            bulk_g2s(smem_u32(down_region + q * kDecodeMaxRowsPerBlock * kDownRowBytes),
-                     src, rank_bytes, down_bar);
-          }
-          bulk_g2s(smem_u32(down_region + kTopK * kDecodeMaxRowsPerBlock * kDownRowBytes),
-                   L.shared_down_proj + static_cast<size_t>(h0) * kInter, rank_bytes, down_bar);
-          down_issued = li + 1;
-        };
+        // The block's slice of the down projection is needed only after the activation barrier.  The
+        // shared expert's rows (known without the routing) go first; the routed experts' rows are
+        // requested AFTER the last gate/up pair, so they arrive while the block waits at the barrier
+        // for the slowest block -- time in which HBM would otherwise idle -- instead of lengthening
+        // the gate/up stream (21.5 -> 20.7 us per layer; issuing them 6 or 12 items before the end
+        // gave 21.6 / 21.4).
+        const uint32_t rank_bytes = nh * kDownRowBytes;
+        mbar_arrive_expect_tx(down_bar, rank_bytes * (n_local + 1));
+        bulk_g2s(smem_u32(down_region + kTopK * kDecodeMaxRowsPerBlock * kDownRowBytes),
+                 L.shared_down_proj + static_cast<size_t>(h0) * kInter, rank_bytes, down_bar);
+        down_issued = li + 1;
         for (int pi = p0; pi < p1 && alive; ++pi) {
-          if (pi - p0 == burst) issue_down();
           const int q = pi / kInter;
           const int i = pi - q * kInter;
           const int e_local = misc->ids[misc->local_rank[q]] - p.expert_lo;
@@ -400,8 +395,15 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           issued[s] = seq / kRingSlots + 1;
           ++seq;
         }
+        // also on the way out after a failed wait: the barrier's byte count must be met before the drain
+        for (int q = 0; q < n_local; ++q) {
+          const int e_local = misc->ids[misc->local_rank[q]] - p.expert_lo;
+          const __nv_bfloat16* src = L.expert_down +
+              (static_cast<size_t>(e_local) * kHidden + h0) * kInter;
+          bulk_g2s(smem_u32(down_region + q * kDecodeMaxRowsPerBlock * kDownRowBytes),
+                   src, rank_bytes, down_bar);
+        }
         if (!alive) break;
-        if (p1 - p0 <= burst) issue_down();
       }
       // Drain: every copy this thread issued must have landed before the block
       // may exit (bounded; a phase that already completed returns at once).
