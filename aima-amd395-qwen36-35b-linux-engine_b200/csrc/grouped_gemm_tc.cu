@@ -209,6 +209,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Programmatic dependent launch: the kernel is launched with stream serialisation relaxed, so its
+  // blocks may become resident -- and run the set-up above (barriers, TMEM) -- while the kernel
+  // before it in the stream is still draining.  Nothing above reads or writes global memory;
+  // everything below does, so this is where the kernel waits for its predecessor to complete and
+  // for that kernel's writes to be visible.  The kernel after this one may be scheduled likewise.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
   const int n_tiles_all = g.tile_count != nullptr ? *g.tile_count : g.max_tiles;
   const int parts = g.parts > 1 ? g.parts : 1;
   const int tile_lo = static_cast<int>(static_cast<long long>(n_tiles_all) * g.part / parts);
@@ -483,8 +491,17 @@ cudaError_t launch_mode(const TcMaps& maps, const TcProblem& pb, int grid, cudaS
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  grouped_gemm_tc_kernel<MODE, kGather><<<grid, kTcThreads, kTcSmemBytes, stream>>>(maps, pb);
-  return cudaGetLastError();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(kTcThreads);
+  config.dynamicSmemBytes = kTcSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;   // see griddepcontrol.wait in the kernel
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, grouped_gemm_tc_kernel<MODE, kGather>, maps, pb);
 }
 
 }  // namespace

@@ -24,6 +24,7 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x,
                     const __nv_bfloat16* __restrict__ weight,
                     __nv_bfloat16* __restrict__ residual_out,
                     __nv_bfloat16* __restrict__ norm_out, int rows, float eps) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a product kernel that follows may set itself up
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * kNormWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;

@@ -486,6 +486,9 @@ plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert
                     int32_t* __restrict__ padded_rows,
                     int32_t* __restrict__ sorted_rows, int32_t* __restrict__ row_position) {
   static_assert(kPlanWarps * 32 == kExperts, "one thread per expert in the prologue");
+  // the product kernel that follows may place its blocks and set itself up while this one runs; it
+  // waits for this kernel's completion before it touches global memory (griddepcontrol.wait there)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ int next[kPlanWarps][kExperts];
   __shared__ int offsets[kExperts + 1];
   __shared__ int tile_base[kExperts + 1];
@@ -579,6 +582,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
                const __nv_bfloat16* __restrict__ next_norm_weight,
                __nv_bfloat16* __restrict__ next_norm_out, float eps) {
   __shared__ float group_sums[8];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // next layer's router product may set itself up
   const int token = blockIdx.x;
   const int t = threadIdx.x;
   float slot[kTopK][8];
