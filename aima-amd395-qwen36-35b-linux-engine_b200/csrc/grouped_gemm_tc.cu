@@ -214,8 +214,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
   // before it in the stream is still draining.  Nothing above reads or writes global memory;
   // everything below does, so this is where the kernel waits for its predecessor to complete and
   // for that kernel's writes to be visible.  The kernel after this one may be scheduled likewise.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  pdl_enter();
 
   const int n_tiles_all = g.tile_count != nullptr ? *g.tile_count : g.max_tiles;
   const int parts = g.parts > 1 ? g.parts : 1;
@@ -491,17 +490,7 @@ cudaError_t launch_mode(const TcMaps& maps, const TcProblem& pb, int grid, cudaS
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(grid);
-  config.blockDim = dim3(kTcThreads);
-  config.dynamicSmemBytes = kTcSmemBytes;
-  config.stream = stream;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;   // see griddepcontrol.wait in the kernel
-  config.attrs = attribute;
-  config.numAttrs = 1;
-  return cudaLaunchKernelEx(&config, grouped_gemm_tc_kernel<MODE, kGather>, maps, pb);
+  return launch_pdl(grouped_gemm_tc_kernel<MODE, kGather>, dim3(grid), dim3(kTcThreads), kTcSmemBytes, stream, maps, pb);
 }
 
 }  // namespace

@@ -273,6 +273,7 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int token = blockIdx.x * kCertWarps + warp;
+  pdl_enter();
   if (token >= tokens) return;
 
   uint4 xp[8];
@@ -400,6 +401,7 @@ plan_count_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert_l
   const int lane = threadIdx.x & 31;
   for (int e = lane; e < kExperts; e += 32) cnt[warp][e] = 0;
   __syncwarp();
+  pdl_enter();
   const int unit = blockIdx.x * kPlanWarps + warp;
   const int row0 = unit * kPlanRowsPerWarp;
   if (row0 >= routed_rows) return;
@@ -424,6 +426,7 @@ plan_count_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert_l
 // expert's total.  Grid = 256 / kPlanWarps blocks.
 __global__ void __launch_bounds__(kPlanWarps * 32)
 plan_scan_kernel(int32_t* __restrict__ unit_counts, int units, int32_t* __restrict__ expert_counts) {
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int e = blockIdx.x * kPlanWarps + (threadIdx.x >> 5);
   int running = 0;
@@ -486,9 +489,7 @@ plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert
                     int32_t* __restrict__ padded_rows,
                     int32_t* __restrict__ sorted_rows, int32_t* __restrict__ row_position) {
   static_assert(kPlanWarps * 32 == kExperts, "one thread per expert in the prologue");
-  // the product kernel that follows may place its blocks and set itself up while this one runs; it
-  // waits for this kernel's completion before it touches global memory (griddepcontrol.wait there)
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  pdl_enter();
   __shared__ int next[kPlanWarps][kExperts];
   __shared__ int offsets[kExperts + 1];
   __shared__ int tile_base[kExperts + 1];
@@ -543,13 +544,18 @@ cudaError_t launch_plan(PrefillWorkspace* ws, const int32_t* ids, int rows, int 
                         cudaStream_t stream, int* launches) {
   const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
   const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
-  plan_count_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(ids, rows, expert_lo, expert_hi, ws->unit_counts);
-  plan_scan_kernel<<<kExperts / kPlanWarps, kPlanWarps * 32, 0, stream>>>(ws->unit_counts, units, ws->expert_counts);
-  plan_scatter_kernel<<<plan_blocks, kPlanWarps * 32, 0, stream>>>(
-      ids, rows, expert_lo, expert_hi, ws->unit_counts, ws->expert_counts, ws->expert_offsets, ws->tile_expert,
-      ws->tile_row0, ws->tile_rows, ws->tile_count, ws->padded_rows, ws->sorted_rows, ws->row_position);
+  cudaError_t code = launch_pdl(plan_count_kernel, dim3(plan_blocks), dim3(kPlanWarps * 32), 0, stream, ids, rows,
+                                expert_lo, expert_hi, ws->unit_counts);
+  if (code == cudaSuccess)
+    code = launch_pdl(plan_scan_kernel, dim3(kExperts / kPlanWarps), dim3(kPlanWarps * 32), 0, stream,
+                      ws->unit_counts, units, ws->expert_counts);
+  if (code == cudaSuccess)
+    code = launch_pdl(plan_scatter_kernel, dim3(plan_blocks), dim3(kPlanWarps * 32), 0, stream, ids, rows,
+                      expert_lo, expert_hi, ws->unit_counts, ws->expert_counts, ws->expert_offsets,
+                      ws->tile_expert, ws->tile_row0, ws->tile_rows, ws->tile_count, ws->padded_rows,
+                      ws->sorted_rows, ws->row_position);
   *launches += 3;
-  return cudaGetLastError();
+  return code;
 }
 
 // ---------------------------------------------------------------------------
@@ -914,6 +920,7 @@ void prefill_workspace_free(PrefillWorkspace* ws) {
 int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStream_t stream,
                          int* launches, char* error, size_t error_bytes) {
   const int T = call.tokens;
+  const PdlScope pdl_scope(T <= pdl_max_tokens());
   const int rows = T * kTopK;
   const aima_moe_debug_views* dbg = call.debug;
   int count = 0;
@@ -968,12 +975,12 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
     rx.status = ws->status; rx.sm_count = ws->sm_count; rx.a_rows = static_cast<uint64_t>(T); rx.experts_in_b = 1;
     if ((code = launch_grouped_gemm_tc(kGemmPlainF32, r, rx, stream)) != cudaSuccess)
       return set_error(error, error_bytes, code, "router logits product");
-    prefill_router_certified_kernel<<<(T + kCertWarps - 1) / kCertWarps, kCertWarps * 32, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(call.h2), call.layer.router, call.layer.shared_gate,
-        ws->approx_logits, call.router_row_norms, call.router_bias, call.quant_eighths, T, ws->topk_ids,
-        ws->topk_scores, ws->topk_weights, ws->shared_sigmoid,
-        dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats);
-    if ((code = cudaGetLastError()) != cudaSuccess)
+    code = launch_pdl(prefill_router_certified_kernel, dim3((T + kCertWarps - 1) / kCertWarps), dim3(kCertWarps * 32),
+                      0, stream, static_cast<const __nv_bfloat16*>(call.h2), call.layer.router,
+                      call.layer.shared_gate, ws->approx_logits, call.router_row_norms, call.router_bias,
+                      call.quant_eighths, T, ws->topk_ids, ws->topk_scores, ws->topk_weights, ws->shared_sigmoid,
+                      dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats);
+    if (code != cudaSuccess)
       return set_error(error, error_bytes, code, "prefill_router_certified_kernel");
     count += 2;
   }
@@ -1094,6 +1101,7 @@ size_t ep_prefill_region_bytes(int capacity_tokens, int world, EpPrefillLayout* 
 int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPrefill* ep,
                             cudaStream_t stream, int* launches, char* error, size_t error_bytes) {
   const int T_loc = call.tokens;
+  const PdlScope pdl_scope(false);   // plain stream order: kernels of this path wait for peers, nothing may sit resident ahead of them
   const int W = ep->world;
   const int T = T_loc * W;
   const int rows_loc = T_loc * kTopK;

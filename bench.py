@@ -625,9 +625,12 @@ def run_prefill(args) -> None:
     package = load_package()
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
+    sampler = ClockSampler(device.index or 0)      # covers warm-up and the timed passes of this workload
+    sampler.start()
     if args.stack_layers > 1:
         numbers = prefill_stack_numbers(package, device, args.tokens, args.stack_layers, max(args.steps, 1),
                                         args.routing)
+        clocks = sampler.stop()
         tensor_bound = args.tokens >= 8192
         print(json.dumps({
             "metric": "moe_prefill_tokens_per_second", "value": numbers["tokens_per_s"], "unit": "tokens/s",
@@ -643,9 +646,10 @@ def run_prefill(args) -> None:
                          "traffic": None, "peak_source": numbers["peak_source"]},
             "ms_per_layer": numbers["ms_per_layer"], "tensor_frac": numbers["tensor_frac"],
             "hbm_frac": numbers["hbm_frac"],
-            "gpu_launches": numbers["kernel_launches_per_pass"] * args.steps}))
+            "gpu_launches": numbers["kernel_launches_per_pass"] * args.steps, "clocks": clocks}))
         return
     numbers = prefill_layer_numbers(package, device, args.tokens, max(args.steps, 1), args.routing)
+    clocks = sampler.stop()
     line = {"metric": "moe_prefill_tokens_per_second", "value": numbers["tokens_per_s"], "unit": "tokens/s",
             "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": numbers["ms_per_layer"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -653,7 +657,7 @@ def run_prefill(args) -> None:
             "roofline": {"bound": "tensor", "achieved": numbers["achieved_tflops"], "peak": numbers["peak_tflops"],
                          "unit": "TFLOP/s", "frac": numbers["frac"], "traffic": None,
                          "peak_source": numbers["peak_source"]},
-            "gpu_launches": numbers["kernel_launches_per_layer"] * args.steps}
+            "gpu_launches": numbers["kernel_launches_per_layer"] * args.steps, "clocks": clocks}
     print(json.dumps(line))
 
 
