@@ -93,6 +93,8 @@ constexpr int kScanWarps = 4;
 __global__ void __launch_bounds__(kScanWarps * 32)
 lm_head_scan_kernel(const int8_t* __restrict__ q_weight, const float* __restrict__ scales,
                     const __nv_bfloat16* __restrict__ hidden, float* __restrict__ logits, int rows) {
+  // the three short kernels after this one are placed while its last blocks drain (see pdl_enter)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int warp_global = blockIdx.x * kScanWarps + (threadIdx.x >> 5);
   const int warps_total = gridDim.x * kScanWarps;
@@ -180,6 +182,7 @@ lm_head_bound_kernel(const float* __restrict__ logits, const float* __restrict__
                      float* __restrict__ partial, int rows) {
   __shared__ double norm_reduction[kLmThreads];
   __shared__ float reduction[kLmThreads];
+  pdl_enter();
   const float hidden_l2 = hidden_norm_in_block(hidden, norm_reduction);
   float local_max = -CUDART_INF_F;
   for (int row = blockIdx.x * kLmThreads + threadIdx.x; row < rows; row += gridDim.x * kLmThreads) {
@@ -210,6 +213,7 @@ lm_head_collect_kernel(const float* __restrict__ logits, const float* __restrict
                        uint32_t* __restrict__ candidate_ids, int rows) {
   static_assert(kLmThreads == kLmBoundBlocks, "one thread per partial maximum");
   __shared__ float reduction[kLmBoundBlocks];
+  pdl_enter();
   reduction[threadIdx.x] = partial[threadIdx.x];
   __syncthreads();
   for (int stride = kLmBoundBlocks / 2; stride != 0; stride >>= 1) {
@@ -243,6 +247,7 @@ lm_head_exact_kernel(const __nv_bfloat16* __restrict__ weight, const __nv_bfloat
   __shared__ uint32_t indices[kExactWarps];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  pdl_enter();
   const uint32_t count = min(wire->candidate_count, static_cast<uint32_t>(AIMA_MOE_LM_HEAD_CANDIDATES));
   const uint4* xrow = reinterpret_cast<const uint4*>(hidden) + lane;
   float local_value = -CUDART_INF_F;
@@ -293,13 +298,20 @@ cudaError_t lm_head_certify(const LmHeadBuffers& b, const void* weight, const vo
                             int rows, int sm_count, cudaStream_t stream, int* launches) {
   const __nv_bfloat16* h = static_cast<const __nv_bfloat16*>(hidden);
   lm_head_scan_kernel<<<sm_count * 16, kScanWarps * 32, 0, stream>>>(b.q_weight, b.scales, h, logits, rows);
-  lm_head_bound_kernel<<<kLmBoundBlocks, kLmThreads, 0, stream>>>(logits, b.residual_l2, h, b.wire, b.partial, rows);
-  lm_head_collect_kernel<<<(rows + kLmThreads - 1) / kLmThreads, kLmThreads, 0, stream>>>(
-      logits, b.residual_l2, b.partial, b.wire, b.candidate_ids, rows);
-  lm_head_exact_kernel<<<1, kExactWarps * 32, 0, stream>>>(static_cast<const __nv_bfloat16*>(weight), h, b.wire,
-                                                           b.candidate_ids, logits);
+  cudaError_t code = cudaGetLastError();
+  const PdlScope pdl_scope(true);
+  if (code == cudaSuccess)
+    code = launch_pdl(lm_head_bound_kernel, dim3(kLmBoundBlocks), dim3(kLmThreads), 0, stream,
+                      static_cast<const float*>(logits), static_cast<const float*>(b.residual_l2), h, b.wire, b.partial, rows);
+  if (code == cudaSuccess)
+    code = launch_pdl(lm_head_collect_kernel, dim3((rows + kLmThreads - 1) / kLmThreads), dim3(kLmThreads), 0, stream,
+                      static_cast<const float*>(logits), static_cast<const float*>(b.residual_l2),
+                      static_cast<const float*>(b.partial), b.wire, b.candidate_ids, rows);
+  if (code == cudaSuccess)
+    code = launch_pdl(lm_head_exact_kernel, dim3(1), dim3(kExactWarps * 32), 0, stream,
+                      static_cast<const __nv_bfloat16*>(weight), h, b.wire, b.candidate_ids, logits);
   *launches = 4;
-  return cudaGetLastError();
+  return code;
 }
 
 }  // namespace aima
