@@ -109,6 +109,62 @@ __device__ __forceinline__ float butterfly_sum(float v) {
   return v;
 }
 
+// Eight canonical warp reductions at once.  v[d] is this lane's partial of sum d;
+// the result is the butterfly (16, 8, 4, 2, 1) total of sum d(lane), with
+// d(lane) = 4 * bit4 + 2 * bit3 + bit2 of the lane index.  Each level pairs the
+// same lanes as butterfly_sum, so the bits are identical, with 9 shuffles
+// instead of 40.
+__device__ __forceinline__ float warp_reduce8(const float* v, int lane) {
+  const bool b4 = (lane & 16) != 0, b3 = (lane & 8) != 0, b2 = (lane & 4) != 0;
+  float a[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float keep = b4 ? v[j + 4] : v[j];
+    const float send = b4 ? v[j] : v[j + 4];
+    a[j] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+  }
+  float b[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float keep = b3 ? a[j + 2] : a[j];
+    const float send = b3 ? a[j] : a[j + 2];
+    b[j] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+  }
+  const float keep = b2 ? b[1] : b[0];
+  const float send = b2 ? b[0] : b[1];
+  float c = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+  c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, 2));
+  c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, 1));
+  return c;
+}
+__device__ __forceinline__ int reduce8_slot(int lane) {
+  return ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+}
+
+
+// Sum of squares of a 2048-wide row in the order of the reference's RMSNorm kernels
+// (native/src/native_pointwise.hip.cpp:109-142): partial t of 256 adds the squares of elements t,
+// t + 256, ..., t + 1792 in that order; the partials fold by halving, partial[t] += partial[t + width],
+// width = 128 .. 1.  With element 256 g + 8 l + j of the row in v[8 g + j] of lane l, a lane holds the
+// eight elements of partials 8 l .. 8 l + 7: the halvings of width 128 .. 8 are the lane butterfly of
+// each partial j, the last three are ((q0 + q4) + (q2 + q6)) + ((q1 + q5) + (q3 + q7)) -- the 16, 8, 4
+// exchanges after warp_reduce8.  Every lane returns the total.
+__device__ __forceinline__ float row_sumsq_2048(const float* v, int lane) {
+  float part[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) acc = __fmaf_rn(v[8 * g + j], v[8 * g + j], acc);
+    part[j] = acc;
+  }
+  float q = warp_reduce8(part, lane);       // q_j on the lanes with reduce8_slot(lane) == j
+  q = __fadd_rn(q, __shfl_xor_sync(0xffffffffu, q, 16));   // j ^ 4
+  q = __fadd_rn(q, __shfl_xor_sync(0xffffffffu, q, 8));    // j ^ 2
+  q = __fadd_rn(q, __shfl_xor_sync(0xffffffffu, q, 4));    // j ^ 1
+  return q;
+}
+
 // acc += x[0..7] * w[0..7]; w is one 16-byte vector of 8 BF16 values.
 __device__ __forceinline__ float fma8(const float* x, const uint4& w, float acc) {
   acc = __fmaf_rn(x[0], bf16_lo(w.x), acc);

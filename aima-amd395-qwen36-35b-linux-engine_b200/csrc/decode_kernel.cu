@@ -8,33 +8,46 @@
 // benchmarks/shape-lab/four_layer_mini_engine.py:304-326, 391-473, 844-859,
 // 1152-1220 and native/src/native_pointwise.hip.cpp:94-107, 184-205.
 //
-// Structure.  One block per SM.  Warp 15 is a producer that streams weight rows
-// from HBM into shared memory with 1-D bulk (TMA) copies; warps 0-14 consume
-// them with the canonical warp dot product.  The kernel is bandwidth bound
-// (57.7 MB of weights per layer for ~30 MFLOP), so everything is arranged to
-// keep bulk copies in flight across the three grid-wide synchronisations a
-// layer needs:
+// Structure.  One block per SM, 16 warps.  Warp 15 is a producer that streams
+// weight rows from HBM into ONE ring of 24 shared-memory slots of 8 KB with 1-D
+// bulk (TMA) copies; warps 1-12 consume them with the canonical warp dot
+// product (slot s always belongs to warp 1 + s % 12); warp 0 runs the exchanges
+// between blocks, the top-8 and the layer plan; warp 13 predicts the next
+// layer's experts.  The kernel is bandwidth bound (57.7 MB of weights per layer
+// for ~30 MFLOP) but its layer is a serial chain of three grid-wide hand-overs,
+// so everything is arranged to keep bulk copies in flight across them.  Items
+// of a layer pass through the ring in this order:
 //
-//   R   every block: norm of the 2048-vector (per warp, registers), its share
-//       of the 256 router rows and of the 513 shared-expert input pairs
+//   R   router rows c, c+G of this layer; the same two rows of the NEXT layer's
+//       router (prediction, see below); the block's share of the 512
+//       shared-expert input pairs; the shared gate row
+//   B   "blind" pairs: gate/up row pairs of the experts PREDICTED for this layer,
+//       requested while the chain of the previous layer is still running
 //   --- logits exchange: every logit travels as one 64-bit word {tag, value};
-//       warp 0 of every block polls the 256 words, then takes the top-8
-//   1   routed gate/up rows of the 8 chosen experts (8 KB "pair" items through
-//       a 10-slot ring); meanwhile the block's slice of the down projection
-//       (8 experts + shared, <= 126 KB) is already being copied into a second
-//       shared-memory region
+//       warp 0 of every block polls the 256 words, takes the top-8, freezes the
+//       blind issue and publishes the layer plan (which predicted positions hold
+//       a chosen expert, which chosen experts still have to be fetched)
+//   P   the pairs not covered by a valid blind item, with the real experts
+//   D   the block's slice of the down projection: shared expert and every chosen
+//       expert, two items of <= 7 rows each
 //   --- grid barrier: all SwiGLU activations known
-//   2   down products for the block's <= 14 output elements, weighted sum,
-//       shared expert, residual add, store
+//       down products for the block's <= 14 output elements from the D items,
+//       weighted sum, shared expert, residual add
 //   --- output exchange: the 2048 outputs travel as 32-bit words {tag, bf16};
 //       four warps of every block poll them into shared memory
-// Data that carries its own tag needs no separate barrier and no second round
-// trip through L2; only the activation hand-over is a counter barrier, and it
-// hides behind the arrival of the down-projection rows.
 //
-// Every wait (mbarrier, grid barrier, hand-over of the expert ids to the
-// producer) is bounded; on expiry the block raises a status word, drains its
-// outstanding copies and returns, so the context stays usable.
+// Prediction.  HBM would idle from the moment a layer's down rows have landed
+// until the next layer's top-8 is known (output exchange, norm, router rows,
+// logits exchange, top-8: about 40 % of a layer).  Applying the next layer's
+// router to THIS layer's normalised input costs one more ring item per block
+// and predicts most of the next layer's experts; their rows are requested into
+// the ring during that idle time.  A position whose prediction was wrong is
+// dropped unread and fetched again with the right expert, so the result does not
+// depend on the prediction: outputs are bit-identical with and without it.
+//
+// Every wait (mbarrier, grid barrier, hand-overs between the warps of a block)
+// is bounded; on expiry the block raises a status word, drains its outstanding
+// copies and returns, so the context stays usable.
 #include "decode_kernel.cuh"
 
 #include <math_constants.h>
@@ -42,45 +55,64 @@
 namespace aima {
 namespace {
 
-// Ring of weight "pair" slots.  Item i always lands in slot i % kRingSlots and is
-// always consumed by warp i % kRingSlots: a parity wait on an mbarrier is only
+// Item i always lands in slot i % kRingSlots and is always consumed by warp
+// 1 + (i % kRingSlots) % kStreamWarps: a parity wait on an mbarrier is only
 // meaningful when the waiter is at most one phase behind, so consecutive uses
-// of a slot must be consumed in order by one warp.  Warps kRingSlots..14 only
-// take part in the top-8 and down-projection phases.
-constexpr int kRingSlots = 10;
-constexpr int kSlotBytes = 8192;               // two 4 KB weight rows
+// of a slot must be consumed in order by one warp.
+constexpr int kRingSlots = 24;
+constexpr int kStreamWarps = 12;
+constexpr int kFirstStreamWarp = 1;
+constexpr int kPredictWarp = 13;
+constexpr int kProducerWarp = 15;
+constexpr int kSlotBytes = 8192;               // two 4 KB weight rows, or <= 7 down rows of 1 KB
 constexpr int kRowBytes = kHidden * 2;         // 4096
 constexpr int kDownRowBytes = kInter * 2;      // 1024
-constexpr int kDownRegionRanks = kTopK + 1;    // 8 routed + shared
 constexpr int kDotsStride = 12;
+constexpr int kPositions = kTopK;              // ring positions a layer's experts are dealt to
+constexpr int kListEntries = 4 * kPositions;   // per block: at most 4 pairs of each position
+constexpr unsigned kFrozen = 0x10000u;
 
 // shared-memory map (bytes)
 constexpr int kOffRing = 0;
-constexpr int kOffDown = kOffRing + kRingSlots * kSlotBytes;                       // 81920
-constexpr int kOffAct = kOffDown + kDownRegionRanks * kDecodeMaxRowsPerBlock * kDownRowBytes;  // +129024
-constexpr int kActBytes = kDownRegionRanks * kInter * 2 + 16;                      // 9 x 512 BF16 + gate logit
+constexpr int kOffAct = kOffRing + kRingSlots * kSlotBytes;                        // 196608
+constexpr int kActBytes = (kTopK + 1) * kInter * 2 + 16;                           // 9 x 512 BF16 + gate logit
 constexpr int kOffDots = kOffAct + kActBytes;                                      // +9232
 constexpr int kOffX = kOffDots + kDecodeMaxRowsPerBlock * kDotsStride * 4;         // +672: layer input, packed BF16
 constexpr int kOffNorm = kOffX + kHidden * 2;                                      // +4096: norm weight row
 constexpr int kOffMisc = kOffNorm + kHidden * 2;                                   // +4096
-constexpr int kMiscBytes = 512;
+constexpr int kMiscBytes = 1024;
 constexpr int kOffBars = kOffMisc + kMiscBytes;
-constexpr int kBarCount = 2 * kRingSlots + 2;
+constexpr int kBarCount = 2 * kRingSlots + 1;
 constexpr int kSmemTotal = kOffBars + kBarCount * 8;
 static_assert(kSmemTotal <= 227 * 1024, "decode kernel shared memory exceeds 227 KB");
 static_assert(kSmemTotal == kDecodeSmemBytes, "keep decode_kernel.cuh in step");
+static_assert((kDecodeMaxRowsPerBlock + 1) / 2 * kDownRowBytes <= kSlotBytes, "a down item must fit a slot");
+static_assert(kFirstStreamWarp + kStreamWarps <= kDecodeConsumerWarps, "stream warps are consumer warps");
+static_assert(kRingSlots % kStreamWarps == 0, "every stream warp owns the same number of slots");
 
 struct Misc {
-  int ids[kTopK];          // selected experts in selection order
-  float weights[kTopK];    // BF16-rounded routing weights as FP32
-  int local_rank[kTopK];   // ranks r whose expert lives on this GPU, ascending
+  int ids[kTopK];                 // selected experts in selection order (rank r)
+  float weights[kTopK];           // BF16-rounded routing weights as FP32
+  int local_rank[kTopK];          // ranks whose expert lives on this GPU, ascending
   int n_local;
-  volatile int ids_layer;  // (layer ordinal + 1) the ids above belong to
-  volatile int abort_flag; // block-local copy of a raised status
-  volatile int decision;   // block-uniform "keep going" verdict (see uniform_alive)
+  // ---- layer plan: which expert each ring position carries ----
+  int expert_of_pos[kPositions];  // chosen expert dealt to position q, -1: position unused
+  int rank_of_pos[kPositions];    // its selection rank
+  int pred_of_pos[kPositions];    // expert the blind items of position q were requested with, -1: none
+  int active_pos[kPositions];     // used positions, ascending
+  int n_active;
+  unsigned active_mask;           // bit q: position q carries a chosen expert
+  unsigned valid_mask;            // bit q: the blind items of position q hold that expert's rows
+  int n_blind;                    // list entries [0, n_blind) were handled blind
+  volatile int plan_layer;        // (layer ordinal + 1) the plan above belongs to
+  // ---- prediction ----
+  int pred[2][kPositions];        // predicted experts of layer ordinal li at [li & 1], -1: not held here
+  volatile int pred_layer;        // predictions are published for all layer ordinals < pred_layer
+  unsigned blind_state[2];        // [li & 1]: list entries claimed blind so far | kFrozen
+  volatile int abort_flag;        // block-local copy of a raised status
+  volatile int decision;          // block-uniform "keep going" verdict (see uniform_alive)
 };
 static_assert(sizeof(Misc) <= kMiscBytes, "Misc too large");
-static_assert(kRingSlots <= kDecodeConsumerWarps, "each ring slot needs its own consumer warp");
 
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" :: "n"(kDecodeConsumerThreads) : "memory");
@@ -95,7 +127,9 @@ __device__ __forceinline__ void raise_status(const DecodeParams& p,
 // Records where the first bounded wait gave up: status[1] = site, [2] = block,
 // [3] = warp, [4] = item / layer detail.  Sites: 1 producer slot acquire,
 // 2 consumer item (router / shared rows), 3 consumer item (routed rows),
-// 4 down-projection region, 5 grid barrier, 6 expert-id hand-over.
+// 4 consumer item (down rows), 5 grid barrier, 6 plan hand-over to the producer,
+// 7 output exchange, 8 norm row, 9 logits exchange, 10 prediction hand-over,
+// 11 expert-parallel peer word, 12 predicted-logits exchange.
 __device__ __forceinline__ void record_site(const DecodeParams& p, int site, int detail,
                                             const unsigned* diag = nullptr) {
   if (atomicCAS(p.status + 1, 0, site) == 0) {
@@ -151,41 +185,6 @@ __device__ __forceinline__ bool uniform_alive(volatile int* abort_flag,
   return *decision != 0;
 }
 
-// Eight canonical warp reductions at once.  v[d] is this lane's partial of sum d;
-// the result is the butterfly (16, 8, 4, 2, 1) total of sum d(lane), with
-// d(lane) = 4 * bit4 + 2 * bit3 + bit2 of the lane index.  Each level pairs the
-// same lanes as butterfly_sum, so the bits are identical, with 9 shuffles
-// instead of 40.
-__device__ __forceinline__ float warp_reduce8(const float* v, int lane) {
-  const bool b4 = (lane & 16) != 0, b3 = (lane & 8) != 0, b2 = (lane & 4) != 0;
-  float a[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float keep = b4 ? v[j + 4] : v[j];
-    const float send = b4 ? v[j] : v[j + 4];
-    a[j] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 16));
-  }
-  float b[2];
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const float keep = b3 ? a[j + 2] : a[j];
-    const float send = b3 ? a[j] : a[j + 2];
-    b[j] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 8));
-  }
-  const float keep = b2 ? b[1] : b[0];
-  const float send = b2 ? b[0] : b[1];
-  float c = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, 4));
-  c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, 2));
-  c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, 1));
-  return c;
-}
-__device__ __forceinline__ int reduce8_slot(int lane) {
-  return ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-}
-__device__ __forceinline__ int reduce8_lane(int d) {
-  return ((d >> 2) & 1) * 16 + ((d >> 1) & 1) * 8 + (d & 1) * 4;
-}
-
 __device__ __forceinline__ uint32_t order_key(float f) {
   const uint32_t u = __float_as_uint(f);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
@@ -229,13 +228,49 @@ __device__ __forceinline__ int shared_pairs_of(int c, int G) {
   return c < kSharedInter ? (kSharedInter - 1 - c) / G + 1 : 0;
 }
 
+// The pairs of one expert position are dealt round-robin over the blocks, starting at a block that
+// depends on the position, so that every block holds 3 or 4 pairs of EVERY position (27 or 28 in all
+// at 148 blocks) whatever experts the positions carry.  List entry k = 8 j + q is the j-th pair of
+// position q in this block; returns its row index inside the expert, >= kInter when it does not exist.
+__device__ __forceinline__ int list_entry_row(int k, int c, int G) {
+  const int q = k & (kPositions - 1);
+  const int j = k >> 3;
+  int first = c + (q * G) / kPositions;
+  if (first >= G) first -= G;
+  return first + j * G;
+}
+
+// Iterative arg-max over 256 keys (8 per lane: key q of lane l belongs to expert 32 q + l), ties to
+// the lowest expert id; lane r < 8 ends up with the r-th selection.  Consumes k.
+__device__ __forceinline__ void warp_top8(uint32_t (&k)[8], int lane, float& my_score, int& my_id) {
+  my_score = 0.0f;
+  my_id = 0;
+#pragma unroll 1
+  for (int r = 0; r < kTopK; ++r) {
+    uint32_t local = k[0];
+#pragma unroll
+    for (int q = 1; q < 8; ++q) local = max(local, k[q]);
+    const uint32_t best = __reduce_max_sync(0xffffffffu, local);
+    int candidate = 0x7fffffff;
+#pragma unroll
+    for (int q = 7; q >= 0; --q) {
+      if (k[q] == best) candidate = 32 * q + lane;
+    }
+    const int winner = __reduce_min_sync(0xffffffffu, candidate);
+    if (lane == r) { my_score = key_value(best); my_id = winner; }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      if (winner == 32 * q + lane) k[q] = 0u;
+    }
+  }
+}
+
 }  // namespace
 
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 moe_decode_persistent_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem + kOffRing;
-  uint8_t* down_region = smem + kOffDown;
   uint16_t* act_s = reinterpret_cast<uint16_t*>(smem + kOffAct);
   float* dots = reinterpret_cast<float*>(smem + kOffDots);
   uint8_t* x_s = smem + kOffX;
@@ -244,8 +279,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
   const uint32_t bars = smem_u32(smem + kOffBars);
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (kRingSlots + s); };
-  const uint32_t down_bar = bars + 8u * (2 * kRingSlots);
-  const uint32_t norm_bar = bars + 8u * (2 * kRingSlots + 1);
+  const uint32_t norm_bar = bars + 8u * (2 * kRingSlots);
 
   const int G = gridDim.x;
   const int c = blockIdx.x;
@@ -259,14 +293,17 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(down_bar, 1);
     mbar_init(norm_bar, 1);
     // every ring slot starts out released: complete phase 0 of its empty barrier
     for (int s = 0; s < kRingSlots; ++s) mbar_arrive(empty_bar(s));
-    misc->ids_layer = 0;
+    misc->plan_layer = 0;
+    misc->pred_layer = 1;          // layer ordinal 0 has no prediction: nothing to wait for
+    misc->blind_state[0] = 0u;
+    misc->blind_state[1] = 0u;
     misc->abort_flag = 0;
     misc->decision = 1;
     misc->n_local = 0;
+    misc->n_active = 0;
     mbar_fence_init();
   }
   __syncthreads();
@@ -274,136 +311,150 @@ moe_decode_persistent_kernel(const DecodeParams p) {
   const int h0 = (c * kHidden) / G;
   const int h1 = ((c + 1) * kHidden) / G;
   const int nh = h1 - h0;
+  const int half_rows = (nh + 1) / 2;
   const int eb = c + G;                       // second router row of this block
   const int n_shared_pairs = shared_pairs_of(c, G);
   const bool owns_gate_row = (c == G - 1);
+  const bool speculate = p.speculate != 0;
   const unsigned long long bar_base = *p.bar_base;
   const unsigned epoch0 = *p.epoch_base;      // exchange tag of layer ordinal li is epoch0 + li + 1
+  unsigned long long* const pred_logits = p.logits + kDecodeReplicas * kExperts;
 
-  if (warp == kDecodeConsumerWarps) {
+  if (warp == kProducerWarp) {
     // ------------------------------ producer ------------------------------
-    unsigned seq = 0;
-    unsigned issued[kRingSlots];
-#pragma unroll
-    for (int s = 0; s < kRingSlots; ++s) issued[s] = 0;
-    unsigned down_issued = 0;
-    unsigned norm_issued = 0;
-    bool alive = true;
-
-    // acquire a ring slot for item `seq`; returns slot index or -1
-    auto acquire = [&](unsigned item) -> int {
-      const int s = item % kRingSlots;
-      const unsigned use = item / kRingSlots;
-      unsigned diag[4] = {0, 0, 0, 0};
-      if (!mbar_wait_bounded(empty_bar(s), use & 1u, abort_flag, diag)) {
-        if (*abort_flag == kStatusTimeoutMbarrier) {
-          atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
-          record_site(p, 1, static_cast<int>(item), diag);
-        }
-        return -1;
-      }
-      return s;
-    };
-
     if (lane == 0) {
+      unsigned seq = 0;
+      unsigned issued[kRingSlots];
+      for (int s = 0; s < kRingSlots; ++s) issued[s] = 0;
+      unsigned norm_issued = 0;
+      bool alive = true;
+
+      // acquire the ring slot of item `seq`; returns its address or 0
+      auto acquire = [&]() -> uint32_t {
+        const int s = seq % kRingSlots;
+        const unsigned use = seq / kRingSlots;
+        unsigned diag[4] = {0, 0, 0, 0};
+        if (!mbar_wait_bounded(empty_bar(s), use & 1u, abort_flag, diag)) {
+          if (*abort_flag == kStatusTimeoutMbarrier) {
+            atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+            record_site(p, 1, static_cast<int>(seq), diag);
+          }
+          alive = false;
+          return 0u;
+        }
+        return smem_u32(ring + s * kSlotBytes);
+      };
+      // one or two pieces into the slot of item `seq`
+      auto issue = [&](const void* src0, uint32_t bytes0, const void* src1, uint32_t bytes1) -> bool {
+        const uint32_t dst = acquire();
+        if (dst == 0u) return false;
+        const int s = seq % kRingSlots;
+        mbar_arrive_expect_tx(full_bar(s), bytes0 + bytes1);
+        bulk_g2s(dst, src0, bytes0, full_bar(s));
+        if (bytes1 != 0u) bulk_g2s(dst + bytes0, src1, bytes1, full_bar(s));
+        issued[s] = seq / kRingSlots + 1;
+        ++seq;
+        return true;
+      };
+      // bounded wait for a hand-over word in shared memory to reach `want`
+      auto wait_word = [&](volatile int* word, int want, int code, int site, int detail) -> bool {
+        if (*word >= want) return true;
+        const unsigned long long start = global_timer_ns();
+        unsigned spins = 0;
+        while (*word < want) {
+          if ((++spins & 255u) == 0u) {
+            if (*abort_flag != 0) { alive = false; return false; }
+            if (global_timer_ns() - start > kWaitBudgetNs) {
+              raise_status(p, abort_flag, code);
+              record_site(p, site, detail);
+              alive = false;
+              return false;
+            }
+          }
+        }
+        return true;
+      };
+
       for (int li = 0; li < p.n_layers && alive; ++li) {
         const LayerPtrs L = p.layers[p.first_layer + li];
-        // ---- norm weight row into its own region (its readers finished before the ids of the
-        //      previous layer were published, which this thread has waited for) ----
+        const bool has_next = speculate && (li + 1 < p.n_layers);
+        auto issue_pair = [&](int expert, int row) -> bool {
+          const __nv_bfloat16* gate_row = L.expert_gate_up +
+              (static_cast<size_t>(expert - p.expert_lo) * (2 * kInter) + row) * kHidden;
+          return issue(gate_row, kRowBytes, gate_row + static_cast<size_t>(kInter) * kHidden, kRowBytes);
+        };
+        // ---- norm weight row into its own region (its readers finished before the plan of the
+        //      previous layer was published, which this thread has waited for) ----
         mbar_arrive_expect_tx(norm_bar, kRowBytes);
         bulk_g2s(smem_u32(norm_s), L.norm_weight, kRowBytes, norm_bar);
         norm_issued = li + 1;
-        // ---- R items: router rows, shared input pairs, shared gate row ----
-        {
-          const int s = acquire(seq);
-          if (s < 0) { alive = false; break; }
-          const uint32_t dst = smem_u32(ring + s * kSlotBytes);
-          const uint32_t bytes = kRowBytes * (eb < kExperts ? 2 : 1);
-          mbar_arrive_expect_tx(full_bar(s), bytes);
-          bulk_g2s(dst, L.router + static_cast<size_t>(c) * kHidden, kRowBytes, full_bar(s));
-          if (eb < kExperts)
-            bulk_g2s(dst + kRowBytes, L.router + static_cast<size_t>(eb) * kHidden, kRowBytes, full_bar(s));
-          issued[s] = seq / kRingSlots + 1;
-          ++seq;
+        // ---- R items: router rows, the next layer's router rows, shared input pairs, shared gate row ----
+        if (!issue(L.router + static_cast<size_t>(c) * kHidden, kRowBytes,
+                   L.router + static_cast<size_t>(eb < kExperts ? eb : c) * kHidden, eb < kExperts ? kRowBytes : 0u)) break;
+        if (has_next) {
+          const __nv_bfloat16* next_router = p.layers[p.first_layer + li + 1].router;
+          if (!issue(next_router + static_cast<size_t>(c) * kHidden, kRowBytes,
+                     next_router + static_cast<size_t>(eb < kExperts ? eb : c) * kHidden, eb < kExperts ? kRowBytes : 0u)) break;
         }
         for (int k = 0; k < n_shared_pairs && alive; ++k) {
           const int i = c + k * G;
-          const int s = acquire(seq);
-          if (s < 0) { alive = false; break; }
-          const uint32_t dst = smem_u32(ring + s * kSlotBytes);
-          mbar_arrive_expect_tx(full_bar(s), 2 * kRowBytes);
-          bulk_g2s(dst, L.shared_gate_proj + static_cast<size_t>(i) * kHidden, kRowBytes, full_bar(s));
-          bulk_g2s(dst + kRowBytes, L.shared_up_proj + static_cast<size_t>(i) * kHidden, kRowBytes, full_bar(s));
-          issued[s] = seq / kRingSlots + 1;
-          ++seq;
+          issue(L.shared_gate_proj + static_cast<size_t>(i) * kHidden, kRowBytes,
+                L.shared_up_proj + static_cast<size_t>(i) * kHidden, kRowBytes);
         }
         if (!alive) break;
-        if (owns_gate_row) {
-          const int s = acquire(seq);
-          if (s < 0) { alive = false; break; }
-          const uint32_t dst = smem_u32(ring + s * kSlotBytes);
-          mbar_arrive_expect_tx(full_bar(s), kRowBytes);
-          bulk_g2s(dst, L.shared_gate, kRowBytes, full_bar(s));
-          issued[s] = seq / kRingSlots + 1;
-          ++seq;
-        }
-        // ---- wait for this layer's expert ids ----
-        {
-          const unsigned long long start = global_timer_ns();
-          unsigned spins = 0;
-          while (misc->ids_layer != li + 1) {
-            if ((++spins & 255u) == 0u) {
-              if (*abort_flag != 0) { alive = false; break; }
-              if (global_timer_ns() - start > kWaitBudgetNs) {
-                raise_status(p, abort_flag, kStatusTimeoutIds);
-                record_site(p, 6, li);
-                alive = false;
-                break;
-              }
-            }
+        if (owns_gate_row && !issue(L.shared_gate, kRowBytes, nullptr, 0u)) break;
+        // ---- B items: pairs of the predicted experts, until the real routing is known ----
+        if (speculate && li > 0) {
+          if (!wait_word(&misc->pred_layer, li + 1, kStatusTimeoutIds, 10, li)) break;
+          __threadfence_block();
+          unsigned* state = &misc->blind_state[li & 1];
+          while (alive) {
+            const unsigned ticket = atomicAdd(state, 1u);
+            if ((ticket & kFrozen) != 0u || ticket >= static_cast<unsigned>(kListEntries)) break;
+            const int k = static_cast<int>(ticket);
+            const int row = list_entry_row(k, c, G);
+            const int expert = misc->pred[li & 1][k & (kPositions - 1)];
+            if (row >= kInter || expert < 0) continue;
+            issue_pair(expert, row);
           }
           if (!alive) break;
-          __threadfence_block();
         }
-        const int n_local = misc->n_local;
-        const int n_pairs = n_local * kInter;
-        const int p0 = static_cast<int>((static_cast<long long>(c) * n_pairs) / G);
-        const int p1 = static_cast<int>((static_cast<long long>(c + 1) * n_pairs) / G);
-        // The block's slice of the down projection is needed only after the activation barrier.  The
-        // shared expert's rows (known without the routing) go first; the routed experts' rows are
-        // requested AFTER the last gate/up pair, so they arrive while the block waits at the barrier
-        // for the slowest block -- time in which HBM would otherwise idle -- instead of lengthening
-        // the gate/up stream (21.5 -> 20.7 us per layer; issuing them 6 or 12 items before the end
-        // gave 21.6 / 21.4).
-        const uint32_t rank_bytes = nh * kDownRowBytes;
-        mbar_arrive_expect_tx(down_bar, rank_bytes * (n_local + 1));
-        bulk_g2s(smem_u32(down_region + kTopK * kDecodeMaxRowsPerBlock * kDownRowBytes),
-                 L.shared_down_proj + static_cast<size_t>(h0) * kInter, rank_bytes, down_bar);
-        down_issued = li + 1;
-        for (int pi = p0; pi < p1 && alive; ++pi) {
-          const int q = pi / kInter;
-          const int i = pi - q * kInter;
-          const int e_local = misc->ids[misc->local_rank[q]] - p.expert_lo;
-          const int s = acquire(seq);
-          if (s < 0) { alive = false; break; }
-          const uint32_t dst = smem_u32(ring + s * kSlotBytes);
-          const __nv_bfloat16* gate_row = L.expert_gate_up +
-              (static_cast<size_t>(e_local) * (2 * kInter) + i) * kHidden;
-          mbar_arrive_expect_tx(full_bar(s), 2 * kRowBytes);
-          bulk_g2s(dst, gate_row, kRowBytes, full_bar(s));
-          bulk_g2s(dst + kRowBytes, gate_row + static_cast<size_t>(kInter) * kHidden, kRowBytes, full_bar(s));
-          issued[s] = seq / kRingSlots + 1;
-          ++seq;
+        // ---- wait for this layer's plan ----
+        if (!wait_word(&misc->plan_layer, li + 1, kStatusTimeoutIds, 6, li)) break;
+        __threadfence_block();
+        const int n_blind = misc->n_blind;
+        const unsigned active_mask = misc->active_mask;
+        const unsigned valid_mask = misc->valid_mask;
+        // ---- P items: entries not handled blind, then entries whose blind item holds the wrong expert ----
+        for (int k = n_blind; k < kListEntries && alive; ++k) {
+          const int q = k & (kPositions - 1);
+          const int row = list_entry_row(k, c, G);
+          if (row >= kInter || ((active_mask >> q) & 1u) == 0u) continue;
+          issue_pair(misc->expert_of_pos[q], row);
         }
-        // also on the way out after a failed wait: the barrier's byte count must be met before the drain
-        for (int q = 0; q < n_local; ++q) {
-          const int e_local = misc->ids[misc->local_rank[q]] - p.expert_lo;
-          const __nv_bfloat16* src = L.expert_down +
-              (static_cast<size_t>(e_local) * kHidden + h0) * kInter;
-          bulk_g2s(smem_u32(down_region + q * kDecodeMaxRowsPerBlock * kDownRowBytes),
-                   src, rank_bytes, down_bar);
+        for (int k = 0; k < n_blind && alive; ++k) {
+          const int q = k & (kPositions - 1);
+          const int row = list_entry_row(k, c, G);
+          if (row >= kInter || ((active_mask >> q) & 1u) == 0u || ((valid_mask >> q) & 1u) != 0u) continue;
+          issue_pair(misc->expert_of_pos[q], row);
         }
         if (!alive) break;
+        // ---- D items: the block's rows of the down projections, shared expert first ----
+        const uint32_t bytes_lo = half_rows * kDownRowBytes;
+        const uint32_t bytes_hi = (nh - half_rows) * kDownRowBytes;
+        {
+          const __nv_bfloat16* src = L.shared_down_proj + static_cast<size_t>(h0) * kInter;
+          if (!issue(src, bytes_lo, nullptr, 0u)) break;
+          if (!issue(src + static_cast<size_t>(half_rows) * kInter, bytes_hi, nullptr, 0u)) break;
+        }
+        const int n_active = misc->n_active;
+        for (int a = 0; a < n_active && alive; ++a) {
+          const int expert = misc->expert_of_pos[misc->active_pos[a]];
+          const __nv_bfloat16* src = L.expert_down +
+              (static_cast<size_t>(expert - p.expert_lo) * kHidden + h0) * kInter;
+          if (!issue(src, bytes_lo, nullptr, 0u)) break;
+          issue(src + static_cast<size_t>(half_rows) * kInter, bytes_hi, nullptr, 0u);
+        }
       }
       // Drain: every copy this thread issued must have landed before the block
       // may exit (bounded; a phase that already completed returns at once).
@@ -414,10 +465,6 @@ moe_decode_persistent_kernel(const DecodeParams p) {
             mbar_wait_bounded(full_bar(s), (issued[s] - 1u) & 1u, &ignore);
           }
         }
-        if (down_issued != 0) {
-          volatile int ignore = 0;
-          mbar_wait_bounded(down_bar, (down_issued - 1u) & 1u, &ignore);
-        }
         if (norm_issued != 0) {
           volatile int ignore = 0;
           mbar_wait_bounded(norm_bar, (norm_issued - 1u) & 1u, &ignore);
@@ -425,13 +472,76 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp == kPredictWarp) {
+    // ------------------------------ prediction ----------------------------
+    // Top-8 of the next layer's router applied to this layer's input; the ids go to the producer,
+    // which requests their rows while this layer's tail and the next layer's head are running.
+    if (speculate) {
+      for (int li = 0; li + 1 < p.n_layers; ++li) {
+        // sleep until this block's own plan for layer li exists: the predicted logits were written
+        // right after the real ones, so they are (nearly) complete by then and few polls are needed
+        {
+          const unsigned long long start = global_timer_ns();
+          bool ok = true;
+          while (misc->plan_layer < li + 1) {
+            __nanosleep(200);
+            if (*abort_flag != 0 || global_timer_ns() - start > 2 * kWaitBudgetNs) { ok = false; break; }
+          }
+          if (!ok) break;
+        }
+        const unsigned tag = epoch0 + li + 1;
+        unsigned long long w[8];
+        bool ready = false;
+        const unsigned long long start = global_timer_ns();
+        unsigned spins = 0;
+        while (!ready) {
+          bool mine = true;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            w[q] = ld_strong_u64(pred_logits + (c % kDecodeReplicas) * kExperts + 32 * q + lane);
+            mine = mine && static_cast<unsigned>(w[q] >> 32) == tag;
+          }
+          ready = __all_sync(0xffffffffu, mine);
+          if (!ready) {
+            __nanosleep(100);
+            if ((++spins & 15u) == 0u) {
+              if (*abort_flag != 0) break;
+              if (global_timer_ns() - start > kWaitBudgetNs) {
+                raise_status(p, abort_flag, kStatusTimeoutPeer);
+                record_site(p, 12, li);
+                break;
+              }
+            }
+          }
+        }
+        if (!ready) break;
+        uint32_t k[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) k[q] = order_key(__uint_as_float(static_cast<uint32_t>(w[q])));
+        float score;
+        int id;
+        warp_top8(k, lane, score, id);
+        if (lane < kPositions)
+          misc->pred[(li + 1) & 1][lane] = (id >= p.expert_lo && id < p.expert_hi) ? id : -1;
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          misc->pred_layer = li + 2;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp < kDecodeConsumerWarps) {
     // ------------------------------ consumers -----------------------------
-    const int ctid = threadIdx.x;                 // 0 .. 511
+    const int ctid = threadIdx.x;                 // 0 .. 415
+    const bool streams = warp >= kFirstStreamWarp && warp < kFirstStreamWarp + kStreamWarps;
     unsigned seq = 0;                             // mirrors the producer's item counter
     unsigned long long nbar = 0;
     bool alive = true;
 
+    auto owns = [&](unsigned item) -> bool {
+      return kFirstStreamWarp + static_cast<int>((item % kRingSlots) % kStreamWarps) == warp;
+    };
     // wait for item `item`, return slot pointer (nullptr on abort)
     auto wait_item = [&](unsigned item, int site) -> const uint8_t* {
       const int s = item % kRingSlots;
@@ -466,10 +576,15 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       a = butterfly_sum(a);
       b = butterfly_sum(b);
     };
+    auto hooked_logit = [&](float v, int expert) -> float {
+      if (p.router_bias != nullptr) v = __fadd_rn(v, p.router_bias[expert]);
+      if (p.quant_eighths) v = __fmul_rn(rintf(__fmul_rn(v, 8.0f)), 0.125f);
+      return v;
+    };
 
-    // tracing stamps: 0 layer start, 1 norm done, 2 router/shared rows done, 3 logits barrier,
-    // 4 top-8 done, 5 routed gate/up done, 6 activation barrier, 7 activations loaded,
-    // 8 down region landed, 9 down dots done, 10 output stored, 11 output barrier
+    // tracing stamps: 0 layer start, 1 norm done, 2 router/shared rows done, 3 logits arrived,
+    // 4 plan published, 5 routed gate/up done, 6 activation barrier, 7 activations loaded,
+    // 8 = 7, 9 down dots done, 10 output stored, 11 = 10
     auto stamp = [&](int li, int k) {
       if (p.timeline != nullptr && c == 0 && ctid == 0)
         p.timeline[li * kDecodeTraceStamps + k] = global_timer_ns();
@@ -477,6 +592,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     for (int li = 0; li < p.n_layers; ++li) {
       const bool first = (li == 0);
       const bool last = (li == p.n_layers - 1);
+      const bool has_next = speculate && !last;
 
       stamp(li, 0);
       const uint32_t* xw_src = (li & 1) ? p.xbuf1 : p.xbuf0;     // tagged words written by layer li - 1
@@ -522,23 +638,26 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         }
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
-      // ---- norm, once per block: canonical sum of squares (warp g sums group g), then every
-      //      thread normalises one 8-element chunk into h2_s (the activation region is idle now)
+      // ---- norm, once per block.  Sum of squares in the order of the reference kernel
+      //      (native/src/native_pointwise.hip.cpp:109-142): partial t of 256 adds elements t, t + 256, ...
+      //      in that order, the partials fold by halving.  Warp j holds partial 8 l + j on lane l: the
+      //      butterfly does the halvings of width 128 .. 8, the last three widths are the tree below.
+      //      Then every thread normalises one 8-element chunk into h2_s (the activation region is idle now)
       uint8_t* h2_s = reinterpret_cast<uint8_t*>(act_s);
       if (warp < 8) {
-        float xv[8];
-        unpack8(reinterpret_cast<const uint4*>(x_s)[warp * 32 + lane], xv);
         float acc = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc = __fmaf_rn(xv[j], xv[j], acc);
+        for (int g = 0; g < 8; ++g) {
+          const float v = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(x_s)[256 * g + 8 * lane + warp]);
+          acc = __fmaf_rn(v, v, acc);
+        }
         acc = butterfly_sum(acc);
         if (lane == 0) dots[warp] = acc;
       }
       consumer_sync();
       {
-        float total = dots[0];
-#pragma unroll
-        for (int g = 1; g < 8; ++g) total = __fadd_rn(total, dots[g]);
+        const float total = __fadd_rn(__fadd_rn(__fadd_rn(dots[0], dots[4]), __fadd_rn(dots[2], dots[6])),
+                                      __fadd_rn(__fadd_rn(dots[1], dots[5]), __fadd_rn(dots[3], dots[7])));
         const float inv = det_rsqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(kHidden)), p.eps));
         if (!mbar_wait_bounded(norm_bar, li & 1u, abort_flag)) {
           if (*abort_flag == kStatusTimeoutMbarrier) {
@@ -568,41 +687,37 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       consumer_sync();
       // streaming warps keep h2 in registers: element k = 256 g + 8 lane + j at xr[8 g + j]
       float xr[64];
-      if (warp < kRingSlots) {
+      if (streams) {
 #pragma unroll
         for (int g = 0; g < 8; ++g) unpack8(reinterpret_cast<const uint4*>(h2_s)[g * 32 + lane], xr + 8 * g);
       }
 
       stamp(li, 1);
       // ---- R items ----
-      const int n_r_items = 1 + n_shared_pairs + (owns_gate_row ? 1 : 0);
+      const int n_r_items = 1 + (has_next ? 1 : 0) + n_shared_pairs + (owns_gate_row ? 1 : 0);
+      const int first_shared = 1 + (has_next ? 1 : 0);
       for (int k = 0; k < n_r_items && alive; ++k) {
         const unsigned item = seq + k;
-        if (static_cast<int>(item % kRingSlots) != warp) continue;
+        if (!owns(item)) continue;
         const uint8_t* slot = wait_item(item, 2);
         if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; break; }
         float a, b;
         pair_dot(slot, xr, a, b);
         release_item(item);
         if (lane == 0) {
-          if (k == 0) {
-            float v0 = a, v1 = b;
-            if (p.router_bias != nullptr) {
-              v0 = __fadd_rn(v0, p.router_bias[c]);
-              if (eb < kExperts) v1 = __fadd_rn(v1, p.router_bias[eb]);
-            }
-            if (p.quant_eighths) {
-              v0 = __fmul_rn(rintf(__fmul_rn(v0, 8.0f)), 0.125f);
-              v1 = __fmul_rn(rintf(__fmul_rn(v1, 8.0f)), 0.125f);
-            }
+          if (k < first_shared) {
+            // k = 0: this layer's logits; k = 1: the next layer's router on the same input
+            unsigned long long* dst = (k == 0) ? p.logits : pred_logits;
+            const float v0 = hooked_logit(a, c);
+            const float v1 = eb < kExperts ? hooked_logit(b, eb) : 0.0f;
             const unsigned long long tag = static_cast<unsigned long long>(epoch0 + li + 1) << 32;
 #pragma unroll
             for (int rep = 0; rep < kDecodeReplicas; ++rep) {
-              st_strong_u64(p.logits + rep * kExperts + c, tag | __float_as_uint(v0));
-              if (eb < kExperts) st_strong_u64(p.logits + rep * kExperts + eb, tag | __float_as_uint(v1));
+              st_strong_u64(dst + rep * kExperts + c, tag | __float_as_uint(v0));
+              if (eb < kExperts) st_strong_u64(dst + rep * kExperts + eb, tag | __float_as_uint(v1));
             }
-          } else if (k <= n_shared_pairs) {
-            const int i = c + (k - 1) * G;
+          } else if (k < first_shared + n_shared_pairs) {
+            const int i = c + (k - first_shared) * G;
             const float g = round_bf16(a);
             const float u = round_bf16(b);
             const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(g), u));
@@ -619,7 +734,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       seq += n_r_items;
       stamp(li, 2);
 
-      // ---- logits exchange + top-8 (ties to the lowest expert id) + softmax, warp 0 ----
+      // ---- logits exchange + top-8 (ties to the lowest expert id) + softmax + layer plan, warp 0 ----
       if (warp == 0) {
         const unsigned tag = epoch0 + li + 1;
         unsigned long long w[8];
@@ -649,11 +764,6 @@ moe_decode_persistent_kernel(const DecodeParams p) {
 #pragma unroll
                 for (int q = 0; q < 8; ++q) n_bad += static_cast<unsigned>(w[q] >> 32) != tag ? 1 : 0;
                 n_bad = __reduce_add_sync(0xffffffffu, n_bad);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  const unsigned m = __ballot_sync(0xffffffffu, static_cast<unsigned>(w[q] >> 32) != tag);
-                  if (lane == 0 && p.status[1] == 0) p.status[16 + q] = static_cast<int>(m);
-                }
                 if (bad == first_bad) {
                   const unsigned long long word = w[(first_bad >> 5) & 7];
                   unsigned diag[4] = {tag, static_cast<unsigned>(first_bad),
@@ -673,26 +783,18 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           k[q] = order_key(value);
           if (p.dbg_logits != nullptr && c == 0) p.dbg_logits[32 * q + lane] = value;
         }
-        float my_score = 0.0f;      // lane r keeps the r-th selected value
-        int my_id = 0;
-#pragma unroll 1
-        for (int r = 0; r < kTopK; ++r) {
-          uint32_t local = k[0];
-#pragma unroll
-          for (int q = 1; q < 8; ++q) local = max(local, k[q]);
-          const uint32_t best = __reduce_max_sync(0xffffffffu, local);
-          int candidate = 0x7fffffff;
-#pragma unroll
-          for (int q = 7; q >= 0; --q) {
-            if (k[q] == best) candidate = 32 * q + lane;
-          }
-          const int winner = __reduce_min_sync(0xffffffffu, candidate);
-          if (lane == r) { my_score = key_value(best); my_id = winner; }
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            if (winner == 32 * q + lane) k[q] = 0u;
-          }
+        float my_score;      // lane r keeps the r-th selected value
+        int my_id;
+        warp_top8(k, lane, my_score, my_id);
+        // The routing is known: stop the blind issue.  The value the counter held says exactly how many
+        // list entries the producer has claimed blind (it may still be placing the last of them).
+        unsigned claimed = 0u;
+        if (lane == 0) {
+          claimed = atomicOr(&misc->blind_state[li & 1], kFrozen) & (kFrozen - 1u);
+          misc->blind_state[(li + 1) & 1] = 0u;      // nobody uses the other word before this layer's plan
         }
+        claimed = __shfl_sync(0xffffffffu, claimed, 0);
+        const int n_blind = min(static_cast<int>(claimed), kListEntries);
         // softmax over the eight: exp(s_r - s_0) / sum, summed in selection order
         const float top = __shfl_sync(0xffffffffu, my_score, 0);
         const float ex = det_expf(__fsub_rn(my_score, top));
@@ -700,12 +802,38 @@ moe_decode_persistent_kernel(const DecodeParams p) {
 #pragma unroll
         for (int r = 0; r < kTopK; ++r) denom = __fadd_rn(denom, __shfl_sync(0xffffffffu, ex, r));
         const uint16_t wb = float_to_bf16_bits(__fdiv_rn(ex, denom));
-        const bool local_expert = my_id >= p.expert_lo && my_id < p.expert_hi;
-        const unsigned local_mask = __ballot_sync(0xffffffffu, lane < kTopK && local_expert);
+        const bool local_expert = lane < kTopK && my_id >= p.expert_lo && my_id < p.expert_hi;
+        const unsigned local_mask = __ballot_sync(0xffffffffu, local_expert);
+        // ---- deal the chosen experts held here to the ring positions: an expert the prediction placed
+        //      at position q stays there (its blind items are valid); the others take the remaining
+        //      positions in ascending order ----
+        const int pred_q = (lane < kPositions && n_blind > 0) ? misc->pred[li & 1][lane] : -1;
+        int rank_q = -1;
+#pragma unroll
+        for (int r = 0; r < kTopK; ++r) {
+          const int id_r = __shfl_sync(0xffffffffu, my_id, r);
+          if (((local_mask >> r) & 1u) != 0u && pred_q >= 0 && pred_q == id_r) rank_q = r;
+        }
+        const bool matched = lane < kPositions && rank_q >= 0;
+        const unsigned valid_mask = __ballot_sync(0xffffffffu, matched);
+        const unsigned matched_ranks = __reduce_or_sync(0xffffffffu, matched ? (1u << rank_q) : 0u);
+        const unsigned free_pos = ((1u << kPositions) - 1u) & ~valid_mask;
+        if (lane < kPositions && !matched) {
+          unsigned left = local_mask & ~matched_ranks;
+          const int skip = __popc(free_pos & ((1u << lane) - 1u));
+          for (int t = 0; t < skip && left != 0u; ++t) left &= left - 1u;
+          rank_q = left != 0u ? __ffs(left) - 1 : -1;
+        }
+        const int expert_q = __shfl_sync(0xffffffffu, my_id, rank_q >= 0 ? rank_q : 0);
+        const unsigned active_mask = __ballot_sync(0xffffffffu, lane < kPositions && rank_q >= 0);
         if (lane < kTopK) {
           misc->ids[lane] = my_id;
           misc->weights[lane] = bf16_bits_to_float(wb);
           if (local_expert) misc->local_rank[__popc(local_mask & ((1u << lane) - 1u))] = lane;
+          misc->expert_of_pos[lane] = rank_q >= 0 ? expert_q : -1;
+          misc->rank_of_pos[lane] = rank_q;
+          misc->pred_of_pos[lane] = pred_q;
+          if (rank_q >= 0) misc->active_pos[__popc(active_mask & ((1u << lane) - 1u))] = lane;
           if (c == 0) {
             if (p.dbg_ids != nullptr) p.dbg_ids[lane] = my_id;
             if (p.dbg_scores != nullptr) p.dbg_scores[lane] = my_score;
@@ -715,86 +843,111 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         __syncwarp();
         if (lane == 0) {
           misc->n_local = __popc(local_mask);
+          misc->n_active = __popc(active_mask);
+          misc->active_mask = active_mask;
+          misc->valid_mask = valid_mask;
+          misc->n_blind = n_blind;
           __threadfence_block();
-          misc->ids_layer = li + 1;
+          misc->plan_layer = li + 1;
         }
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 4);
 
-      // ---- phase 1: routed gate/up pairs of the experts held on this GPU ----
+      // ---- routed gate/up pairs of the experts held on this GPU ----
       const int n_local = misc->n_local;
-      const int n_pairs = n_local * kInter;
-      const int p0 = static_cast<int>((static_cast<long long>(c) * n_pairs) / G);
-      const int p1 = static_cast<int>((static_cast<long long>(c + 1) * n_pairs) / G);
-      for (int pi = p0; pi < p1 && alive; ++pi) {
-        const unsigned item = seq + (pi - p0);
-        if (static_cast<int>(item % kRingSlots) != warp) continue;
-        const uint8_t* slot = wait_item(item, 3);
-        if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; break; }
-        float a, b;
-        pair_dot(slot, xr, a, b);
-        release_item(item);
-        if (lane == 0) {
-          const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), b));
+      const int n_active = misc->n_active;
+      const int n_blind = misc->n_blind;
+      const unsigned active_mask = misc->active_mask;
+      const unsigned valid_mask = misc->valid_mask;
+      {
+        unsigned item = seq;
+        // use == false: the slot holds rows of an expert that was not chosen; wait for them to land
+        // (the copy must not be in flight when the slot is reused) and hand the slot back unread
+        auto consume_pair = [&](int q, int row, bool use) -> bool {
+          if (owns(item)) {
+            const uint8_t* slot = wait_item(item, 3);
+            if (!__all_sync(0xffffffffu, slot != nullptr)) return false;
+            float a = 0.0f, b = 0.0f;
+            if (use) pair_dot(slot, xr, a, b);
+            release_item(item);
+            if (use && lane == 0) {
+              const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), b));
+              const int slot_index = misc->rank_of_pos[q] * kInter + row;
 #pragma unroll
-          for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + pi] = bits;
+              for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + slot_index] = bits;
+            }
+          }
+          ++item;
+          return true;
+        };
+        for (int k = 0; k < n_blind && alive; ++k) {
+          const int q = k & (kPositions - 1);
+          const int row = list_entry_row(k, c, G);
+          if (row >= kInter || misc->pred_of_pos[q] < 0) continue;
+          alive = consume_pair(q, row, ((valid_mask >> q) & 1u) != 0u);
         }
+        for (int k = n_blind; k < kListEntries && alive; ++k) {
+          const int q = k & (kPositions - 1);
+          const int row = list_entry_row(k, c, G);
+          if (row >= kInter || ((active_mask >> q) & 1u) == 0u) continue;
+          alive = consume_pair(q, row, true);
+        }
+        for (int k = 0; k < n_blind && alive; ++k) {
+          const int q = k & (kPositions - 1);
+          const int row = list_entry_row(k, c, G);
+          if (row >= kInter || ((active_mask >> q) & 1u) == 0u || ((valid_mask >> q) & 1u) != 0u) continue;
+          alive = consume_pair(q, row, true);
+        }
+        seq = item;
       }
-      seq += (p1 - p0);
       stamp(li, 5);
       if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
       stamp(li, 6);
 
-      // ---- phase 2: down products for outputs h0 .. h1-1 ----
+      // ---- down products for outputs h0 .. h1-1 ----
       for (int v = ctid; v < kActBytes / 16; v += kDecodeConsumerThreads) {
         reinterpret_cast<uint4*>(act_s)[v] = ld_cg_u4(
             reinterpret_cast<const uint4*>(p.act + (c % kDecodeReplicas) * kDecodeActStride) + v);
       }
       consumer_sync();
       stamp(li, 7);
-      if (!mbar_wait_bounded(down_bar, li & 1u, abort_flag)) {
-        if (*abort_flag == kStatusTimeoutMbarrier) {
-          atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
-          record_site(p, 4, li);
-        }
-        alive = false;
-      }
-      alive = __all_sync(0xffffffffu, alive);
       stamp(li, 8);
-      if (alive) {
-        // unit = (rank slot q, half of the block's output rows): the activation row is unpacked
-        // once and up to seven dots against it share one eight-way reduction
-        const int half_rows = (nh + 1) / 2;
-        const int n_units = 2 * (n_local + 1);
-        for (int unit = warp; unit < n_units; unit += kDecodeConsumerWarps) {
-          const int q = unit >> 1;
+      {
+        // item = (expert, half of the block's output rows): the activation row is unpacked once and up
+        // to seven dots against it share one eight-way reduction
+        const int n_items = 2 * (n_active + 1);
+        for (int unit = 0; unit < n_items && alive; ++unit) {
+          const unsigned item = seq + unit;
+          if (!owns(item)) continue;
+          const uint8_t* slot = wait_item(item, 4);
+          if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; break; }
+          const int column = unit < 2 ? kTopK : misc->rank_of_pos[misc->active_pos[(unit - 2) >> 1]];
           const int row_base = (unit & 1) * half_rows;
-          const int region = (q == n_local) ? kTopK : q;
+          const int rows = (unit & 1) ? nh - half_rows : half_rows;
           float af[16];
           {
-            const uint4* arow = reinterpret_cast<const uint4*>(act_s + region * kInter) + lane;
+            const uint4* arow = reinterpret_cast<const uint4*>(act_s + column * kInter) + lane;
             unpack8(arow[0], af);
             unpack8(arow[32], af + 8);
           }
           float part[8];
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            const int hh = row_base + u;
             float acc = 0.0f;
-            if (u < half_rows && hh < nh) {
-              const uint4* wrow = reinterpret_cast<const uint4*>(
-                  down_region + (region * kDecodeMaxRowsPerBlock + hh) * kDownRowBytes) + lane;
+            if (u < rows) {
+              const uint4* wrow = reinterpret_cast<const uint4*>(slot + u * kDownRowBytes) + lane;
               acc = fma8(af, wrow[0], acc);
               acc = fma8(af + 8, wrow[32], acc);
             }
             part[u] = acc;
           }
+          release_item(item);
           const float total = warp_reduce8(part, lane);
           const int u = reduce8_slot(lane);
-          const int hh = row_base + u;
-          if ((lane & 3) == 0 && u < half_rows && hh < nh) dots[hh * kDotsStride + region] = total;
+          if ((lane & 3) == 0 && u < rows) dots[(row_base + u) * kDotsStride + column] = total;
         }
+        seq += n_items;
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 9);
@@ -812,19 +965,20 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           const int q = rest / nh;
           const int hh = rest - q * nh;
           const int peer = peer_slot + (peer_slot >= p.rank ? 1 : 0);
-          const int slot = misc->local_rank[q];
-          st_sys_u64(p.ep_dots[peer] + parity_base + static_cast<size_t>(slot) * kHidden + h0 + hh,
-                     tag64 | __float_as_uint(dots[hh * kDotsStride + q]));
+          const int r = misc->local_rank[q];
+          st_sys_u64(p.ep_dots[peer] + parity_base + static_cast<size_t>(r) * kHidden + h0 + hh,
+                     tag64 | __float_as_uint(dots[hh * kDotsStride + r]));
         }
       }
       if (ctid < nh) {
         const int h = h0 + ctid;
         float acc = 0.0f;
         if (p.world == 1) {
-          for (int q = 0; q < n_local; ++q) {
-            const float d = dots[ctid * kDotsStride + q];
-            acc = __fmaf_rn(misc->weights[misc->local_rank[q]], d, acc);
-            if (p.dbg_slot_dots != nullptr) p.dbg_slot_dots[misc->local_rank[q] * kHidden + h] = d;
+#pragma unroll
+          for (int r = 0; r < kTopK; ++r) {
+            const float d = dots[ctid * kDotsStride + r];
+            acc = __fmaf_rn(misc->weights[r], d, acc);
+            if (p.dbg_slot_dots != nullptr) p.dbg_slot_dots[r * kHidden + h] = d;
           }
         } else {
           const unsigned tag = epoch0 + li + 1;
@@ -834,7 +988,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           for (int r = 0; r < kTopK; ++r) {
             float d;
             if (q < n_local && misc->local_rank[q] == r) {
-              d = dots[ctid * kDotsStride + q];
+              d = dots[ctid * kDotsStride + r];
               ++q;
             } else {
               unsigned long long word = ld_sys_u64(mine + static_cast<size_t>(r) * kHidden);
@@ -885,14 +1039,11 @@ moe_decode_persistent_kernel(const DecodeParams p) {
 
 cudaError_t launch_moe_decode(const DecodeParams& params, int grid_blocks,
                               cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(moe_decode_persistent_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kDecodeSmemBytes);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the function
+  const cudaError_t e = cudaFuncSetAttribute(moe_decode_persistent_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kDecodeSmemBytes);
+  if (e != cudaSuccess) return e;
   DecodeParams local = params;
   void* args[] = {&local};
   return cudaLaunchCooperativeKernel(

@@ -5,16 +5,19 @@
 
 namespace aima {
 
-constexpr int kDecodeConsumerWarps = 15;  // + 1 producer = 16 warps, 4 per SM sub-partition
+// 16 warps, 4 per SM sub-partition: warp 0 control (exchanges, top-8, layer plan), warps 1-12
+// stream the weight ring, warp 13 predicts the next layer's experts, warp 14 is spare, warp 15
+// issues the bulk copies.  Warps 0-12 form the "consumer" group that meets at named barrier 1.
+constexpr int kDecodeConsumerWarps = 13;
 constexpr int kDecodeConsumerThreads = kDecodeConsumerWarps * 32;
-constexpr int kDecodeThreads = kDecodeConsumerThreads + 32;  // + producer warp
-// Each block owns hidden/grid output elements and stages their down-projection
-// rows (8 experts + shared, 1 KB each) in shared memory: at most 14 per block,
+constexpr int kDecodeThreads = 16 * 32;
+// Each block owns hidden/grid output elements; their down-projection rows (1 KB each) pass
+// through the ring in two items of at most 7 rows per expert: at most 14 rows per block,
 // i.e. the grid must have at least ceil(2048 / 14) = 147 blocks.
 constexpr int kDecodeMaxRowsPerBlock = 14;
 constexpr int kDecodeMinBlocks = (kHidden + kDecodeMaxRowsPerBlock - 1) / kDecodeMaxRowsPerBlock;
 constexpr int kDecodeMaxBlocks = kExperts;  // router rows are dealt c, c + grid
-constexpr int kDecodeSmemBytes = 229728;
+constexpr int kDecodeSmemBytes = 216120;
 constexpr int kDecodeTraceStamps = 12;
 constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU expert-parallel exchange buffer
 // Everything all 148 blocks read back from global memory (router logits, the
@@ -22,6 +25,7 @@ constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU exp
 // block c reads copy c % kDecodeReplicas: 148 readers of the same few L2 lines
 // otherwise queue at the L2 slices that own them.
 constexpr int kDecodeReplicas = 8;
+constexpr int kDecodeLogitWords = 2 * kDecodeReplicas * kExperts;   // real + predicted, 64-bit words
 constexpr int kDecodeActStride = 9 * kInter + 64;   // BF16 elements per activation copy; [9*512] = gate logit bits (2 x u16)
 
 struct DecodeParams {
@@ -30,7 +34,9 @@ struct DecodeParams {
   __nv_bfloat16* x_out;          // [2048] residual stream leaving the last layer
   uint32_t* xbuf0;               // [replicas][2048] inter-layer ping-pong, words = tag16 << 16 | bf16
   uint32_t* xbuf1;
-  unsigned long long* logits;    // [replicas][256] words = tag32 << 32 | FP32 logit bits
+  unsigned long long* logits;    // [2][replicas][256] words = tag32 << 32 | FP32 logit bits; the second
+                                 // half carries the NEXT layer's router applied to this layer's input
+                                 // (the prediction that lets its expert rows be requested early)
   uint16_t* act;                 // [replicas][kDecodeActStride] BF16 activations: 8 ranks + shared,
                                  // then the shared-expert gate logit as FP32 bits
   unsigned long long* bar_counter;  // monotonic grid-barrier arrivals
@@ -39,6 +45,7 @@ struct DecodeParams {
   int* status;                   // device status word, 0 = healthy
   const float* router_bias;      // [256] or nullptr
   int quant_eighths;
+  int speculate;                 // 1: request the predicted experts' rows before the routing is known
   float eps;
   int first_layer;
   int n_layers;

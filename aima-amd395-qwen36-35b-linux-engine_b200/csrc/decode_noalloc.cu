@@ -32,12 +32,12 @@ constexpr size_t kOffTable = 0;                                   // LayerPtrs[A
 constexpr size_t kOffSync = 1024;                                 // barrier counter (+0), base (+128), tag base (+192)
 constexpr size_t kOffStatus = kOffSync + 256;                     // device status words
 constexpr size_t kOffLogits = kOffStatus + 256;                   // replicated tagged 64-bit router logits
-constexpr size_t kOffX0 = kOffLogits + static_cast<size_t>(kDecodeReplicas) * kExperts * 8;   // tagged vector 0
+constexpr size_t kOffX0 = kOffLogits + static_cast<size_t>(kDecodeLogitWords) * 8;            // tagged vector 0
 constexpr size_t kOffX1 = kOffX0 + static_cast<size_t>(kDecodeReplicas) * kHidden * 4;        // tagged vector 1
 constexpr size_t kOffAct = kOffX1 + static_cast<size_t>(kDecodeReplicas) * kHidden * 4;       // activation copies
 constexpr size_t kClearBytes = kOffAct - kOffSync;                // everything that carries a tag or a count
 constexpr size_t kScratchBytes = kOffAct + static_cast<size_t>(kDecodeReplicas) * kDecodeActStride * 2;
-static_assert(sizeof(LayerPtrs) * AIMA_MOE_NOALLOC_MAX_LAYERS <= kOffX0, "layer table overflows its slot");
+static_assert(sizeof(LayerPtrs) * AIMA_MOE_NOALLOC_MAX_LAYERS <= kOffSync - kOffTable, "layer table overflows its slot");
 static_assert(kScratchBytes <= AIMA_MOE_NOALLOC_SCRATCH_BYTES, "scratch exceeds the stated maximum");
 
 // In host code this name is only a stand-in for the device array; its device
@@ -195,6 +195,7 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   params.world = 1;
   params.rank = 0;
   params.quant_eighths = 0;
+  params.speculate = 1;
   params.eps = rms_eps;
   params.first_layer = 0;
   params.n_layers = static_cast<int>(n_layers);

@@ -130,7 +130,7 @@ int validate_config(const aima_moe_config* config) {
 }
 
 // exchange area: sync words 256 B, status 256 B, replicated tagged logits and two replicated tagged vectors
-constexpr size_t kLogitsBytes = static_cast<size_t>(kDecodeReplicas) * kExperts * 8;
+constexpr size_t kLogitsBytes = static_cast<size_t>(kDecodeLogitWords) * 8;   // real + predicted
 constexpr size_t kXbufBytes = static_cast<size_t>(kDecodeReplicas) * kHidden * 4;
 constexpr size_t kExchangeBytes = 256 + 256 + kLogitsBytes + 2 * kXbufBytes;
 
@@ -213,6 +213,7 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
   params.status = handle->status;
   params.router_bias = handle->router_bias;
   params.quant_eighths = handle->quant_eighths;
+  params.speculate = (handle->config.flags & AIMA_MOE_FLAG_NO_DECODE_PREDICTION) == 0 ? 1 : 0;
   params.eps = handle->config.rms_eps;
   params.first_layer = static_cast<int>(first_layer);
   params.n_layers = static_cast<int>(n_layers);

@@ -14,10 +14,9 @@ namespace {
 
 constexpr int kNormWarpsPerBlock = 8;
 
-// One warp per row.  Lane l holds elements 256 g + 8 l + j (g, j in 0..7), the
-// same ownership as the canonical dot product, so the sum of squares runs as 8
-// groups of 32 eight-element partials: butterfly inside a group, groups added
-// left to right.
+// One warp per row.  Lane l holds elements 256 g + 8 l + j (g, j in 0..7) in
+// v[8 g + j]; the sum of squares follows the reference kernel's order
+// (row_sumsq_2048 in common.cuh).
 __global__ void __launch_bounds__(kNormWarpsPerBlock * 32)
 rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x,
                     const __nv_bfloat16* __restrict__ residual,
@@ -30,7 +29,6 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x,
   if (row >= rows) return;
   const size_t base = static_cast<size_t>(row) * kHidden;
   float v[64];
-  float total = 0.0f;
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
     const size_t off = base + 256 * g + 8 * lane;
@@ -53,12 +51,8 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x,
             make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
     }
-    float part = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) part = __fmaf_rn(v[8 * g + j], v[8 * g + j], part);
-    part = butterfly_sum(part);
-    total = (g == 0) ? part : __fadd_rn(total, part);
   }
+  const float total = row_sumsq_2048(v, lane);
   const float inv = det_rsqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(kHidden)), eps));
 #pragma unroll
   for (int g = 0; g < 8; ++g) {

@@ -630,19 +630,31 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
     reinterpret_cast<uint4*>(dbg_routed + base)[t] =
         make_uint4(packed_routed[0], packed_routed[1], packed_routed[2], packed_routed[3]);
   }
-  // Optional exit: RMSNorm of the row just produced (the next layer's input norm), with the
-  // arithmetic of rmsnorm_rows_kernel -- thread t owns the eight elements 8t .. 8t+7, i.e. lane
-  // t % 32 of group t / 32, so the warp butterflies are the canonical group sums.
+  // Optional exit: RMSNorm of the row just produced (the next layer's input norm).  Sum of squares in
+  // the order of the reference kernel (native/src/native_pointwise.hip.cpp:109-142): partial p of 256
+  // adds elements p, p + 256, ... in that order, the partials fold by halving.  Thread t holds elements
+  // 8 t .. 8 t + 7, so the squares go through shared memory once and thread p picks up its eight.
   if (next_norm_out != nullptr) {
-    float part = 0.0f;
+    __shared__ float squares[kHidden];
+    __shared__ float partial[256];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) part = __fmaf_rn(o8[j], o8[j], part);
-    part = butterfly_sum(part);
-    if ((t & 31) == 0) group_sums[t >> 5] = part;
+    for (int j = 0; j < 8; ++j) squares[8 * t + j] = __fmul_rn(o8[j], o8[j]);   // exact: BF16 squared fits FP32
     __syncthreads();
-    float total = group_sums[0];
+    float acc = 0.0f;
 #pragma unroll
-    for (int g = 1; g < 8; ++g) total = __fadd_rn(total, group_sums[g]);
+    for (int i = 0; i < 8; ++i) acc = __fadd_rn(acc, squares[t + 256 * i]);
+    partial[t] = acc;
+    __syncthreads();
+    if (t < 32) {
+      // widths 128, 64, 32 fold four groups of 64 partials onto lane t, widths 16 .. 1 are lane shuffles
+      float q = __fadd_rn(__fadd_rn(__fadd_rn(partial[t], partial[t + 128]), __fadd_rn(partial[t + 64], partial[t + 192])),
+                          __fadd_rn(__fadd_rn(partial[t + 32], partial[t + 160]), __fadd_rn(partial[t + 96], partial[t + 224])));
+#pragma unroll
+      for (int width = 16; width >= 1; width >>= 1) q = __fadd_rn(q, __shfl_down_sync(0xffffffffu, q, width));
+      if (t == 0) group_sums[0] = q;
+    }
+    __syncthreads();
+    const float total = group_sums[0];
     const float inv = det_rsqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(kHidden)), eps));
     float w[8];
     unpack8(__ldg(reinterpret_cast<const uint4*>(next_norm_weight) + t), w);

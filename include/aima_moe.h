@@ -95,6 +95,10 @@ typedef struct aima_moe_config {
  * the other (the copies and the HBM-bound products slow each other down), so it is off by default. */
 #define AIMA_MOE_FLAG_EP_PIPELINE_2 32u
 #define AIMA_MOE_FLAG_EP_PIPELINE_4 64u
+/* Decode, for A/B timing and qualification: do not predict the next layer's experts (its router applied
+ * to the current layer's input) and do not request their rows ahead of the routing.  Same bits either
+ * way; with the prediction a layer's weight stream overlaps the hand-overs of the previous layer. */
+#define AIMA_MOE_FLAG_NO_DECODE_PREDICTION 128u
 
 /* One layer's tensors in checkpoint layout
  * (doc/reference/amd395-qwen36-35b-a3b-bf16/qwen36-shape-manifest.json:162-180,

@@ -124,29 +124,25 @@ float aima_or_dot(const uint16_t* x, const uint16_t* w, int k_size) {
   return p[0];
 }
 
-/* canonical sum of squares of one 2048-wide row */
+/* Sum of squares of one 2048-wide row in the order of the reference kernels
+ * (native/src/native_pointwise.hip.cpp:109-142, prefill_rmsnorm_2048_kernel):
+ * thread t of 256 adds the squares of elements t, t+256, ..., t+1792 in that
+ * order, then the 256 partials are folded by halving: partial[t] +=
+ * partial[t + width] for width = 128, 64, ..., 1.  (The square of a BF16 value
+ * is exact in FP32, so a fused and an unfused multiply-add give the same bits.) */
 static float sumsq_2048(const uint16_t* x) {
   float part[256];
   for (int t = 0; t < 256; ++t) {
     float acc = 0.0f;
-    for (int j = 0; j < 8; ++j) {
-      const float v = bf2f(x[8 * t + j]);
+    for (int i = 0; i < 8; ++i) {
+      const float v = bf2f(x[t + 256 * i]);
       acc = fmaf(v, v, acc);
     }
     part[t] = acc;
   }
-  float total = 0.0f;
-  for (int g = 0; g < 8; ++g) {
-    float p[32];
-    memcpy(p, part + 32 * g, sizeof p);
-    for (int s = 16; s >= 1; s >>= 1) {
-      float q[32];
-      for (int l = 0; l < 32; ++l) q[l] = p[l] + p[l ^ s];
-      memcpy(p, q, sizeof p);
-    }
-    total = (g == 0) ? p[0] : total + p[0];
-  }
-  return total;
+  for (int width = 128; width != 0; width >>= 1)
+    for (int t = 0; t < width; ++t) part[t] = part[t] + part[t + width];
+  return part[0];
 }
 
 static inline float rsqrt_cr(float v) {
@@ -292,6 +288,86 @@ void aima_or_topk_decode(const float* logits, int32_t* ids, float* scores,
   softmax8(sv, scores, weights);
 }
 
+
+/* ----------------------------------------------------------------------- */
+/* Pointwise stages, one function per reference kernel so that each can be   */
+/* compared with that kernel compiled from the reference checkout.           */
+/* ----------------------------------------------------------------------- */
+
+/* shared_silu_multiply_batched_kernel (native_moe_prefill.hip.cpp:210-219) and
+ * shared_activation_kernel (native_pointwise.hip.cpp:184-194): SiLU is NOT
+ * rounded before the multiply. */
+void aima_or_shared_silu_mul(const uint16_t* gate, const uint16_t* up,
+                             uint16_t* out, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    out[i] = f2bf(silu_f32(bf2f(gate[i])) * bf2f(up[i]));
+}
+
+/* shared_sigmoid_scale_batched_kernel (native_moe_prefill.hip.cpp:221-232) and
+ * shared_gate_kernel (native_pointwise.hip.cpp:196-205):
+ * out = bf16(bf16(sigmoid(gate[token])) * down). */
+void aima_or_sigmoid_scale(const uint16_t* gate, const uint16_t* down,
+                           uint16_t* out, size_t tokens) {
+  for (size_t t = 0; t < tokens; ++t) {
+    const float sig = bf2f(f2bf(sigmoid_f32(bf2f(gate[t]))));
+    for (int h = 0; h < AIMA_H; ++h)
+      out[t * AIMA_H + h] = f2bf(sig * bf2f(down[t * AIMA_H + h]));
+  }
+}
+
+/* expert_silu_multiply_kernel (native_moe_prefill.hip.cpp:384-402):
+ * gate_up [rows, 1024] -> act [rows, 512], SiLU rounded to BF16 first. */
+void aima_or_expert_silu_mul(const uint16_t* gate_up, uint16_t* act, size_t rows) {
+  for (size_t r = 0; r < rows; ++r)
+    for (int i = 0; i < AIMA_I; ++i) {
+      const float g = bf2f(gate_up[r * 2 * AIMA_I + i]);
+      const float u = bf2f(gate_up[r * 2 * AIMA_I + AIMA_I + i]);
+      act[r * AIMA_I + i] = f2bf(bf2f(f2bf(silu_f32(g))) * u);
+    }
+}
+
+/* moe_sum8_kernel (native_moe_prefill.hip.cpp:404-431): [tokens, 8, 2048] ->
+ * [tokens, 2048], FP32 tree (((r0+r4)+(r1+r5))+(r2+r6))+(r3+r7). */
+void aima_or_sum8(const uint16_t* in, uint16_t* out, size_t tokens) {
+  for (size_t t = 0; t < tokens; ++t) {
+    const uint16_t* s = in + t * AIMA_K * AIMA_H;
+    for (int h = 0; h < AIMA_H; ++h) {
+      const float s04 = bf2f(s[h]) + bf2f(s[4 * AIMA_H + h]);
+      const float s15 = bf2f(s[AIMA_H + h]) + bf2f(s[5 * AIMA_H + h]);
+      const float s26 = bf2f(s[2 * AIMA_H + h]) + bf2f(s[6 * AIMA_H + h]);
+      const float s37 = bf2f(s[3 * AIMA_H + h]) + bf2f(s[7 * AIMA_H + h]);
+      float sum = s04 + s15;
+      sum = sum + s26;
+      sum = sum + s37;
+      out[t * AIMA_H + h] = f2bf(sum);
+    }
+  }
+}
+
+/* bf16_add_pair_kernel (native/src/native_pointwise.hip.cpp:94-107). */
+void aima_or_add_pair(const uint16_t* left, const uint16_t* right,
+                      const uint16_t* residual, uint16_t* intermediate,
+                      uint16_t* out, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    const uint16_t combined = f2bf(bf2f(left[i]) + bf2f(right[i]));
+    if (intermediate) intermediate[i] = combined;
+    out[i] = f2bf(bf2f(residual[i]) + bf2f(combined));
+  }
+}
+
+/* router_topk8_softmax_256_kernel over `tokens` rows of BF16 logits. */
+void aima_or_topk_prefill_rows(const uint16_t* logits, int tokens, int32_t* ids,
+                               float* scores, uint16_t* weights) {
+  for (int t = 0; t < tokens; ++t) {
+    float row[AIMA_E];
+    for (int e = 0; e < AIMA_E; ++e) row[e] = bf2f(logits[(size_t)t * AIMA_E + e]);
+    aima_or_topk_prefill(row, ids + (size_t)t * AIMA_K, scores + (size_t)t * AIMA_K,
+                         weights + (size_t)t * AIMA_K);
+  }
+}
+
+float aima_or_rsqrt(float v) { return rsqrt_cr(v); }
+
 /* ----------------------------------------------------------------------- */
 /* Layer weights in checkpoint layout                                       */
 /* (doc/reference/amd395-qwen36-35b-a3b-bf16/qwen36-shape-manifest.json:162-180)
@@ -328,20 +404,15 @@ typedef struct {
 static void shared_expert(const uint16_t* h2, const aima_or_layer* L,
                           uint16_t* shared_scaled) {
   const uint16_t gate_logit = f2bf(aima_or_dot(h2, L->shared_gate, AIMA_H));
-  uint16_t act[AIMA_SI];
+  uint16_t gate[AIMA_SI], up[AIMA_SI], act[AIMA_SI], down[AIMA_H];
   for (int i = 0; i < AIMA_SI; ++i) {
-    const float g = bf2f(f2bf(aima_or_dot(
-        h2, L->shared_gate_proj + (size_t)i * AIMA_H, AIMA_H)));
-    const float u = bf2f(f2bf(aima_or_dot(
-        h2, L->shared_up_proj + (size_t)i * AIMA_H, AIMA_H)));
-    act[i] = f2bf(silu_f32(g) * u);
+    gate[i] = f2bf(aima_or_dot(h2, L->shared_gate_proj + (size_t)i * AIMA_H, AIMA_H));
+    up[i] = f2bf(aima_or_dot(h2, L->shared_up_proj + (size_t)i * AIMA_H, AIMA_H));
   }
-  const float sig = bf2f(f2bf(sigmoid_f32(bf2f(gate_logit))));
-  for (int h = 0; h < AIMA_H; ++h) {
-    const float d = bf2f(f2bf(aima_or_dot(
-        act, L->shared_down_proj + (size_t)h * AIMA_SI, AIMA_SI)));
-    shared_scaled[h] = f2bf(sig * d);
-  }
+  aima_or_shared_silu_mul(gate, up, act, AIMA_SI);
+  for (int h = 0; h < AIMA_H; ++h)
+    down[h] = f2bf(aima_or_dot(act, L->shared_down_proj + (size_t)h * AIMA_SI, AIMA_SI));
+  aima_or_sigmoid_scale(&gate_logit, down, shared_scaled, 1);
 }
 
 /* Decode MoE half of one layer for ONE token.
@@ -438,15 +509,11 @@ int aima_or_prefill_layer(const uint16_t* h2_all, const uint16_t* residual_all,
 
     uint16_t* slot_out = (uint16_t*)malloc(sizeof(uint16_t) * AIMA_K * AIMA_H);
     for (int r = 0; r < AIMA_K; ++r) {
+      uint16_t gate_up[2 * AIMA_I];
       uint16_t act[AIMA_I];
-      for (int i = 0; i < AIMA_I; ++i) {
-        const uint16_t* wg = L->gate_up[ids[r]] + (size_t)i * AIMA_H;
-        const uint16_t* wu = wg + (size_t)AIMA_I * AIMA_H;
-        const float g = bf2f(f2bf(aima_or_dot(h2, wg, AIMA_H)));
-        const float u = bf2f(f2bf(aima_or_dot(h2, wu, AIMA_H)));
-        const float silu = bf2f(f2bf(silu_f32(g)));
-        act[i] = f2bf(silu * u);
-      }
+      for (int i = 0; i < 2 * AIMA_I; ++i)
+        gate_up[i] = f2bf(aima_or_dot(h2, L->gate_up[ids[r]] + (size_t)i * AIMA_H, AIMA_H));
+      aima_or_expert_silu_mul(gate_up, act, 1);
       const float wr = bf2f(weights[r]);
       for (int h = 0; h < AIMA_H; ++h) {
         const float d = aima_or_dot(act, L->down[ids[r]] + (size_t)h * AIMA_I,
@@ -455,18 +522,8 @@ int aima_or_prefill_layer(const uint16_t* h2_all, const uint16_t* residual_all,
       }
     }
     uint16_t routed[AIMA_H];
-    for (int h = 0; h < AIMA_H; ++h) {
-      const float s04 = bf2f(slot_out[h]) + bf2f(slot_out[4 * AIMA_H + h]);
-      const float s15 = bf2f(slot_out[AIMA_H + h]) + bf2f(slot_out[5 * AIMA_H + h]);
-      const float s26 = bf2f(slot_out[2 * AIMA_H + h]) + bf2f(slot_out[6 * AIMA_H + h]);
-      const float s37 = bf2f(slot_out[3 * AIMA_H + h]) + bf2f(slot_out[7 * AIMA_H + h]);
-      float sum = s04 + s15;
-      sum = sum + s26;
-      sum = sum + s37;
-      routed[h] = f2bf(sum);
-      const float combined = bf2f(f2bf(bf2f(routed[h]) + bf2f(shared_scaled[h])));
-      out[(size_t)s * AIMA_H + h] = f2bf(bf2f(resid[h]) + combined);
-    }
+    aima_or_sum8(slot_out, routed, 1);
+    aima_or_add_pair(routed, shared_scaled, resid, NULL, out + (size_t)s * AIMA_H, AIMA_H);
     free(slot_out);
     if (dbg != NULL) {
       if (dbg->h2) memcpy(dbg->h2 + (size_t)s * AIMA_H, h2, sizeof(uint16_t) * AIMA_H);
