@@ -9,6 +9,7 @@
 #pragma once
 
 #include <cstdlib>
+#include <mutex>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -326,6 +327,25 @@ inline int pdl_max_tokens() {
     return (v != nullptr && v[0] != '\0') ? std::atoi(v) : 2048;
   }();
   return limit;
+}
+
+
+// Opt-in of one kernel to more than 48 KB of dynamic shared memory.  The attribute belongs to the
+// (function, device) pair, so it is set once per device the calling thread has made current -- a
+// process may drive several GPUs -- under a mutex, because several host threads may launch at once.
+template <auto Kernel>
+inline cudaError_t opt_in_dynamic_smem(int bytes) {
+  static std::mutex mutex;
+  static unsigned long long done[4] = {0, 0, 0, 0};      // one bit per device ordinal
+  int device = -1;
+  cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) return error;
+  std::lock_guard<std::mutex> lock(mutex);
+  const bool tracked = device >= 0 && device < 256;
+  if (tracked && ((done[device >> 6] >> (device & 63)) & 1ull) != 0ull) return cudaSuccess;
+  error = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (error == cudaSuccess && tracked) done[device >> 6] |= 1ull << (device & 63);
+  return error;
 }
 
 template <typename... KernelArgs, typename... Args>

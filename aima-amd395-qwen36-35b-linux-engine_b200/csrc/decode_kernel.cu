@@ -9,29 +9,40 @@
 // 1152-1220 and native/src/native_pointwise.hip.cpp:94-107, 184-205.
 //
 // Structure.  One block per SM, 16 warps.  Warp 15 is a producer that streams
-// weight rows from HBM into ONE ring of 24 shared-memory slots of 8 KB with 1-D
-// bulk (TMA) copies; warps 1-12 consume them with the canonical warp dot
-// product (slot s always belongs to warp 1 + s % 12); warp 0 runs the exchanges
-// between blocks, the top-8 and the layer plan; warp 13 predicts the next
-// layer's experts.  The kernel is bandwidth bound (57.7 MB of weights per layer
-// for ~30 MFLOP) but its layer is a serial chain of three grid-wide hand-overs,
-// so everything is arranged to keep bulk copies in flight across them.  Items
+// weights from HBM into ONE ring of 6 shared-memory slots of 32 KB (two halves
+// of 16 KB) with 1-D bulk (TMA) copies; warps 1-12 consume them with the
+// canonical warp dot product, as three groups of four warps (slot s always
+// belongs to group s % 3, its up to four rows or row pairs to the group's four
+// warps); warp 0 runs the exchanges between blocks, the top-8 and the layer
+// plan; warp 13 predicts the next layer's experts.  The kernel is bandwidth
+// bound (57.7 MB of weights per layer for ~30 MFLOP) but its layer is a serial
+// chain of three grid-wide hand-overs, so everything is arranged to keep bulk
+// copies in flight across them.
+//
+// A bulk copy costs its issuing thread and the copy engine a fixed time whatever
+// its size (one lane sustains about 8 copies of 4 KB per microsecond, 33 GB/s per
+// SM, 4.9 TB/s over the chip: measured, and what an earlier version of this
+// kernel that copied row by row was bound by), so every block is dealt
+// CONTIGUOUS rows and fetches them 12-16 KB at a time, two lanes issuing.  Items
 // of a layer pass through the ring in this order:
 //
-//   R   router rows c, c+G of this layer; the same two rows of the NEXT layer's
-//       router (prediction, see below); the block's share of the 512
-//       shared-expert input pairs; the shared gate row
-//   B   "blind" pairs: gate/up row pairs of the experts PREDICTED for this layer,
-//       requested while the chain of the previous layer is still running
+//   R1  router rows 2c, 2c+1 of this layer (half A) and the same two rows of the
+//       NEXT layer's router (half B; prediction, see below); block 128 instead
+//       carries the shared expert's gate row
+//   R2  the block's 3-4 contiguous rows of the shared expert's gate (A) and up (B)
+//       projections
+//   B   "blind" chunks: for each of the 8 expert positions the block's 3-4
+//       contiguous gate rows (A) and up rows (B) of the expert PREDICTED for that
+//       position, requested while the chain of the previous layer is still running
 //   --- logits exchange: every logit travels as one 64-bit word {tag, value};
 //       warp 0 of every block polls the 256 words, takes the top-8, freezes the
 //       blind issue and publishes the layer plan (which predicted positions hold
 //       a chosen expert, which chosen experts still have to be fetched)
-//   P   the pairs not covered by a valid blind item, with the real experts
-//   D   the block's slice of the down projection: shared expert and every chosen
-//       expert, two items of <= 7 rows each
+//   P   the chunks not covered by a valid blind item, with the real experts
+//   D   the block's <= 14 rows of the down projections, two experts per item
+//       (shared expert first)
 //   --- grid barrier: all SwiGLU activations known
-//       down products for the block's <= 14 output elements from the D items,
+//       down products for the block's output elements from the D items,
 //       weighted sum, shared expert, residual add
 //   --- output exchange: the 2048 outputs travel as 32-bit words {tag, bf16};
 //       four warps of every block poll them into shared memory
@@ -55,21 +66,25 @@
 namespace aima {
 namespace {
 
-// Item i always lands in slot i % kRingSlots and is always consumed by warp
-// 1 + (i % kRingSlots) % kStreamWarps: a parity wait on an mbarrier is only
-// meaningful when the waiter is at most one phase behind, so consecutive uses
-// of a slot must be consumed in order by one warp.
-constexpr int kRingSlots = 24;
-constexpr int kStreamWarps = 12;
+// Item i always lands in slot i % kRingSlots and is always consumed by warp group
+// (i % kRingSlots) % kGroups: a parity wait on an mbarrier is only meaningful when
+// the waiter is at most one phase behind, so consecutive uses of a slot must be
+// consumed in order by the same warps.  Every warp of the group waits for and
+// releases every item of its slots, whether it has a row of it or not.
+constexpr int kRingSlots = 6;
+constexpr int kGroups = 3;
+constexpr int kGroupWarps = 4;
+constexpr int kStreamWarps = kGroups * kGroupWarps;
 constexpr int kFirstStreamWarp = 1;
 constexpr int kPredictWarp = 13;
 constexpr int kProducerWarp = 15;
-constexpr int kSlotBytes = 8192;               // two 4 KB weight rows, or <= 7 down rows of 1 KB
+constexpr int kHalfBytes = 16384;              // <= 4 weight rows of 4 KB, or <= 14 down rows of 1 KB
+constexpr int kSlotBytes = 2 * kHalfBytes;
 constexpr int kRowBytes = kHidden * 2;         // 4096
 constexpr int kDownRowBytes = kInter * 2;      // 1024
 constexpr int kDotsStride = 12;
 constexpr int kPositions = kTopK;              // ring positions a layer's experts are dealt to
-constexpr int kListEntries = 4 * kPositions;   // per block: at most 4 pairs of each position
+constexpr int kRouterBlocks = kExperts / 2;    // blocks 0 .. 127 hold two router rows each, block 128 the shared gate row
 constexpr unsigned kFrozen = 0x10000u;
 
 // shared-memory map (bytes)
@@ -86,9 +101,12 @@ constexpr int kBarCount = 2 * kRingSlots + 1;
 constexpr int kSmemTotal = kOffBars + kBarCount * 8;
 static_assert(kSmemTotal <= 227 * 1024, "decode kernel shared memory exceeds 227 KB");
 static_assert(kSmemTotal == kDecodeSmemBytes, "keep decode_kernel.cuh in step");
-static_assert((kDecodeMaxRowsPerBlock + 1) / 2 * kDownRowBytes <= kSlotBytes, "a down item must fit a slot");
+static_assert(kDecodeMaxRowsPerBlock * kDownRowBytes <= kHalfBytes, "a block's down rows of one expert must fit half a slot");
+static_assert((kInter + kDecodeMinBlocks - 1) / kDecodeMinBlocks <= kGroupWarps, "a chunk has at most one row per warp of a group");
+static_assert(kGroupWarps * kRowBytes <= kHalfBytes, "a chunk of weight rows must fit half a slot");
 static_assert(kFirstStreamWarp + kStreamWarps <= kDecodeConsumerWarps, "stream warps are consumer warps");
-static_assert(kRingSlots % kStreamWarps == 0, "every stream warp owns the same number of slots");
+static_assert(kRingSlots % kGroups == 0, "every group owns the same number of slots");
+static_assert(kDecodeMinBlocks > kRouterBlocks, "block 128 must exist: it carries the shared gate row");
 
 struct Misc {
   int ids[kTopK];                 // selected experts in selection order (rank r)
@@ -103,12 +121,12 @@ struct Misc {
   int n_active;
   unsigned active_mask;           // bit q: position q carries a chosen expert
   unsigned valid_mask;            // bit q: the blind items of position q hold that expert's rows
-  int n_blind;                    // list entries [0, n_blind) were handled blind
+  int n_blind;                    // positions [0, n_blind) were handled blind
   volatile int plan_layer;        // (layer ordinal + 1) the plan above belongs to
   // ---- prediction ----
   int pred[2][kPositions];        // predicted experts of layer ordinal li at [li & 1], -1: not held here
   volatile int pred_layer;        // predictions are published for all layer ordinals < pred_layer
-  unsigned blind_state[2];        // [li & 1]: list entries claimed blind so far | kFrozen
+  unsigned blind_state[2];        // [li & 1]: positions claimed blind so far | kFrozen
   volatile int abort_flag;        // block-local copy of a raised status
   volatile int decision;          // block-uniform "keep going" verdict (see uniform_alive)
 };
@@ -223,21 +241,15 @@ __device__ __forceinline__ void st_strong_u32(void* p, uint32_t v) {
   asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
 
-// Number of shared-expert input pairs block c owns: i = c, c+G, ... < 512.
-__device__ __forceinline__ int shared_pairs_of(int c, int G) {
-  return c < kSharedInter ? (kSharedInter - 1 - c) / G + 1 : 0;
-}
-
-// The pairs of one expert position are dealt round-robin over the blocks, starting at a block that
-// depends on the position, so that every block holds 3 or 4 pairs of EVERY position (27 or 28 in all
-// at 148 blocks) whatever experts the positions carry.  List entry k = 8 j + q is the j-th pair of
-// position q in this block; returns its row index inside the expert, >= kInter when it does not exist.
-__device__ __forceinline__ int list_entry_row(int k, int c, int G) {
-  const int q = k & (kPositions - 1);
-  const int j = k >> 3;
-  int first = c + (q * G) / kPositions;
-  if (first >= G) first -= G;
-  return first + j * G;
+// The 512 rows of a projection are dealt to the blocks as contiguous ranges of 3 or 4 (at 148 blocks):
+// range b covers rows [512 b / G, 512 (b + 1) / G).  For the routed experts the range a block takes
+// depends on the expert position, so that every block holds 27 or 28 rows in all whatever experts
+// the positions carry.
+__device__ __forceinline__ int range_lo(int b, int G) { return (b * kInter) / G; }
+__device__ __forceinline__ int position_range(int q, int c, int G) {
+  int b = c + (q * G) / kPositions;
+  if (b >= G) b -= G;
+  return b;
 }
 
 // Iterative arg-max over 256 keys (8 per lane: key q of lane l belongs to expert 32 q + l), ties to
@@ -291,11 +303,12 @@ moe_decode_persistent_kernel(const DecodeParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRingSlots; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(empty_bar(s), kGroupWarps);
     }
     mbar_init(norm_bar, 1);
     // every ring slot starts out released: complete phase 0 of its empty barrier
-    for (int s = 0; s < kRingSlots; ++s) mbar_arrive(empty_bar(s));
+    for (int s = 0; s < kRingSlots; ++s)
+      for (int m = 0; m < kGroupWarps; ++m) mbar_arrive(empty_bar(s));
     misc->plan_layer = 0;
     misc->pred_layer = 1;          // layer ordinal 0 has no prediction: nothing to wait for
     misc->blind_state[0] = 0u;
@@ -312,9 +325,11 @@ moe_decode_persistent_kernel(const DecodeParams p) {
   const int h1 = ((c + 1) * kHidden) / G;
   const int nh = h1 - h0;
   const int half_rows = (nh + 1) / 2;
-  const int eb = c + G;                       // second router row of this block
-  const int n_shared_pairs = shared_pairs_of(c, G);
-  const bool owns_gate_row = (c == G - 1);
+  const bool has_router_rows = c < kRouterBlocks;          // router rows 2c, 2c + 1
+  const bool owns_gate_row = (c == kRouterBlocks);         // shared expert's gate row
+  const bool has_r1 = has_router_rows || owns_gate_row;
+  const int sh_lo = range_lo(c, G);                        // shared-expert input rows [sh_lo, sh_hi)
+  const int sh_rows = range_lo(c + 1, G) - sh_lo;
   const bool speculate = p.speculate != 0;
   const unsigned long long bar_base = *p.bar_base;
   const unsigned epoch0 = *p.epoch_base;      // exchange tag of layer ordinal li is epoch0 + li + 1
@@ -322,100 +337,107 @@ moe_decode_persistent_kernel(const DecodeParams p) {
 
   if (warp == kProducerWarp) {
     // ------------------------------ producer ------------------------------
-    if (lane == 0) {
+    // Lanes 0 and 1 walk the same item sequence; lane 0 announces an item's bytes and issues the
+    // copy into half A, lane 1 the copy into half B, so two copies are placed at a time.
+    if (lane < 2) {
+      constexpr unsigned kPair = 0x3u;
       unsigned seq = 0;
       unsigned issued[kRingSlots];
       for (int s = 0; s < kRingSlots; ++s) issued[s] = 0;
       unsigned norm_issued = 0;
       bool alive = true;
 
-      // acquire the ring slot of item `seq`; returns its address or 0
-      auto acquire = [&]() -> uint32_t {
+      // One item: `bytes_a` from src_a into half A, `bytes_b` from src_b into half B (either may be 0,
+      // not both).  Returns false after a failed wait (both lanes agree).
+      auto issue = [&](const void* src_a, uint32_t bytes_a, const void* src_b, uint32_t bytes_b) -> bool {
         const int s = seq % kRingSlots;
         const unsigned use = seq / kRingSlots;
         unsigned diag[4] = {0, 0, 0, 0};
-        if (!mbar_wait_bounded(empty_bar(s), use & 1u, abort_flag, diag)) {
-          if (*abort_flag == kStatusTimeoutMbarrier) {
-            atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
-            record_site(p, 1, static_cast<int>(seq), diag);
-          }
-          alive = false;
-          return 0u;
+        bool ok = mbar_wait_bounded(empty_bar(s), use & 1u, abort_flag, diag);
+        if (!ok && lane == 0 && *abort_flag == kStatusTimeoutMbarrier) {
+          atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
+          record_site(p, 1, static_cast<int>(seq), diag);
         }
-        return smem_u32(ring + s * kSlotBytes);
-      };
-      // one or two pieces into the slot of item `seq`
-      auto issue = [&](const void* src0, uint32_t bytes0, const void* src1, uint32_t bytes1) -> bool {
-        const uint32_t dst = acquire();
-        if (dst == 0u) return false;
-        const int s = seq % kRingSlots;
-        mbar_arrive_expect_tx(full_bar(s), bytes0 + bytes1);
-        bulk_g2s(dst, src0, bytes0, full_bar(s));
-        if (bytes1 != 0u) bulk_g2s(dst + bytes0, src1, bytes1, full_bar(s));
+        ok = __all_sync(kPair, ok);
+        if (!ok) { alive = false; return false; }
+        const uint32_t dst = smem_u32(ring + s * kSlotBytes);
+        if (lane == 0) mbar_arrive_expect_tx(full_bar(s), bytes_a + bytes_b);
+        __syncwarp(kPair);
+        if (lane == 0 && bytes_a != 0u) bulk_g2s(dst, src_a, bytes_a, full_bar(s));
+        if (lane == 1 && bytes_b != 0u) bulk_g2s(dst + kHalfBytes, src_b, bytes_b, full_bar(s));
         issued[s] = seq / kRingSlots + 1;
         ++seq;
         return true;
       };
       // bounded wait for a hand-over word in shared memory to reach `want`
       auto wait_word = [&](volatile int* word, int want, int code, int site, int detail) -> bool {
-        if (*word >= want) return true;
-        const unsigned long long start = global_timer_ns();
-        unsigned spins = 0;
-        while (*word < want) {
-          if ((++spins & 255u) == 0u) {
-            if (*abort_flag != 0) { alive = false; return false; }
-            if (global_timer_ns() - start > kWaitBudgetNs) {
-              raise_status(p, abort_flag, code);
-              record_site(p, site, detail);
-              alive = false;
-              return false;
+        bool ok = true;
+        if (*word < want) {
+          const unsigned long long start = global_timer_ns();
+          unsigned spins = 0;
+          while (*word < want) {
+            if ((++spins & 255u) == 0u) {
+              if (*abort_flag != 0) { ok = false; break; }
+              if (global_timer_ns() - start > kWaitBudgetNs) {
+                raise_status(p, abort_flag, code);
+                record_site(p, site, detail);
+                ok = false;
+                break;
+              }
             }
           }
         }
-        return true;
+        ok = __all_sync(kPair, ok);
+        if (!ok) alive = false;
+        return ok;
       };
 
       for (int li = 0; li < p.n_layers && alive; ++li) {
         const LayerPtrs L = p.layers[p.first_layer + li];
         const bool has_next = speculate && (li + 1 < p.n_layers);
-        auto issue_pair = [&](int expert, int row) -> bool {
-          const __nv_bfloat16* gate_row = L.expert_gate_up +
-              (static_cast<size_t>(expert - p.expert_lo) * (2 * kInter) + row) * kHidden;
-          return issue(gate_row, kRowBytes, gate_row + static_cast<size_t>(kInter) * kHidden, kRowBytes);
+        // the block's chunk of expert `expert` for position q: gate rows into half A, up rows into half B
+        auto issue_chunk = [&](int expert, int q) -> bool {
+          const int b = position_range(q, c, G);
+          const int lo = range_lo(b, G);
+          const uint32_t bytes = static_cast<uint32_t>(range_lo(b + 1, G) - lo) * kRowBytes;
+          const __nv_bfloat16* gate_rows = L.expert_gate_up +
+              (static_cast<size_t>(expert - p.expert_lo) * (2 * kInter) + lo) * kHidden;
+          return issue(gate_rows, bytes, gate_rows + static_cast<size_t>(kInter) * kHidden, bytes);
         };
         // ---- norm weight row into its own region (its readers finished before the plan of the
         //      previous layer was published, which this thread has waited for) ----
-        mbar_arrive_expect_tx(norm_bar, kRowBytes);
-        bulk_g2s(smem_u32(norm_s), L.norm_weight, kRowBytes, norm_bar);
+        if (lane == 0) {
+          mbar_arrive_expect_tx(norm_bar, kRowBytes);
+          bulk_g2s(smem_u32(norm_s), L.norm_weight, kRowBytes, norm_bar);
+        }
         norm_issued = li + 1;
-        // ---- R items: router rows, the next layer's router rows, shared input pairs, shared gate row ----
-        if (!issue(L.router + static_cast<size_t>(c) * kHidden, kRowBytes,
-                   L.router + static_cast<size_t>(eb < kExperts ? eb : c) * kHidden, eb < kExperts ? kRowBytes : 0u)) break;
-        if (has_next) {
-          const __nv_bfloat16* next_router = p.layers[p.first_layer + li + 1].router;
-          if (!issue(next_router + static_cast<size_t>(c) * kHidden, kRowBytes,
-                     next_router + static_cast<size_t>(eb < kExperts ? eb : c) * kHidden, eb < kExperts ? kRowBytes : 0u)) break;
+        // ---- R1: router rows (+ the next layer's), or the shared gate row; R2: shared input rows ----
+        if (has_r1) {
+          const __nv_bfloat16* src_a = has_router_rows ? L.router + static_cast<size_t>(2 * c) * kHidden : L.shared_gate;
+          const uint32_t bytes_a = has_router_rows ? 2 * kRowBytes : kRowBytes;
+          const bool predict_rows = has_next && has_router_rows;
+          const __nv_bfloat16* src_b =
+              predict_rows ? p.layers[p.first_layer + li + 1].router + static_cast<size_t>(2 * c) * kHidden : nullptr;
+          if (!issue(src_a, bytes_a, src_b, predict_rows ? 2 * kRowBytes : 0u)) break;
         }
-        for (int k = 0; k < n_shared_pairs && alive; ++k) {
-          const int i = c + k * G;
-          issue(L.shared_gate_proj + static_cast<size_t>(i) * kHidden, kRowBytes,
-                L.shared_up_proj + static_cast<size_t>(i) * kHidden, kRowBytes);
+        if (sh_rows > 0) {
+          if (!issue(L.shared_gate_proj + static_cast<size_t>(sh_lo) * kHidden, sh_rows * kRowBytes,
+                     L.shared_up_proj + static_cast<size_t>(sh_lo) * kHidden, sh_rows * kRowBytes)) break;
         }
-        if (!alive) break;
-        if (owns_gate_row && !issue(L.shared_gate, kRowBytes, nullptr, 0u)) break;
-        // ---- B items: pairs of the predicted experts, until the real routing is known ----
+        // ---- B items: chunks of the predicted experts, until the real routing is known ----
         if (speculate && li > 0) {
           if (!wait_word(&misc->pred_layer, li + 1, kStatusTimeoutIds, 10, li)) break;
           __threadfence_block();
           unsigned* state = &misc->blind_state[li & 1];
           while (alive) {
-            const unsigned ticket = atomicAdd(state, 1u);
-            if ((ticket & kFrozen) != 0u || ticket >= static_cast<unsigned>(kListEntries)) break;
-            const int k = static_cast<int>(ticket);
-            const int row = list_entry_row(k, c, G);
-            const int expert = misc->pred[li & 1][k & (kPositions - 1)];
-            if (row >= kInter || expert < 0) continue;
-            issue_pair(expert, row);
+            unsigned ticket = 0u;
+            if (lane == 0) ticket = atomicAdd(state, 1u);
+            ticket = __shfl_sync(kPair, ticket, 0);
+            if ((ticket & kFrozen) != 0u || ticket >= static_cast<unsigned>(kPositions)) break;
+            const int q = static_cast<int>(ticket);
+            const int expert = misc->pred[li & 1][q];
+            if (expert < 0) continue;
+            issue_chunk(expert, q);
           }
           if (!alive) break;
         }
@@ -425,40 +447,37 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         const int n_blind = misc->n_blind;
         const unsigned active_mask = misc->active_mask;
         const unsigned valid_mask = misc->valid_mask;
-        // ---- P items: entries not handled blind, then entries whose blind item holds the wrong expert ----
-        for (int k = n_blind; k < kListEntries && alive; ++k) {
-          const int q = k & (kPositions - 1);
-          const int row = list_entry_row(k, c, G);
-          if (row >= kInter || ((active_mask >> q) & 1u) == 0u) continue;
-          issue_pair(misc->expert_of_pos[q], row);
+        // ---- P items: positions not handled blind, then positions whose blind chunk holds the wrong expert ----
+        for (int q = n_blind; q < kPositions && alive; ++q) {
+          if (((active_mask >> q) & 1u) == 0u) continue;
+          issue_chunk(misc->expert_of_pos[q], q);
         }
-        for (int k = 0; k < n_blind && alive; ++k) {
-          const int q = k & (kPositions - 1);
-          const int row = list_entry_row(k, c, G);
-          if (row >= kInter || ((active_mask >> q) & 1u) == 0u || ((valid_mask >> q) & 1u) != 0u) continue;
-          issue_pair(misc->expert_of_pos[q], row);
+        for (int q = 0; q < n_blind && alive; ++q) {
+          if (((active_mask >> q) & 1u) == 0u || ((valid_mask >> q) & 1u) != 0u) continue;
+          issue_chunk(misc->expert_of_pos[q], q);
         }
         if (!alive) break;
-        // ---- D items: the block's rows of the down projections, shared expert first ----
-        const uint32_t bytes_lo = half_rows * kDownRowBytes;
-        const uint32_t bytes_hi = (nh - half_rows) * kDownRowBytes;
-        {
-          const __nv_bfloat16* src = L.shared_down_proj + static_cast<size_t>(h0) * kInter;
-          if (!issue(src, bytes_lo, nullptr, 0u)) break;
-          if (!issue(src + static_cast<size_t>(half_rows) * kInter, bytes_hi, nullptr, 0u)) break;
-        }
+        // ---- D items: the block's rows of the down projections, two experts per item, shared expert first ----
+        const uint32_t down_bytes = static_cast<uint32_t>(nh) * kDownRowBytes;
         const int n_active = misc->n_active;
-        for (int a = 0; a < n_active && alive; ++a) {
-          const int expert = misc->expert_of_pos[misc->active_pos[a]];
-          const __nv_bfloat16* src = L.expert_down +
-              (static_cast<size_t>(expert - p.expert_lo) * kHidden + h0) * kInter;
-          if (!issue(src, bytes_lo, nullptr, 0u)) break;
-          issue(src + static_cast<size_t>(half_rows) * kInter, bytes_hi, nullptr, 0u);
+        for (int e = 0; e < 1 + n_active && alive; e += 2) {
+          const __nv_bfloat16* src[2] = {nullptr, nullptr};
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const int entry = e + k;
+            if (entry == 0) {
+              src[k] = L.shared_down_proj + static_cast<size_t>(h0) * kInter;
+            } else if (entry <= n_active) {
+              const int expert = misc->expert_of_pos[misc->active_pos[entry - 1]];
+              src[k] = L.expert_down + (static_cast<size_t>(expert - p.expert_lo) * kHidden + h0) * kInter;
+            }
+          }
+          issue(src[0], down_bytes, src[1], src[1] != nullptr ? down_bytes : 0u);
         }
       }
-      // Drain: every copy this thread issued must have landed before the block
+      // Drain: every copy these lanes issued must have landed before the block
       // may exit (bounded; a phase that already completed returns at once).
-      if (*abort_flag != 0) {
+      if (*abort_flag != 0 && lane == 0) {
         for (int s = 0; s < kRingSlots; ++s) {
           if (issued[s] != 0) {
             volatile int ignore = 0;
@@ -535,12 +554,14 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     // ------------------------------ consumers -----------------------------
     const int ctid = threadIdx.x;                 // 0 .. 415
     const bool streams = warp >= kFirstStreamWarp && warp < kFirstStreamWarp + kStreamWarps;
+    const int group = streams ? (warp - kFirstStreamWarp) / kGroupWarps : -1;
+    const int member = streams ? (warp - kFirstStreamWarp) % kGroupWarps : -1;
     unsigned seq = 0;                             // mirrors the producer's item counter
     unsigned long long nbar = 0;
     bool alive = true;
 
     auto owns = [&](unsigned item) -> bool {
-      return kFirstStreamWarp + static_cast<int>((item % kRingSlots) % kStreamWarps) == warp;
+      return static_cast<int>((item % kRingSlots) % kGroups) == group;
     };
     // wait for item `item`, return slot pointer (nullptr on abort)
     auto wait_item = [&](unsigned item, int site) -> const uint8_t* {
@@ -560,12 +581,18 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(item % kRingSlots));
     };
-    // two canonical 2048-dots of the register-resident vector against the two
-    // rows of a slot
-    auto pair_dot = [&](const uint8_t* slot, const float* xr, float& a, float& b) {
+    // canonical 2048-dot of the register-resident vector against one row / two rows at once
+    auto row_dot = [&](const uint8_t* row, const float* xr) -> float {
+      float a = 0.0f;
+      const uint4* r0 = reinterpret_cast<const uint4*>(row) + lane;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a = fma8(xr + 8 * i, r0[i * 32], a);
+      return butterfly_sum(a);
+    };
+    auto pair_dot = [&](const uint8_t* row_a, const uint8_t* row_b, const float* xr, float& a, float& b) {
       a = 0.0f; b = 0.0f;
-      const uint4* r0 = reinterpret_cast<const uint4*>(slot) + lane;
-      const uint4* r1 = reinterpret_cast<const uint4*>(slot + kRowBytes) + lane;
+      const uint4* r0 = reinterpret_cast<const uint4*>(row_a) + lane;
+      const uint4* r1 = reinterpret_cast<const uint4*>(row_b) + lane;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const uint4 w0 = r0[i * 32];
@@ -693,45 +720,58 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       }
 
       stamp(li, 1);
-      // ---- R items ----
-      const int n_r_items = 1 + (has_next ? 1 : 0) + n_shared_pairs + (owns_gate_row ? 1 : 0);
-      const int first_shared = 1 + (has_next ? 1 : 0);
-      for (int k = 0; k < n_r_items && alive; ++k) {
-        const unsigned item = seq + k;
-        if (!owns(item)) continue;
-        const uint8_t* slot = wait_item(item, 2);
-        if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; break; }
-        float a, b;
-        pair_dot(slot, xr, a, b);
-        release_item(item);
-        if (lane == 0) {
-          if (k < first_shared) {
-            // k = 0: this layer's logits; k = 1: the next layer's router on the same input
-            unsigned long long* dst = (k == 0) ? p.logits : pred_logits;
-            const float v0 = hooked_logit(a, c);
-            const float v1 = eb < kExperts ? hooked_logit(b, eb) : 0.0f;
-            const unsigned long long tag = static_cast<unsigned long long>(epoch0 + li + 1) << 32;
+      // ---- R1: warp m of the group takes row m of {router 2c, router 2c+1, next router 2c, next router 2c+1};
+      //      in block 128 warp 0 takes the shared gate row ----
+      if (has_r1) {
+        const unsigned item = seq++;
+        if (streams && owns(item) && alive) {
+          const uint8_t* slot = wait_item(item, 2);
+          if (!__all_sync(0xffffffffu, slot != nullptr)) alive = false;
+          if (alive) {
+            const bool predicted = member >= 2;
+            const bool has_row = has_router_rows ? (!predicted || has_next) : (member == 0);
+            float v = 0.0f;
+            if (has_row) v = row_dot(slot + (predicted ? kHalfBytes : 0) + (member & 1) * kRowBytes, xr);
+            release_item(item);
+            if (has_row && lane == 0) {
+              if (has_router_rows) {
+                const int expert = 2 * c + (member & 1);
+                unsigned long long* dst = predicted ? pred_logits : p.logits;
+                const unsigned long long word =
+                    (static_cast<unsigned long long>(epoch0 + li + 1) << 32) | __float_as_uint(hooked_logit(v, expert));
 #pragma unroll
-            for (int rep = 0; rep < kDecodeReplicas; ++rep) {
-              st_strong_u64(dst + rep * kExperts + c, tag | __float_as_uint(v0));
-              if (eb < kExperts) st_strong_u64(dst + rep * kExperts + eb, tag | __float_as_uint(v1));
+                for (int rep = 0; rep < kDecodeReplicas; ++rep) st_strong_u64(dst + rep * kExperts + expert, word);
+              } else {
+                const float gate = round_bf16(v);
+#pragma unroll
+                for (int rep = 0; rep < kDecodeReplicas; ++rep)
+                  *reinterpret_cast<float*>(p.act + rep * kDecodeActStride + 9 * kInter) = gate;
+              }
             }
-          } else if (k < first_shared + n_shared_pairs) {
-            const int i = c + (k - first_shared) * G;
-            const float g = round_bf16(a);
-            const float u = round_bf16(b);
-            const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(g), u));
-#pragma unroll
-            for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + kTopK * kInter + i] = bits;
-          } else {
-            const float gate = round_bf16(a);
-#pragma unroll
-            for (int rep = 0; rep < kDecodeReplicas; ++rep)
-              *reinterpret_cast<float*>(p.act + rep * kDecodeActStride + 9 * kInter) = gate;
           }
         }
       }
-      seq += n_r_items;
+      // ---- R2: warp m takes shared-expert input pair sh_lo + m ----
+      if (sh_rows > 0) {
+        const unsigned item = seq++;
+        if (streams && owns(item) && alive) {
+          const uint8_t* slot = wait_item(item, 2);
+          if (!__all_sync(0xffffffffu, slot != nullptr)) alive = false;
+          if (alive) {
+            float a = 0.0f, b = 0.0f;
+            if (member < sh_rows) pair_dot(slot + member * kRowBytes, slot + kHalfBytes + member * kRowBytes, xr, a, b);
+            release_item(item);
+            if (member < sh_rows && lane == 0) {
+              const float g = round_bf16(a);
+              const float u = round_bf16(b);
+              const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(g), u));
+#pragma unroll
+              for (int rep = 0; rep < kDecodeReplicas; ++rep)
+                p.act[rep * kDecodeActStride + kTopK * kInter + sh_lo + member] = bits;
+            }
+          }
+        }
+      }
       stamp(li, 2);
 
       // ---- logits exchange + top-8 (ties to the lowest expert id) + softmax + layer plan, warp 0 ----
@@ -787,14 +827,14 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         int my_id;
         warp_top8(k, lane, my_score, my_id);
         // The routing is known: stop the blind issue.  The value the counter held says exactly how many
-        // list entries the producer has claimed blind (it may still be placing the last of them).
+        // positions the producer has claimed blind (it may still be placing the last of them).
         unsigned claimed = 0u;
         if (lane == 0) {
           claimed = atomicOr(&misc->blind_state[li & 1], kFrozen) & (kFrozen - 1u);
           misc->blind_state[(li + 1) & 1] = 0u;      // nobody uses the other word before this layer's plan
         }
         claimed = __shfl_sync(0xffffffffu, claimed, 0);
-        const int n_blind = min(static_cast<int>(claimed), kListEntries);
+        const int n_blind = min(static_cast<int>(claimed), kPositions);
         // softmax over the eight: exp(s_r - s_0) / sum, summed in selection order
         const float top = __shfl_sync(0xffffffffu, my_score, 0);
         const float ex = det_expf(__fsub_rn(my_score, top));
@@ -805,9 +845,9 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         const bool local_expert = lane < kTopK && my_id >= p.expert_lo && my_id < p.expert_hi;
         const unsigned local_mask = __ballot_sync(0xffffffffu, local_expert);
         // ---- deal the chosen experts held here to the ring positions: an expert the prediction placed
-        //      at position q stays there (its blind items are valid); the others take the remaining
-        //      positions in ascending order ----
-        const int pred_q = (lane < kPositions && n_blind > 0) ? misc->pred[li & 1][lane] : -1;
+        //      at a position claimed blind stays there (its blind chunk is valid); the others take the
+        //      remaining positions in ascending order ----
+        const int pred_q = (lane < n_blind) ? misc->pred[li & 1][lane] : -1;
         int rank_q = -1;
 #pragma unroll
         for (int r = 0; r < kTopK; ++r) {
@@ -817,6 +857,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         const bool matched = lane < kPositions && rank_q >= 0;
         const unsigned valid_mask = __ballot_sync(0xffffffffu, matched);
         const unsigned matched_ranks = __reduce_or_sync(0xffffffffu, matched ? (1u << rank_q) : 0u);
+        // an expert predicted at a position that was NOT claimed blind may still be among the chosen:
+        // it simply has no valid chunk and is dealt like the others
         const unsigned free_pos = ((1u << kPositions) - 1u) & ~valid_mask;
         if (lane < kPositions && !matched) {
           unsigned left = local_mask & ~matched_ranks;
@@ -854,52 +896,46 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 4);
 
-      // ---- routed gate/up pairs of the experts held on this GPU ----
+      // ---- routed gate/up chunks of the experts held on this GPU: warp m takes pair m of a chunk ----
       const int n_local = misc->n_local;
       const int n_active = misc->n_active;
       const int n_blind = misc->n_blind;
       const unsigned active_mask = misc->active_mask;
       const unsigned valid_mask = misc->valid_mask;
       {
-        unsigned item = seq;
         // use == false: the slot holds rows of an expert that was not chosen; wait for them to land
         // (the copy must not be in flight when the slot is reused) and hand the slot back unread
-        auto consume_pair = [&](int q, int row, bool use) -> bool {
-          if (owns(item)) {
-            const uint8_t* slot = wait_item(item, 3);
-            if (!__all_sync(0xffffffffu, slot != nullptr)) return false;
-            float a = 0.0f, b = 0.0f;
-            if (use) pair_dot(slot, xr, a, b);
-            release_item(item);
-            if (use && lane == 0) {
-              const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), b));
-              const int slot_index = misc->rank_of_pos[q] * kInter + row;
+        auto consume_chunk = [&](int q, bool use) {
+          const unsigned item = seq++;
+          if (!streams || !owns(item) || !alive) return;
+          const uint8_t* slot = wait_item(item, 3);
+          if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; return; }
+          const int b = position_range(q, c, G);
+          const int lo = range_lo(b, G);
+          const int rows = range_lo(b + 1, G) - lo;
+          const bool mine = use && member < rows;
+          float a = 0.0f, bb = 0.0f;
+          if (mine) pair_dot(slot + member * kRowBytes, slot + kHalfBytes + member * kRowBytes, xr, a, bb);
+          release_item(item);
+          if (mine && lane == 0) {
+            const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), bb));
+            const int index = misc->rank_of_pos[q] * kInter + lo + member;
 #pragma unroll
-              for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + slot_index] = bits;
-            }
+            for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + index] = bits;
           }
-          ++item;
-          return true;
         };
-        for (int k = 0; k < n_blind && alive; ++k) {
-          const int q = k & (kPositions - 1);
-          const int row = list_entry_row(k, c, G);
-          if (row >= kInter || misc->pred_of_pos[q] < 0) continue;
-          alive = consume_pair(q, row, ((valid_mask >> q) & 1u) != 0u);
+        for (int q = 0; q < n_blind; ++q) {
+          if (misc->pred_of_pos[q] < 0) continue;
+          consume_chunk(q, ((valid_mask >> q) & 1u) != 0u);
         }
-        for (int k = n_blind; k < kListEntries && alive; ++k) {
-          const int q = k & (kPositions - 1);
-          const int row = list_entry_row(k, c, G);
-          if (row >= kInter || ((active_mask >> q) & 1u) == 0u) continue;
-          alive = consume_pair(q, row, true);
+        for (int q = n_blind; q < kPositions; ++q) {
+          if (((active_mask >> q) & 1u) == 0u) continue;
+          consume_chunk(q, true);
         }
-        for (int k = 0; k < n_blind && alive; ++k) {
-          const int q = k & (kPositions - 1);
-          const int row = list_entry_row(k, c, G);
-          if (row >= kInter || ((active_mask >> q) & 1u) == 0u || ((valid_mask >> q) & 1u) != 0u) continue;
-          alive = consume_pair(q, row, true);
+        for (int q = 0; q < n_blind; ++q) {
+          if (((active_mask >> q) & 1u) == 0u || ((valid_mask >> q) & 1u) != 0u) continue;
+          consume_chunk(q, true);
         }
-        seq = item;
       }
       stamp(li, 5);
       if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
@@ -914,40 +950,45 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       stamp(li, 7);
       stamp(li, 8);
       {
-        // item = (expert, half of the block's output rows): the activation row is unpacked once and up
-        // to seven dots against it share one eight-way reduction
-        const int n_items = 2 * (n_active + 1);
-        for (int unit = 0; unit < n_items && alive; ++unit) {
-          const unsigned item = seq + unit;
-          if (!owns(item)) continue;
+        // item = two experts (shared expert first); warps 0, 1 of the group take the halves of the first
+        // expert's rows, warps 2, 3 those of the second: the activation row is unpacked once and up to
+        // seven dots against it share one eight-way reduction
+        const int n_entries = 1 + n_active;
+        for (int e = 0; e < n_entries; e += 2) {
+          const unsigned item = seq++;
+          if (!streams || !owns(item) || !alive) continue;
           const uint8_t* slot = wait_item(item, 4);
-          if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; break; }
-          const int column = unit < 2 ? kTopK : misc->rank_of_pos[misc->active_pos[(unit - 2) >> 1]];
-          const int row_base = (unit & 1) * half_rows;
-          const int rows = (unit & 1) ? nh - half_rows : half_rows;
-          float af[16];
-          {
+          if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; continue; }
+          const int entry = e + (member >> 1);
+          const bool mine = entry < n_entries;
+          const int column = (entry == 0 || !mine) ? kTopK : misc->rank_of_pos[misc->active_pos[entry - 1]];
+          const int row_base = (member & 1) * half_rows;
+          const int rows = mine ? ((member & 1) ? nh - half_rows : half_rows) : 0;
+          float part[8];
+          if (mine) {
+            float af[16];
             const uint4* arow = reinterpret_cast<const uint4*>(act_s + column * kInter) + lane;
             unpack8(arow[0], af);
             unpack8(arow[32], af + 8);
-          }
-          float part[8];
+            const uint8_t* rows_ptr = slot + (member >> 1) * kHalfBytes + row_base * kDownRowBytes;
 #pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            float acc = 0.0f;
-            if (u < rows) {
-              const uint4* wrow = reinterpret_cast<const uint4*>(slot + u * kDownRowBytes) + lane;
-              acc = fma8(af, wrow[0], acc);
-              acc = fma8(af + 8, wrow[32], acc);
+            for (int u = 0; u < 8; ++u) {
+              float acc = 0.0f;
+              if (u < rows) {
+                const uint4* wrow = reinterpret_cast<const uint4*>(rows_ptr + u * kDownRowBytes) + lane;
+                acc = fma8(af, wrow[0], acc);
+                acc = fma8(af + 8, wrow[32], acc);
+              }
+              part[u] = acc;
             }
-            part[u] = acc;
           }
           release_item(item);
-          const float total = warp_reduce8(part, lane);
-          const int u = reduce8_slot(lane);
-          if ((lane & 3) == 0 && u < rows) dots[(row_base + u) * kDotsStride + column] = total;
+          if (mine) {
+            const float total = warp_reduce8(part, lane);
+            const int u = reduce8_slot(lane);
+            if ((lane & 3) == 0 && u < rows) dots[(row_base + u) * kDotsStride + column] = total;
+          }
         }
-        seq += n_items;
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 9);
@@ -1039,10 +1080,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
 
 cudaError_t launch_moe_decode(const DecodeParams& params, int grid_blocks,
                               cudaStream_t stream) {
-  // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the function
-  const cudaError_t e = cudaFuncSetAttribute(moe_decode_persistent_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kDecodeSmemBytes);
+  const cudaError_t e = opt_in_dynamic_smem<moe_decode_persistent_kernel>(kDecodeSmemBytes);
   if (e != cudaSuccess) return e;
   DecodeParams local = params;
   void* args[] = {&local};

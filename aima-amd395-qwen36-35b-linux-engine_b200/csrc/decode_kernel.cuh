@@ -17,7 +17,7 @@ constexpr int kDecodeThreads = 16 * 32;
 constexpr int kDecodeMaxRowsPerBlock = 14;
 constexpr int kDecodeMinBlocks = (kHidden + kDecodeMaxRowsPerBlock - 1) / kDecodeMaxRowsPerBlock;
 constexpr int kDecodeMaxBlocks = kExperts;  // router rows are dealt c, c + grid
-constexpr int kDecodeSmemBytes = 216120;
+constexpr int kDecodeSmemBytes = 215832;
 constexpr int kDecodeTraceStamps = 12;
 constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU expert-parallel exchange buffer
 // Everything all 148 blocks read back from global memory (router logits, the

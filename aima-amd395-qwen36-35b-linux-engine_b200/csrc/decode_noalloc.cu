@@ -104,8 +104,21 @@ int scratch_for_current_device(unsigned char** scratch, int* grid) {
   return AIMA_MOE_OK;
 }
 
-bool tensor_ok(const void* pointer, uint64_t bytes, uint64_t expected) {
-  return pointer != nullptr && bytes == expected && reinterpret_cast<uintptr_t>(pointer) % 16 == 0;
+// Null, size and alignment first; then residency: the kernel reads these pointers with bulk copies
+// and plain loads, so host memory or another GPU's memory must be turned away here, on the host,
+// with an error code -- not met on the device as a fault.  cudaPointerGetAttributes allocates nothing.
+bool resident_on(const void* pointer, int device) {
+  cudaPointerAttributes attributes{};
+  if (cudaPointerGetAttributes(&attributes, pointer) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  if (attributes.type == cudaMemoryTypeManaged) return true;
+  return attributes.type == cudaMemoryTypeDevice && attributes.device == device;
+}
+bool tensor_ok(const void* pointer, uint64_t bytes, uint64_t expected, int device) {
+  return pointer != nullptr && bytes == expected && reinterpret_cast<uintptr_t>(pointer) % 16 == 0 &&
+         resident_on(pointer, device);
 }
 
 }  // namespace
@@ -130,24 +143,34 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   if (in0 < out0 + kHidden * 2 && out0 < in0 + kHidden * 2)
     return noalloc_fail(AIMA_MOE_ERR_ALIAS, "x_out aliases x_in");
 
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return noalloc_fail(AIMA_MOE_ERR_NO_DEVICE, "no CUDA device is current");
+  }
+  if (!tensor_ok(x_in, kHidden * 2, kHidden * 2, device) || !tensor_ok(x_out, kHidden * 2, kHidden * 2, device))
+    return noalloc_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "x_in and x_out must be memory of the current device");
+  if (device_status != nullptr && !resident_on(device_status, device))
+    return noalloc_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "device_status must be memory of the current device");
+
   LayerTable table{};
   for (uint32_t i = 0; i < n_layers; ++i) {
     const aima_moe_layer_weights& w = layers[i];
     if (w.struct_bytes != sizeof(aima_moe_layer_weights))
       return noalloc_fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_layer_weights size mismatch");
     const bool ok =
-        tensor_ok(w.router, w.router_bytes, 2ull * kExperts * kHidden) &&
-        tensor_ok(w.expert_gate_up, w.expert_gate_up_bytes, 2ull * kExperts * 2 * kInter * kHidden) &&
-        tensor_ok(w.expert_down, w.expert_down_bytes, 2ull * kExperts * kHidden * kInter) &&
-        tensor_ok(w.shared_expert_gate, w.shared_expert_gate_bytes, 2ull * kHidden) &&
-        tensor_ok(w.shared_gate_proj, w.shared_gate_proj_bytes, 2ull * kSharedInter * kHidden) &&
-        tensor_ok(w.shared_up_proj, w.shared_up_proj_bytes, 2ull * kSharedInter * kHidden) &&
-        tensor_ok(w.shared_down_proj, w.shared_down_proj_bytes, 2ull * kHidden * kSharedInter) &&
-        tensor_ok(w.post_attention_norm, w.post_attention_norm_bytes, 2ull * kHidden);
+        tensor_ok(w.router, w.router_bytes, 2ull * kExperts * kHidden, device) &&
+        tensor_ok(w.expert_gate_up, w.expert_gate_up_bytes, 2ull * kExperts * 2 * kInter * kHidden, device) &&
+        tensor_ok(w.expert_down, w.expert_down_bytes, 2ull * kExperts * kHidden * kInter, device) &&
+        tensor_ok(w.shared_expert_gate, w.shared_expert_gate_bytes, 2ull * kHidden, device) &&
+        tensor_ok(w.shared_gate_proj, w.shared_gate_proj_bytes, 2ull * kSharedInter * kHidden, device) &&
+        tensor_ok(w.shared_up_proj, w.shared_up_proj_bytes, 2ull * kSharedInter * kHidden, device) &&
+        tensor_ok(w.shared_down_proj, w.shared_down_proj_bytes, 2ull * kHidden * kSharedInter, device) &&
+        tensor_ok(w.post_attention_norm, w.post_attention_norm_bytes, 2ull * kHidden, device);
     if (!ok)
       return noalloc_fail(AIMA_MOE_ERR_INVALID_ARGUMENT,
-                          "a layer tensor is null, misaligned or has the wrong byte size "
-                          "(all 256 experts and the norm weight are required)");
+                          "a layer tensor is null, misaligned, not memory of the current device or has the "
+                          "wrong byte size (all 256 experts and the norm weight are required)");
     LayerPtrs& e = table.entry[i];
     e.router = static_cast<const __nv_bfloat16*>(w.router);
     e.expert_gate_up = static_cast<const __nv_bfloat16*>(w.expert_gate_up);

@@ -483,13 +483,8 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, 
 
 template <int MODE, bool kGather = false>
 cudaError_t launch_mode(const TcMaps& maps, const TcProblem& pb, int grid, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(grouped_gemm_tc_kernel<MODE, kGather>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  const cudaError_t e = opt_in_dynamic_smem<grouped_gemm_tc_kernel<MODE, kGather>>(kTcSmemBytes);
+  if (e != cudaSuccess) return e;
   return launch_pdl(grouped_gemm_tc_kernel<MODE, kGather>, dim3(grid), dim3(kTcThreads), kTcSmemBytes, stream, maps, pb);
 }
 

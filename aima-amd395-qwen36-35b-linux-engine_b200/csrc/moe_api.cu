@@ -160,6 +160,18 @@ bool ranges_overlap(const void* a, size_t a_bytes, const void* b, size_t b_bytes
   return a0 < b0 + b_bytes && b0 < a0 + a_bytes;
 }
 
+// A handle's buffers, layer table and kernels' attributes belong to the device it was prepared on.
+int check_current_device(const aima_moe_handle* handle) {
+  int device = -1;
+  const cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaGetDevice");
+  if (device != handle->device)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT,
+                "the handle was prepared on device %d but device %d is current; make its device current first",
+                handle->device, device);
+  return AIMA_MOE_OK;
+}
+
 int reset_decode_sync(aima_moe_handle* handle) {
   // tags restart from zero, so every tagged word must be cleared with the counters
   cudaError_t error = cudaMemset(handle->decode_scratch, 0, kExchangeBytes);
@@ -176,6 +188,7 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
                         void* stream) {
   if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
   std::lock_guard<std::mutex> lock(handle->mutex);
+  if (const int wrong_device = check_current_device(handle); wrong_device != AIMA_MOE_OK) return wrong_device;
   if (x_in == nullptr || x_out == nullptr)
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "decode input/output is null");
   if (n_layers == 0 || first_layer >= handle->config.layers ||
@@ -371,6 +384,7 @@ AIMA_EXPORT int aima_moe_bind_layer(aima_moe_handle* handle, uint32_t layer,
                                     const aima_moe_layer_weights* weights) {
   if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
   std::lock_guard<std::mutex> lock(handle->mutex);
+  if (const int wrong_device = check_current_device(handle); wrong_device != AIMA_MOE_OK) return wrong_device;
   if (weights == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "weights is null");
   if (weights->struct_bytes != sizeof(aima_moe_layer_weights))
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "aima_moe_layer_weights size mismatch");
@@ -450,6 +464,7 @@ AIMA_EXPORT int aima_moe_prefill_launch(aima_moe_handle* handle, uint32_t layer,
                                         const aima_moe_debug_views* debug, void* stream) {
   if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
   std::lock_guard<std::mutex> lock(handle->mutex);
+  if (const int wrong_device = check_current_device(handle); wrong_device != AIMA_MOE_OK) return wrong_device;
   if (h2 == nullptr || residual == nullptr || out == nullptr)
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "prefill input/output is null");
   if (tokens == 0) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "tokens is zero");
@@ -503,6 +518,7 @@ AIMA_EXPORT int aima_moe_prefill_stack_launch(aima_moe_handle* handle, uint32_t 
                                               uint32_t tokens, void* stream) {
   if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
   std::lock_guard<std::mutex> lock(handle->mutex);
+  if (const int wrong_device = check_current_device(handle); wrong_device != AIMA_MOE_OK) return wrong_device;
   if (x_in == nullptr || x_out == nullptr)
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "prefill stack input/output is null");
   if (tokens == 0 || tokens > handle->config.max_prefill_tokens)
@@ -587,6 +603,7 @@ AIMA_EXPORT int aima_moe_prefill_fused_launch(aima_moe_handle* handle, uint32_t 
                                               void* stream) {
   if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
   std::lock_guard<std::mutex> lock(handle->mutex);
+  if (const int wrong_device = check_current_device(handle); wrong_device != AIMA_MOE_OK) return wrong_device;
   if (attn_out == nullptr || residual_in == nullptr || layer_out == nullptr)
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "fused prefill input/output is null");
   if ((next_norm_weight == nullptr) != (next_norm_out == nullptr))
@@ -665,6 +682,7 @@ AIMA_EXPORT int aima_moe_gemm_bf16_launch(aima_moe_handle* handle, const void* a
                                           void* d, uint32_t m, uint32_t n, uint32_t k, void* stream) {
   if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
   std::lock_guard<std::mutex> lock(handle->mutex);
+  if (const int wrong_device = check_current_device(handle); wrong_device != AIMA_MOE_OK) return wrong_device;
   if (a == nullptr || b == nullptr || d == nullptr)
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "gemm pointer is null");
   if (m == 0 || n == 0 || k == 0 || k % 64 != 0 || n % 8 != 0)

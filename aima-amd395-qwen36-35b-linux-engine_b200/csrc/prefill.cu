@@ -963,13 +963,8 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   const bool exact_router = ws->exact_router || (dbg != nullptr && dbg->router_logits != nullptr) ||
                             call.router_row_norms == nullptr;
   if (exact_router) {
-    static bool router_configured = false;
-    if (!router_configured) {
-      code = cudaFuncSetAttribute(prefill_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kRouterSmemBytes);
-      if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaFuncSetAttribute router");
-      router_configured = true;
-    }
+    code = opt_in_dynamic_smem<prefill_router_kernel>(kRouterSmemBytes);
+    if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaFuncSetAttribute router");
     prefill_router_kernel<<<(T + kRouterWarps - 1) / kRouterWarps, kRouterWarps * 32, kRouterSmemBytes, stream>>>(
         static_cast<const __nv_bfloat16*>(call.h2), call.layer.router, call.layer.shared_gate,
         call.router_bias, call.quant_eighths, T, ws->topk_ids, ws->topk_scores, ws->topk_weights,

@@ -261,8 +261,14 @@ int aima_moe_gemm_bf16_launch(aima_moe_handle* handle, const void* a, const void
  * copied to that device int32 on the stream after the kernel.
  *
  * The first call on each device resolves the address of the static array (the
- * device must be current); make that first call before starting any stream
- * capture.  All calls on a device share the one array and it keeps the previous
+ * device must be current) and, being the first use of the library's device code
+ * there, makes the driver load the module: that is when the driver places the
+ * array and the kernel image in device memory.  So make that first call early --
+ * before the host hands the remaining HBM to its own arenas, and before starting
+ * any stream capture.  Every tensor, x_in, x_out and device_status must be memory
+ * of the current device (checked on the host; nothing is enqueued otherwise).
+ * Without `device_status` a bounded wait that ran out goes unreported: the next
+ * call clears the status word.  All calls on a device share the one array and it keeps the previous
  * call's contents (the call clears the words that must start at zero), so two
  * calls whose kernels overlap on the GPU -- different streams, or different host
  * threads -- race with each other: issue them on one stream or order them with

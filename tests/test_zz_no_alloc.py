@@ -3,15 +3,22 @@
 aima_moe_decode_layers_noalloc serves hosts that may not allocate device memory while they run
 (all HBM already handed to their own arenas, or a request path on which cudaMalloc's device-wide
 synchronisation is not acceptable).  It must give the same bits as the handle-based
-aima_moe_decode_stack_launch, on two calls in a row (the second call reuses the static scratch
-array with the first call's contents in it), both in a fresh process and after the other tests.
+aima_moe_decode_stack_launch and as the CPU oracle, on two calls in a row (the second call reuses
+the static scratch array with the first call's contents in it), both in a fresh process and after
+the other tests; it must leave the amount of free device memory unchanged; and it must turn away
+memory that is not the current device's on the host, before anything is enqueued.
 """
 from __future__ import annotations
 
 import ctypes
+import sys
+from pathlib import Path
 
 import pytest
 import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "oracle"))
+import moe_oracle  # noqa: E402  (the checker)
 
 pytestmark = pytest.mark.gpu
 
@@ -32,6 +39,7 @@ def test_noalloc_decode_matches_the_handle_based_entry_point(package, layers):
         for layer, weights in enumerate(layers):
             provider.bind_layer(layer, weights)
         status = torch.full((1,), -1, dtype=torch.int32, device=device)
+        views = [moe_oracle.OracleLayer({name: tensor.cpu() for name, tensor in weights.items()}) for weights in layers]
         for call in range(2):
             x = package.synth.activations(SEED + call, 1, "residual", 0)[0].to(device)
             want = torch.empty_like(x)
@@ -42,6 +50,19 @@ def test_noalloc_decode_matches_the_handle_based_entry_point(package, layers):
             torch.cuda.synchronize()
             assert int(status.item()) == 0
             assert torch.equal(got, want), f"call {call}"          # bit-exact, as in the decode tests
+            # and against the CPU oracle, layer by layer
+            expected = x.cpu()
+            for view in views:
+                expected = moe_oracle.decode_layer(expected, view)["out"]
+            assert torch.equal(got.cpu(), expected), f"call {call}: differs from the oracle"
+            if call == 1:
+                # the documented property itself: a call (after the first one on the device) leaves the
+                # free device memory as it found it
+                free_before, _ = torch.cuda.mem_get_info()
+                package.provider.decode_layers_noalloc(layers, x, got, device_status=status)
+                torch.cuda.synchronize()
+                free_after, _ = torch.cuda.mem_get_info()
+                assert free_after == free_before
         # a single layer through the static scratch as well
         x = package.synth.activations(SEED + 7, 1, "residual", 0)[0].to(device)
         want = provider.decode_layer(x, 1)
@@ -71,3 +92,14 @@ def test_noalloc_decode_rejects_what_it_cannot_hold(package, layers):
     assert missing.value.status == -1
     lib = package.load_library()
     assert lib.aima_moe_decode_layers_noalloc(None, 1, None, None, ctypes.c_float(1e-6), None, None) == -1
+    # host memory for the vectors or for a weight: refused on the host with an error code, nothing enqueued
+    host_x = x.cpu()
+    with pytest.raises(package.AimaMoeError) as host_vector:
+        package.provider.decode_layers_noalloc([layers[0]], host_x, y)
+    assert host_vector.value.status == -1
+    host_weight = dict(layers[0])
+    host_weight["router"] = layers[0]["router"].cpu()
+    with pytest.raises(package.AimaMoeError) as host_tensor:
+        package.provider.decode_layers_noalloc([host_weight], x, y)
+    assert host_tensor.value.status == -1
+    torch.cuda.synchronize()                                          # the context is untouched
