@@ -271,10 +271,8 @@ __device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
 // another thread of the block already raised `abort_flag`.  `diag` (may be
 // nullptr) receives {spins, elapsed ns lo, barrier word lo, barrier word hi}
 // when this call is the one that ran out of budget.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  volatile int* abort_flag,
-                                                  unsigned* diag = nullptr) {
-  if (mbar_test(bar, parity)) return true;
+static __device__ __noinline__ bool mbar_wait_bounded_slow(uint32_t bar, uint32_t parity,
+                                                    volatile int* abort_flag, unsigned* diag) {
   const unsigned long long start = global_timer_ns();
   unsigned spins = 0;
   while (!mbar_test(bar, parity)) {
@@ -296,6 +294,18 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
   }
   return true;
+}
+// The common case -- the phase has completed, or completes within a few probes -- stays inline; the
+// timed loop is one shared out-of-line function, which keeps the persistent kernels' text small
+// (their per-layer code runs once per layer, so every kilobyte of it is an instruction-cache miss).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag,
+                                                  unsigned* diag = nullptr) {
+#pragma unroll 1
+  for (int probe = 0; probe < 4; ++probe) {
+    if (mbar_test(bar, parity)) return true;
+  }
+  return mbar_wait_bounded_slow(bar, parity, abort_flag, diag);
 }
 
 // Programmatic dependent launch.  A kernel launched with launch_pdl may have its blocks placed

@@ -31,30 +31,32 @@
 //       carries the shared expert's gate row
 //   R2  the block's 3-4 contiguous rows of the shared expert's gate (A) and up (B)
 //       projections
-//   B   "blind" chunks: for each of the 8 expert positions the block's 3-4
-//       contiguous gate rows (A) and up rows (B) of the expert PREDICTED for that
-//       position, requested while the chain of the previous layer is still running
+//   B   "blind" items, requested with the experts PREDICTED for this layer while the previous
+//       layer is still running: for each of the 8 expert positions the block's 3-4 contiguous
+//       gate rows (A) and up rows (B).  The streaming warps turn them into activations as soon
+//       as this layer's input is normalised, i.e. WHILE warp 0 is still waiting for the logits
 //   --- logits exchange: every logit travels as one 64-bit word {tag, value};
 //       warp 0 of every block polls the 256 words, takes the top-8, freezes the
 //       blind issue and publishes the layer plan (which predicted positions hold
 //       a chosen expert, which chosen experts still have to be fetched)
-//   P   the chunks not covered by a valid blind item, with the real experts
-//   D   the block's <= 14 rows of the down projections, two experts per item
-//       (shared expert first)
+//   P   the gate/up chunks not covered by a valid blind item, with the real experts
+//   D   the block's <= 14 rows of the down projections, two experts per item (shared expert first)
 //   --- grid barrier: all SwiGLU activations known
-//       down products for the block's output elements from the D items,
+//       down products for the block's output elements from the down items,
 //       weighted sum, shared expert, residual add
 //   --- output exchange: the 2048 outputs travel as 32-bit words {tag, bf16};
 //       four warps of every block poll them into shared memory
 //
-// Prediction.  HBM would idle from the moment a layer's down rows have landed
-// until the next layer's top-8 is known (output exchange, norm, router rows,
-// logits exchange, top-8: about 40 % of a layer).  Applying the next layer's
-// router to THIS layer's normalised input costs one more ring item per block
-// and predicts most of the next layer's experts; their rows are requested into
-// the ring during that idle time.  A position whose prediction was wrong is
-// dropped unread and fetched again with the right expert, so the result does not
-// depend on the prediction: outputs are bit-identical with and without it.
+// Prediction.  A grid-wide hand-over through L2 costs about 1.5 us of pure latency
+// (store, then a poll round trip), a layer has three of them, and nothing that
+// depends on the routing can be requested before the second.  Applying the next
+// layer's router to THIS layer's normalised input costs one more half item per
+// block and predicts most of the next layer's experts.  Their rows are requested
+// into the ring as slots fall free, their activations are computed before the
+// routing is known, and a layer whose prediction was right has nothing left to
+// fetch after its plan.  A position whose prediction was wrong is fetched again
+// with the right expert and its activations are overwritten, so the result does
+// not depend on the prediction: outputs are bit-identical with and without it.
 //
 // Every wait (mbarrier, grid barrier, hand-overs between the warps of a block)
 // is bounded; on expiry the block raises a status word, drains its outstanding
@@ -75,9 +77,12 @@ constexpr int kRingSlots = 6;
 constexpr int kGroups = 3;
 constexpr int kGroupWarps = 4;
 constexpr int kStreamWarps = kGroups * kGroupWarps;
-constexpr int kFirstStreamWarp = 1;
-constexpr int kPredictWarp = 13;
-constexpr int kProducerWarp = 15;
+// Warp roles.  An SM sub-partition issues for warps w, w + 4, w + 8, w + 12; warp 0 runs the serial part
+// of every layer (polls, top-8, plan), so the other three warps of ITS sub-partition are the ones with
+// little to issue (producer, predictor, spare) and the twelve streaming warps share the other three.
+constexpr int kControlWarp = 0;
+constexpr int kProducerWarp = 4;
+constexpr int kPredictWarp = 8;
 constexpr int kHalfBytes = 16384;              // <= 4 weight rows of 4 KB, or <= 14 down rows of 1 KB
 constexpr int kSlotBytes = 2 * kHalfBytes;
 constexpr int kRowBytes = kHidden * 2;         // 4096
@@ -85,6 +90,11 @@ constexpr int kDownRowBytes = kInter * 2;      // 1024
 constexpr int kDotsStride = 12;
 constexpr int kPositions = kTopK;              // ring positions a layer's experts are dealt to
 constexpr int kRouterBlocks = kExperts / 2;    // blocks 0 .. 127 hold two router rows each, block 128 the shared gate row
+// Blind tickets of a layer: ticket q is the gate/up chunk of position q.  (Down rows are not requested
+// blind: they would sit in the ring until after the activation barrier, and a chunk that has to be
+// fetched again after the plan could then find its slot taken by an item that cannot be consumed
+// before it -- a cycle.  They are requested right after the plan, when the ring is empty.)
+constexpr int kTickets = kPositions;
 constexpr unsigned kFrozen = 0x10000u;
 
 // shared-memory map (bytes)
@@ -104,7 +114,7 @@ static_assert(kSmemTotal == kDecodeSmemBytes, "keep decode_kernel.cuh in step");
 static_assert(kDecodeMaxRowsPerBlock * kDownRowBytes <= kHalfBytes, "a block's down rows of one expert must fit half a slot");
 static_assert((kInter + kDecodeMinBlocks - 1) / kDecodeMinBlocks <= kGroupWarps, "a chunk has at most one row per warp of a group");
 static_assert(kGroupWarps * kRowBytes <= kHalfBytes, "a chunk of weight rows must fit half a slot");
-static_assert(kFirstStreamWarp + kStreamWarps <= kDecodeConsumerWarps, "stream warps are consumer warps");
+static_assert(kStreamWarps + 1 == kDecodeConsumerWarps, "control warp + stream warps meet at the consumer barrier");
 static_assert(kRingSlots % kGroups == 0, "every group owns the same number of slots");
 static_assert(kDecodeMinBlocks > kRouterBlocks, "block 128 must exist: it carries the shared gate row");
 
@@ -121,12 +131,13 @@ struct Misc {
   int n_active;
   unsigned active_mask;           // bit q: position q carries a chosen expert
   unsigned valid_mask;            // bit q: the blind items of position q hold that expert's rows
-  int n_blind;                    // positions [0, n_blind) were handled blind
+  int n_blind;                    // tickets [0, n_blind) were handled blind
   volatile int plan_layer;        // (layer ordinal + 1) the plan above belongs to
   // ---- prediction ----
   int pred[2][kPositions];        // predicted experts of layer ordinal li at [li & 1], -1: not held here
   volatile int pred_layer;        // predictions are published for all layer ordinals < pred_layer
-  unsigned blind_state[2];        // [li & 1]: positions claimed blind so far | kFrozen
+  unsigned blind_state[2];        // [li & 1]: tickets claimed blind so far | kFrozen
+  volatile int blind_done[2];     // [li & 1]: tickets the producer has dealt with (placed or skipped)
   volatile int abort_flag;        // block-local copy of a raised status
   volatile int decision;          // block-uniform "keep going" verdict (see uniform_alive)
 };
@@ -136,8 +147,8 @@ __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" :: "n"(kDecodeConsumerThreads) : "memory");
 }
 
-__device__ __forceinline__ void raise_status(const DecodeParams& p,
-                                             volatile int* abort_flag, int code) {
+__device__ __noinline__ void raise_status(const DecodeParams& p,
+                                          volatile int* abort_flag, int code) {
   atomicCAS(p.status, 0, code);
   *abort_flag = code;
 }
@@ -148,8 +159,8 @@ __device__ __forceinline__ void raise_status(const DecodeParams& p,
 // 4 consumer item (down rows), 5 grid barrier, 6 plan hand-over to the producer,
 // 7 output exchange, 8 norm row, 9 logits exchange, 10 prediction hand-over,
 // 11 expert-parallel peer word, 12 predicted-logits exchange.
-__device__ __forceinline__ void record_site(const DecodeParams& p, int site, int detail,
-                                            const unsigned* diag = nullptr) {
+__device__ __noinline__ void record_site(const DecodeParams& p, int site, int detail,
+                                         const unsigned* diag = nullptr) {
   if (atomicCAS(p.status + 1, 0, site) == 0) {
     p.status[2] = blockIdx.x;
     p.status[3] = threadIdx.x >> 5;
@@ -279,6 +290,10 @@ __device__ __forceinline__ void warp_top8(uint32_t (&k)[8], int lane, float& my_
 
 }  // namespace
 
+// kEp: expert parallelism (world > 1).  kExtras: qualification outputs, tracing stamps and the harness's
+// router hooks.  The plain single-GPU instantiation carries neither: its per-layer code runs once per
+// layer, so what it does not execute should not be in its text either.
+template <bool kEp, bool kExtras>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 moe_decode_persistent_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -313,6 +328,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     misc->pred_layer = 1;          // layer ordinal 0 has no prediction: nothing to wait for
     misc->blind_state[0] = 0u;
     misc->blind_state[1] = 0u;
+    misc->blind_done[0] = 0;
+    misc->blind_done[1] = 0;
     misc->abort_flag = 0;
     misc->decision = 1;
     misc->n_local = 0;
@@ -345,6 +362,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       unsigned issued[kRingSlots];
       for (int s = 0; s < kRingSlots; ++s) issued[s] = 0;
       unsigned norm_issued = 0;
+      unsigned landed = 0;           // items [0, landed) are known to have arrived
       bool alive = true;
 
       // One item: `bytes_a` from src_a into half A, `bytes_b` from src_b into half B (either may be 0,
@@ -353,7 +371,17 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         const int s = seq % kRingSlots;
         const unsigned use = seq / kRingSlots;
         unsigned diag[4] = {0, 0, 0, 0};
-        bool ok = mbar_wait_bounded(empty_bar(s), use & 1u, abort_flag, diag);
+        bool ok = true;
+        // Requests queue in the SM's path to L2, and every small load or store of the block -- the polls
+        // and stores of the grid-wide hand-overs -- waits behind them: no more than max_in_flight items
+        // are outstanding at a time (enough to cover bandwidth x latency, not more).
+        if (p.max_in_flight > 0) {
+          while (ok && seq - landed >= static_cast<unsigned>(p.max_in_flight)) {
+            ok = mbar_wait_bounded(full_bar(landed % kRingSlots), (landed / kRingSlots) & 1u, abort_flag, diag);
+            ++landed;
+          }
+        }
+        ok = ok && mbar_wait_bounded(empty_bar(s), use & 1u, abort_flag, diag);
         if (!ok && lane == 0 && *abort_flag == kStatusTimeoutMbarrier) {
           atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
           record_site(p, 1, static_cast<int>(seq), diag);
@@ -392,6 +420,12 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         return ok;
       };
 
+      // producer-side tracing stamps: 12 router / shared items placed, 13 blind issue over, 14 last
+      // gate/up chunk placed, 15 last down item placed
+      auto stamp = [&](int li, int k) {
+        if (kExtras && p.timeline != nullptr && lane == 0)
+          p.timeline[(static_cast<size_t>(c) * kMaxLayers + li) * kDecodeTraceSlots + k] = global_timer_ns();
+      };
       for (int li = 0; li < p.n_layers && alive; ++li) {
         const LayerPtrs L = p.layers[p.first_layer + li];
         const bool has_next = speculate && (li + 1 < p.n_layers);
@@ -424,42 +458,51 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           if (!issue(L.shared_gate_proj + static_cast<size_t>(sh_lo) * kHidden, sh_rows * kRowBytes,
                      L.shared_up_proj + static_cast<size_t>(sh_lo) * kHidden, sh_rows * kRowBytes)) break;
         }
-        // ---- B items: chunks of the predicted experts, until the real routing is known ----
+        stamp(li, 12);
+        // ---- B items: gate/up chunks of the predicted experts, until the real routing is known ----
         if (speculate && li > 0) {
           if (!wait_word(&misc->pred_layer, li + 1, kStatusTimeoutIds, 10, li)) break;
           __threadfence_block();
           unsigned* state = &misc->blind_state[li & 1];
+          const int* pred = misc->pred[li & 1];
           while (alive) {
             unsigned ticket = 0u;
             if (lane == 0) ticket = atomicAdd(state, 1u);
             ticket = __shfl_sync(kPair, ticket, 0);
-            if ((ticket & kFrozen) != 0u || ticket >= static_cast<unsigned>(kPositions)) break;
+            if ((ticket & kFrozen) != 0u || ticket >= static_cast<unsigned>(kTickets)) break;
             const int q = static_cast<int>(ticket);
-            const int expert = misc->pred[li & 1][q];
-            if (expert < 0) continue;
-            issue_chunk(expert, q);
+            if (pred[q] >= 0) issue_chunk(pred[q], q);
+            // the ticket is dealt with (its copies are on their way, or there was nothing to copy)
+            __syncwarp(kPair);
+            if (lane == 0) {
+              __threadfence_block();
+              misc->blind_done[li & 1] = q + 1;
+            }
           }
           if (!alive) break;
         }
+        stamp(li, 13);
         // ---- wait for this layer's plan ----
         if (!wait_word(&misc->plan_layer, li + 1, kStatusTimeoutIds, 6, li)) break;
         __threadfence_block();
         const int n_blind = misc->n_blind;
         const unsigned active_mask = misc->active_mask;
         const unsigned valid_mask = misc->valid_mask;
-        // ---- P items: positions not handled blind, then positions whose blind chunk holds the wrong expert ----
+        // ---- P items: chunks not handled blind, then chunks whose blind item holds the wrong expert ----
+#pragma unroll 1
         for (int q = n_blind; q < kPositions && alive; ++q) {
-          if (((active_mask >> q) & 1u) == 0u) continue;
-          issue_chunk(misc->expert_of_pos[q], q);
+          if (((active_mask >> q) & 1u) != 0u) issue_chunk(misc->expert_of_pos[q], q);
         }
+#pragma unroll 1
         for (int q = 0; q < n_blind && alive; ++q) {
-          if (((active_mask >> q) & 1u) == 0u || ((valid_mask >> q) & 1u) != 0u) continue;
-          issue_chunk(misc->expert_of_pos[q], q);
+          if (((active_mask >> q) & 1u) != 0u && ((valid_mask >> q) & 1u) == 0u) issue_chunk(misc->expert_of_pos[q], q);
         }
         if (!alive) break;
+        stamp(li, 14);
         // ---- D items: the block's rows of the down projections, two experts per item, shared expert first ----
         const uint32_t down_bytes = static_cast<uint32_t>(nh) * kDownRowBytes;
         const int n_active = misc->n_active;
+#pragma unroll 1
         for (int e = 0; e < 1 + n_active && alive; e += 2) {
           const __nv_bfloat16* src[2] = {nullptr, nullptr};
 #pragma unroll
@@ -474,6 +517,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           }
           issue(src[0], down_bytes, src[1], src[1] != nullptr ? down_bytes : 0u);
         }
+        stamp(li, 15);
       }
       // Drain: every copy these lanes issued must have landed before the block
       // may exit (bounded; a phase that already completed returns at once).
@@ -550,12 +594,14 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       }
     }
     __syncwarp();
-  } else if (warp < kDecodeConsumerWarps) {
+  } else if (warp == kControlWarp || (warp & 3) != 0) {
     // ------------------------------ consumers -----------------------------
-    const int ctid = threadIdx.x;                 // 0 .. 415
-    const bool streams = warp >= kFirstStreamWarp && warp < kFirstStreamWarp + kStreamWarps;
-    const int group = streams ? (warp - kFirstStreamWarp) / kGroupWarps : -1;
-    const int member = streams ? (warp - kFirstStreamWarp) % kGroupWarps : -1;
+    const bool streams = warp != kControlWarp;
+    const int stream_index = (warp >> 2) * 3 + (warp & 3) - 1;      // 0 .. 11 over warps 1,2,3,5,6,7,...
+    const int cw = streams ? 1 + stream_index : 0;                  // consumer warp ordinal 0 .. 12
+    const int ctid = cw * 32 + lane;                                // 0 .. 415
+    const int group = streams ? stream_index / kGroupWarps : -1;
+    const int member = streams ? stream_index % kGroupWarps : -1;
     unsigned seq = 0;                             // mirrors the producer's item counter
     unsigned long long nbar = 0;
     bool alive = true;
@@ -604,18 +650,24 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       b = butterfly_sum(b);
     };
     auto hooked_logit = [&](float v, int expert) -> float {
-      if (p.router_bias != nullptr) v = __fadd_rn(v, p.router_bias[expert]);
-      if (p.quant_eighths) v = __fmul_rn(rintf(__fmul_rn(v, 8.0f)), 0.125f);
+      if (kExtras && p.router_bias != nullptr) v = __fadd_rn(v, p.router_bias[expert]);
+      if (kExtras && p.quant_eighths) v = __fmul_rn(rintf(__fmul_rn(v, 8.0f)), 0.125f);
       return v;
     };
 
-    // tracing stamps: 0 layer start, 1 norm done, 2 router/shared rows done, 3 logits arrived,
-    // 4 plan published, 5 routed gate/up done, 6 activation barrier, 7 activations loaded,
-    // 8 = 7, 9 down dots done, 10 output stored, 11 = 10
-    auto stamp = [&](int li, int k) {
-      if (p.timeline != nullptr && c == 0 && ctid == 0)
-        p.timeline[li * kDecodeTraceStamps + k] = global_timer_ns();
+    // tracing stamps (thread 0 of the block unless stated): 0 layer start, 1 norm done, 2 this block's
+    // logits written (by the warp that computed them), 3 all logits arrived, 4 plan published and blind
+    // chunks consumed, 5 routed gate/up done, 6 activation barrier, 7 activations loaded, 8 first down
+    // item of the first streaming warp has landed, 9 down dots done, 10 output stored, 11 that warp's
+    // down items done
+    auto stamp_now = [&](int li, int k) {
+      if (kExtras && p.timeline != nullptr)
+        p.timeline[(static_cast<size_t>(c) * kMaxLayers + li) * kDecodeTraceSlots + k] = global_timer_ns();
     };
+    auto stamp = [&](int li, int k) {
+      if (ctid == 0) stamp_now(li, k);
+    };
+#pragma unroll 1
     for (int li = 0; li < p.n_layers; ++li) {
       const bool first = (li == 0);
       const bool last = (li == p.n_layers - 1);
@@ -631,9 +683,9 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         if (ctid < kHidden / 8) {
           reinterpret_cast<uint4*>(x_s)[ctid] = ld_cg_u4(reinterpret_cast<const uint4*>(p.x_in) + ctid);
         }
-      } else if (warp < 4) {
+      } else if (cw < 4) {
         // poll this warp's 512 tagged words until every tag is the previous layer's
-        const uint4* src = reinterpret_cast<const uint4*>(xw_src + (c % kDecodeReplicas) * kHidden) + warp * 128 + lane;
+        const uint4* src = reinterpret_cast<const uint4*>(xw_src + (c % kDecodeReplicas) * kHidden) + cw * 128 + lane;
         uint4 w[4];
         bool ready = false;
         const unsigned long long start = global_timer_ns();
@@ -661,25 +713,25 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           uint2 packed;
           packed.x = (w[i].x & 0xffffu) | (w[i].y << 16);
           packed.y = (w[i].z & 0xffffu) | (w[i].w << 16);
-          reinterpret_cast<uint2*>(x_s)[warp * 128 + i * 32 + lane] = packed;
+          reinterpret_cast<uint2*>(x_s)[cw * 128 + i * 32 + lane] = packed;
         }
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
       // ---- norm, once per block.  Sum of squares in the order of the reference kernel
       //      (native/src/native_pointwise.hip.cpp:109-142): partial t of 256 adds elements t, t + 256, ...
-      //      in that order, the partials fold by halving.  Warp j holds partial 8 l + j on lane l: the
+      //      in that order, the partials fold by halving.  Consumer warp j holds partial 8 l + j on lane l: the
       //      butterfly does the halvings of width 128 .. 8, the last three widths are the tree below.
       //      Then every thread normalises one 8-element chunk into h2_s (the activation region is idle now)
       uint8_t* h2_s = reinterpret_cast<uint8_t*>(act_s);
-      if (warp < 8) {
+      if (cw < 8) {
         float acc = 0.0f;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          const float v = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(x_s)[256 * g + 8 * lane + warp]);
+          const float v = bf16_bits_to_float(reinterpret_cast<const uint16_t*>(x_s)[256 * g + 8 * lane + cw]);
           acc = __fmaf_rn(v, v, acc);
         }
         acc = butterfly_sum(acc);
-        if (lane == 0) dots[warp] = acc;
+        if (lane == 0) dots[cw] = acc;
       }
       consumer_sync();
       {
@@ -708,7 +760,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           }
           const uint4 out = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           reinterpret_cast<uint4*>(h2_s)[ctid] = out;
-          if (p.dbg_h2 != nullptr && c == 0) reinterpret_cast<uint4*>(p.dbg_h2)[ctid] = out;
+          if (kExtras && p.dbg_h2 != nullptr && c == 0) reinterpret_cast<uint4*>(p.dbg_h2)[ctid] = out;
         }
       }
       consumer_sync();
@@ -741,6 +793,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
                     (static_cast<unsigned long long>(epoch0 + li + 1) << 32) | __float_as_uint(hooked_logit(v, expert));
 #pragma unroll
                 for (int rep = 0; rep < kDecodeReplicas; ++rep) st_strong_u64(dst + rep * kExperts + expert, word);
+                if (!predicted) stamp_now(li, 2);
               } else {
                 const float gate = round_bf16(v);
 #pragma unroll
@@ -772,10 +825,64 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           }
         }
       }
-      stamp(li, 2);
+
+      // A gate/up chunk for position q: warp m of the owning group takes pair m.  use == false: the
+      // slot holds rows of an expert that was not chosen; wait for them to land (the copy must not
+      // be in flight when the slot is reused) and hand the slot back unread.  Activations are filed
+      // under the POSITION; the down products look the rank up in the plan.
+      auto consume_chunk = [&](int q, bool use) {
+        const unsigned item = seq++;
+        if (!streams || !owns(item) || !alive) return;
+        const uint8_t* slot = wait_item(item, 3);
+        if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; return; }
+        const int b = position_range(q, c, G);
+        const int lo = range_lo(b, G);
+        const int rows = range_lo(b + 1, G) - lo;
+        const bool mine = use && member < rows;
+        float a = 0.0f, bb = 0.0f;
+        if (mine) pair_dot(slot + member * kRowBytes, slot + kHalfBytes + member * kRowBytes, xr, a, bb);
+        release_item(item);
+        if (mine && lane == 0) {
+          const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), bb));
+          const int index = q * kInter + lo + member;
+#pragma unroll
+          for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + index] = bits;
+        }
+      };
+      // ---- blind gate/up chunks, consumed while warp 0 waits for the logits: the predicted expert's
+      //      activations are right whenever the prediction is, and overwritten otherwise.  Every warp
+      //      takes the chunks in ticket order until it meets the first ticket that was not claimed
+      //      before the routing was known (n_blind, published with the plan) ----
+      int blind_seen = 0;                 // gate/up tickets this warp has walked past
+      if (speculate && li > 0 && streams) {
+        const unsigned long long start = global_timer_ns();
+        unsigned spins = 0;
+#pragma unroll 1
+        while (blind_seen < kPositions && alive) {
+          if (misc->blind_done[li & 1] > blind_seen) {
+            __threadfence_block();
+            if (misc->pred[li & 1][blind_seen] >= 0) consume_chunk(blind_seen, true);
+            ++blind_seen;
+            continue;
+          }
+          if (misc->plan_layer == li + 1) {
+            __threadfence_block();
+            if (blind_seen >= misc->n_blind) break;       // never claimed: dealt with after the plan
+          }
+          if ((++spins & 255u) == 0u) {
+            if (*abort_flag != 0) { alive = false; break; }
+            if (global_timer_ns() - start > kWaitBudgetNs) {
+              raise_status(p, abort_flag, kStatusTimeoutIds);
+              record_site(p, 13, li * 16 + blind_seen);
+              alive = false;
+              break;
+            }
+          }
+        }
+      }
 
       // ---- logits exchange + top-8 (ties to the lowest expert id) + softmax + layer plan, warp 0 ----
-      if (warp == 0) {
+      if (warp == kControlWarp) {
         const unsigned tag = epoch0 + li + 1;
         unsigned long long w[8];
         bool ready = false;
@@ -821,7 +928,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         for (int q = 0; q < 8; ++q) {
           const float value = __uint_as_float(static_cast<uint32_t>(w[q]));
           k[q] = order_key(value);
-          if (p.dbg_logits != nullptr && c == 0) p.dbg_logits[32 * q + lane] = value;
+          if (kExtras && p.dbg_logits != nullptr && c == 0) p.dbg_logits[32 * q + lane] = value;
         }
         float my_score;      // lane r keeps the r-th selected value
         int my_id;
@@ -831,10 +938,11 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         unsigned claimed = 0u;
         if (lane == 0) {
           claimed = atomicOr(&misc->blind_state[li & 1], kFrozen) & (kFrozen - 1u);
-          misc->blind_state[(li + 1) & 1] = 0u;      // nobody uses the other word before this layer's plan
+          misc->blind_state[(li + 1) & 1] = 0u;      // nobody uses the other words before this layer's plan
+          misc->blind_done[(li + 1) & 1] = 0;
         }
         claimed = __shfl_sync(0xffffffffu, claimed, 0);
-        const int n_blind = min(static_cast<int>(claimed), kPositions);
+        const int n_blind = min(static_cast<int>(claimed), kTickets);
         // softmax over the eight: exp(s_r - s_0) / sum, summed in selection order
         const float top = __shfl_sync(0xffffffffu, my_score, 0);
         const float ex = det_expf(__fsub_rn(my_score, top));
@@ -845,21 +953,39 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         const bool local_expert = lane < kTopK && my_id >= p.expert_lo && my_id < p.expert_hi;
         const unsigned local_mask = __ballot_sync(0xffffffffu, local_expert);
         // ---- deal the chosen experts held here to the ring positions: an expert the prediction placed
-        //      at a position claimed blind stays there (its blind chunk is valid); the others take the
-        //      remaining positions in ascending order ----
-        const int pred_q = (lane < n_blind) ? misc->pred[li & 1][lane] : -1;
+        //      at a position stays there; the others take the remaining positions in ascending order.
+        //      Activations are filed by position, so this assignment must be the same in every block:
+        //      it uses the whole prediction (identical everywhere), not only the part this block had
+        //      claimed blind before the routing was known ----
+        int pred_all = -1;
+        if (speculate && li > 0) {
+          // the prediction for this layer was published during the previous one; make sure of it
+          const unsigned long long wait_start = global_timer_ns();
+          while (misc->pred_layer < li + 1) {
+            if (*abort_flag != 0 || global_timer_ns() - wait_start > kWaitBudgetNs) {
+              if (*abort_flag == 0 && lane == 0) {
+                raise_status(p, abort_flag, kStatusTimeoutIds);
+                record_site(p, 10, li);
+              }
+              break;
+            }
+          }
+          __threadfence_block();
+          if (lane < kPositions) pred_all = misc->pred[li & 1][lane];
+        }
+        const int pred_q = lane < n_blind ? pred_all : -1;     // what this block's blind chunks were requested with
         int rank_q = -1;
 #pragma unroll
         for (int r = 0; r < kTopK; ++r) {
           const int id_r = __shfl_sync(0xffffffffu, my_id, r);
-          if (((local_mask >> r) & 1u) != 0u && pred_q >= 0 && pred_q == id_r) rank_q = r;
+          if (((local_mask >> r) & 1u) != 0u && pred_all >= 0 && pred_all == id_r) rank_q = r;
         }
         const bool matched = lane < kPositions && rank_q >= 0;
-        const unsigned valid_mask = __ballot_sync(0xffffffffu, matched);
+        const unsigned matched_mask = __ballot_sync(0xffffffffu, matched);
         const unsigned matched_ranks = __reduce_or_sync(0xffffffffu, matched ? (1u << rank_q) : 0u);
-        // an expert predicted at a position that was NOT claimed blind may still be among the chosen:
-        // it simply has no valid chunk and is dealt like the others
-        const unsigned free_pos = ((1u << kPositions) - 1u) & ~valid_mask;
+        // a matched position holds valid rows only if this block had claimed it blind
+        const unsigned valid_mask = __ballot_sync(0xffffffffu, matched && lane < n_blind);
+        const unsigned free_pos = ((1u << kPositions) - 1u) & ~matched_mask;
         if (lane < kPositions && !matched) {
           unsigned left = local_mask & ~matched_ranks;
           const int skip = __popc(free_pos & ((1u << lane) - 1u));
@@ -877,9 +1003,9 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           misc->pred_of_pos[lane] = pred_q;
           if (rank_q >= 0) misc->active_pos[__popc(active_mask & ((1u << lane) - 1u))] = lane;
           if (c == 0) {
-            if (p.dbg_ids != nullptr) p.dbg_ids[lane] = my_id;
-            if (p.dbg_scores != nullptr) p.dbg_scores[lane] = my_score;
-            if (p.dbg_weights != nullptr) reinterpret_cast<uint16_t*>(p.dbg_weights)[lane] = wb;
+            if (kExtras && p.dbg_ids != nullptr) p.dbg_ids[lane] = my_id;
+            if (kExtras && p.dbg_scores != nullptr) p.dbg_scores[lane] = my_score;
+            if (kExtras && p.dbg_weights != nullptr) reinterpret_cast<uint16_t*>(p.dbg_weights)[lane] = wb;
           }
         }
         __syncwarp();
@@ -896,47 +1022,34 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 4);
 
-      // ---- routed gate/up chunks of the experts held on this GPU: warp m takes pair m of a chunk ----
+      // ---- routed gate/up chunks that were not (or wrongly) covered blind ----
       const int n_local = misc->n_local;
-      const int n_active = misc->n_active;
       const int n_blind = misc->n_blind;
+      const int n_blind_chunks = n_blind;
+      const int n_active = misc->n_active;
       const unsigned active_mask = misc->active_mask;
       const unsigned valid_mask = misc->valid_mask;
-      {
-        // use == false: the slot holds rows of an expert that was not chosen; wait for them to land
-        // (the copy must not be in flight when the slot is reused) and hand the slot back unread
-        auto consume_chunk = [&](int q, bool use) {
-          const unsigned item = seq++;
-          if (!streams || !owns(item) || !alive) return;
-          const uint8_t* slot = wait_item(item, 3);
-          if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; return; }
-          const int b = position_range(q, c, G);
-          const int lo = range_lo(b, G);
-          const int rows = range_lo(b + 1, G) - lo;
-          const bool mine = use && member < rows;
-          float a = 0.0f, bb = 0.0f;
-          if (mine) pair_dot(slot + member * kRowBytes, slot + kHalfBytes + member * kRowBytes, xr, a, bb);
-          release_item(item);
-          if (mine && lane == 0) {
-            const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), bb));
-            const int index = misc->rank_of_pos[q] * kInter + lo + member;
-#pragma unroll
-            for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + index] = bits;
-          }
-        };
-        for (int q = 0; q < n_blind; ++q) {
-          if (misc->pred_of_pos[q] < 0) continue;
-          consume_chunk(q, ((valid_mask >> q) & 1u) != 0u);
+      if (warp == kControlWarp) {
+        // warp 0 took no part in the blind walk: count the items it skipped
+        for (int q = 0; q < n_blind_chunks; ++q) {
+          if (misc->pred_of_pos[q] >= 0) ++seq;
         }
-        for (int q = n_blind; q < kPositions; ++q) {
-          if (((active_mask >> q) & 1u) == 0u) continue;
-          consume_chunk(q, true);
-        }
-        for (int q = 0; q < n_blind; ++q) {
-          if (((active_mask >> q) & 1u) == 0u || ((valid_mask >> q) & 1u) != 0u) continue;
-          consume_chunk(q, true);
+      } else {
+        // tickets claimed blind that this warp had not reached when it left the walk above
+#pragma unroll 1
+        for (; blind_seen < n_blind_chunks; ++blind_seen) {
+          if (misc->pred_of_pos[blind_seen] >= 0) consume_chunk(blind_seen, ((valid_mask >> blind_seen) & 1u) != 0u);
         }
       }
+#pragma unroll 1
+      for (int q = n_blind_chunks; q < kPositions; ++q) {
+        if (((active_mask >> q) & 1u) != 0u) consume_chunk(q, true);
+      }
+#pragma unroll 1
+      for (int q = 0; q < n_blind_chunks; ++q) {
+        if (((active_mask >> q) & 1u) != 0u && ((valid_mask >> q) & 1u) == 0u) consume_chunk(q, true);
+      }
+      consumer_sync();
       stamp(li, 5);
       if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
       stamp(li, 6);
@@ -948,26 +1061,29 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       }
       consumer_sync();
       stamp(li, 7);
-      stamp(li, 8);
       {
-        // item = two experts (shared expert first); warps 0, 1 of the group take the halves of the first
-        // expert's rows, warps 2, 3 those of the second: the activation row is unpacked once and up to
-        // seven dots against it share one eight-way reduction
-        const int n_entries = 1 + n_active;
-        for (int e = 0; e < n_entries; e += 2) {
+        // A down item holds the block's rows of up to two experts; warps 0, 1 of the group take the halves
+        // of the first expert's rows, warps 2, 3 those of the second: the activation row is unpacked
+        // once and up to seven dots against it share one eight-way reduction.  entry 0 is the shared
+        // expert, entry e >= 1 position e - 1; use_x == false: that half is absent or holds rows of an
+        // expert that was not chosen.
+        bool down_stamped = false;
+        auto consume_down = [&](int entry_a, bool use_a, int entry_b, bool use_b) {
           const unsigned item = seq++;
-          if (!streams || !owns(item) || !alive) continue;
+          if (!streams || !owns(item) || !alive) return;
           const uint8_t* slot = wait_item(item, 4);
-          if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; continue; }
-          const int entry = e + (member >> 1);
-          const bool mine = entry < n_entries;
-          const int column = (entry == 0 || !mine) ? kTopK : misc->rank_of_pos[misc->active_pos[entry - 1]];
+          if (!__all_sync(0xffffffffu, slot != nullptr)) { alive = false; return; }
+          if (cw == 1 && lane == 0 && !down_stamped) { stamp_now(li, 8); down_stamped = true; }
+          const int entry = (member >> 1) ? entry_b : entry_a;
+          const bool mine = (member >> 1) ? use_b : use_a;
+          const int act_row = entry == 0 ? kTopK : entry - 1;                       // activations are filed by position
+          const int column = (entry == 0 || !mine) ? kTopK : misc->rank_of_pos[entry - 1];
           const int row_base = (member & 1) * half_rows;
           const int rows = mine ? ((member & 1) ? nh - half_rows : half_rows) : 0;
           float part[8];
           if (mine) {
             float af[16];
-            const uint4* arow = reinterpret_cast<const uint4*>(act_s + column * kInter) + lane;
+            const uint4* arow = reinterpret_cast<const uint4*>(act_s + act_row * kInter) + lane;
             unpack8(arow[0], af);
             unpack8(arow[32], af + 8);
             const uint8_t* rows_ptr = slot + (member >> 1) * kHalfBytes + row_base * kDownRowBytes;
@@ -988,7 +1104,16 @@ moe_decode_persistent_kernel(const DecodeParams p) {
             const int u = reduce8_slot(lane);
             if ((lane & 3) == 0 && u < rows) dots[(row_base + u) * kDotsStride + column] = total;
           }
+        };
+        // entries: 0 the shared expert, e >= 1 the e-th used position
+#pragma unroll 1
+        for (int e = 0; e < 1 + n_active; e += 2) {
+          const int entry_a = e == 0 ? 0 : misc->active_pos[e - 1] + 1;
+          const bool has_b = e + 1 <= n_active;
+          const int entry_b = has_b ? misc->active_pos[e] + 1 : 0;
+          consume_down(entry_a, true, entry_b, has_b);
         }
+        if (cw == 1 && lane == 0) stamp_now(li, 11);
       }
       if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 9);
@@ -996,7 +1121,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       //      (plain stores over NVLink into its exchange buffer), those held elsewhere are polled
       //      from this GPU's own buffer; words carry the layer tag, buffers alternate per layer.
       //      Block c of every GPU owns the same output rows, so a peer can be at most one layer ahead.
-      if (p.world > 1 && alive) {
+      if (kEp && alive) {
         const unsigned long long tag64 = static_cast<unsigned long long>(epoch0 + li + 1) << 32;
         const size_t parity_base = static_cast<size_t>(li & 1) * kTopK * kHidden;
         const int sends = n_local * nh * (p.world - 1);
@@ -1014,12 +1139,12 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       if (ctid < nh) {
         const int h = h0 + ctid;
         float acc = 0.0f;
-        if (p.world == 1) {
+        if (!kEp) {
 #pragma unroll
           for (int r = 0; r < kTopK; ++r) {
             const float d = dots[ctid * kDotsStride + r];
             acc = __fmaf_rn(misc->weights[r], d, acc);
-            if (p.dbg_slot_dots != nullptr) p.dbg_slot_dots[r * kHidden + h] = d;
+            if (kExtras && p.dbg_slot_dots != nullptr) p.dbg_slot_dots[r * kHidden + h] = d;
           }
         } else {
           const unsigned tag = epoch0 + li + 1;
@@ -1048,7 +1173,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
               d = __uint_as_float(static_cast<uint32_t>(word));
             }
             acc = __fmaf_rn(misc->weights[r], d, acc);
-            if (p.dbg_slot_dots != nullptr) p.dbg_slot_dots[r * kHidden + h] = d;
+            if (kExtras && p.dbg_slot_dots != nullptr) p.dbg_slot_dots[r * kHidden + h] = d;
           }
         }
         const float routed = round_bf16(acc);
@@ -1064,11 +1189,10 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           for (int rep = 0; rep < kDecodeReplicas; ++rep)
             st_strong_u32(xw_dst + rep * kHidden + h, (tag_out << 16) | out_bits);
         }
-        if (p.dbg_routed != nullptr) p.dbg_routed[h] = __float2bfloat16_rn(routed);
-        if (p.dbg_shared_scaled != nullptr) p.dbg_shared_scaled[h] = __float2bfloat16_rn(shared_scaled);
+        if (kExtras && p.dbg_routed != nullptr) p.dbg_routed[h] = __float2bfloat16_rn(routed);
+        if (kExtras && p.dbg_shared_scaled != nullptr) p.dbg_shared_scaled[h] = __float2bfloat16_rn(shared_scaled);
       }
       stamp(li, 10);
-      stamp(li, 11);
     }
     if (c == 0 && ctid == 0 && *abort_flag == 0) {
       *p.bar_base = bar_base + nbar * G;
@@ -1078,15 +1202,32 @@ moe_decode_persistent_kernel(const DecodeParams p) {
   __syncthreads();
 }
 
-cudaError_t launch_moe_decode(const DecodeParams& params, int grid_blocks,
-                              cudaStream_t stream) {
-  const cudaError_t e = opt_in_dynamic_smem<moe_decode_persistent_kernel>(kDecodeSmemBytes);
+namespace {
+template <bool kEp, bool kExtras>
+cudaError_t launch_variant(const DecodeParams& params, int grid_blocks, cudaStream_t stream) {
+  const cudaError_t e = opt_in_dynamic_smem<moe_decode_persistent_kernel<kEp, kExtras>>(kDecodeSmemBytes);
   if (e != cudaSuccess) return e;
   DecodeParams local = params;
   void* args[] = {&local};
   return cudaLaunchCooperativeKernel(
-      reinterpret_cast<const void*>(moe_decode_persistent_kernel), dim3(grid_blocks),
+      reinterpret_cast<const void*>(moe_decode_persistent_kernel<kEp, kExtras>), dim3(grid_blocks),
       dim3(kDecodeThreads), args, kDecodeSmemBytes, stream);
+}
+}  // namespace
+
+cudaError_t launch_moe_decode(const DecodeParams& params, int grid_blocks,
+                              cudaStream_t stream) {
+  const bool extras = params.timeline != nullptr || params.router_bias != nullptr || params.quant_eighths != 0 ||
+                      params.dbg_h2 != nullptr || params.dbg_logits != nullptr || params.dbg_ids != nullptr ||
+                      params.dbg_scores != nullptr || params.dbg_weights != nullptr ||
+                      params.dbg_shared_scaled != nullptr || params.dbg_routed != nullptr ||
+                      params.dbg_slot_dots != nullptr;
+  if (params.world > 1) {
+    return extras ? launch_variant<true, true>(params, grid_blocks, stream)
+                  : launch_variant<true, false>(params, grid_blocks, stream);
+  }
+  return extras ? launch_variant<false, true>(params, grid_blocks, stream)
+                : launch_variant<false, false>(params, grid_blocks, stream);
 }
 
 }  // namespace aima

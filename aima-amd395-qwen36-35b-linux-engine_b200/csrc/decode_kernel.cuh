@@ -5,9 +5,10 @@
 
 namespace aima {
 
-// 16 warps, 4 per SM sub-partition: warp 0 control (exchanges, top-8, layer plan), warps 1-12
-// stream the weight ring, warp 13 predicts the next layer's experts, warp 14 is spare, warp 15
-// issues the bulk copies.  Warps 0-12 form the "consumer" group that meets at named barrier 1.
+// 16 warps, 4 per SM sub-partition: warp 0 control (exchanges, top-8, layer plan), warp 4 issues the
+// bulk copies, warp 8 predicts the next layer's experts, warp 12 is spare, the other twelve stream
+// the weight ring.  Warp 0 and the twelve streaming warps form the "consumer" group of 13 warps that
+// meets at named barrier 1.
 constexpr int kDecodeConsumerWarps = 13;
 constexpr int kDecodeConsumerThreads = kDecodeConsumerWarps * 32;
 constexpr int kDecodeThreads = 16 * 32;
@@ -18,13 +19,15 @@ constexpr int kDecodeMaxRowsPerBlock = 14;
 constexpr int kDecodeMinBlocks = (kHidden + kDecodeMaxRowsPerBlock - 1) / kDecodeMaxRowsPerBlock;
 constexpr int kDecodeMaxBlocks = kExperts;  // router rows are dealt c, c + grid
 constexpr int kDecodeSmemBytes = 215832;
-constexpr int kDecodeTraceStamps = 12;
+constexpr int kDecodeTraceStamps = 12;       // consumer-side stamps per layer (the public timeline)
+constexpr int kDecodeTraceSlots = 16;        // per (block, layer): those 12 + 4 producer-side stamps
 constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU expert-parallel exchange buffer
 // Everything all 148 blocks read back from global memory (router logits, the
 // activation vector, the layer output) is written kDecodeReplicas times, and
 // block c reads copy c % kDecodeReplicas: 148 readers of the same few L2 lines
 // otherwise queue at the L2 slices that own them.
 constexpr int kDecodeReplicas = 8;
+constexpr int kDecodeDefaultInFlight = 0;     // ring items outstanding per block (0: no limit)
 constexpr int kDecodeLogitWords = 2 * kDecodeReplicas * kExperts;   // real + predicted, 64-bit words
 constexpr int kDecodeActStride = 9 * kInter + 64;   // BF16 elements per activation copy; [9*512] = gate logit bits (2 x u16)
 
@@ -46,6 +49,7 @@ struct DecodeParams {
   const float* router_bias;      // [256] or nullptr
   int quant_eighths;
   int speculate;                 // 1: request the predicted experts' rows before the routing is known
+  int max_in_flight;             // ring items a block may have requested but not yet received (0: no limit)
   float eps;
   int first_layer;
   int n_layers;
@@ -56,8 +60,8 @@ struct DecodeParams {
   unsigned long long* ep_dots[8];
   int world;
   int rank;
-  // optional tracing: block 0 stamps %globaltimer at kDecodeTraceStamps points
-  // of every layer into timeline[layer_ordinal * kDecodeTraceStamps + k]
+  // optional tracing: every block stamps %globaltimer at kDecodeTraceSlots points of every layer into
+  // timeline[(block * kMaxLayers + layer_ordinal) * kDecodeTraceSlots + k]
   unsigned long long* timeline;
   // optional qualification outputs (last processed layer wins)
   __nv_bfloat16* dbg_h2;

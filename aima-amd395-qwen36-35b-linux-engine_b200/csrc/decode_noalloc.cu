@@ -219,6 +219,7 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   params.rank = 0;
   params.quant_eighths = 0;
   params.speculate = 1;
+  params.max_in_flight = kDecodeDefaultInFlight;
   params.eps = rms_eps;
   params.first_layer = 0;
   params.n_layers = static_cast<int>(n_layers);

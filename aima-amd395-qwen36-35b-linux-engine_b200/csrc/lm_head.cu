@@ -22,48 +22,58 @@ constexpr int kHiddenSafetyUlps = 4;
 
 // ---------------------------------------------------------------------------
 // Build: q = clamp(rint(w / scale)), scale = max|w| * fl(1/127), residual_l2 = ||w - q * scale||_2
-// rounded up by 8 ULPs.  One block per row; thread t takes columns t, t + 256, ...; sums are
-// FP64, added pairwise in shared memory (offset 128, 64, ... 1) -- the order the CPU oracle uses.
+// rounded up by 8 ULPs (the arithmetic of native/src/native_lm_head.hip.cpp:53-115).
+// One warp per row, 16-byte loads: lane l holds elements 256 g + 8 l + j (g, j in 0..7), writes its
+// eight int8 results of a group with one 8-byte store.  The reference sums the squared residuals in
+// FP64 as 256 partials (partial t = columns t, t + 256, ... in that order) folded by halving; a lane
+// holds all eight columns of partials 8 l .. 8 l + 7, so the halvings of width 128 .. 8 are the lane
+// butterfly of each partial and the last three are ((q0+q4)+(q2+q6))+((q1+q5)+(q3+q7)).
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kLmThreads)
+constexpr int kQuantizeWarps = 8;
+__global__ void __launch_bounds__(kQuantizeWarps * 32)
 lm_head_quantize_kernel(const __nv_bfloat16* __restrict__ source, int8_t* __restrict__ q_weight,
-                        float* __restrict__ scales, float* __restrict__ residual_l2) {
-  __shared__ float reduction[kLmThreads];
-  __shared__ double squared[kLmThreads];
-  const size_t base = static_cast<size_t>(blockIdx.x) * kHidden;
-  const int t = threadIdx.x;
-  float local_max = 0.0f;
-  for (int column = t; column < kHidden; column += kLmThreads)
-    local_max = fmaxf(local_max, fabsf(__bfloat162float(source[base + column])));
-  reduction[t] = local_max;
-  __syncthreads();
-  for (int offset = kLmThreads / 2; offset > 0; offset >>= 1) {
-    if (t < offset) reduction[t] = fmaxf(reduction[t], reduction[t + offset]);
-    __syncthreads();
+                        float* __restrict__ scales, float* __restrict__ residual_l2, int rows) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kQuantizeWarps + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t base = static_cast<size_t>(row) * kHidden;
+  float v[64];
+  float largest = 0.0f;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    unpack8(__ldg(reinterpret_cast<const uint4*>(source + base + 256 * g) + lane), v + 8 * g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) largest = fmaxf(largest, fabsf(v[8 * g + j]));
   }
-  const float maximum = fmaxf(reduction[0], 1.0e-12f);
-  const float scale = __fmul_rn(maximum, 1.0f / 127.0f);   // multiplication by the rounded reciprocal
-  if (t == 0) scales[blockIdx.x] = scale;
-  double local_squared = 0.0;
-  for (int column = t; column < kHidden; column += kLmThreads) {
-    const float value = __bfloat162float(source[base + column]);
-    const float rounded = rintf(__fdiv_rn(value, scale));
-    const int quantized = static_cast<int>(fminf(127.0f, fmaxf(-127.0f, rounded)));
-    q_weight[base + column] = static_cast<int8_t>(quantized);
-    const float reconstructed = __fmul_rn(static_cast<float>(quantized), scale);
-    const double residual = static_cast<double>(__fsub_rn(value, reconstructed));
-    local_squared = __dadd_rn(local_squared, __dmul_rn(residual, residual));
+#pragma unroll
+  for (int s = 16; s >= 1; s >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, s));
+  const float scale = __fmul_rn(fmaxf(largest, 1.0e-12f), 1.0f / 127.0f);   // multiplication by the rounded reciprocal
+  double partial[8] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float value = v[8 * g + j];
+      const int quantized = static_cast<int>(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(value, scale)))));
+      packed[j >> 2] |= (static_cast<uint32_t>(quantized) & 0xffu) << (8 * (j & 3));
+      const double residual = static_cast<double>(__fsub_rn(value, __fmul_rn(static_cast<float>(quantized), scale)));
+      partial[j] = __dadd_rn(partial[j], __dmul_rn(residual, residual));
+    }
+    *reinterpret_cast<uint2*>(q_weight + base + 256 * g + 8 * lane) = make_uint2(packed[0], packed[1]);
   }
-  squared[t] = local_squared;
-  __syncthreads();
-  for (int offset = kLmThreads / 2; offset > 0; offset >>= 1) {
-    if (t < offset) squared[t] = __dadd_rn(squared[t], squared[t + offset]);
-    __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) partial[j] = __dadd_rn(partial[j], __shfl_xor_sync(0xffffffffu, partial[j], s));
   }
-  if (t == 0) {
-    float norm = static_cast<float>(sqrt(squared[0]));
+  if (lane == 0) {
+    const double total = __dadd_rn(__dadd_rn(__dadd_rn(partial[0], partial[4]), __dadd_rn(partial[2], partial[6])),
+                                   __dadd_rn(__dadd_rn(partial[1], partial[5]), __dadd_rn(partial[3], partial[7])));
+    float norm = static_cast<float>(sqrt(total));
     for (int step = 0; step < kResidualSafetyUlps; ++step) norm = nextafterf(norm, CUDART_INF_F);
-    residual_l2[blockIdx.x] = norm;
+    scales[row] = scale;
+    residual_l2[row] = norm;
   }
 }
 
@@ -289,8 +299,9 @@ lm_head_exact_kernel(const __nv_bfloat16* __restrict__ weight, const __nv_bfloat
 
 cudaError_t lm_head_quantize(const void* weight, int rows, int8_t* q_weight, float* scales, float* residual_l2,
                              cudaStream_t stream) {
-  lm_head_quantize_kernel<<<rows, kLmThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(weight), q_weight,
-                                                           scales, residual_l2);
+  if (rows <= 0) return cudaSuccess;
+  lm_head_quantize_kernel<<<(rows + kQuantizeWarps - 1) / kQuantizeWarps, kQuantizeWarps * 32, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(weight), q_weight, scales, residual_l2, rows);
   return cudaGetLastError();
 }
 

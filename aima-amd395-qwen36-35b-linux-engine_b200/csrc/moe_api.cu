@@ -92,12 +92,16 @@ struct aima_moe_handle {
   unsigned long long* ep_peers[8] = {};
   void* ep_ipc_opened[8] = {};
   float* router_row_norms = nullptr;        // [kMaxLayers][256], device, filled by bind_layer
-  unsigned long long* timeline = nullptr;   // [kMaxLayers * kDecodeTraceStamps], device
+  unsigned long long* timeline = nullptr;   // [kDecodeMaxBlocks][kMaxLayers][kDecodeTraceSlots], device
   bool tracing = false;
   uint32_t traced_layers = 0;
 
   const float* router_bias = nullptr;
   int quant_eighths = 0;
+  // qualification: routing supplied by the harness for single-layer prefill calls of exactly this many tokens
+  const int32_t* forced_ids = nullptr;
+  const void* forced_weights = nullptr;
+  uint32_t forced_tokens = 0;
 
   aima_moe_metrics metrics{};
   cudaStream_t last_stream = nullptr;
@@ -136,6 +140,16 @@ constexpr size_t kExchangeBytes = 256 + 256 + kLogitsBytes + 2 * kXbufBytes;
 
 size_t decode_scratch_size() {
   return kExchangeBytes + align_up(static_cast<size_t>(kDecodeReplicas) * kDecodeActStride * 2, 256);
+}
+
+// AIMA_MOE_DECODE_IN_FLIGHT in the environment overrides how many ring items a block of the decode
+// kernel may have outstanding (0: no limit).
+int decode_max_in_flight() {
+  static const int value = [] {
+    const char* v = std::getenv("AIMA_MOE_DECODE_IN_FLIGHT");
+    return (v != nullptr && v[0] != '\0') ? std::atoi(v) : kDecodeDefaultInFlight;
+  }();
+  return value;
 }
 
 int check_device_tensor(const void* pointer, uint64_t bytes, uint64_t expected,
@@ -227,6 +241,7 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
   params.router_bias = handle->router_bias;
   params.quant_eighths = handle->quant_eighths;
   params.speculate = (handle->config.flags & AIMA_MOE_FLAG_NO_DECODE_PREDICTION) == 0 ? 1 : 0;
+  params.max_in_flight = decode_max_in_flight();
   params.eps = handle->config.rms_eps;
   params.first_layer = static_cast<int>(first_layer);
   params.n_layers = static_cast<int>(n_layers);
@@ -327,7 +342,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
   error = cudaMemset(handle->dev_layers, 0, sizeof(LayerPtrs) * kMaxLayers);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMemset layer table"));
 
-  error = cudaMalloc(&handle->timeline, sizeof(unsigned long long) * kMaxLayers * kDecodeTraceStamps);
+  error = cudaMalloc(&handle->timeline, sizeof(unsigned long long) * kDecodeMaxBlocks * kMaxLayers * kDecodeTraceSlots);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMalloc decode timeline"));
   if (config->world > 1) {
     handle->ep_prefill.world = static_cast<int>(config->world);
@@ -367,6 +382,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
     handle->prefill.status = handle->status;
     handle->prefill.use_simt_gemm = (config->flags & AIMA_MOE_FLAG_SIMT_PRODUCTS) != 0;
     handle->prefill.exact_router = (config->flags & AIMA_MOE_FLAG_EXACT_ROUTER) != 0;
+    handle->prefill.router_audit_stride = (config->flags & AIMA_MOE_FLAG_AUDIT_ROUTER) != 0 ? 64 : 0;
     handle->prefill.fused_dispatch = (config->flags & AIMA_MOE_FLAG_MATERIALIZED_DISPATCH) == 0;
     handle->prefill.ep_parts = (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_4)   ? 4
                                : (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_2) ? 2
@@ -447,6 +463,22 @@ AIMA_EXPORT int aima_moe_set_router_hooks(aima_moe_handle* handle, const void* b
   return AIMA_MOE_OK;
 }
 
+AIMA_EXPORT int aima_moe_set_forced_routing(aima_moe_handle* handle, const int32_t* ids,
+                                            const void* weights_bf16, uint32_t tokens) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if ((ids == nullptr) != (weights_bf16 == nullptr))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "forced routing needs both ids and weights, or neither");
+  if (ids != nullptr && (tokens == 0 || tokens > handle->config.max_prefill_tokens))
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "forced routing for %u tokens does not fit the workspace", tokens);
+  if (ids != nullptr && handle->config.world > 1)
+    return fail(AIMA_MOE_ERR_UNSUPPORTED, "forced routing is a single-GPU qualification hook");
+  handle->forced_ids = ids;
+  handle->forced_weights = weights_bf16;
+  handle->forced_tokens = ids != nullptr ? tokens : 0;
+  return AIMA_MOE_OK;
+}
+
 AIMA_EXPORT int aima_moe_decode_launch(aima_moe_handle* handle, uint32_t layer,
                                        const void* after_attn, void* out,
                                        const aima_moe_debug_views* debug, void* stream) {
@@ -499,6 +531,13 @@ AIMA_EXPORT int aima_moe_prefill_launch(aima_moe_handle* handle, uint32_t layer,
   call.router_bias = handle->router_bias;
   call.quant_eighths = handle->quant_eighths;
   call.debug = debug;
+  if (handle->forced_ids != nullptr) {
+    if (handle->forced_tokens != tokens)
+      return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "forced routing was set for %u tokens, the call has %u",
+                  handle->forced_tokens, tokens);
+    call.forced_ids = handle->forced_ids;
+    call.forced_weights = handle->forced_weights;
+  }
   int launches = 0;
   const int status =
       handle->config.world > 1
@@ -717,11 +756,14 @@ AIMA_EXPORT int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics*
     error = cudaMemcpy(&handle->metrics.last_padded_routed_rows, handle->prefill.padded_rows,
                        sizeof(int32_t), cudaMemcpyDeviceToHost);
     if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy padded row count");
-    int32_t stats[2] = {0, 0};
+    int32_t stats[5] = {0, 0, 0, 0, 0};
     error = cudaMemcpy(stats, handle->prefill.router_stats, sizeof stats, cudaMemcpyDeviceToHost);
     if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy router statistics");
     handle->metrics.router_candidates = static_cast<uint64_t>(static_cast<uint32_t>(stats[0]));
     handle->metrics.router_tokens = static_cast<uint64_t>(static_cast<uint32_t>(stats[1]));
+    handle->metrics.router_bound_violations = static_cast<uint64_t>(static_cast<uint32_t>(stats[2]));
+    handle->metrics.router_audited_tokens = static_cast<uint64_t>(static_cast<uint32_t>(stats[3]));
+    handle->metrics.router_audit_mismatches = static_cast<uint64_t>(static_cast<uint32_t>(stats[4]));
   }
   if (metrics != nullptr) {
     if (metrics->struct_bytes != sizeof(aima_moe_metrics))
@@ -812,15 +854,41 @@ AIMA_EXPORT int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t*
   if (handle == nullptr || stamps_ns == nullptr || written == nullptr)
     return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "timeline argument is null");
   std::lock_guard<std::mutex> lock(handle->mutex);
-  const uint32_t available = handle->traced_layers * kDecodeTraceStamps;
-  const uint32_t count = available < capacity ? available : capacity;
+  const uint32_t layers = handle->traced_layers < capacity / kDecodeTraceStamps ? handle->traced_layers
+                                                                               : capacity / kDecodeTraceStamps;
   cudaError_t error = cudaStreamSynchronize(handle->last_stream);
   if (error != cudaSuccess) return fail_cuda(error, "cudaStreamSynchronize");
-  if (count != 0) {
-    error = cudaMemcpy(stamps_ns, handle->timeline, sizeof(uint64_t) * count, cudaMemcpyDeviceToHost);
+  if (layers != 0) {
+    // block 0's record: kDecodeTraceSlots words per layer, of which the first kDecodeTraceStamps are returned
+    error = cudaMemcpy2D(stamps_ns, sizeof(uint64_t) * kDecodeTraceStamps, handle->timeline,
+                         sizeof(uint64_t) * kDecodeTraceSlots, sizeof(uint64_t) * kDecodeTraceStamps, layers,
+                         cudaMemcpyDeviceToHost);
     if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy decode timeline");
   }
-  *written = count;
+  *written = layers * kDecodeTraceStamps;
+  return AIMA_MOE_OK;
+}
+
+AIMA_EXPORT int aima_moe_read_decode_block_timelines(aima_moe_handle* handle, uint64_t* stamps_ns,
+                                                     uint32_t capacity, uint32_t* blocks, uint32_t* layers) {
+  if (handle == nullptr || stamps_ns == nullptr || blocks == nullptr || layers == nullptr)
+    return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "timeline argument is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  const uint32_t n_blocks = static_cast<uint32_t>(handle->decode_grid);
+  const uint32_t n_layers = handle->traced_layers;
+  if (static_cast<uint64_t>(n_blocks) * n_layers * kDecodeTraceSlots > capacity)
+    return fail(AIMA_MOE_ERR_CAPACITY, "timeline buffer holds %u words, %u blocks x %u layers x %d are needed",
+                capacity, n_blocks, n_layers, kDecodeTraceSlots);
+  cudaError_t error = cudaStreamSynchronize(handle->last_stream);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaStreamSynchronize");
+  if (n_layers != 0) {
+    error = cudaMemcpy2D(stamps_ns, sizeof(uint64_t) * kDecodeTraceSlots * n_layers, handle->timeline,
+                         sizeof(uint64_t) * kDecodeTraceSlots * kMaxLayers,
+                         sizeof(uint64_t) * kDecodeTraceSlots * n_layers, n_blocks, cudaMemcpyDeviceToHost);
+    if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy decode block timelines");
+  }
+  *blocks = n_blocks;
+  *layers = n_layers;
   return AIMA_MOE_OK;
 }
 

@@ -56,7 +56,7 @@ __device__ __forceinline__ float warp_eighth_largest(const float* v, int lane) {
 // The reference's prefill selection on the final (BF16-rounded) logits of one
 // token held as v[q] = logit of expert 32 q + lane: threshold, gather in expert
 // order, fixed bitonic network, softmax; lanes 0..7 write slot `lane`.
-__device__ __forceinline__ void route_token(const float* v, int lane, float* sel_v, int* sel_i,
+__device__ __forceinline__ int route_token(const float* v, int lane, float* sel_v, int* sel_i,
                                             size_t token, int32_t* __restrict__ ids,
                                             float* __restrict__ scores, float* __restrict__ weights,
                                             __nv_bfloat16* __restrict__ dbg_weights) {
@@ -130,6 +130,12 @@ __device__ __forceinline__ void route_token(const float* v, int lane, float* sel
       if (dbg_weights != nullptr) reinterpret_cast<uint16_t*>(dbg_weights)[o] = wb;
     }
   }
+  int selected = -1;      // lane r < 8 returns the expert of slot r
+#pragma unroll
+  for (int r = 0; r < kTopK; ++r) {
+    if (lane == r) selected = si[r];
+  }
+  return selected;
 }
 
 // logit transform shared by both router kernels: optional harness hooks, then
@@ -237,6 +243,13 @@ prefill_router_kernel(const __nv_bfloat16* __restrict__ h2,
 // upper bound reaches the lower bound of the 8th-largest value can be selected;
 // those few are recomputed with the canonical dot and the reference's rule runs
 // on them alone, so ids, scores and weights stay bit-exact.
+//
+// The bound is a statement about hardware whose accumulation order is not
+// published, so the kernel checks it where it can: every candidate has both
+// values, and if one lies further from its tensor-core value than the bound
+// allows, the whole token is recomputed with the canonical dot (all 256
+// experts) and counted.  With audit_stride > 0 every audit_stride-th token is
+// recomputed in full as well and its ids compared with the certified ones.
 // One warp per token.
 // ---------------------------------------------------------------------------
 constexpr int kCertWarps = 8;
@@ -267,7 +280,8 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
                                 const float* __restrict__ bias, int quant_eighths, int tokens,
                                 int32_t* __restrict__ ids, float* __restrict__ scores,
                                 float* __restrict__ weights, float* __restrict__ shared_sigmoid,
-                                __nv_bfloat16* __restrict__ dbg_weights, int32_t* __restrict__ stats) {
+                                __nv_bfloat16* __restrict__ dbg_weights, int32_t* __restrict__ stats,
+                                int audit_stride) {
   __shared__ float sel_v_s[kCertWarps * 8];
   __shared__ int sel_i_s[kCertWarps * 8];
   const int warp = threadIdx.x >> 5;
@@ -324,10 +338,8 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
     pending &= pending - 1u;
     return 32 * group + owner;
   };
-  while (true) {
-    const int e0 = pop();
-    if (e0 < 0) break;
-    const int e1 = pop();
+  // canonical logits of two experts at once (e1 < 0: only e0); the owner lanes file them in v
+  auto exact_pair = [&](int e0, int e1, float& acc0, float& acc1) {
     const uint4* row0 = reinterpret_cast<const uint4*>(router + static_cast<size_t>(e0) * kHidden) + lane;
     const uint4* row1 = reinterpret_cast<const uint4*>(router + static_cast<size_t>(e1 >= 0 ? e1 : e0) * kHidden) + lane;
     uint4 w0[8], w1[8];
@@ -335,7 +347,8 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
     for (int i = 0; i < 8; ++i) w0[i] = __ldg(row0 + i * 32);
 #pragma unroll
     for (int i = 0; i < 8; ++i) w1[i] = __ldg(row1 + i * 32);
-    float acc0 = 0.0f, acc1 = 0.0f;
+    acc0 = 0.0f;
+    acc1 = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       acc0 = fma8_packed(xp[i], w0[i], acc0);
@@ -348,10 +361,46 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
       if (e0 == 32 * q + lane) v[q] = finish_logit(acc0, b[q], quant_eighths);
       if (e1 == 32 * q + lane) v[q] = finish_logit(acc1, b[q], quant_eighths);
     }
+  };
+  // is the canonical value further from the tensor-core value than the bound the filter relied on?
+  auto outside_bound = [&](float exact, int e) -> bool {
+    const float a = approx[static_cast<size_t>(token) * kExperts + e];
+    const float be = bias != nullptr ? bias[e] : 0.0f;
+    const float delta = kCertKappa * x_norm * row_norms[e] + 9.5367431640625e-07f * fabsf(a + be);
+    return fabsf(exact - a) > delta;
+  };
+  bool violated = false;
+  while (true) {
+    const int e0 = pop();
+    if (e0 < 0) break;
+    const int e1 = pop();
+    float acc0, acc1;
+    exact_pair(e0, e1, acc0, acc1);
+    if ((e0 & 31) == lane) violated = violated || outside_bound(acc0, e0);
+    if (e1 >= 0 && (e1 & 31) == lane) violated = violated || outside_bound(acc1, e1);
     recomputed += e1 >= 0 ? 2 : 1;
   }
-  route_token(v, lane, sel_v_s + warp * 8, sel_i_s + warp * 8, static_cast<size_t>(token), ids, scores,
-              weights, dbg_weights);
+  violated = __any_sync(0xffffffffu, violated);
+  if (violated) {
+    // the premise of the filter failed for this token: take nothing from it
+    for (int e = 0; e < kExperts; e += 2) {
+      float acc0, acc1;
+      exact_pair(e, e + 1, acc0, acc1);
+    }
+  }
+  const int certified_id = route_token(v, lane, sel_v_s + warp * 8, sel_i_s + warp * 8, static_cast<size_t>(token),
+                                       ids, scores, weights, dbg_weights);
+  bool audited = false, audit_mismatch = false;
+  if (audit_stride > 0 && token % audit_stride == 0 && !violated) {
+    for (int e = 0; e < kExperts; e += 2) {
+      float acc0, acc1;
+      exact_pair(e, e + 1, acc0, acc1);
+    }
+    const int exact_id = route_token(v, lane, sel_v_s + warp * 8, sel_i_s + warp * 8, static_cast<size_t>(token),
+                                     ids, scores, weights, dbg_weights);
+    audited = true;
+    audit_mismatch = __any_sync(0xffffffffu, lane < kTopK && exact_id != certified_id);
+  }
   {
     const uint4* row = reinterpret_cast<const uint4*>(shared_gate) + lane;
     float acc = 0.0f;
@@ -363,6 +412,9 @@ prefill_router_certified_kernel(const __nv_bfloat16* __restrict__ h2,
       if (stats != nullptr) {
         atomicAdd(stats, recomputed);
         atomicAdd(stats + 1, 1);
+        if (violated) atomicAdd(stats + 2, 1);
+        if (audited) atomicAdd(stats + 3, 1);
+        if (audit_mismatch) atomicAdd(stats + 4, 1);
       }
     }
   }
@@ -827,7 +879,7 @@ Layout layout_for(size_t T) {
   l.weights = take(rows * 4);
   l.sigmoid = take(T * 4);
   l.approx = take(T * kExperts * 4);
-  l.stats = take(16);
+  l.stats = take(32);
   l.unit_counts = take(units * kExperts * 4);
   l.counts = take(kExperts * 4);
   l.offsets = take((kExperts + 1) * 4);
@@ -929,6 +981,21 @@ void prefill_workspace_free(PrefillWorkspace* ws) {
   *ws = PrefillWorkspace{};
 }
 
+// Qualification: routing supplied by the harness replaces the router's ids and weights (the router still
+// runs: the shared expert's sigmoid gate comes from it).  Mirrors the reference's "oracle-seeded
+// routing" rerun (native/src/native_moe_prefill.hip.cpp:1059-1123), which isolates the expert
+// arithmetic from tie-order effects.
+__global__ void forced_routing_kernel(const int32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ weights,
+                                      int n, int32_t* __restrict__ topk_ids, float* __restrict__ topk_weights,
+                                      float* __restrict__ topk_scores) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int id = ids[i];
+  topk_ids[i] = (id >= 0 && id < kExperts) ? id : 0;
+  topk_weights[i] = __bfloat162float(weights[i]);
+  topk_scores[i] = 0.0f;
+}
+
 int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStream_t stream,
                          int* launches, char* error, size_t error_bytes) {
   const int T = call.tokens;
@@ -986,10 +1053,18 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
                       0, stream, static_cast<const __nv_bfloat16*>(call.h2), call.layer.router,
                       call.layer.shared_gate, ws->approx_logits, call.router_row_norms, call.router_bias,
                       call.quant_eighths, T, ws->topk_ids, ws->topk_scores, ws->topk_weights, ws->shared_sigmoid,
-                      dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats);
+                      dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats, ws->router_audit_stride);
     if (code != cudaSuccess)
       return set_error(error, error_bytes, code, "prefill_router_certified_kernel");
     count += 2;
+  }
+
+  if (call.forced_ids != nullptr) {
+    forced_routing_kernel<<<(rows + 255) / 256, 256, 0, stream>>>(
+        call.forced_ids, static_cast<const __nv_bfloat16*>(call.forced_weights), rows, ws->topk_ids,
+        ws->topk_weights, ws->topk_scores);
+    if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "forced_routing_kernel");
+    ++count;
   }
 
   // the shared down product scales by the sigmoid the router kernel wrote
@@ -1160,7 +1235,7 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
       static_cast<const __nv_bfloat16*>(call.h2), call.layer.router, call.layer.shared_gate,
       ws->approx_logits, call.router_row_norms, call.router_bias, call.quant_eighths, T_loc, ws->topk_ids,
       ws->topk_scores, ws->topk_weights, ws->shared_sigmoid,
-      dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats);
+      dbg ? static_cast<__nv_bfloat16*>(dbg->topk_weights) : nullptr, ws->router_stats, ws->router_audit_stride);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "prefill_router_certified_kernel");
   count += 2;
   if ((code = cudaEventRecord(ws->router_event, stream)) != cudaSuccess ||

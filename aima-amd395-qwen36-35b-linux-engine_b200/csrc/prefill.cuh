@@ -41,7 +41,9 @@ struct PrefillWorkspace {
   float* topk_weights = nullptr;      // [T, 8] BF16-rounded, stored as FP32
   float* shared_sigmoid = nullptr;    // [T]    bf16(sigmoid(bf16 gate logit)) as FP32
   float* approx_logits = nullptr;     // [T, 256] tensor-core router logits (candidate filter only)
-  int32_t* router_stats = nullptr;    // [2] candidates recomputed exactly, tokens routed
+  int32_t* router_stats = nullptr;    // [5] candidates recomputed exactly, tokens routed, tokens whose candidates broke the
+                                      //     filter's bound (recomputed in full), tokens audited, audit mismatches
+  int router_audit_stride = 0;        // qualification: every n-th token is also routed from all 256 canonical logits
   // dispatch plan
   int32_t* unit_counts = nullptr;     // [units, 256] per-warp-unit histogram / prefix
   int32_t* expert_counts = nullptr;   // [256]
@@ -99,6 +101,9 @@ struct PrefillCall {
   const float* router_bias;
   int quant_eighths;
   const aima_moe_debug_views* debug;
+  // qualification: routing supplied by the harness instead of the router's (ids i32 [T, 8], weights BF16 [T, 8])
+  const int32_t* forced_ids = nullptr;
+  const void* forced_weights = nullptr;
   // optional fused exit: RMSNorm of the layer output with this weight (the next layer's input norm)
   const void* next_norm_weight = nullptr;
   void* next_norm_out = nullptr;

@@ -77,6 +77,8 @@ class Metrics(ctypes.Structure):
         ("workspace_bytes", c_uint64), ("derived_weight_bytes", c_uint64),
         ("last_padded_routed_rows", c_int32), ("device_status", c_int32),
         ("router_candidates", c_uint64), ("router_tokens", c_uint64),
+        ("router_bound_violations", c_uint64), ("router_audited_tokens", c_uint64),
+        ("router_audit_mismatches", c_uint64),
     ]
 
 
@@ -130,9 +132,12 @@ EXPORTS = [
     ("aima_moe_ep_connect", c_int, [c_void_p, c_uint32, c_void_p, c_void_p]),
     ("aima_moe_read_ep_prefill_stages", c_int,
      [c_void_p, ctypes.POINTER(c_float), c_uint32, ctypes.POINTER(c_uint32)]),
+    ("aima_moe_set_forced_routing", c_int, [c_void_p, c_void_p, c_void_p, c_uint32]),
     ("aima_moe_set_tracing", c_int, [c_void_p, c_int]),
     ("aima_moe_read_decode_timeline", c_int,
      [c_void_p, ctypes.POINTER(c_uint64), c_uint32, ctypes.POINTER(c_uint32)]),
+    ("aima_moe_read_decode_block_timelines", c_int,
+     [c_void_p, ctypes.POINTER(c_uint64), c_uint32, ctypes.POINTER(c_uint32), ctypes.POINTER(c_uint32)]),
     ("aima_moe_lm_head_build", c_int, [c_void_p, c_uint32, ctypes.POINTER(c_void_p), c_void_p]),
     ("aima_moe_lm_head_views", c_int,
      [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)]),
@@ -319,6 +324,13 @@ class MoeProvider:
         self._hook_bias = bias
         self.lib.check(self.lib.aima_moe_set_router_hooks(self.handle, _ptr(bias), int(quantize_eighths)))
 
+    def set_forced_routing(self, ids: Any = None, weights: Any = None) -> None:
+        """Qualification: int32 [T, 8] expert ids and BF16 [T, 8] weights used by the next single-layer
+        prefill calls of T tokens instead of the router's; None clears."""
+        self._forced = (ids, weights)          # keep the device tensors alive while set
+        tokens = 0 if ids is None else int(ids.shape[0])
+        self.lib.check(self.lib.aima_moe_set_forced_routing(self.handle, _ptr(ids), _ptr(weights), tokens))
+
     # -- debug views ---------------------------------------------------------
     def make_debug(self, tokens: int, prefill: bool, with_logits: bool = True,
                    with_slot_rows: bool = False) -> tuple[DebugViews, dict[str, Any]]:
@@ -456,6 +468,17 @@ class MoeProvider:
         self.lib.check(self.lib.aima_moe_read_decode_timeline(self.handle, buffer, capacity, ctypes.byref(written)))
         values = list(buffer[: written.value])
         return [values[i:i + 12] for i in range(0, len(values), 12)]
+
+    def decode_block_timelines(self) -> list[list[list[int]]]:
+        """[block][layer][16] GPU nanosecond stamps of the last traced decode launch."""
+        capacity = 256 * MAX_LAYERS * 16
+        buffer = (c_uint64 * capacity)()
+        blocks, layers = c_uint32(), c_uint32()
+        self.lib.check(self.lib.aima_moe_read_decode_block_timelines(self.handle, buffer, capacity,
+                                                                     ctypes.byref(blocks), ctypes.byref(layers)))
+        n_layers = layers.value
+        return [[list(buffer[(b * n_layers + l) * 16:(b * n_layers + l + 1) * 16]) for l in range(n_layers)]
+                for b in range(blocks.value)]
 
     def gemm(self, a: Any, b: Any) -> Any:
         """D[m, n] = A[m, k] . B[n, k]^T on the tensor cores (BF16 in/out)."""

@@ -40,6 +40,20 @@ BYTES_PER_LAYER_WEIGHTS = 1_048_576 + 256 * 6_291_456 + 6_291_456 + 4_096 + 4_09
 DECODE_TRAFFIC_PER_LAYER = 59_460_000
 
 
+MIN_TIMED_SECONDS = 1.0      # the K-step loop is repeated until at least this much has been timed
+MAX_REPEATS = 400
+
+
+def decode_config(world: int) -> dict:
+    """The `config` object of the decode line; both arms (--impl ours / reference) print exactly this."""
+    per_rank = 256 // max(world, 1)
+    return {"workload": f"decode_b1_stack{LAYERS} (BASELINE config 1)", "layers": LAYERS,
+            "hidden": HIDDEN, "experts": 256, "top_k": 8,
+            "l2": "inputs larger than L2 (2.3 GB of weights per step)",
+            "multi_gpu": (f"expert parallel, {per_rank} experts per GPU, per-slot down products "
+                          "exchanged by peer stores over NVLink") if world > 1 else "single GPU"}
+
+
 def measured_peaks() -> tuple[float, str]:
     path = ROOT / "MEASURED_PEAKS.json"
     try:
@@ -161,10 +175,10 @@ def run_reference(args) -> None:
     line = {
         "impl": "reference", "metric": "moe_decode_b1_tokens_per_second", "value": value,
         "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "decode_b1_stack40 (BASELINE config 1)", "layers": LAYERS,
-                   "timed_tokens": steps, "note": "CPU path; bounded sample extrapolated to 40 layers"},
+        "config": decode_config(args.gpus),
+        "timed_tokens": steps, "note": "CPU path; bounded sample extrapolated to 40 layers",
         "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -210,20 +224,37 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def timed(step_fn) -> tuple[float, int, float]:
+        """Times exactly args.steps steps per repeat (barrier + synchronize on both sides, CUDA events on the
+        launching stream, maximum over ranks) and repeats until MIN_TIMED_SECONDS have been timed; returns
+        the median ms per step, the number of repeats and the total timed milliseconds."""
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        per_step, total = [], 0.0
+        while True:
+            barrier()
+            start.record()
+            for step in range(args.steps):
+                step_fn(step)
+            stop.record()
+            barrier()
+            ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+            if distributed:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)       # every rank sees the same figure, hence the same repeat count
+            ms = float(ms.item())
+            per_step.append(ms / args.steps)
+            total += ms
+            if total >= MIN_TIMED_SECONDS * 1000.0 or len(per_step) >= MAX_REPEATS:
+                return statistics.median(per_step), len(per_step), total
+
     # ---- device-resident loop ----
     for step in range(args.warmup):
         provider.decode_stack(buffers[step & 1], buffers[(step + 1) & 1])
     provider.sync_metrics()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for step in range(args.steps):
-        provider.decode_stack(buffers[(args.warmup + step) & 1], buffers[(args.warmup + step + 1) & 1])
-    stop.record()
-    barrier()
-    device_ms = start.elapsed_time(stop)
+    offset = args.warmup & 1
+    device_ms_per_step, repeats, device_total_ms = timed(
+        lambda step: provider.decode_stack(buffers[(offset + step) & 1], buffers[(offset + step + 1) & 1]))
     provider.sync_metrics()
 
     # ---- end to end through the public call with host buffers ----
@@ -233,7 +264,7 @@ def run_ours(args) -> None:
     dev_in = torch.empty(HIDDEN, dtype=torch.bfloat16, device=device)
     dev_out = torch.empty(HIDDEN, dtype=torch.bfloat16, device=device)
 
-    def e2e_step():
+    def e2e_step(_step=0):
         dev_in.copy_(host_in, non_blocking=True)
         provider.decode_stack(dev_in, dev_out)
         host_out.copy_(dev_out, non_blocking=True)
@@ -242,46 +273,39 @@ def run_ours(args) -> None:
 
     for _ in range(max(3, args.warmup)):
         e2e_step()
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e_start.record()
-    for _ in range(args.steps):
-        e2e_step()
-    e_stop.record()
-    barrier()
-    e2e_ms = e_start.elapsed_time(e_stop)
+    e2e_ms_per_step, e2e_repeats, _ = timed(e2e_step)
     clocks = sampler.stop()
     provider.sync_metrics()
 
+    # ---- N > 1: are the ranks' results the single-GPU bits?  (outside the timed region) ----
+    parity = None
     if distributed:
-        times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=device)
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        device_ms, e2e_ms = (float(v) for v in times.tolist())
+        parity = expert_parallel_parity(package, provider, synth, device, rank, world, dist)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
-        tokens = args.steps                        # expert parallel: all ranks work on the same token
-        value = tokens / (device_ms / 1000.0)
-        achieved = BYTES_PER_TOKEN * args.steps / (device_ms / 1000.0) / 1.0e9
+        value = 1000.0 / device_ms_per_step        # expert parallel: all ranks work on the same token
+        achieved = BYTES_PER_TOKEN / (device_ms_per_step / 1000.0) / 1.0e9
         line = {
             "metric": "moe_decode_b1_tokens_per_second", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": device_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak",
+            "ms_per_step": device_ms_per_step, "higher_is_better": True,
+            # one token stream served by N GPUs: the total work is fixed as N grows
+            "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"decode_b1_stack{LAYERS} (BASELINE config 1)", "layers": LAYERS,
-                       "hidden": HIDDEN, "experts": 256, "top_k": 8,
-                       "l2": "inputs larger than L2 (2.3 GB of weights per step)",
-                       "multi_gpu": (f"expert parallel, {per_rank} experts per GPU, per-slot down products "
-                                     "exchanged by peer stores over NVLink") if world > 1 else "single GPU"},
+            "config": decode_config(world),
+            "timing": {"repeats": repeats, "steps_per_repeat": args.steps, "timed_seconds": device_total_ms / 1000.0,
+                       "statistic": "median over the repeats of (K-step loop time / K)"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak * world, "unit": "GB/s",
                          "frac": achieved / (peak * world), "traffic": DECODE_TRAFFIC_PER_LAYER * LAYERS,
                          "peak_source": peak_kind, "bytes_per_step": BYTES_PER_TOKEN},
-            "e2e": {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s",
-                    "h2d_bytes_per_step": HIDDEN * 2, "d2h_bytes_per_step": HIDDEN * 2},
-            "gpu_launches": args.steps,
+            "e2e": {"value": 1000.0 / e2e_ms_per_step, "unit": "tokens/s",
+                    "h2d_bytes_per_step": HIDDEN * 2, "d2h_bytes_per_step": HIDDEN * 2, "repeats": e2e_repeats},
+            "gpu_launches": args.steps * repeats,
             "clocks": clocks,
         }
+        if parity is not None:
+            line["parity"] = parity
         if world == 1 and not args.no_prefill:
             line["prefill"] = prefill_layer_numbers(package, device, 8192, 20, "zipf", weights=keep[0])
         if world == 1 and not args.no_cpu_baseline:
@@ -291,6 +315,41 @@ def run_ours(args) -> None:
     provider.release()
     if distributed:
         dist.destroy_process_group()
+
+
+def expert_parallel_parity(package, provider, synth, device, rank: int, world: int, dist) -> dict:
+    """Checks, outside any timed region, that every rank ends a decode step with the same bits and that
+    these are the bits a single GPU computes (rank 0 runs the first layers alone with all 256 experts)."""
+    import hashlib
+
+    import torch
+
+    check_layers = min(2, LAYERS)
+    x = synth.activations(SEED + 1, 1, "residual", 0)[0].to(device)
+    y = torch.empty_like(x)
+    provider.decode_stack(x, y, first_layer=0, n_layers=check_layers)
+    provider.sync_metrics()
+    digest = hashlib.sha256(y.cpu().view(torch.int16).numpy().tobytes()).hexdigest()
+    digests = [None] * world
+    dist.all_gather_object(digests, digest)
+    single_equal = None
+    if rank == 0:
+        single = package.MoeProvider(layers=check_layers)
+        try:
+            keep = []
+            for layer in range(check_layers):
+                weights = synth.layer_weights_cuda_fast(SEED, layer, device)
+                single.bind_layer(layer, weights)
+                keep.append(weights)
+            z = torch.empty_like(x)
+            single.decode_stack(x, z, first_layer=0, n_layers=check_layers)
+            single.sync_metrics()
+            single_equal = bool(torch.equal(z, y))
+        finally:
+            single.release()
+    dist.barrier()
+    return {"layers_checked": check_layers, "ranks_identical": len(set(digests)) == 1,
+            "equals_single_gpu": single_equal, "sha256": digest}
 
 
 PREFILL_FLOP_PER_TOKEN = 50_331_648 + 6_295_552 + 1_048_576            # routed, shared, router

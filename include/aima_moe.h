@@ -95,6 +95,11 @@ typedef struct aima_moe_config {
  * the other (the copies and the HBM-bound products slow each other down), so it is off by default. */
 #define AIMA_MOE_FLAG_EP_PIPELINE_2 32u
 #define AIMA_MOE_FLAG_EP_PIPELINE_4 64u
+/* Qualification of the certified prefill router: every 64th token is ALSO routed from all 256 canonical
+ * logits; aima_moe_metrics counts the tokens audited and those whose expert ids differed.  (The idea of
+ * the reference's certified LM head, native/src/native_lm_head_certificate.hip.cpp:33-39, applied to
+ * the router; the reference's own router has no filter to audit.) */
+#define AIMA_MOE_FLAG_AUDIT_ROUTER 256u
 /* Decode, for A/B timing and qualification: do not predict the next layer's experts (its router applied
  * to the current layer's input) and do not request their rows ahead of the routing.  Same bits either
  * way; with the prediction a layer's weight stream overlaps the hand-overs of the previous layer. */
@@ -160,6 +165,13 @@ typedef struct aima_moe_metrics {
   uint64_t router_candidates;    /* experts recomputed exactly by the certified
                                     prefill router since prepare()             */
   uint64_t router_tokens;        /* tokens it routed                           */
+  uint64_t router_bound_violations; /* tokens one of whose candidates lay further
+                                    from its tensor-core logit than the filter's
+                                    bound allows; such a token is routed from all
+                                    256 canonical logits instead (expected: 0)  */
+  uint64_t router_audited_tokens;   /* AIMA_MOE_FLAG_AUDIT_ROUTER: tokens also
+                                    routed from all 256 canonical logits        */
+  uint64_t router_audit_mismatches; /* ... whose ids differed (expected: 0)      */
 } aima_moe_metrics;
 
 /* Validates the configuration, selects the current CUDA device, allocates the
@@ -177,6 +189,15 @@ int aima_moe_bind_layer(aima_moe_handle* handle, uint32_t layer,
  * multiples of 1/8, used to build skewed and tie-heavy routing in benchmarks. */
 int aima_moe_set_router_hooks(aima_moe_handle* handle, const void* bias_f32,
                               int quantize_eighths);
+
+/* Qualification hook mirroring the reference's "oracle-seeded routing" rerun
+ * (native/src/native_moe_prefill.hip.cpp:1059-1123): while set, single-GPU
+ * aima_moe_prefill_launch calls of exactly `tokens` rows use these expert ids
+ * (int32 [tokens, 8], device) and routing weights (bf16 [tokens, 8], device)
+ * instead of the router's, which isolates the expert arithmetic from tie-order
+ * effects.  The pointers must stay valid until cleared with (NULL, NULL, 0). */
+int aima_moe_set_forced_routing(aima_moe_handle* handle, const int32_t* ids,
+                                const void* weights_bf16, uint32_t tokens);
 
 /* Prefill MoE half of `layer` for `tokens` rows.
  * h2 = post-attention RMSNorm output, residual = after_attn, both bf16
@@ -313,16 +334,24 @@ int aima_moe_ep_connect(aima_moe_handle* handle, uint32_t peer, const void* ipc_
 
 /* Tracing, the counterpart of AIMA_NATIVE_PREFILL_TIMELINE
  * (native/src/native_resident_engine.hip.cpp:105-108, 1226-1259): when enabled,
- * block 0 of the decode kernel stamps the GPU's nanosecond timer at
+ * the blocks of the decode kernel stamp the GPU's nanosecond timer at
  * AIMA_MOE_DECODE_TRACE_STAMPS points of every layer (layer start, norm done,
- * router/shared rows done, logits barrier, top-8 done, routed gate/up done,
- * activation barrier, activations loaded, down region landed, down dots done,
- * output stored, output barrier).  read_decode_timeline synchronises and copies
+ * router/shared rows done, logits arrived, layer plan published, routed gate/up
+ * done, activation barrier, activations loaded, (same), down dots done, output
+ * stored, (same)).  read_decode_timeline synchronises and copies block 0's
  * layers x AIMA_MOE_DECODE_TRACE_STAMPS stamps of the last decode launch. */
 #define AIMA_MOE_DECODE_TRACE_STAMPS 12
 int aima_moe_set_tracing(aima_moe_handle* handle, int enabled);
 int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t* stamps_ns,
                                   uint32_t capacity, uint32_t* written);
+/* The same for EVERY block of the decode kernel, which is what shows the skew between blocks at the
+ * kernel's grid-wide hand-overs: *blocks x *layers x AIMA_MOE_DECODE_TRACE_SLOTS words; slots 0-11 as
+ * above, 12-15 stamped by the block's copy-issuing warp (router / shared items placed, blind issue
+ * over, last gate/up chunk placed, last down item placed).  AIMA_MOE_ERR_CAPACITY if the buffer is
+ * too small (at most 256 blocks x AIMA_MOE_MAX_LAYERS). */
+#define AIMA_MOE_DECODE_TRACE_SLOTS 16
+int aima_moe_read_decode_block_timelines(aima_moe_handle* handle, uint64_t* stamps_ns, uint32_t capacity,
+                                         uint32_t* blocks, uint32_t* layers);
 
 /* With tracing on and world > 1: milliseconds of the AIMA_MOE_EP_PREFILL_STAGES
  * stages of the last expert-parallel prefill call on this rank (route, routing

@@ -739,3 +739,59 @@ int aima_or_lm_head_certify(const uint16_t* weight, const int8_t* q, const float
 #ifdef __cplusplus
 }
 #endif
+
+/* Prefill routing of `tokens` rows at once (OpenMP over the rows): BF16-rounded logits, then the
+ * prefill selection rule; the same two steps aima_or_prefill_layer takes per row. */
+void aima_or_router_prefill_rows(const uint16_t* h2, const aima_or_layer* L, int tokens,
+                                 float* logits, int32_t* ids, float* scores, uint16_t* weights) {
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < tokens; ++t) {
+    float* row = logits + (size_t)t * AIMA_E;
+    aima_or_router_logits(h2 + (size_t)t * AIMA_H, L->router, L->router_bias,
+                          L->router_quant_eighths, row);
+    for (int e = 0; e < AIMA_E; ++e) row[e] = bf2f(f2bf(row[e]));
+    aima_or_topk_prefill(row, ids + (size_t)t * AIMA_K, scores + (size_t)t * AIMA_K,
+                         weights + (size_t)t * AIMA_K);
+  }
+}
+
+/* aima_or_prefill_layer with the routing supplied by the caller for every selected row (ids and BF16
+ * weights indexed by position in `sel`): the expert arithmetic alone, as in the reference's
+ * "oracle-seeded routing" rerun (native/src/native_moe_prefill.hip.cpp:1059-1123). */
+int aima_or_prefill_layer_forced(const uint16_t* h2_all, const uint16_t* residual_all,
+                                 const aima_or_layer* L, const int32_t* sel, int n_sel,
+                                 const int32_t* forced_ids, const uint16_t* forced_weights,
+                                 uint16_t* out, uint16_t* routed_out, uint16_t* shared_out) {
+  int failed = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int s = 0; s < n_sel; ++s) {
+    const size_t t = sel ? (size_t)sel[s] : (size_t)s;
+    const uint16_t* h2 = h2_all + t * AIMA_H;
+    const int32_t* ids = forced_ids + (size_t)s * AIMA_K;
+    const uint16_t* weights = forced_weights + (size_t)s * AIMA_K;
+    int missing = 0;
+    for (int r = 0; r < AIMA_K; ++r)
+      if (ids[r] < 0 || ids[r] >= AIMA_E || L->gate_up[ids[r]] == NULL || L->down[ids[r]] == NULL) missing = 1;
+    if (missing) { failed = 1; continue; }
+    uint16_t shared_scaled[AIMA_H];
+    shared_expert(h2, L, shared_scaled);
+    uint16_t* slot_out = (uint16_t*)malloc(sizeof(uint16_t) * AIMA_K * AIMA_H);
+    for (int r = 0; r < AIMA_K; ++r) {
+      uint16_t gate_up[2 * AIMA_I];
+      uint16_t act[AIMA_I];
+      for (int i = 0; i < 2 * AIMA_I; ++i)
+        gate_up[i] = f2bf(aima_or_dot(h2, L->gate_up[ids[r]] + (size_t)i * AIMA_H, AIMA_H));
+      aima_or_expert_silu_mul(gate_up, act, 1);
+      const float wr = bf2f(weights[r]);
+      for (int h = 0; h < AIMA_H; ++h)
+        slot_out[r * AIMA_H + h] = f2bf(aima_or_dot(act, L->down[ids[r]] + (size_t)h * AIMA_I, AIMA_I) * wr);
+    }
+    uint16_t routed[AIMA_H];
+    aima_or_sum8(slot_out, routed, 1);
+    aima_or_add_pair(routed, shared_scaled, residual_all + t * AIMA_H, NULL, out + (size_t)s * AIMA_H, AIMA_H);
+    free(slot_out);
+    if (routed_out) memcpy(routed_out + (size_t)s * AIMA_H, routed, sizeof routed);
+    if (shared_out) memcpy(shared_out + (size_t)s * AIMA_H, shared_scaled, sizeof shared_scaled);
+  }
+  return failed ? -1 : 0;
+}

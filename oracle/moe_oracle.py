@@ -73,6 +73,12 @@ def lib() -> ctypes.CDLL:
         _LIB.aima_or_prefill_layer.restype = c_int
         _LIB.aima_or_prefill_layer.argtypes = [c_void_p, c_void_p, POINTER(Layer), c_void_p, c_int,
                                                c_void_p, POINTER(Debug)]
+        _LIB.aima_or_router_prefill_rows.restype = None
+        _LIB.aima_or_router_prefill_rows.argtypes = [c_void_p, POINTER(Layer), c_int, c_void_p, c_void_p, c_void_p,
+                                                     c_void_p]
+        _LIB.aima_or_prefill_layer_forced.restype = c_int
+        _LIB.aima_or_prefill_layer_forced.argtypes = [c_void_p, c_void_p, POINTER(Layer), c_void_p, c_int, c_void_p,
+                                                      c_void_p, c_void_p, c_void_p, c_void_p]
         _LIB.aima_or_dispatch_plan.restype = None
         _LIB.aima_or_dispatch_plan.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         _LIB.aima_or_gemv.restype = None
@@ -198,15 +204,30 @@ def router_prefill(h2: torch.Tensor, layer: OracleLayer) -> dict[str, torch.Tens
     ids = torch.zeros(tokens, K, dtype=torch.int32)
     scores = torch.zeros(tokens, K, dtype=torch.float32)
     weights = torch.zeros(tokens, K, dtype=torch.bfloat16)
-    library = lib()
-    for t in range(tokens):
-        library.aima_or_router_logits(c_void_p(h2[t].data_ptr()), layer.c.router, layer.c.router_bias,
-                                      layer.c.router_quant_eighths, c_void_p(logits[t].data_ptr()))
-    logits = logits.to(torch.bfloat16).to(torch.float32).contiguous()
-    for t in range(tokens):
-        library.aima_or_topk_prefill(c_void_p(logits[t].data_ptr()), c_void_p(ids[t].data_ptr()),
-                                     c_void_p(scores[t].data_ptr()), c_void_p(weights[t].data_ptr()))
+    lib().aima_or_router_prefill_rows(_bf16_ptr(h2), ctypes.byref(layer.c), tokens, c_void_p(logits.data_ptr()),
+                                      c_void_p(ids.data_ptr()), c_void_p(scores.data_ptr()), _bf16_ptr(weights))
     return {"logits": logits, "ids": ids, "scores": scores, "weights": weights}
+
+
+def prefill_layer_forced(h2: torch.Tensor, residual: torch.Tensor, layer: OracleLayer, select: list[int],
+                         ids: torch.Tensor, weights: torch.Tensor) -> dict[str, torch.Tensor]:
+    """Expert arithmetic of the rows in `select` with the routing supplied: ids int32 [len(select), 8],
+    weights BF16 [len(select), 8]."""
+    h2 = h2.reshape(-1, H).contiguous()
+    residual = residual.reshape(-1, H).contiguous()
+    sel = torch.tensor(list(select), dtype=torch.int32)
+    ids = ids.to(torch.int32).contiguous()
+    weights = weights.to(torch.bfloat16).contiguous()
+    assert ids.shape == (len(select), K) and weights.shape == (len(select), K)
+    out = torch.zeros(len(select), H, dtype=torch.bfloat16)
+    routed = torch.zeros(len(select), H, dtype=torch.bfloat16)
+    shared = torch.zeros(len(select), H, dtype=torch.bfloat16)
+    status = lib().aima_or_prefill_layer_forced(_bf16_ptr(h2), _bf16_ptr(residual), ctypes.byref(layer.c),
+                                                c_void_p(sel.data_ptr()), len(select), c_void_p(ids.data_ptr()),
+                                                _bf16_ptr(weights), _bf16_ptr(out), _bf16_ptr(routed), _bf16_ptr(shared))
+    if status != 0:
+        raise RuntimeError("oracle: a forced expert id is out of range or has no weights materialised")
+    return {"out": out, "routed": routed, "shared_scaled": shared}
 
 
 def topk_prefill(logits: torch.Tensor) -> dict[str, torch.Tensor]:

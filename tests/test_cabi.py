@@ -36,7 +36,7 @@ def test_struct_sizes_match_the_header(package):
     assert ctypes.sizeof(p.Config) == 12 * 4
     assert ctypes.sizeof(p.LayerWeights) == 8 + 8 * 16
     assert ctypes.sizeof(p.DebugViews) == 8 + 12 * 8
-    assert ctypes.sizeof(p.Metrics) == 8 + 5 * 8 + 8 + 16
+    assert ctypes.sizeof(p.Metrics) == 8 + 5 * 8 + 8 + 16 + 24
 
 
 def test_argument_checks_fail_closed_without_a_device(package, built_library):

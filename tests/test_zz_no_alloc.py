@@ -93,13 +93,18 @@ def test_noalloc_decode_rejects_what_it_cannot_hold(package, layers):
     lib = package.load_library()
     assert lib.aima_moe_decode_layers_noalloc(None, 1, None, None, ctypes.c_float(1e-6), None, None) == -1
     # host memory for the vectors or for a weight: refused on the host with an error code, nothing enqueued
+    # (raw pointers through the C ABI: the Python wrapper itself would refuse a CPU tensor)
+    struct = package.provider.layer_weights_struct(layers[0])
+    array = (type(struct) * 1)(struct)
     host_x = x.cpu()
-    with pytest.raises(package.AimaMoeError) as host_vector:
-        package.provider.decode_layers_noalloc([layers[0]], host_x, y)
-    assert host_vector.value.status == -1
-    host_weight = dict(layers[0])
-    host_weight["router"] = layers[0]["router"].cpu()
-    with pytest.raises(package.AimaMoeError) as host_tensor:
-        package.provider.decode_layers_noalloc([host_weight], x, y)
-    assert host_tensor.value.status == -1
-    torch.cuda.synchronize()                                          # the context is untouched
+    pointer = lambda tensor: ctypes.c_void_p(int(tensor.data_ptr()))
+    status = lib.aima_moe_decode_layers_noalloc(array, 1, pointer(host_x), pointer(y), ctypes.c_float(1e-6), None, None)
+    assert status == -1 and b"current device" in lib.aima_moe_last_error_string()
+    host_router = layers[0]["router"].cpu()
+    struct.router = pointer(host_router)
+    array = (type(struct) * 1)(struct)
+    status = lib.aima_moe_decode_layers_noalloc(array, 1, pointer(x), pointer(y), ctypes.c_float(1e-6), None, None)
+    assert status == -1
+    torch.cuda.synchronize()                                          # nothing ran, the context is untouched
+    package.provider.decode_layers_noalloc([layers[0]], x, y)
+    torch.cuda.synchronize()
