@@ -68,6 +68,7 @@ struct TcExtra {
   int sm_count;         // persistent grid size
   uint64_t a_rows;      // rows of the A allocation (TMA bounds; reads beyond are zero-filled)
   int experts_in_b;     // experts held in b0 (expert modes), else 1
+  bool pair = false;    // expert modes: two-SM form; the plan's tiles then hold up to 256 rows
 };
 
 // tcgen05 / TMEM / TMA implementation (grouped_gemm_tc.cu).

@@ -171,6 +171,90 @@ __device__ __forceinline__ void store_staged(const uint8_t* stage, int lane, __n
 }
 
 
+// One epilogue warp drains its part of a 128-row x 256-column FP32 accumulator: TMEM lanes
+// 32 ew .. 32 ew + 31 (rows row0 + 32 ew ... of the output), half `eh` of the unit's columns.
+template <int MODE>
+__device__ __forceinline__ void drain_accumulator(const GroupedGemm& g, const TcProblem& pb, uint32_t tmem_base,
+                                                  int buf, int ew, int eh, int lane, uint8_t* stage, int chunk,
+                                                  int row0, int rows) {
+  constexpr bool kDual = (MODE == kGemmExpertGateUp || MODE == kGemmSharedGateUp);
+  const int r = ew * 32 + lane;                // row inside the tile
+  const bool row_ok = r < rows;
+  const int row = row0 + r;
+  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(buf * kBN);
+  const int rows_ok = min(32, rows - ew * 32);           // valid rows among this warp's 32 (may be <= 0)
+  if (kDual) {
+    // columns [0,128) gate, [128,256) up  ->  128 activations per row, stored 64 at a time
+    __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + chunk * (kBN / 2);
+#pragma unroll 1
+    for (int c0 = eh * (kBN / 4); c0 < (eh + 1) * (kBN / 4); c0 += 64) {
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t gr[32], ur[32];
+        tmem_ld32(taddr + c0 + 32 * half, gr);
+        tmem_ld32(taddr + kBN / 2 + c0 + 32 * half, ur);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float gate = round_bf16(__uint_as_float(gr[j]));
+          const float up = round_bf16(__uint_as_float(ur[j]));
+          const float s = det_silu(gate);
+          v[j] = (MODE == kGemmExpertGateUp) ? __fmul_rn(round_bf16(s), up) : __fmul_rn(s, up);
+        }
+        stage_32(stage, lane, half, v);
+      }
+      store_staged(stage, lane, dst + c0, static_cast<size_t>(g.ldc), rows_ok, 64);
+    }
+  } else if (MODE != kGemmPlainF32) {
+    float scale = 1.0f;
+    if (row_ok) {
+      if (MODE == kGemmExpertDown) scale = g.row_scale[g.sorted_rows[row]];
+      if (MODE == kGemmSharedDown) scale = g.row_scale[row];
+    }
+    const int col_base = chunk * kBN;
+    __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + col_base;
+#pragma unroll 1
+    for (int c0 = eh * (kBN / 2); c0 < (eh + 1) * (kBN / 2); c0 += 64) {
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t ar[32];
+        tmem_ld32(taddr + c0 + 32 * half, ar);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float acc = __uint_as_float(ar[j]);
+          if (MODE == kGemmExpertDown) v[j] = __fmul_rn(acc, scale);
+          else if (MODE == kGemmSharedDown) v[j] = __fmul_rn(scale, round_bf16(acc));
+          else v[j] = acc;
+        }
+        stage_32(stage, lane, half, v);
+      }
+      store_staged(stage, lane, dst + c0, static_cast<size_t>(g.ldc), rows_ok,
+                   max(0, min(64, pb.n_valid - col_base - c0)));
+    }
+  } else {
+    // FP32 output (approximate router logits): every thread stores its own row
+    const int col_base = chunk * kBN;
+#pragma unroll 1
+    for (int c0 = eh * (kBN / 2); c0 < (eh + 1) * (kBN / 2); c0 += 32) {
+      uint32_t ar[32];
+      tmem_ld32(taddr + c0, ar);
+      tmem_ld_wait();
+      if (row_ok) {
+        float4* out = reinterpret_cast<float4*>(g.c_f32 + static_cast<size_t>(row) * g.ldc + col_base + c0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (col_base + c0 + 4 * j + 4 <= pb.n_valid)
+            out[j] = make_float4(__uint_as_float(ar[4 * j]), __uint_as_float(ar[4 * j + 1]),
+                                 __uint_as_float(ar[4 * j + 2]), __uint_as_float(ar[4 * j + 3]));
+        }
+      }
+    }
+  }
+}
+
 template <int MODE, bool kGather = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) {
@@ -366,82 +450,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       if (!mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_flag)) { alive = false; if (lane == 0) timeout(); break; }
       tc_fence_after();
-      const int r = ew * 32 + lane;                // row inside the tile
-      const bool row_ok = r < rows;
-      const int row = row0 + r;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + static_cast<uint32_t>(buf * kBN);
-      uint8_t* stage = smem_gen + kStages * kStageBytes + 256 + (warp - 4) * kStoreStageBytes;
-      const int rows_ok = min(32, rows - ew * 32);           // valid rows among this warp's 32 (may be <= 0)
-      if (kDual) {
-        // columns [0,128) gate, [128,256) up  ->  128 activations per row, stored 64 at a time
-        __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + chunk * (kBN / 2);
-#pragma unroll 1
-        for (int c0 = eh * (kBN / 4); c0 < (eh + 1) * (kBN / 4); c0 += 64) {
-#pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
-            uint32_t gr[32], ur[32];
-            tmem_ld32(taddr + c0 + 32 * half, gr);
-            tmem_ld32(taddr + kBN / 2 + c0 + 32 * half, ur);
-            tmem_ld_wait();
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float gate = round_bf16(__uint_as_float(gr[j]));
-              const float up = round_bf16(__uint_as_float(ur[j]));
-              const float s = det_silu(gate);
-              v[j] = (MODE == kGemmExpertGateUp) ? __fmul_rn(round_bf16(s), up) : __fmul_rn(s, up);
-            }
-            stage_32(stage, lane, half, v);
-          }
-          store_staged(stage, lane, dst + c0, static_cast<size_t>(g.ldc), rows_ok, 64);
-        }
-      } else if (MODE != kGemmPlainF32) {
-        float scale = 1.0f;
-        if (row_ok) {
-          if (MODE == kGemmExpertDown) scale = g.row_scale[g.sorted_rows[row]];
-          if (MODE == kGemmSharedDown) scale = g.row_scale[row];
-        }
-        const int col_base = chunk * kBN;
-        __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + col_base;
-#pragma unroll 1
-        for (int c0 = eh * (kBN / 2); c0 < (eh + 1) * (kBN / 2); c0 += 64) {
-#pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
-            uint32_t ar[32];
-            tmem_ld32(taddr + c0 + 32 * half, ar);
-            tmem_ld_wait();
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float acc = __uint_as_float(ar[j]);
-              if (MODE == kGemmExpertDown) v[j] = __fmul_rn(acc, scale);
-              else if (MODE == kGemmSharedDown) v[j] = __fmul_rn(scale, round_bf16(acc));
-              else v[j] = acc;
-            }
-            stage_32(stage, lane, half, v);
-          }
-          store_staged(stage, lane, dst + c0, static_cast<size_t>(g.ldc), rows_ok,
-                       max(0, min(64, pb.n_valid - col_base - c0)));
-        }
-      } else {
-        // FP32 output (approximate router logits): every thread stores its own row
-        const int col_base = chunk * kBN;
-#pragma unroll 1
-        for (int c0 = eh * (kBN / 2); c0 < (eh + 1) * (kBN / 2); c0 += 32) {
-          uint32_t ar[32];
-          tmem_ld32(taddr + c0, ar);
-          tmem_ld_wait();
-          if (row_ok) {
-            float4* out = reinterpret_cast<float4*>(g.c_f32 + static_cast<size_t>(row) * g.ldc + col_base + c0);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (col_base + c0 + 4 * j + 4 <= pb.n_valid)
-                out[j] = make_float4(__uint_as_float(ar[4 * j]), __uint_as_float(ar[4 * j + 1]),
-                                     __uint_as_float(ar[4 * j + 2]), __uint_as_float(ar[4 * j + 3]));
-            }
-          }
-        }
-      }
+      drain_accumulator<MODE>(g, pb, tmem_base, buf, ew, eh, lane,
+                              smem_gen + kStages * kStageBytes + 256 + (warp - 4) * kStoreStageBytes, chunk, row0, rows);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(buf));
@@ -450,6 +460,281 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
   tc_fence_before();
   __syncthreads();
   if (warp == 2) tmem_dealloc(tmem_base, kTmemColumns);
+}
+
+// ---------------------------------------------------------------------------
+// Two-SM form.  A pair of blocks (a cluster of two) works on one tile of up to 256 rows of one expert x
+// 256 accumulator columns with tcgen05.mma.cta_group::2: block r of the pair holds rows 128 r .. 128 r + 127
+// of A and one half of B (128 weight rows) per K block, 32 KB per stage instead of 48, so six stages fit
+// and every weight byte enters shared memory once per 256 rows instead of once per 128.  The leader (block 0
+// of the pair) issues the MMAs for both; each block drains the 128 accumulator rows in its own tensor memory.
+//
+//   full[s]    leader only.  Completed by the TMA loads of BOTH blocks (cta_group::2 loads signal the
+//              leader's barrier), by the leader's gather threads and by the peer's forwarder.
+//   gdone[s]   peer only, gather mode: its gather threads' copies of a stage have landed; its forwarder
+//              (the peer's otherwise idle MMA warp) then arrives on the leader's full[s].
+//   empty[s]   both blocks: the MMAs reading stage s have retired (tcgen05.commit, multicast to the pair).
+//   tfull[b]   both blocks: accumulator b is complete (commit, multicast).
+//   tempty[b]  leader only: the eight epilogue warps of each block have drained accumulator b.
+// No load uses cluster multicast: each block fetches its own operands.
+// ---------------------------------------------------------------------------
+constexpr int kStages2 = 6;
+constexpr int kStage2ABytes = kBM * kBK * 2;              // 16 KB: this block's 128 rows of A
+constexpr int kStage2BBytes = (kBN / 2) * kBK * 2;        // 16 KB: this block's half of B
+constexpr int kStage2Bytes = kStage2ABytes + kStage2BBytes;
+constexpr int kTc2BarrierBytes = 512;
+constexpr int kTc2SmemBytes = kStages2 * kStage2Bytes + 1024 /*alignment slack*/ + kTc2BarrierBytes +
+                              kEpilogueWarps * kStoreStageBytes;
+static_assert(kTc2SmemBytes <= 227 * 1024, "two-SM product kernel exceeds 227 KB of shared memory");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in block `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
+// TMA tile load of one block of the pair; the bytes are accounted on the LEADER's barrier
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               :: "r"(smem_dst), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  const uint32_t zero = 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+// arrives on the barrier at the same shared-memory offset in both blocks of the pair once the MMAs issued so far retire
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               :: "r"(bar), "h"(both) : "memory");
+}
+
+// D = F32, A = B = BF16, both K-major, M = 256 (128 rows per block), N = 256.
+constexpr uint32_t kInstrDesc2 =
+    (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kBN >> 3) << 17) |
+    (static_cast<uint32_t>((2 * kBM) >> 4) << 24);
+
+template <int MODE, bool kGather>
+__global__ void __launch_bounds__(kTcThreads, 1)
+grouped_gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) {
+  static_assert(MODE == kGemmExpertGateUp || MODE == kGemmExpertDown, "two-SM form: the expert products");
+  constexpr bool kDual = (MODE == kGemmExpertGateUp);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages2 * kStage2Bytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages2 + s); };
+  auto gdone_bar = [&](int s) { return bar_base + 8u * (2 * kStages2 + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (3 * kStages2 + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (3 * kStages2 + 2 + b); };
+  uint8_t* tail = smem_gen + kStages2 * kStage2Bytes + 8 * (3 * kStages2 + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 8);
+  uint8_t* store_stage = smem_gen + kStages2 * kStage2Bytes + kTc2BarrierBytes;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0: leader of the pair
+  const bool leader = rank == 0;
+  const GroupedGemm& g = pb.g;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(full_bar(s), kGather ? 1 + kGatherThreads + 1 : 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(gdone_bar(s), kGatherThreads);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 2 * kEpilogueWarps);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 2) tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemColumns);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // both blocks' barriers exist before either signals the other's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_enter();
+
+  const int n_tiles = g.tile_count != nullptr ? *g.tile_count : g.max_tiles;
+  const int total_units = n_tiles * pb.n_chunks;
+  const int n_pairs = gridDim.x >> 1;
+  const int pair = blockIdx.x >> 1;
+  const int k_blocks = g.k / kBK;
+
+  // unit -> the tile's expert, this block's first row, its number of valid rows (0 .. 128) and the tile's last row
+  auto unit_tile = [&](int unit, int& chunk, int& expert, int& row0, int& rows, int& tile_last) {
+    const int tile = unit / pb.n_chunks;
+    chunk = unit - tile * pb.n_chunks;
+    expert = g.tile_expert[tile] - g.expert_base;
+    const int tile_rows = g.tile_rows[tile];
+    const int tile_row0 = g.tile_row0[tile];
+    tile_last = tile_row0 + tile_rows - 1;
+    row0 = tile_row0 + static_cast<int>(rank) * kBM;
+    rows = max(0, min(kBM, tile_rows - static_cast<int>(rank) * kBM));
+  };
+  auto timeout = [&]() { atomicCAS(pb.status, 0, kStatusTimeoutMbarrier); };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both blocks) -----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int unit = pair; unit < total_units && alive; unit += n_pairs) {
+        int chunk, expert, row0, rows, tile_last;
+        unit_tile(unit, chunk, expert, row0, rows, tile_last);
+        // this block's half of B: gate_up -- the leader takes the 128 gate rows of the chunk, the peer the 128
+        // up rows; down -- rows 128 r .. of the chunk's 256 output columns
+        const int b_row = kDual ? expert * pb.b_rows_per_expert + static_cast<int>(rank) * pb.up_row_offset + chunk * (kBN / 2)
+                                : expert * pb.b_rows_per_expert + chunk * kBN + static_cast<int>(rank) * (kBN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          const uint32_t a_dst = smem_base + stage * kStage2Bytes;
+          const uint32_t b_dst = a_dst + kStage2ABytes;
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
+          const uint32_t leader_full = map_to_rank(full_bar(stage), 0);
+          if (leader) mbar_arrive_expect_tx(full_bar(stage), 2 * (kGather ? kStage2BBytes : kStage2Bytes));
+          if (!kGather) tma_load_2d_pair(a_dst, &maps.a, kb * kBK, row0, leader_full);
+          tma_load_2d_pair(b_dst, &maps.b0, kb * kBK, b_row, leader_full);
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (kGather && (warp == 2 || warp == 3)) {
+    // ------------------------------ A-row gather (both blocks) -----------------
+    const int lt = (warp - 2) * 32 + lane;
+    const int piece = lt & 7;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int unit = pair; unit < total_units && alive; unit += n_pairs) {
+      int chunk, expert, row0, rows, tile_last;
+      unit_tile(unit, chunk, expert, row0, rows, tile_last);
+      int source[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int r = (lt >> 3) + 8 * j;
+        // rows past the tile's end repeat its last row (a tile has at least one row)
+        const int token = g.sorted_rows[min(row0 + r, tile_last)] >> 3;
+        source[j] = token * g.lda + piece * 8;
+      }
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag)) { alive = false; timeout(); break; }
+        const uint32_t base = smem_base + stage * kStage2Bytes;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int r = (lt >> 3) + 8 * j;
+          cp_async_16(base + r * 128 + ((piece ^ (r & 7)) << 4), g.gather_src + source[j] + kb * kBK);
+        }
+        cp_async_arrive_noinc(leader ? full_bar(stage) : gdone_bar(stage));
+        if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+      }
+    }
+    cp_async_wait_all();
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ------------------------------ MMA issuer (leader) ------------------------
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool alive = true;
+      for (int unit = pair; unit < total_units && alive; unit += n_pairs, ++local) {
+        const int buf = local & 1;
+        const uint32_t use = static_cast<uint32_t>(local >> 1);
+        if (!mbar_wait_bounded(tempty_bar(buf), (use & 1u) ^ 1u, abort_flag)) { alive = false; timeout(); break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(buf * kBN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag)) { alive = false; timeout(); break; }
+          if (kGather) fence_async_proxy();
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * kStage2Bytes;
+          const uint32_t b_addr = a_addr + kStage2ABytes;
+          const uint64_t adesc = smem_desc_k_major_sw128(a_addr);
+          const uint64_t bdesc = smem_desc_k_major_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            umma_bf16_pair(tmem_d, adesc + static_cast<uint64_t>(k * 2), bdesc + static_cast<uint64_t>(k * 2),
+                           kInstrDesc2, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(empty_bar(stage));
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+        if (alive) umma_commit_pair(tfull_bar(buf));
+      }
+    } else if (lane == 0 && kGather) {
+      // ------------------------------ forwarder (peer) ---------------------------
+      // this block's gathered rows of a stage have landed: make them visible to the tensor cores and
+      // tell the leader, whose MMA reads them
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int unit = pair; unit < total_units && alive; unit += n_pairs) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(gdone_bar(stage), phase, abort_flag)) { alive = false; timeout(); break; }
+          fence_async_proxy();
+          mbar_arrive_cluster(map_to_rank(full_bar(stage), 0));
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue (both blocks) ---------------------
+    const int ew = (warp - 4) & 3;
+    const int eh = (warp - 4) >> 2;
+    int local = 0;
+    bool alive = true;
+    for (int unit = pair; unit < total_units && alive; unit += n_pairs, ++local) {
+      int chunk, expert, row0, rows, tile_last;
+      unit_tile(unit, chunk, expert, row0, rows, tile_last);
+      const int buf = local & 1;
+      const uint32_t use = static_cast<uint32_t>(local >> 1);
+      if (!mbar_wait_bounded(tfull_bar(buf), use & 1u, abort_flag)) { alive = false; if (lane == 0) timeout(); break; }
+      tc_fence_after();
+      if (rows > 0)
+        drain_accumulator<MODE>(g, pb, tmem_base, buf, ew, eh, lane, store_stage + (warp - 4) * kStoreStageBytes,
+                                chunk, row0, rows);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_rank(tempty_bar(buf), 0));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                 // neither block leaves while the other may still signal it or read its memory
+  if (warp == 2) tmem_dealloc_pair(tmem_base, kTmemColumns);
 }
 
 // ---- host side --------------------------------------------------------------
@@ -486,6 +771,28 @@ cudaError_t launch_mode(const TcMaps& maps, const TcProblem& pb, int grid, cudaS
   const cudaError_t e = opt_in_dynamic_smem<grouped_gemm_tc_kernel<MODE, kGather>>(kTcSmemBytes);
   if (e != cudaSuccess) return e;
   return launch_pdl(grouped_gemm_tc_kernel<MODE, kGather>, dim3(grid), dim3(kTcThreads), kTcSmemBytes, stream, maps, pb);
+}
+
+// two-SM form: clusters of two blocks, launched like launch_pdl
+template <int MODE, bool kGather>
+cudaError_t launch_pair_mode(const TcMaps& maps, const TcProblem& pb, int grid, cudaStream_t stream) {
+  const cudaError_t e = opt_in_dynamic_smem<grouped_gemm_tc2_kernel<MODE, kGather>>(kTc2SmemBytes);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid & ~1);
+  config.blockDim = dim3(kTcThreads);
+  config.dynamicSmemBytes = kTc2SmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = 2;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = t_pdl_relaxed ? 1 : 0;
+  config.attrs = attributes;
+  config.numAttrs = 2;
+  return cudaLaunchKernelEx(&config, grouped_gemm_tc2_kernel<MODE, kGather>, maps, pb);
 }
 
 }  // namespace
@@ -527,6 +834,13 @@ cudaError_t launch_grouped_gemm_tc(GemmMode mode, const GroupedGemm& g, const Tc
   (void)dual;
   if (!ok) return cudaErrorNotSupported;
   const int grid = extra.sm_count;
+  if (extra.pair && g.tile_expert != nullptr && g.parts <= 1) {
+    if (mode == kGemmExpertGateUp)
+      return gather ? launch_pair_mode<kGemmExpertGateUp, true>(maps, pb, grid, stream)
+                    : launch_pair_mode<kGemmExpertGateUp, false>(maps, pb, grid, stream);
+    if (mode == kGemmExpertDown) return launch_pair_mode<kGemmExpertDown, false>(maps, pb, grid, stream);
+    return cudaErrorInvalidValue;      // the plan holds 256-row tiles: only the two-SM kernels can take them
+  }
   switch (mode) {
     case kGemmExpertGateUp:
       return gather ? launch_mode<kGemmExpertGateUp, true>(maps, pb, grid, stream)

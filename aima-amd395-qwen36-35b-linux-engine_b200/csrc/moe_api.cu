@@ -384,6 +384,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
     handle->prefill.exact_router = (config->flags & AIMA_MOE_FLAG_EXACT_ROUTER) != 0;
     handle->prefill.router_audit_stride = (config->flags & AIMA_MOE_FLAG_AUDIT_ROUTER) != 0 ? 64 : 0;
     handle->prefill.fused_dispatch = (config->flags & AIMA_MOE_FLAG_MATERIALIZED_DISPATCH) == 0;
+    handle->prefill.pair_products = (config->flags & AIMA_MOE_FLAG_TWO_SM_PRODUCTS) != 0 && config->world == 1;
     handle->prefill.ep_parts = (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_4)   ? 4
                                : (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_2) ? 2
                                                                                : 1;

@@ -500,12 +500,12 @@ plan_scan_kernel(int32_t* __restrict__ unit_counts, int units, int32_t* __restri
 
 // Exclusive offsets of the 256 experts from their counts, in shared memory (all 256 threads of a
 // block take part); thread 0 .. 255 returns with offsets[0 .. 256] and tile_base[0 .. 256] filled.
-__device__ __forceinline__ int expert_offsets_in_block(const int32_t* __restrict__ expert_counts,
+__device__ __forceinline__ int expert_offsets_in_block(const int32_t* __restrict__ expert_counts, int tile_cap,
                                                        int* offsets, int* tile_base, int* warp_sums) {
   const int e = threadIdx.x;
   const int lane = e & 31, warp = e >> 5;
   const int count = expert_counts[e];
-  int v0 = count, v1 = (count + kTileRows - 1) / kTileRows, v2 = (count + 31) / 32 * 32;
+  int v0 = count, v1 = (count + tile_cap - 1) / tile_cap, v2 = (count + 31) / 32 * 32;
   const int mine0 = v0, mine1 = v1;
 #pragma unroll
   for (int d = 1; d < 32; d *= 2) {
@@ -539,14 +539,14 @@ plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert
                     int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row0,
                     int32_t* __restrict__ tile_rows, int32_t* __restrict__ tile_count,
                     int32_t* __restrict__ padded_rows,
-                    int32_t* __restrict__ sorted_rows, int32_t* __restrict__ row_position) {
+                    int32_t* __restrict__ sorted_rows, int32_t* __restrict__ row_position, int tile_cap) {
   static_assert(kPlanWarps * 32 == kExperts, "one thread per expert in the prologue");
   pdl_enter();
   __shared__ int next[kPlanWarps][kExperts];
   __shared__ int offsets[kExperts + 1];
   __shared__ int tile_base[kExperts + 1];
   __shared__ int warp_sums[24];
-  const int padded = expert_offsets_in_block(expert_counts, offsets, tile_base, warp_sums);
+  const int padded = expert_offsets_in_block(expert_counts, tile_cap, offsets, tile_base, warp_sums);
   if (blockIdx.x == 0) {
     const int e = threadIdx.x;
     const int count = offsets[e + 1] - offsets[e];
@@ -560,8 +560,8 @@ plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert
     for (int t = 0; t < n_tiles; ++t) {
       const int index = tile_base[e] + t;
       tile_expert[index] = e;
-      tile_row0[index] = offsets[e] + t * kTileRows;
-      tile_rows[index] = min(kTileRows, count - t * kTileRows);
+      tile_row0[index] = offsets[e] + t * tile_cap;
+      tile_rows[index] = min(tile_cap, count - t * tile_cap);
     }
   }
   const int warp = threadIdx.x >> 5;
@@ -592,8 +592,9 @@ plan_scatter_kernel(const int32_t* __restrict__ ids, int routed_rows, int expert
 }
 
 // Enqueues the dispatch plan for `rows` routed rows whose expert ids are `ids`.
+// tile_cap: rows per tile of the plan -- 128 for the one-SM product kernels, 256 for the two-SM form
 cudaError_t launch_plan(PrefillWorkspace* ws, const int32_t* ids, int rows, int expert_lo, int expert_hi,
-                        cudaStream_t stream, int* launches) {
+                        cudaStream_t stream, int* launches, int tile_cap = kTileRows) {
   const int units = (rows + kPlanRowsPerWarp - 1) / kPlanRowsPerWarp;
   const int plan_blocks = (units + kPlanWarps - 1) / kPlanWarps;
   cudaError_t code = launch_pdl(plan_count_kernel, dim3(plan_blocks), dim3(kPlanWarps * 32), 0, stream, ids, rows,
@@ -605,7 +606,7 @@ cudaError_t launch_plan(PrefillWorkspace* ws, const int32_t* ids, int rows, int 
     code = launch_pdl(plan_scatter_kernel, dim3(plan_blocks), dim3(kPlanWarps * 32), 0, stream, ids, rows,
                       expert_lo, expert_hi, ws->unit_counts, ws->expert_counts, ws->expert_offsets,
                       ws->tile_expert, ws->tile_row0, ws->tile_rows, ws->tile_count, ws->padded_rows,
-                      ws->sorted_rows, ws->row_position);
+                      ws->sorted_rows, ws->row_position, tile_cap);
   *launches += 3;
   return code;
 }
@@ -1082,7 +1083,13 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   if ((code = cudaEventRecord(ws->join_event, side)) != cudaSuccess)
     return set_error(error, error_bytes, code, "join event of the shared-expert stream");
 
-  if ((code = launch_plan(ws, ws->topk_ids, rows, 0, kExperts, stream, &count)) != cudaSuccess)
+  // Expert products: one block per 128-row tile; the two-SM form (a pair of blocks per 256-row tile) behind a
+  // flag.  Both stream every expert's weights once at T = 8192 and are bound by that stream -- 302 / 170 us
+  // (gate_up / down) against 308 / 218 us for the pair with materialised rows, and the pair's row gather has to
+  // cross to the leader's barrier, which doubles its gate_up time -- so the simpler form is the default.
+  const bool pair_products = ws->pair_products && !ws->use_simt_gemm;
+  if ((code = launch_plan(ws, ws->topk_ids, rows, 0, kExperts, stream, &count, pair_products ? 2 * kTileRows : kTileRows)) !=
+      cudaSuccess)
     return set_error(error, error_bytes, code, "dispatch plan");
 
   // Dispatch is fused into the gate_up kernel: two of its warps fetch each tile's rows by token index
@@ -1108,6 +1115,7 @@ int prefill_layer_launch(PrefillWorkspace* ws, const PrefillCall& call, cudaStre
   TcExtra extra{};
   extra.status = ws->status; extra.sm_count = ws->sm_count;
   extra.experts_in_b = call.experts_local;
+  extra.pair = pair_products;
   if (fused_dispatch) {
     g.gather_src = static_cast<const __nv_bfloat16*>(call.h2);
     extra.a_rows = static_cast<uint64_t>(T);

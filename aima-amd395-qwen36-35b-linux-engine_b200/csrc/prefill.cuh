@@ -18,6 +18,7 @@ struct PrefillWorkspace {
   bool use_simt_gemm = false;         // qualification: CUDA-core products instead of tcgen05
   bool exact_router = false;          // qualification: all 256 logits with the canonical dot
   bool fused_dispatch = true;         // gate_up kernel gathers its rows itself (no materialised copy)
+  bool pair_products = false;         // qualification: expert products in the two-SM form (cta_group::2, 256-row tiles)
   uint8_t* base = nullptr;
   // The shared expert does not depend on the routing: it runs on a second stream, forked from and
   // joined to the caller's stream with events, next to the router, the plan and the row gather.

@@ -232,6 +232,9 @@ FLAG_EXACT_ROUTER = 2
 FLAG_MATERIALIZED_DISPATCH = 8
 FLAG_EP_PIPELINE_2 = 32
 FLAG_EP_PIPELINE_4 = 64
+FLAG_NO_DECODE_PREDICTION = 128
+FLAG_AUDIT_ROUTER = 256
+FLAG_TWO_SM_PRODUCTS = 512
 
 
 def layer_weights_struct(weights: Mapping[str, Any]) -> LayerWeights:

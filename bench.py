@@ -282,6 +282,22 @@ def run_ours(args) -> None:
     if distributed:
         parity = expert_parallel_parity(package, provider, synth, device, rank, world, dist)
 
+    # ---- N > 1: expert-parallel prefill, T = 8192 uniform: one layer and a four-layer stack (the workload
+    #      that can scale; device-timed, maximum over ranks; rank 0's stage times and exposed communication) ----
+    ep_prefill = None
+    if distributed and not args.no_prefill:
+        provider.release()
+        provider = None
+        del keep
+        torch.cuda.empty_cache()
+        one_layer = ep_prefill_numbers(package, dist, device, world, rank, 8192, 1, "uniform", 20)
+        stack = ep_prefill_numbers(package, dist, device, world, rank, 8192, 4, "uniform", 5)
+        if rank == 0:
+            ep_prefill = {"one_layer": one_layer, "stack4": stack,
+                          "exposed_communication_ms": one_layer["exposed_communication_ms"],
+                          "note": "single-GPU reference for the speed-up: the `prefill` object of the N = 1 line "
+                                  "(T = 8192 Zipf) or `--workload prefill --routing uniform`"}
+
     if rank == 0:
         peak, peak_kind = measured_peaks()
         value = 1000.0 / device_ms_per_step        # expert parallel: all ranks work on the same token
@@ -306,13 +322,16 @@ def run_ours(args) -> None:
         }
         if parity is not None:
             line["parity"] = parity
+        if ep_prefill is not None:
+            line["prefill"] = ep_prefill
         if world == 1 and not args.no_prefill:
             line["prefill"] = prefill_layer_numbers(package, device, 8192, 20, "zipf", weights=keep[0])
         if world == 1 and not args.no_cpu_baseline:
             baseline = cpu_reference_tokens_per_second(2, 6, os.cpu_count() or 1)
             line["cpu_baseline"] = {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
-    provider.release()
+    if provider is not None:
+        provider.release()
     if distributed:
         dist.destroy_process_group()
 
@@ -379,12 +398,13 @@ def apply_routing(provider, synth, device, routing: str) -> None:
         provider.set_router_hooks(None, True)
 
 
-def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing: str, weights=None) -> dict:
+def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing: str, weights=None,
+                          flags: int = 0) -> dict:
     """Device-timed prefill of ONE MoE layer (BASELINE config 2: T = 8192, Zipf(1.1) router bias)."""
     import torch
 
     synth = package.synth
-    provider = package.MoeProvider(layers=1, max_prefill_tokens=tokens)
+    provider = package.MoeProvider(layers=1, max_prefill_tokens=tokens, flags=flags)
     try:
         if weights is None:
             weights = synth.layer_weights_cuda_fast(SEED, 0, device)
@@ -462,6 +482,76 @@ def prefill_stack_numbers(package, device, tokens: int, layers: int, iterations:
             "kernel_launches_per_pass": int(per_pass)}
 
 
+def ep_prefill_numbers(package, dist, device, world: int, rank: int, tokens: int, n_layers: int, routing: str,
+                       steps: int, pipeline: int = 1) -> dict | None:
+    """Expert-parallel prefill of `tokens` tokens (sharded tokens / world per GPU) through `n_layers` layers:
+    device-timed ms per step (maximum over ranks), rank 0's stage times of one traced layer and the
+    communication that is not hidden behind the products.  Returns the numbers on rank 0, None elsewhere."""
+    import torch
+
+    synth = package.synth
+    per_rank_experts = 256 // world
+    tokens_local = tokens // world
+    flags = {1: 0, 2: package.provider.FLAG_EP_PIPELINE_2, 4: package.provider.FLAG_EP_PIPELINE_4}[pipeline]
+    provider = package.MoeProvider(layers=n_layers, max_prefill_tokens=tokens, world=world, rank=rank, flags=flags)
+    try:
+        keep = []
+        for layer in range(n_layers):
+            weights = synth.layer_weights_cuda_fast(SEED, layer, device, rank * per_rank_experts,
+                                                    (rank + 1) * per_rank_experts)
+            provider.bind_layer(layer, weights)
+            keep.append(weights)
+        provider.ep_connect_all(dist.new_group(backend="gloo"))
+        apply_routing(provider, synth, device, routing)
+        generator = torch.Generator(device=device).manual_seed(SEED + rank)
+        h2 = torch.randn(tokens_local, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
+        resid = torch.randn(tokens_local, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
+        out = torch.empty_like(resid)
+
+        def one_step() -> None:
+            if n_layers > 1:
+                provider.prefill_stack(resid, out, 0, n_layers)          # norm + MoE half per layer (config 3 / 4)
+            else:
+                provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+
+        for _ in range(3):
+            one_step()
+        provider.sync_metrics()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            one_step()
+        stop.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        provider.sync_metrics()
+        ms = start.elapsed_time(stop) / steps
+        provider.set_tracing(True)
+        provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
+        stages = provider.ep_prefill_stages()
+        times = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        ms = float(times.item())
+    finally:
+        provider.release()
+    if rank != 0:
+        return None
+    peak, kind = measured_tensor_peak()
+    tflops = tokens * PREFILL_FLOP_PER_TOKEN * n_layers / (ms * 1.0e-3) / 1.0e12
+    exposed = sum(stages.get(name, 0.0) for name in ("routing_exchange", "dispatch", "row_return"))
+    return {"workload": f"prefill_T{tokens}_{n_layers}layer_{routing} (BASELINE config 3 / 4 bucket)",
+            "tokens": tokens, "layers": n_layers, "routing": routing, "tokens_per_gpu": tokens_local,
+            "pipeline_parts": pipeline, "ms_per_step": ms, "ms_per_layer": ms / n_layers,
+            "tokens_per_s": tokens / (ms * 1.0e-3), "achieved_tflops": tflops, "peak_tflops": peak * world,
+            "peak_source": kind, "frac": tflops / (peak * world),
+            "stage_ms_rank0": stages, "exposed_communication_ms": exposed,
+            "exposed_communication_fraction_of_layer": exposed / (ms / n_layers),
+            "multi_gpu": f"expert parallel, {per_rank_experts} experts per GPU, dispatch by peer loads, "
+                         "combine by peer stores over NVLink"}
+
+
 def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) -> None:
     """One prefill layer with tokens sharded over `world` GPUs (BASELINE config 3 per bucket)."""
     import torch
@@ -469,74 +559,28 @@ def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) ->
     from __graft_entry__ import load_package
 
     package = load_package()
-    synth = package.synth
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("nccl", device_id=device)
-    per_rank_experts = 256 // world
-    tokens_local = args.tokens // world
-    flags = {1: 0, 2: package.provider.FLAG_EP_PIPELINE_2, 4: package.provider.FLAG_EP_PIPELINE_4}[args.ep_pipeline]
     n_layers = max(args.stack_layers, 1)
-    provider = package.MoeProvider(layers=n_layers, max_prefill_tokens=args.tokens, world=world, rank=rank, flags=flags)
-    keep = []
-    for layer in range(n_layers):
-        weights = synth.layer_weights_cuda_fast(SEED, layer, device, rank * per_rank_experts,
-                                                (rank + 1) * per_rank_experts)
-        provider.bind_layer(layer, weights)
-        keep.append(weights)
-    provider.ep_connect_all(dist.new_group(backend="gloo"))
-    apply_routing(provider, synth, device, args.routing)
-    generator = torch.Generator(device=device).manual_seed(SEED + rank)
-    h2 = torch.randn(tokens_local, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
-    resid = torch.randn(tokens_local, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
-    out = torch.empty_like(resid)
     steps = max(args.steps, 1)
-
-    def one_step() -> None:
-        if n_layers > 1:
-            provider.prefill_stack(resid, out, 0, n_layers)          # norm + MoE half per layer (config 3 / 4)
-        else:
-            provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
-
-    for _ in range(3):
-        one_step()
-    provider.sync_metrics()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    dist.barrier()
-    torch.cuda.synchronize()
-    start.record()
-    for _ in range(steps):
-        one_step()
-    stop.record()
-    dist.barrier()
-    torch.cuda.synchronize()
-    provider.sync_metrics()
-    ms = start.elapsed_time(stop) / steps
-    provider.set_tracing(True)
-    provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out)
-    stages = provider.ep_prefill_stages()
-    times = torch.tensor([ms], dtype=torch.float64, device=device)
-    dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms = float(times.item())
+    numbers = ep_prefill_numbers(package, dist, device, world, rank, args.tokens, n_layers, args.routing, steps,
+                                 args.ep_pipeline)
     if rank == 0:
-        peak, kind = measured_tensor_peak()
-        tflops = args.tokens * PREFILL_FLOP_PER_TOKEN * n_layers / (ms * 1.0e-3) / 1.0e12
-        exposed = sum(stages.get(name, 0.0) for name in ("routing_exchange", "dispatch", "row_return"))
         print(json.dumps({
-            "metric": "moe_prefill_tokens_per_second", "value": args.tokens / (ms * 1.0e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"prefill_T{args.tokens}_{n_layers}layer_{args.routing} (BASELINE config 3 / 4 bucket)",
-                       "layers": n_layers, "ms_per_layer": ms / n_layers,
-                       "routing": args.routing, "tokens_per_gpu": tokens_local, "pipeline_parts": args.ep_pipeline,
-                       "multi_gpu": f"expert parallel, {per_rank_experts} experts per GPU, dispatch by peer loads, "
-                                    "combine by peer stores over NVLink"},
-            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak * world, "unit": "TFLOP/s",
-                         "frac": tflops / (peak * world), "traffic": None, "peak_source": kind},
-            "stage_ms_rank0": stages, "exposed_communication_ms_rank0": exposed,
+            "metric": "moe_prefill_tokens_per_second", "value": numbers["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": numbers["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": numbers["workload"], "layers": n_layers, "ms_per_layer": numbers["ms_per_layer"],
+                       "routing": args.routing, "tokens_per_gpu": numbers["tokens_per_gpu"],
+                       "pipeline_parts": args.ep_pipeline, "multi_gpu": numbers["multi_gpu"]},
+            "roofline": {"bound": "tensor", "achieved": numbers["achieved_tflops"], "peak": numbers["peak_tflops"],
+                         "unit": "TFLOP/s", "frac": numbers["frac"], "traffic": None,
+                         "peak_source": numbers["peak_source"]},
+            "stage_ms_rank0": numbers["stage_ms_rank0"],
+            "exposed_communication_ms_rank0": numbers["exposed_communication_ms"],
         }))
-    provider.release()
     dist.destroy_process_group()
 
 
@@ -707,7 +751,7 @@ def run_prefill(args) -> None:
             "hbm_frac": numbers["hbm_frac"],
             "gpu_launches": numbers["kernel_launches_per_pass"] * args.steps, "clocks": clocks}))
         return
-    numbers = prefill_layer_numbers(package, device, args.tokens, max(args.steps, 1), args.routing)
+    numbers = prefill_layer_numbers(package, device, args.tokens, max(args.steps, 1), args.routing, flags=args.flags)
     clocks = sampler.stop()
     line = {"metric": "moe_prefill_tokens_per_second", "value": numbers["tokens_per_s"], "unit": "tokens/s",
             "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": numbers["ms_per_layer"],
@@ -737,6 +781,8 @@ def main() -> None:
     parser.add_argument("--routing", choices=["zipf", "uniform", "hot", "ties"], default="zipf")
     parser.add_argument("--ep-pipeline", type=int, choices=[1, 2, 4], default=1,
                         help="--workload prefill on N > 1 GPUs: parts of the dispatch / products / return pipeline")
+    parser.add_argument("--flags", type=int, default=0,
+                        help="--workload prefill, one layer: AIMA_MOE_FLAG_* bits for A/B runs (qualification)")
     parser.add_argument("--stack-layers", type=int, default=1,
                         help="--workload prefill: run this many layers through the stack entry point (config 3: 40)")
     args = parser.parse_args()

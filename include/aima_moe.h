@@ -100,6 +100,11 @@ typedef struct aima_moe_config {
  * the reference's certified LM head, native/src/native_lm_head_certificate.hip.cpp:33-39, applied to
  * the router; the reference's own router has no filter to audit.) */
 #define AIMA_MOE_FLAG_AUDIT_ROUTER 256u
+/* Prefill, for A/B timing and qualification: run the expert products in the two-SM form
+ * (tcgen05.mma.cta_group::2, a pair of blocks per 256-row tile, each block staging its 128 rows and its half
+ * of the weights) instead of the default one-SM form (128-row tiles, one block per tile).  Same bits; on the
+ * measured workloads the default is as fast or faster.  Single GPU only. */
+#define AIMA_MOE_FLAG_TWO_SM_PRODUCTS 512u
 /* Decode, for A/B timing and qualification: do not predict the next layer's experts (its router applied
  * to the current layer's input) and do not request their rows ahead of the routing.  Same bits either
  * way; with the prediction a layer's weight stream overlaps the hand-overs of the previous layer. */

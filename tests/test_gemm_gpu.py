@@ -87,6 +87,38 @@ def test_prefill_tensor_core_products_match_cuda_core_products(package, gpu_laye
     assert torch.isfinite(out_tc.float()).all()
 
 
+@pytest.mark.parametrize("tokens,regime", [(300, "zipf"), (1024, "uniform"), (2048, "zipf"), (8192, "hot")])
+def test_two_sm_products_equal_one_sm_products(package, gpu_layers, synth, tokens, regime):
+    """The expert products in the two-SM form (tcgen05.mma.cta_group::2, a pair of blocks per 256-row tile)
+    against the one-SM form (128-row tiles): same operands in the same K order, so the same bits -- with
+    experts of fewer than 128 rows (the second block of the pair idle), of 129 .. 256 rows and of many
+    tiles, and the dispatch plan identical apart from the tile size."""
+    device = torch.device("cuda", 0)
+    weights = gpu_layers(0)["cuda"]
+    h2 = synth.activations(SEED + 5 + tokens, tokens, "input", 0).to(device)
+    resid = synth.activations(SEED + 5 + tokens, tokens, "residual", 0).to(device)
+    bias = {"zipf": synth.zipf_router_bias(SEED), "hot": synth.hot_expert_bias(range(3, 256, 32)), "uniform": None}[regime]
+    results = []
+    for flags in (0, package.provider.FLAG_TWO_SM_PRODUCTS):
+        provider = package.MoeProvider(layers=1, max_prefill_tokens=tokens, flags=flags)
+        try:
+            provider.bind_layer(0, weights)
+            provider.set_router_hooks(None if bias is None else bias.to(device), quantize_eighths=False)
+            views, tensors = provider.make_debug(tokens, prefill=True, with_logits=False)
+            out = provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, debug=views)
+            provider.sync_metrics()
+            results.append((out.clone(), {k: v.clone() for k, v in tensors.items()}))
+        finally:
+            provider.release()
+    (out_one, dbg_one), (out_pair, dbg_pair) = results
+    for name in ("topk_ids", "sorted_rows", "expert_counts", "expert_offsets"):
+        assert torch.equal(dbg_pair[name], dbg_one[name]), name
+    assert torch.equal(dbg_pair["routed"], dbg_one["routed"])
+    assert torch.equal(dbg_pair["shared_scaled"], dbg_one["shared_scaled"])
+    assert torch.equal(out_pair, out_one)
+    assert torch.isfinite(out_pair.float()).all()
+
+
 def test_certified_router_equals_exact_router_at_full_size(package, gpu_layers, synth):
     """T = 8192, three routing regimes: the tensor-core-filtered router and the all-256 canonical
     router must select identical experts in identical order (size the CPU oracle cannot reach)."""
