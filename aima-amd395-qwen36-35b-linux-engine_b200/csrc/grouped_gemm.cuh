@@ -60,6 +60,13 @@ struct GroupedGemm {
   // n tiles of the plan (parts <= 1: all of them), so that copies for one part overlap products of another
   int part;
   int parts;
+  // kGemmExpertDown on the tensor cores, expert parallelism: when scatter_tokens_per_rank > 0 the weighted row
+  // of flat routed row f = sorted_rows[row] is not stored to c but straight to the GPU that owns its token,
+  // at row f - owner * 8 * scatter_tokens_per_rank of the [tokens_per_rank * 8, n] matrix at
+  // scatter_region[owner] + scatter_offset (plain peer stores from the epilogue, no copy kernel afterwards)
+  uint8_t* scatter_region[8];
+  size_t scatter_offset;
+  int scatter_tokens_per_rank;
 };
 
 // What the tensor-core launcher needs beyond the problem itself.

@@ -171,6 +171,20 @@ __device__ __forceinline__ void store_staged(const uint8_t* stage, int lane, __n
 }
 
 
+// The same with one destination per row: rows[i] is the address of the first of the 64 columns in the row
+// instruction i writes for this lane (row 4 i + lane / 8 of the warp's 32), nullptr for a row past the tile's end.
+__device__ __forceinline__ void store_staged_rows(const uint8_t* stage, int lane, __nv_bfloat16* const* rows, int cols_ok) {
+  __syncwarp();
+  const int piece = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int row = 4 * i + (lane >> 3);
+    const uint4 w = *reinterpret_cast<const uint4*>(stage + row * 128 + ((piece ^ (row & 7)) * 16));
+    if (rows[i] != nullptr && piece * 8 < cols_ok) *reinterpret_cast<uint4*>(rows[i] + piece * 8) = w;
+  }
+  __syncwarp();
+}
+
 // One epilogue warp drains its part of a 128-row x 256-column FP32 accumulator: TMEM lanes
 // 32 ew .. 32 ew + 31 (rows row0 + 32 ew ... of the output), half `eh` of the unit's columns.
 template <int MODE>
@@ -214,6 +228,23 @@ __device__ __forceinline__ void drain_accumulator(const GroupedGemm& g, const Tc
     }
     const int col_base = chunk * kBN;
     __nv_bfloat16* dst = g.c + static_cast<size_t>(row0 + ew * 32) * g.ldc + col_base;
+    const bool scatter = MODE == kGemmExpertDown && g.scatter_tokens_per_rank > 0;
+    __nv_bfloat16* scatter_rows[8];
+    if (scatter) {
+      // where the eight rows this lane stores live: on the GPU that owns the row's token
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + (lane >> 3);
+        scatter_rows[i] = nullptr;
+        if (rr < rows_ok) {
+          const int flat = g.sorted_rows[row0 + ew * 32 + rr];
+          const int owner = (flat >> 3) / g.scatter_tokens_per_rank;
+          const int local_flat = flat - owner * g.scatter_tokens_per_rank * 8;
+          scatter_rows[i] = reinterpret_cast<__nv_bfloat16*>(g.scatter_region[owner] + g.scatter_offset) +
+                            static_cast<size_t>(local_flat) * g.ldc + col_base;
+        }
+      }
+    }
 #pragma unroll 1
     for (int c0 = eh * (kBN / 2); c0 < (eh + 1) * (kBN / 2); c0 += 64) {
 #pragma unroll 1
@@ -231,8 +262,15 @@ __device__ __forceinline__ void drain_accumulator(const GroupedGemm& g, const Tc
         }
         stage_32(stage, lane, half, v);
       }
-      store_staged(stage, lane, dst + c0, static_cast<size_t>(g.ldc), rows_ok,
-                   max(0, min(64, pb.n_valid - col_base - c0)));
+      const int cols_ok = max(0, min(64, pb.n_valid - col_base - c0));
+      if (scatter) {
+        __nv_bfloat16* at[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) at[i] = scatter_rows[i] != nullptr ? scatter_rows[i] + c0 : nullptr;
+        store_staged_rows(stage, lane, at, cols_ok);
+      } else {
+        store_staged(stage, lane, dst + c0, static_cast<size_t>(g.ldc), rows_ok, cols_ok);
+      }
     }
   } else {
     // FP32 output (approximate router logits): every thread stores its own row

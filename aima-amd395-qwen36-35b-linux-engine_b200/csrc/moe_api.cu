@@ -388,6 +388,9 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
     handle->prefill.ep_parts = (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_4)   ? 4
                                : (config->flags & AIMA_MOE_FLAG_EP_PIPELINE_2) ? 2
                                                                                : 1;
+    // A/B switch: AIMA_MOE_EP_COPY_RETURN in the environment keeps the copy kernel that returns the rows
+    handle->prefill.ep_fused_return = std::getenv("AIMA_MOE_EP_COPY_RETURN") == nullptr;
+    handle->prefill.ep_fused_dispatch = std::getenv("AIMA_MOE_EP_COPY_DISPATCH") == nullptr;
   }
   handle->metrics.struct_bytes = sizeof(aima_moe_metrics);
   handle->metrics.workspace_bytes = handle->decode_scratch_bytes + sizeof(LayerPtrs) * kMaxLayers +

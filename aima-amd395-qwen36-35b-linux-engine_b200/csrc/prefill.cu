@@ -748,6 +748,21 @@ ep_publish_routing_kernel(const int32_t* __restrict__ ids, const float* __restri
   }
 }
 
+// every rank's h2 rows into every rank's [T, 2048] table, block `rank`: the all-gather that replaces a
+// dispatch of single rows (with eight experts out of 256 per token nearly every rank needs nearly every
+// token).  It does not depend on the routing, so it runs beside the router on its own stream; a small grid,
+// since NVLink, not the SMs, sets its pace.
+__global__ void __launch_bounds__(256)
+ep_publish_rows_kernel(const uint4* __restrict__ rows, size_t n_vec, EpPointers peers, int world, int rank,
+                       size_t off_h2) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    const uint4 v = rows[i];
+    for (int q = 0; q < world; ++q)
+      reinterpret_cast<uint4*>(peers.region[q] + off_h2)[static_cast<size_t>(rank) * n_vec + i] = v;
+  }
+}
+
 // after the stores of the previous kernel: raise this rank's flag on every GPU
 __global__ void ep_signal_kernel(EpPointers peers, int world, int rank, size_t off_flag, unsigned epoch) {
   const int q = threadIdx.x;
@@ -767,7 +782,7 @@ __global__ void ep_wait_kernel(const uint8_t* region, int world, size_t off_flag
   while (true) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-    if (v == epoch) break;
+    if (static_cast<int>(v - epoch) >= 0) break;      // a later epoch also means this one has passed
     if ((++spins & 63u) == 0u && global_timer_ns() - start > kWaitBudgetNs) {
       atomicCAS(status, 0, kStatusTimeoutPeer);
       break;
@@ -929,6 +944,7 @@ int prefill_workspace_allocate(PrefillWorkspace* ws, uint32_t capacity_tokens, i
   if (code == cudaSuccess) code = cudaStreamCreateWithFlags(&ws->outbound_stream, cudaStreamNonBlocking);
   if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->plan_event, cudaEventDisableTiming);
   if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->returned_event, cudaEventDisableTiming);
+  if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->published_event, cudaEventDisableTiming);
   for (int k = 0; k < PrefillWorkspace::kMaxParts && code == cudaSuccess; ++k) {
     code = cudaEventCreateWithFlags(&ws->gathered_event[k], cudaEventDisableTiming);
     if (code == cudaSuccess) code = cudaEventCreateWithFlags(&ws->computed_event[k], cudaEventDisableTiming);
@@ -973,6 +989,7 @@ void prefill_workspace_free(PrefillWorkspace* ws) {
   if (ws->side_stream != nullptr) cudaStreamDestroy(ws->side_stream);
   if (ws->plan_event != nullptr) cudaEventDestroy(ws->plan_event);
   if (ws->returned_event != nullptr) cudaEventDestroy(ws->returned_event);
+  if (ws->published_event != nullptr) cudaEventDestroy(ws->published_event);
   for (int k = 0; k < PrefillWorkspace::kMaxParts; ++k) {
     if (ws->gathered_event[k] != nullptr) cudaEventDestroy(ws->gathered_event[k]);
     if (ws->computed_event[k] != nullptr) cudaEventDestroy(ws->computed_event[k]);
@@ -1230,7 +1247,17 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
     return set_error(error, error_bytes, code, "grouped gemm shared gate_up");
   ++count;
 
-  // 1. route this rank's tokens (certified router) and stage its h2 rows where peers can read them
+  // 0. this rank's h2 rows to every GPU, on the inbound stream beside the router (the flags of step 2 cover it)
+  if ((code = cudaStreamWaitEvent(ws->inbound_stream, ws->fork_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "fork of the row all-gather");
+  ep_publish_rows_kernel<<<96, 256, 0, ws->inbound_stream>>>(
+      static_cast<const uint4*>(call.h2), static_cast<size_t>(T_loc) * (kHidden / 8), peers, W, ep->rank, L.off_h2);
+  if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "ep_publish_rows_kernel");
+  ++count;
+  if ((code = cudaEventRecord(ws->published_event, ws->inbound_stream)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "published event");
+
+  // 1. route this rank's tokens (certified router)
   GroupedGemm r{};
   r.max_tiles = (T_loc + kTileRows - 1) / kTileRows; r.dense_rows = T_loc;
   r.a = static_cast<const __nv_bfloat16*>(call.h2); r.lda = kHidden; r.k = kHidden;
@@ -1258,14 +1285,13 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   ++count;
   if ((code = cudaEventRecord(ws->join_event, side)) != cudaSuccess)
     return set_error(error, error_bytes, code, "join event of the shared-expert stream");
-  code = cudaMemcpyAsync(mine + L.off_h2, call.h2, static_cast<size_t>(T_loc) * kHidden * 2,
-                         cudaMemcpyDeviceToDevice, stream);
-  if (code != cudaSuccess) return set_error(error, error_bytes, code, "cudaMemcpyAsync h2 staging");
 
   mark();
   // 2. all-gather of the routing tables by peer stores, then flags
   ep_publish_routing_kernel<<<(rows_loc + 255) / 256, 256, 0, stream>>>(
       ws->topk_ids, ws->topk_weights, rows_loc, peers, W, ep->rank, L.off_ids, L.off_weights);
+  if ((code = cudaStreamWaitEvent(stream, ws->published_event, 0)) != cudaSuccess)
+    return set_error(error, error_bytes, code, "join of the row all-gather");
   ep_signal_kernel<<<1, 32, 0, stream>>>(peers, W, ep->rank, L.off_flags_routing, epoch);
   ep_wait_kernel<<<1, 32, 0, stream>>>(mine, W, L.off_flags_routing, epoch, ws->status);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "routing exchange");
@@ -1286,14 +1312,22 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   //   caller's stream  gate_up and down products of part k once its rows are here
   //   outbound stream  weighted rows of part k stored to the GPUs that own their tokens
   const int parts = ws->ep_parts >= 1 && ws->ep_parts <= PrefillWorkspace::kMaxParts ? ws->ep_parts : 1;
+  // Row return: with one part the down kernel stores its rows to their owners itself (fused_return); with the
+  // pipeline a copy kernel on the outbound stream sends the rows of part k while part k + 1 is computed.
+  const bool fused_return = parts == 1 && ws->ep_fused_return;
+  // Dispatch: all rows are in this GPU's table since the flags of step 2, in global token order, so with one
+  // part the gate_up kernel gathers them itself as on one GPU; otherwise a copy kernel puts them in expert order.
+  const bool fused_dispatch = parts == 1 && ws->ep_fused_dispatch;
+  EpPointers local_blocks{};      // block q of this GPU's table: the tokens of rank q
+  for (int q = 0; q < W; ++q) local_blocks.region[q] = mine + static_cast<size_t>(q) * T_loc * kHidden * 2;
   const int part_blocks = min(((max_tiles_for(T) / parts + 1) * kTileRows + 7) / 8, 2 * ws->sm_count);
   cudaStream_t inbound = ws->inbound_stream, outbound = ws->outbound_stream;
   if ((code = cudaEventRecord(ws->plan_event, stream)) != cudaSuccess ||
       (code = cudaStreamWaitEvent(inbound, ws->plan_event, 0)) != cudaSuccess ||
       (code = cudaStreamWaitEvent(outbound, ws->plan_event, 0)) != cudaSuccess)
     return set_error(error, error_bytes, code, "fork of the dispatch / return streams");
-  for (int k = 0; k < parts; ++k) {
-    ep_gather_rows_kernel<<<part_blocks, 256, 0, inbound>>>(peers, L.off_h2, T_loc, ws->sorted_rows,
+  for (int k = 0; k < parts && !fused_dispatch; ++k) {
+    ep_gather_rows_kernel<<<part_blocks, 256, 0, inbound>>>(local_blocks, L.off_h2, T_loc, ws->sorted_rows,
                                                             ws->expert_offsets, ws->tile_row0, ws->tile_count,
                                                             k, parts, ws->gathered);
     if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "ep_gather_rows_kernel");
@@ -1310,23 +1344,34 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   extra.status = ws->status; extra.sm_count = ws->sm_count;
   extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK; extra.experts_in_b = call.experts_local;
   for (int k = 0; k < parts; ++k) {
-    if ((code = cudaStreamWaitEvent(stream, ws->gathered_event[k], 0)) != cudaSuccess)
+    if (!fused_dispatch && (code = cudaStreamWaitEvent(stream, ws->gathered_event[k], 0)) != cudaSuccess)
       return set_error(error, error_bytes, code, "wait for gathered rows");
     if (k == 0) mark();
     g.part = k;
     g.a = ws->gathered; g.lda = kHidden; g.k = kHidden;
+    g.gather_src = fused_dispatch ? reinterpret_cast<const __nv_bfloat16*>(mine + L.off_h2) : nullptr;
+    extra.a_rows = fused_dispatch ? static_cast<uint64_t>(T) : static_cast<uint64_t>(ws->capacity) * kTopK;
     g.b0 = call.layer.expert_gate_up; g.b_expert_stride = static_cast<size_t>(2 * kInter) * kHidden;
     g.n = kInter; g.c = ws->expert_act; g.ldc = kInter;
     g.row_scale = nullptr; g.sorted_rows = ws->sorted_rows;
     if ((code = launch_grouped_gemm_tc(kGemmExpertGateUp, g, extra, stream)) != cudaSuccess)
       return set_error(error, error_bytes, code, "grouped gemm expert gate_up");
+    g.gather_src = nullptr;
+    extra.a_rows = static_cast<uint64_t>(ws->capacity) * kTopK;
     g.a = ws->expert_act; g.lda = kInter; g.k = kInter;
     g.b0 = call.layer.expert_down; g.b_expert_stride = static_cast<size_t>(kHidden) * kInter;
     g.n = kHidden; g.c = ws->expert_down; g.ldc = kHidden;
     g.row_scale = weights_all;
+    if (fused_return) {
+      // the down kernel's epilogue stores every weighted row where its token lives
+      for (int q = 0; q < W; ++q) g.scatter_region[q] = ep->peers[q];
+      g.scatter_offset = L.off_return;
+      g.scatter_tokens_per_rank = T_loc;
+    }
     if ((code = launch_grouped_gemm_tc(kGemmExpertDown, g, extra, stream)) != cudaSuccess)
       return set_error(error, error_bytes, code, "grouped gemm expert down");
     count += 2;
+    if (fused_return) break;
     if ((code = cudaEventRecord(ws->computed_event[k], stream)) != cudaSuccess ||
         (code = cudaStreamWaitEvent(outbound, ws->computed_event[k], 0)) != cudaSuccess)
       return set_error(error, error_bytes, code, "computed event");
@@ -1338,11 +1383,12 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
   }
   mark();
   // all rows stored: raise this rank's flag on every GPU, then rejoin the caller's stream
-  ep_signal_kernel<<<1, 32, 0, outbound>>>(peers, W, ep->rank, L.off_flags_returned, epoch);
+  ep_signal_kernel<<<1, 32, 0, fused_return ? stream : outbound>>>(peers, W, ep->rank, L.off_flags_returned, epoch);
   if ((code = cudaGetLastError()) != cudaSuccess) return set_error(error, error_bytes, code, "row return");
   ++count;
-  if ((code = cudaEventRecord(ws->returned_event, outbound)) != cudaSuccess ||
-      (code = cudaStreamWaitEvent(stream, ws->returned_event, 0)) != cudaSuccess)
+  if (!fused_return &&
+      ((code = cudaEventRecord(ws->returned_event, outbound)) != cudaSuccess ||
+       (code = cudaStreamWaitEvent(stream, ws->returned_event, 0)) != cudaSuccess))
     return set_error(error, error_bytes, code, "join of the return stream");
 
   mark();

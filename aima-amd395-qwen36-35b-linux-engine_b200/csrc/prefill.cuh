@@ -30,9 +30,12 @@ struct PrefillWorkspace {
   // part, while the products of another part run on the caller's stream.
   static constexpr int kMaxParts = 8;
   int ep_parts = 1;                               // 1: dispatch, products and return run one after the other
+  bool ep_fused_return = true;                    // ep_parts == 1: the down kernel's epilogue stores rows to their owners
+  bool ep_fused_dispatch = true;                  // ep_parts == 1: the gate_up kernel gathers its rows from the all-gathered h2
   cudaStream_t inbound_stream = nullptr;
   cudaStream_t outbound_stream = nullptr;
   cudaEvent_t plan_event = nullptr;               // caller's stream: the plan is written
+  cudaEvent_t published_event = nullptr;          // inbound stream: this rank's h2 rows are stored on every GPU
   cudaEvent_t gathered_event[kMaxParts] = {};     // inbound stream: rows of part k are here
   cudaEvent_t computed_event[kMaxParts] = {};     // caller's stream: products of part k are written
   cudaEvent_t returned_event = nullptr;           // outbound stream: all rows are stored and flagged
@@ -74,7 +77,7 @@ struct EpPrefillLayout {
   size_t off_flags_returned;  // u32[8]  rank q has returned all rows it computed for epoch e
   size_t off_ids;             // i32 [T * 8]  routing ids of all ranks, rank-major
   size_t off_weights;         // f32 [T * 8]
-  size_t off_h2;              // bf16 [T_loc, 2048] this rank's tokens, readable by peers
+  size_t off_h2;              // bf16 [T, 2048] the tokens of all ranks, rank-major; every rank stores its rows here on every GPU
   size_t off_return;          // bf16 [T_loc * 8, 2048] weighted expert outputs of this rank's tokens
   size_t bytes;
 };

@@ -86,7 +86,10 @@ def layer_weights_cuda_fast(seed: int, layer: int, device: Any, expert_lo: int =
     """Full layer generated on the GPU (benchmark stacks: 40 layers = 64.6 GB).
 
     Same distributions as layer_weights_cpu but a different random stream; use
-    it where no CPU copy of the weights is needed.
+    it where no CPU copy of the weights is needed.  The expert tensors are drawn
+    in blocks of 32 experts, each from its own seed, so the experts [lo, hi) a
+    rank of an expert-parallel run asks for are the same values as that slice of
+    the full layer.
     """
     generator = torch.Generator(device=device).manual_seed(_seed(seed, layer, "router"))
 
@@ -96,9 +99,23 @@ def layer_weights_cuda_fast(seed: int, layer: int, device: Any, expert_lo: int =
         return out
 
     weights = {name: normal(shape) for name, shape in _SHAPES.items()}
-    count = expert_hi - expert_lo
-    weights["expert_gate_up"] = normal((count, 2 * EXPERT_INTER, HIDDEN))
-    weights["expert_down"] = normal((count, HIDDEN, EXPERT_INTER))
+    block = 32
+
+    def experts(name: str, tail: tuple[int, ...]) -> torch.Tensor:
+        out = torch.empty((expert_hi - expert_lo,) + tail, dtype=torch.bfloat16, device=device)
+        for index in range(expert_lo // block, (expert_hi + block - 1) // block):
+            block_generator = torch.Generator(device=device).manual_seed(_seed(seed, layer, name, 1 + index))
+            lo, hi = max(expert_lo, index * block), min(expert_hi, (index + 1) * block)
+            if hi - lo == block:
+                out[lo - expert_lo:hi - expert_lo].normal_(0.0, WEIGHT_STD, generator=block_generator)
+            else:
+                whole = torch.empty((block,) + tail, dtype=torch.bfloat16, device=device)
+                whole.normal_(0.0, WEIGHT_STD, generator=block_generator)
+                out[lo - expert_lo:hi - expert_lo] = whole[lo - index * block:hi - index * block]
+        return out
+
+    weights["expert_gate_up"] = experts("expert_gate_up", (2 * EXPERT_INTER, HIDDEN))
+    weights["expert_down"] = experts("expert_down", (HIDDEN, EXPERT_INTER))
     return weights
 
 

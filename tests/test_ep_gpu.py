@@ -145,8 +145,8 @@ def test_expert_parallel_prefill_rank_alone_matches_single_gpu(package, gpu_laye
             mine_ids = ids_all[t0 * 8:t1 * 8]
             remote = (mine_ids < lo) | (mine_ids >= hi)
             ret[remote] = ref["slot_rows"][t0 * 8:t1 * 8][remote]
-            # the peer's staged activations, which this rank's dispatch reads
-            view(peer, off_h2, per_rank * H, torch.bfloat16).view(per_rank, H).copy_(h2[o0:o1])
+            # the peer's activations, which its all-gather stores into block `other` of this rank's table
+            view(own, off_h2, total * H, torch.bfloat16).view(total, H)[o0:o1].copy_(h2[o0:o1])
             provider.ep_connect(rank, pointer=own.data_ptr())
             provider.ep_connect(other, pointer=peer.data_ptr())
             out = provider.launch_selected_moe(post_attention=h2[t0:t1].contiguous(),
@@ -158,6 +158,8 @@ def test_expert_parallel_prefill_rank_alone_matches_single_gpu(package, gpu_laye
             peer_ids = ids_all[o0 * 8:o1 * 8]
             local = (peer_ids >= lo) & (peer_ids < hi)
             assert torch.equal(sent[local], ref["slot_rows"][o0 * 8:o1 * 8][local]), f"rank {rank} returned rows"
+            # and this rank's own activations, stored into block `rank` of the peer's table
+            assert torch.equal(view(peer, off_h2, total * H, torch.bfloat16).view(total, H)[t0:t1], h2[t0:t1])
             assert int(view(peer, off_flag_routing, 8, torch.int32)[rank]) == 1
             assert int(view(peer, off_flag_returned, 8, torch.int32)[rank]) == 1
         finally:
