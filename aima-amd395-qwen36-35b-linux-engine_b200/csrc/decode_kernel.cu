@@ -41,7 +41,9 @@
 //       a chosen expert, which chosen experts still have to be fetched)
 //   P   the gate/up chunks not covered by a valid blind item, with the real experts
 //   D   the block's <= 14 rows of the down projections, two experts per item (shared expert first)
-//   --- grid barrier: all SwiGLU activations known
+//   --- activation exchange: every SwiGLU activation travels as a 32-bit word {tag, bf16}; all warps
+//       of every block poll the words of the used positions and of the shared expert into shared
+//       memory (no barrier: the tags are the synchronisation); then
 //       down products for the block's output elements from the down items,
 //       weighted sum, shared expert, residual add
 //   --- output exchange: the 2048 outputs travel as 32-bit words {tag, bf16};
@@ -54,8 +56,9 @@
 // block and predicts most of the next layer's experts.  Their rows are requested
 // into the ring as slots fall free, their activations are computed before the
 // routing is known, and a layer whose prediction was right has nothing left to
-// fetch after its plan.  A position whose prediction was wrong is fetched again
-// with the right expert and its activations are overwritten, so the result does
+// fetch after its plan.  An activation computed blind is held back until the plan
+// confirms its expert (a tagged word is final for its readers); a position whose
+// prediction was wrong is fetched again with the right expert, so the result does
 // not depend on the prediction: outputs are bit-identical with and without it.
 //
 // Every wait (mbarrier, grid barrier, hand-overs between the warps of a block)
@@ -91,7 +94,7 @@ constexpr int kDotsStride = 12;
 constexpr int kPositions = kTopK;              // ring positions a layer's experts are dealt to
 constexpr int kRouterBlocks = kExperts / 2;    // blocks 0 .. 127 hold two router rows each, block 128 the shared gate row
 // Blind tickets of a layer: ticket q is the gate/up chunk of position q.  (Down rows are not requested
-// blind: they would sit in the ring until after the activation barrier, and a chunk that has to be
+// blind: they would sit in the ring until after the activation exchange, and a chunk that has to be
 // fetched again after the plan could then find its slot taken by an item that cannot be consumed
 // before it -- a cycle.  They are requested right after the plan, when the ring is empty.)
 constexpr int kTickets = kPositions;
@@ -138,6 +141,7 @@ struct Misc {
   volatile int pred_layer;        // predictions are published for all layer ordinals < pred_layer
   unsigned blind_state[2];        // [li & 1]: tickets claimed blind so far | kFrozen
   volatile int blind_done[2];     // [li & 1]: tickets the producer has dealt with (placed or skipped)
+  uint16_t spec_bits[kStreamWarps][kPositions];   // activations computed blind, published once the plan confirms them
   volatile int abort_flag;        // block-local copy of a raised status
   volatile int decision;          // block-uniform "keep going" verdict (see uniform_alive)
 };
@@ -156,7 +160,7 @@ __device__ __noinline__ void raise_status(const DecodeParams& p,
 // Records where the first bounded wait gave up: status[1] = site, [2] = block,
 // [3] = warp, [4] = item / layer detail.  Sites: 1 producer slot acquire,
 // 2 consumer item (router / shared rows), 3 consumer item (routed rows),
-// 4 consumer item (down rows), 5 grid barrier, 6 plan hand-over to the producer,
+// 4 consumer item (down rows), 5 activation exchange, 6 plan hand-over to the producer,
 // 7 output exchange, 8 norm row, 9 logits exchange, 10 prediction hand-over,
 // 11 expert-parallel peer word, 12 predicted-logits exchange.
 __device__ __noinline__ void record_site(const DecodeParams& p, int site, int detail,
@@ -172,34 +176,6 @@ __device__ __noinline__ void record_site(const DecodeParams& p, int site, int de
       p.status[8] = static_cast<int>(diag[3]);
     }
   }
-}
-
-// Grid-wide barrier over the consumer threads of all blocks.
-__device__ __forceinline__ bool grid_barrier(const DecodeParams& p,
-                                             unsigned long long target,
-                                             volatile int* abort_flag,
-                                             volatile int* decision, int ctid) {
-  consumer_sync();
-  if (ctid == 0 && *abort_flag == 0) {
-    __threadfence();
-    atomicAdd(p.bar_counter, 1ull);
-    const unsigned long long start = global_timer_ns();
-    unsigned spins = 0;
-    while (ld_acquire_u64(p.bar_counter) < target) {
-      if ((++spins & 63u) == 0u) {
-        const int remote = ld_relaxed_s32(p.status);
-        if (remote != 0) { *abort_flag = remote; break; }
-        if (global_timer_ns() - start > kWaitBudgetNs) {
-          raise_status(p, abort_flag, kStatusTimeoutGridBarrier);
-          record_site(p, 5, static_cast<int>(target));
-          break;
-        }
-      }
-    }
-  }
-  if (ctid == 0) *decision = (*abort_flag == 0) ? 1 : 0;
-  consumer_sync();
-  return *decision != 0;
 }
 
 // Block-uniform verdict on whether any thread of the block has raised a status.
@@ -234,6 +210,11 @@ __device__ __forceinline__ uint4 ld_strong_u4(const void* p) {
   uint4 v;
   asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_strong_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ void st_strong_u64(void* p, unsigned long long v) {
@@ -348,7 +329,6 @@ moe_decode_persistent_kernel(const DecodeParams p) {
   const int sh_lo = range_lo(c, G);                        // shared-expert input rows [sh_lo, sh_hi)
   const int sh_rows = range_lo(c + 1, G) - sh_lo;
   const bool speculate = p.speculate != 0;
-  const unsigned long long bar_base = *p.bar_base;
   const unsigned epoch0 = *p.epoch_base;      // exchange tag of layer ordinal li is epoch0 + li + 1
   unsigned long long* const pred_logits = p.logits + kDecodeReplicas * kExperts;
 
@@ -603,7 +583,6 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     const int group = streams ? stream_index / kGroupWarps : -1;
     const int member = streams ? stream_index % kGroupWarps : -1;
     unsigned seq = 0;                             // mirrors the producer's item counter
-    unsigned long long nbar = 0;
     bool alive = true;
 
     auto owns = [&](unsigned item) -> bool {
@@ -657,7 +636,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
 
     // tracing stamps (thread 0 of the block unless stated): 0 layer start, 1 norm done, 2 this block's
     // logits written (by the warp that computed them), 3 all logits arrived, 4 plan published and blind
-    // chunks consumed, 5 routed gate/up done, 6 activation barrier, 7 activations loaded, 8 first down
+    // chunks consumed, 5 routed gate/up done, 6 activations of all blocks polled and packed, 7 block agrees to go on, 8 first down
     // item of the first streaming warp has landed, 9 down dots done, 10 output stored, 11 that warp's
     // down items done
     auto stamp_now = [&](int li, int k) {
@@ -667,6 +646,21 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     auto stamp = [&](int li, int k) {
       if (ctid == 0) stamp_now(li, k);
     };
+    if (kEp) {
+      // Expert parallelism leaves the activation words of positions this GPU does not use unwritten, possibly
+      // for many calls, and a 16-bit tag comes round again: every call starts by clearing the words this block
+      // writes (its up to four columns of every position, in every copy), before any of its own stores to them.
+      if (ctid < kPositions * kDecodeReplicas * 4) {
+        const int q = ctid / (kDecodeReplicas * 4);
+        const int rep = (ctid / 4) % kDecodeReplicas;
+        const int m = ctid & 3;
+        const int b = position_range(q, c, G);
+        const int lo = range_lo(b, G);
+        if (m < range_lo(b + 1, G) - lo) st_strong_u32(p.act + rep * kDecodeActStride + q * kInter + lo + m, 0u);
+      }
+      __threadfence();
+      consumer_sync();
+    }
 #pragma unroll 1
     for (int li = 0; li < p.n_layers; ++li) {
       const bool first = (li == 0);
@@ -678,6 +672,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       uint32_t* xw_dst = (li & 1) ? p.xbuf0 : p.xbuf1;
       const unsigned tag_in = (epoch0 + li) & 0xffffu;           // tag of layer li - 1
       const unsigned tag_out = (epoch0 + li + 1) & 0xffffu;
+      // activation words of this layer: a 16-bit tag that is never zero, so a cleared word matches no layer
+      const uint32_t act_tag = (((epoch0 + static_cast<unsigned>(li) + 1u) % 0xffffu) + 1u) << 16;
       // ---- layer input into shared memory (packed BF16) ----
       if (first) {
         if (ctid < kHidden / 8) {
@@ -795,10 +791,10 @@ moe_decode_persistent_kernel(const DecodeParams p) {
                 for (int rep = 0; rep < kDecodeReplicas; ++rep) st_strong_u64(dst + rep * kExperts + expert, word);
                 if (!predicted) stamp_now(li, 2);
               } else {
-                const float gate = round_bf16(v);
+                const uint32_t word = act_tag | float_to_bf16_bits(v);       // the gate logit is used BF16-rounded
 #pragma unroll
                 for (int rep = 0; rep < kDecodeReplicas; ++rep)
-                  *reinterpret_cast<float*>(p.act + rep * kDecodeActStride + 9 * kInter) = gate;
+                  st_strong_u32(p.act + rep * kDecodeActStride + 9 * kInter, word);
               }
             }
           }
@@ -820,7 +816,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
               const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(g), u));
 #pragma unroll
               for (int rep = 0; rep < kDecodeReplicas; ++rep)
-                p.act[rep * kDecodeActStride + kTopK * kInter + sh_lo + member] = bits;
+                st_strong_u32(p.act + rep * kDecodeActStride + kTopK * kInter + sh_lo + member, act_tag | bits);
             }
           }
         }
@@ -830,7 +826,12 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       // slot holds rows of an expert that was not chosen; wait for them to land (the copy must not
       // be in flight when the slot is reused) and hand the slot back unread.  Activations are filed
       // under the POSITION; the down products look the rank up in the plan.
-      auto consume_chunk = [&](int q, bool use) {
+      auto publish_act = [&](int index, uint16_t bits) {
+#pragma unroll
+        for (int rep = 0; rep < kDecodeReplicas; ++rep) st_strong_u32(p.act + rep * kDecodeActStride + index, act_tag | bits);
+      };
+      unsigned spec_have = 0u;            // positions whose blind result this warp holds in spec_bits
+      auto consume_chunk = [&](int q, bool use, bool blind = false) {
         const unsigned item = seq++;
         if (!streams || !owns(item) || !alive) return;
         const uint8_t* slot = wait_item(item, 3);
@@ -844,10 +845,11 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         release_item(item);
         if (mine && lane == 0) {
           const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), bb));
-          const int index = q * kInter + lo + member;
-#pragma unroll
-          for (int rep = 0; rep < kDecodeReplicas; ++rep) p.act[rep * kDecodeActStride + index] = bits;
+          // a word with this layer's tag is final for its readers: a blind result waits for the plan
+          if (blind) misc->spec_bits[stream_index][q] = bits;
+          else publish_act(q * kInter + lo + member, bits);
         }
+        if (blind && mine) spec_have |= 1u << q;
       };
       // ---- blind gate/up chunks, consumed while warp 0 waits for the logits: the predicted expert's
       //      activations are right whenever the prediction is, and overwritten otherwise.  Every warp
@@ -861,7 +863,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         while (blind_seen < kPositions && alive) {
           if (misc->blind_done[li & 1] > blind_seen) {
             __threadfence_block();
-            if (misc->pred[li & 1][blind_seen] >= 0) consume_chunk(blind_seen, true);
+            if (misc->pred[li & 1][blind_seen] >= 0) consume_chunk(blind_seen, true, true);
             ++blind_seen;
             continue;
           }
@@ -1029,6 +1031,15 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       const int n_active = misc->n_active;
       const unsigned active_mask = misc->active_mask;
       const unsigned valid_mask = misc->valid_mask;
+      if (streams && lane == 0) {
+        // blind results the plan has confirmed
+        unsigned confirmed = spec_have & valid_mask;
+        while (confirmed != 0u) {
+          const int q = __ffs(confirmed) - 1;
+          confirmed &= confirmed - 1u;
+          publish_act(q * kInter + range_lo(position_range(q, c, G), G) + member, misc->spec_bits[stream_index][q]);
+        }
+      }
       if (warp == kControlWarp) {
         // warp 0 took no part in the blind walk: count the items it skipped
         for (int q = 0; q < n_blind_chunks; ++q) {
@@ -1051,15 +1062,65 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       }
       consumer_sync();
       stamp(li, 5);
-      if (!grid_barrier(p, bar_base + (++nbar) * G, abort_flag, decision, ctid)) break;
-      stamp(li, 6);
-
-      // ---- down products for outputs h0 .. h1-1 ----
-      for (int v = ctid; v < kActBytes / 16; v += kDecodeConsumerThreads) {
-        reinterpret_cast<uint4*>(act_s)[v] = ld_cg_u4(
-            reinterpret_cast<const uint4*>(p.act + (c % kDecodeReplicas) * kDecodeActStride) + v);
+      // ---- activation exchange: every block polls the tagged words of the used positions and of the shared
+      //      expert (four words = four activations per load, up to three loads per thread) until all carry this
+      //      layer's tag, and packs them into shared memory.  No barrier: the words are the synchronisation.
+      //      A word of layer li + 1 is written only after its writer has seen every block's output of layer li,
+      //      so nobody still waits for layer li's words then ----
+      {
+        constexpr int kGroups4 = (kTopK + 1) * kInter / 4;                       // 1152 groups of four words
+        constexpr int kPerThread = (kGroups4 + kDecodeConsumerThreads - 1) / kDecodeConsumerThreads;
+        const uint32_t* words = p.act + (c % kDecodeReplicas) * kDecodeActStride;
+        const unsigned tag16 = act_tag >> 16;
+        bool need[kPerThread];
+#pragma unroll
+        for (int i = 0; i < kPerThread; ++i) {
+          const int v = ctid + i * kDecodeConsumerThreads;
+          const int row = v / (kInter / 4);
+          need[i] = v < kGroups4 && (row == kTopK || ((active_mask >> row) & 1u) != 0u);
+        }
+        uint4 w[kPerThread];
+        uint32_t gate_word = 0u;
+        bool ready = false;
+        const unsigned long long start = global_timer_ns();
+        unsigned spins = 0;
+        while (!ready) {
+          bool mine = true;
+#pragma unroll
+          for (int i = 0; i < kPerThread; ++i) {
+            if (need[i]) {
+              w[i] = ld_strong_u4(reinterpret_cast<const uint4*>(words) + ctid + i * kDecodeConsumerThreads);
+              mine = mine && (w[i].x >> 16) == tag16 && (w[i].y >> 16) == tag16 && (w[i].z >> 16) == tag16 &&
+                     (w[i].w >> 16) == tag16;
+            }
+          }
+          if (ctid == 0) {
+            gate_word = ld_strong_u32(words + 9 * kInter);
+            mine = mine && (gate_word >> 16) == tag16;
+          }
+          ready = __all_sync(0xffffffffu, mine);
+          if (!ready && (++spins & 63u) == 0u) {
+            if (*abort_flag != 0) break;
+            if (global_timer_ns() - start > kWaitBudgetNs) {
+              raise_status(p, abort_flag, kStatusTimeoutPeer);
+              record_site(p, 5, li);
+              break;
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < kPerThread; ++i) {
+          if (need[i]) {
+            uint2 packed;
+            packed.x = (w[i].x & 0xffffu) | (w[i].y << 16);
+            packed.y = (w[i].z & 0xffffu) | (w[i].w << 16);
+            reinterpret_cast<uint2*>(act_s)[ctid + i * kDecodeConsumerThreads] = packed;
+          }
+        }
+        if (ctid == 0) *reinterpret_cast<float*>(act_s + 9 * kInter) = bf16_bits_to_float(static_cast<uint16_t>(gate_word & 0xffffu));
       }
-      consumer_sync();
+      stamp(li, 6);
+      if (!uniform_alive(abort_flag, decision, ctid)) break;
       stamp(li, 7);
       {
         // A down item holds the block's rows of up to two experts; warps 0, 1 of the group take the halves
@@ -1195,7 +1256,6 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       stamp(li, 10);
     }
     if (c == 0 && ctid == 0 && *abort_flag == 0) {
-      *p.bar_base = bar_base + nbar * G;
       *p.epoch_base = epoch0 + static_cast<unsigned>(p.n_layers);
     }
   }

@@ -29,7 +29,7 @@ constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU exp
 constexpr int kDecodeReplicas = 8;
 constexpr int kDecodeDefaultInFlight = 0;     // ring items outstanding per block (0: no limit)
 constexpr int kDecodeLogitWords = 2 * kDecodeReplicas * kExperts;   // real + predicted, 64-bit words
-constexpr int kDecodeActStride = 9 * kInter + 64;   // BF16 elements per activation copy; [9*512] = gate logit bits (2 x u16)
+constexpr int kDecodeActStride = 9 * kInter + 64;   // 32-bit words per activation copy; word 9*512 = the shared gate logit
 
 struct DecodeParams {
   const LayerPtrs* layers;       // device array indexed by layer
@@ -40,7 +40,7 @@ struct DecodeParams {
   unsigned long long* logits;    // [2][replicas][256] words = tag32 << 32 | FP32 logit bits; the second
                                  // half carries the NEXT layer's router applied to this layer's input
                                  // (the prediction that lets its expert rows be requested early)
-  uint16_t* act;                 // [replicas][kDecodeActStride] BF16 activations: 8 ranks + shared,
+  uint32_t* act;                 // [replicas][kDecodeActStride] tagged words (layer tag << 16 | BF16 activation): 8 positions + shared,
                                  // then the shared-expert gate logit as FP32 bits
   unsigned long long* bar_counter;  // monotonic grid-barrier arrivals
   unsigned long long* bar_base;     // counter value when this launch starts

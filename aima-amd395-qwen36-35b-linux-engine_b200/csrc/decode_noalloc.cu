@@ -36,7 +36,7 @@ constexpr size_t kOffX0 = kOffLogits + static_cast<size_t>(kDecodeLogitWords) * 
 constexpr size_t kOffX1 = kOffX0 + static_cast<size_t>(kDecodeReplicas) * kHidden * 4;        // tagged vector 1
 constexpr size_t kOffAct = kOffX1 + static_cast<size_t>(kDecodeReplicas) * kHidden * 4;       // activation copies
 constexpr size_t kClearBytes = kOffAct - kOffSync;                // everything that carries a tag or a count
-constexpr size_t kScratchBytes = kOffAct + static_cast<size_t>(kDecodeReplicas) * kDecodeActStride * 2;
+constexpr size_t kScratchBytes = kOffAct + static_cast<size_t>(kDecodeReplicas) * kDecodeActStride * 4;
 static_assert(sizeof(LayerPtrs) * AIMA_MOE_NOALLOC_MAX_LAYERS <= kOffSync - kOffTable, "layer table overflows its slot");
 static_assert(kScratchBytes <= AIMA_MOE_NOALLOC_SCRATCH_BYTES, "scratch exceeds the stated maximum");
 
@@ -208,7 +208,7 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   params.xbuf0 = reinterpret_cast<uint32_t*>(scratch + kOffX0);
   params.xbuf1 = reinterpret_cast<uint32_t*>(scratch + kOffX1);
   params.logits = reinterpret_cast<unsigned long long*>(scratch + kOffLogits);
-  params.act = reinterpret_cast<uint16_t*>(scratch + kOffAct);
+  params.act = reinterpret_cast<uint32_t*>(scratch + kOffAct);
   params.bar_counter = reinterpret_cast<unsigned long long*>(scratch + kOffSync);
   params.bar_base = reinterpret_cast<unsigned long long*>(scratch + kOffSync + 128);
   params.epoch_base = reinterpret_cast<unsigned*>(scratch + kOffSync + 192);

@@ -76,7 +76,7 @@ struct aima_moe_handle {
   uint32_t* xbuf0 = nullptr;
   uint32_t* xbuf1 = nullptr;
   unsigned long long* logits = nullptr;
-  uint16_t* act = nullptr;
+  uint32_t* act = nullptr;
   unsigned long long* bar_counter = nullptr;
   unsigned long long* bar_base = nullptr;
   unsigned* epoch_base = nullptr;
@@ -139,7 +139,7 @@ constexpr size_t kXbufBytes = static_cast<size_t>(kDecodeReplicas) * kHidden * 4
 constexpr size_t kExchangeBytes = 256 + 256 + kLogitsBytes + 2 * kXbufBytes;
 
 size_t decode_scratch_size() {
-  return kExchangeBytes + align_up(static_cast<size_t>(kDecodeReplicas) * kDecodeActStride * 2, 256);
+  return kExchangeBytes + align_up(static_cast<size_t>(kDecodeReplicas) * kDecodeActStride * 4, 256);
 }
 
 // AIMA_MOE_DECODE_IN_FLIGHT in the environment overrides how many ring items a block of the decode
@@ -373,7 +373,7 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
   handle->logits = reinterpret_cast<unsigned long long*>(cursor); cursor += kLogitsBytes;
   handle->xbuf0 = reinterpret_cast<uint32_t*>(cursor); cursor += kXbufBytes;
   handle->xbuf1 = reinterpret_cast<uint32_t*>(cursor); cursor += kXbufBytes;
-  handle->act = reinterpret_cast<uint16_t*>(cursor);
+  handle->act = reinterpret_cast<uint32_t*>(cursor);
 
   if (config->max_prefill_tokens > 0) {
     status = prefill_workspace_allocate(&handle->prefill, config->max_prefill_tokens,
