@@ -8,16 +8,16 @@
 // benchmarks/shape-lab/four_layer_mini_engine.py:304-326, 391-473, 844-859,
 // 1152-1220 and native/src/native_pointwise.hip.cpp:94-107, 184-205.
 //
-// Structure.  One block per SM, 16 warps.  Warp 15 is a producer that streams
+// Structure.  One block per SM, 16 warps.  Warp 4 is a producer that streams
 // weights from HBM into ONE ring of 6 shared-memory slots of 32 KB (two halves
-// of 16 KB) with 1-D bulk (TMA) copies; warps 1-12 consume them with the
-// canonical warp dot product, as three groups of four warps (slot s always
-// belongs to group s % 3, its up to four rows or row pairs to the group's four
-// warps); warp 0 runs the exchanges between blocks, the top-8 and the layer
-// plan; warp 13 predicts the next layer's experts.  The kernel is bandwidth
-// bound (57.7 MB of weights per layer for ~30 MFLOP) but its layer is a serial
-// chain of three grid-wide hand-overs, so everything is arranged to keep bulk
-// copies in flight across them.
+// of 16 KB) with 1-D bulk (TMA) copies; the twelve warps w with w % 4 != 0
+// consume them with the canonical warp dot product, as three groups of four
+// warps (slot s always belongs to group s % 3, its up to four rows or row pairs
+// to the group's four warps); warp 0 runs the exchanges between blocks, the
+// top-8 and the layer plan; warp 8 predicts the next layer's experts; warp 12
+// is spare.  The kernel is bandwidth bound (57.7 MB of weights per layer for
+// ~30 MFLOP) but its layer is a serial chain of three grid-wide hand-overs, so
+// everything is arranged to keep bulk copies in flight across them.
 //
 // A bulk copy costs its issuing thread and the copy engine a fixed time whatever
 // its size (one lane sustains about 8 copies of 4 KB per microsecond, 33 GB/s per
@@ -61,7 +61,7 @@
 // prediction was wrong is fetched again with the right expert, so the result does
 // not depend on the prediction: outputs are bit-identical with and without it.
 //
-// Every wait (mbarrier, grid barrier, hand-overs between the warps of a block)
+// Every wait (mbarrier, exchange words, hand-overs between the warps of a block)
 // is bounded; on expiry the block raises a status word, drains its outstanding
 // copies and returns, so the context stays usable.
 #include "decode_kernel.cuh"
@@ -151,9 +151,10 @@ __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" :: "n"(kDecodeConsumerThreads) : "memory");
 }
 
-__device__ __noinline__ void raise_status(const DecodeParams& p,
-                                          volatile int* abort_flag, int code) {
-  atomicCAS(p.status, 0, code);
+// (These two take the status pointer, not the parameter block: a reference to the kernel's parameters handed
+// to an out-of-line function makes every thread copy the whole block to its stack at kernel entry.)
+__device__ __noinline__ void raise_status(int* status, volatile int* abort_flag, int code) {
+  atomicCAS(status, 0, code);
   *abort_flag = code;
 }
 
@@ -163,17 +164,17 @@ __device__ __noinline__ void raise_status(const DecodeParams& p,
 // 4 consumer item (down rows), 5 activation exchange, 6 plan hand-over to the producer,
 // 7 output exchange, 8 norm row, 9 logits exchange, 10 prediction hand-over,
 // 11 expert-parallel peer word, 12 predicted-logits exchange.
-__device__ __noinline__ void record_site(const DecodeParams& p, int site, int detail,
+__device__ __noinline__ void record_site(int* status, int site, int detail,
                                          const unsigned* diag = nullptr) {
-  if (atomicCAS(p.status + 1, 0, site) == 0) {
-    p.status[2] = blockIdx.x;
-    p.status[3] = threadIdx.x >> 5;
-    p.status[4] = detail;
+  if (atomicCAS(status + 1, 0, site) == 0) {
+    status[2] = blockIdx.x;
+    status[3] = threadIdx.x >> 5;
+    status[4] = detail;
     if (diag != nullptr) {
-      p.status[5] = static_cast<int>(diag[0]);
-      p.status[6] = static_cast<int>(diag[1]);
-      p.status[7] = static_cast<int>(diag[2]);
-      p.status[8] = static_cast<int>(diag[3]);
+      status[5] = static_cast<int>(diag[0]);
+      status[6] = static_cast<int>(diag[1]);
+      status[7] = static_cast<int>(diag[2]);
+      status[8] = static_cast<int>(diag[3]);
     }
   }
 }
@@ -364,7 +365,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         ok = ok && mbar_wait_bounded(empty_bar(s), use & 1u, abort_flag, diag);
         if (!ok && lane == 0 && *abort_flag == kStatusTimeoutMbarrier) {
           atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
-          record_site(p, 1, static_cast<int>(seq), diag);
+          record_site(p.status, 1, static_cast<int>(seq), diag);
         }
         ok = __all_sync(kPair, ok);
         if (!ok) { alive = false; return false; }
@@ -387,8 +388,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
             if ((++spins & 255u) == 0u) {
               if (*abort_flag != 0) { ok = false; break; }
               if (global_timer_ns() - start > kWaitBudgetNs) {
-                raise_status(p, abort_flag, code);
-                record_site(p, site, detail);
+                raise_status(p.status, abort_flag, code);
+                record_site(p.status, site, detail);
                 ok = false;
                 break;
               }
@@ -550,8 +551,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
             if ((++spins & 15u) == 0u) {
               if (*abort_flag != 0) break;
               if (global_timer_ns() - start > kWaitBudgetNs) {
-                raise_status(p, abort_flag, kStatusTimeoutPeer);
-                record_site(p, 12, li);
+                raise_status(p.status, abort_flag, kStatusTimeoutPeer);
+                record_site(p.status, 12, li);
                 break;
               }
             }
@@ -596,7 +597,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       if (!mbar_wait_bounded(full_bar(s), use & 1u, abort_flag, diag)) {
         if (*abort_flag == kStatusTimeoutMbarrier) {
           atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
-          record_site(p, site, static_cast<int>(item), diag);
+          record_site(p.status, site, static_cast<int>(item), diag);
         }
         return nullptr;
       }
@@ -698,8 +699,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           if (!ready && (++spins & 63u) == 0u) {
             if (*abort_flag != 0) break;
             if (global_timer_ns() - start > kWaitBudgetNs) {
-              raise_status(p, abort_flag, kStatusTimeoutPeer);
-              record_site(p, 7, li);
+              raise_status(p.status, abort_flag, kStatusTimeoutPeer);
+              record_site(p.status, 7, li);
               break;
             }
           }
@@ -737,7 +738,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         if (!mbar_wait_bounded(norm_bar, li & 1u, abort_flag)) {
           if (*abort_flag == kStatusTimeoutMbarrier) {
             atomicCAS(p.status, 0, kStatusTimeoutMbarrier);
-            record_site(p, 8, li);
+            record_site(p.status, 8, li);
           }
           alive = false;
         }
@@ -874,8 +875,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           if ((++spins & 255u) == 0u) {
             if (*abort_flag != 0) { alive = false; break; }
             if (global_timer_ns() - start > kWaitBudgetNs) {
-              raise_status(p, abort_flag, kStatusTimeoutIds);
-              record_site(p, 13, li * 16 + blind_seen);
+              raise_status(p.status, abort_flag, kStatusTimeoutIds);
+              record_site(p.status, 13, li * 16 + blind_seen);
               alive = false;
               break;
             }
@@ -901,7 +902,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           if (!ready && (++spins & 63u) == 0u) {
             if (*abort_flag != 0) break;
             if (global_timer_ns() - start > kWaitBudgetNs) {
-              raise_status(p, abort_flag, kStatusTimeoutPeer);
+              raise_status(p.status, abort_flag, kStatusTimeoutPeer);
               {
                 // first expert whose word never carried this layer's tag, and what was there instead
                 int bad = 0x7fffffff;
@@ -917,7 +918,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
                   const unsigned long long word = w[(first_bad >> 5) & 7];
                   unsigned diag[4] = {tag, static_cast<unsigned>(first_bad),
                                       static_cast<unsigned>(n_bad) | (alive ? 0x10000u : 0u), static_cast<unsigned>(word >> 32)};
-                  record_site(p, 9, li, diag);
+                  record_site(p.status, 9, li, diag);
                 }
               }
               break;
@@ -966,8 +967,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           while (misc->pred_layer < li + 1) {
             if (*abort_flag != 0 || global_timer_ns() - wait_start > kWaitBudgetNs) {
               if (*abort_flag == 0 && lane == 0) {
-                raise_status(p, abort_flag, kStatusTimeoutIds);
-                record_site(p, 10, li);
+                raise_status(p.status, abort_flag, kStatusTimeoutIds);
+                record_site(p.status, 10, li);
               }
               break;
             }
@@ -1102,8 +1103,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           if (!ready && (++spins & 63u) == 0u) {
             if (*abort_flag != 0) break;
             if (global_timer_ns() - start > kWaitBudgetNs) {
-              raise_status(p, abort_flag, kStatusTimeoutPeer);
-              record_site(p, 5, li);
+              raise_status(p.status, abort_flag, kStatusTimeoutPeer);
+              record_site(p.status, 5, li);
               break;
             }
           }
@@ -1224,8 +1225,8 @@ moe_decode_persistent_kernel(const DecodeParams p) {
                 if ((++spins & 63u) == 0u) {
                   if (*abort_flag != 0) break;
                   if (global_timer_ns() - start > kWaitBudgetNs) {
-                    raise_status(p, abort_flag, kStatusTimeoutPeer);
-                    record_site(p, 11, li * 16 + r);
+                    raise_status(p.status, abort_flag, kStatusTimeoutPeer);
+                    record_site(p.status, 11, li * 16 + r);
                     break;
                   }
                 }
