@@ -26,6 +26,8 @@
 #include "grouped_gemm.cuh"
 
 #include <cuda.h>
+#include <mutex>
+#include <unordered_map>
 #include <cudaTypedefs.h>
 
 namespace aima {
@@ -790,18 +792,50 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // 2-D BF16 tensor [rows, cols] row-major, box 64 columns x box_rows rows (128 for tile loads,
-// 1 for gather4 loads), 128-byte swizzle.
+// 1 for gather4 loads), 128-byte swizzle.  A descriptor depends only on the base address and these
+// numbers, and a layer's weights and the workspace keep their addresses from bind to release, so the
+// encoded descriptors are kept: a prefill layer asks for 18 of them per call, always the same ones.
+struct MapKey {
+  const void* base;
+  uint64_t rows, cols, pitch;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = reinterpret_cast<uint64_t>(k.base) * 0x9e3779b97f4a7c15ull;
+    h ^= (k.rows + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2));
+    h ^= (k.cols * 31 + k.pitch * 131 + k.box_rows + (h << 6) + (h >> 2));
+    return static_cast<size_t>(h);
+  }
+};
+
 bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
               uint32_t box_rows = kBM) {
+  static std::mutex mutex;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{base, rows, cols, pitch_elems, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    const auto hit = cache.find(key);
+    if (hit != cache.end()) { *map = hit->second; return true; }
+  }
   PFN_cuTensorMapEncodeTiled_v12000 encode = encode_fn();
   if (encode == nullptr) return false;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {pitch_elems * 2};
   const cuuint32_t box[2] = {kBK, box_rows};
   const cuuint32_t elem[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cache.size() >= 8192) cache.clear();      // a host that keeps binding new tensors: start over rather than grow
+  cache.emplace(key, *map);
+  return true;
 }
 
 template <int MODE, bool kGather = false>

@@ -36,8 +36,10 @@ FALLBACK_HBM_GBS = 6650.0
 # all weights of one layer: router, 256 experts (gate_up + down), shared expert, shared gate, norm
 BYTES_PER_LAYER_WEIGHTS = 1_048_576 + 256 * 6_291_456 + 6_291_456 + 4_096 + 4_096
 # dram__bytes_read.sum + dram__bytes_write.sum per layer of the decode kernel, from the ncu capture
-# summarised in profiles/ (2-layer case: 118.9 MB per launch)
-DECODE_TRAFFIC_PER_LAYER = 59_460_000
+# summarised in profiles/moe_decode_persistent_kernel_stack2.md (2-layer case: 115.75 MB read + 4.98 MB
+# written per launch; the next layer's router rows the prediction reads are the same bytes the next
+# layer reads again 18 us later, so they cost no second DRAM read)
+DECODE_TRAFFIC_PER_LAYER = 60_365_000
 
 
 MIN_TIMED_SECONDS = 1.0      # the K-step loop is repeated until at least this much has been timed
@@ -121,14 +123,23 @@ class ClockSampler:
 
 
 def cpu_reference_tokens_per_second(sample_layers: int, sample_tokens: int, threads: int) -> dict:
-    """Times the torch-CPU statement of the reference's MoE path for one token per layer and
-    extrapolates linearly to the 40-layer stack."""
+    """Times the reference's CPU statement of the MoE path for one token per layer and extrapolates linearly
+    to the 40-layer stack.  Where the reference's own torch functions are at hand (cut out of the checkout into
+    oracle/_ref/ at build time) those run -- kind "reference"; otherwise the restatement in oracle/ -- kind "port"."""
     import torch
 
     sys.path.insert(0, str(ROOT / "oracle"))
-    import moe_torch_ref as ref
+    import reference_torch
     from __graft_entry__ import load_package
 
+    if reference_torch.available():
+        ref = reference_torch.ReferenceTorch(tokens=1)
+        kind, what = "reference", "the reference's own torch functions (four_layer_mini_engine.py: router_topk, " \
+                                  "expanded_routed_moe, shared_expert, rmsnorm; pure-torch CPU variant)"
+    else:
+        import moe_torch_ref as ref
+        kind, what = "port", "the torch-CPU restatement of the reference MoE path (router, top-8, expanded bmm experts, " \
+                             "shared expert)"
     synth = load_package().synth
     torch.set_num_threads(threads)
     generator = torch.Generator().manual_seed(SEED)
@@ -155,10 +166,8 @@ def cpu_reference_tokens_per_second(sample_layers: int, sample_tokens: int, thre
         x = one_token(x)
     elapsed = time.perf_counter() - start
     per_layer = elapsed / (sample_tokens * sample_layers)
-    return {"value": 1.0 / (per_layer * LAYERS), "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"{sample_tokens} tokens x {sample_layers} layers of the torch-CPU statement of the "
-                      f"reference MoE path (router, top-8, expanded bmm experts, shared expert), "
-                      f"per-layer time x {LAYERS}",
+    return {"value": 1.0 / (per_layer * LAYERS), "unit": "tokens/s", "cores": threads, "kind": kind,
+            "sample": f"{sample_tokens} tokens x {sample_layers} layers of {what}, per-layer time x {LAYERS}",
             "seconds": elapsed}
 
 
@@ -214,6 +223,10 @@ def run_ours(args) -> None:
         keep.append(weights)
     if distributed:
         provider.ep_connect_all(dist.new_group(backend="gloo"))
+    if args.decode_hot:
+        # profiling aid: +20 on eight fixed experts, so every layer picks the same experts (prediction always right;
+        # with few layers the touched weights stay in L2)
+        provider.set_router_hooks(synth.hot_expert_bias(range(3, 256, 32)).to(device), False)
     torch.cuda.synchronize()
 
     x0 = synth.activations(SEED, 1, "residual", 0)[0]
@@ -277,6 +290,9 @@ def run_ours(args) -> None:
     clocks = sampler.stop()
     provider.sync_metrics()
 
+    if args.decode_timeline and rank == 0:
+        decode_timeline_report(provider, buffers)
+
     # ---- N > 1: are the ranks' results the single-GPU bits?  (outside the timed region) ----
     parity = None
     if distributed:
@@ -334,6 +350,37 @@ def run_ours(args) -> None:
         provider.release()
     if distributed:
         dist.destroy_process_group()
+
+
+DECODE_STAMPS = ["layer entered", "input normalised", "own logits written", "all logits seen", "plan published",
+                 "routed gate/up chunks consumed", "activations of all blocks packed", "block agrees to go on",
+                 "first down item landed", "down products done", "output words stored", "down items consumed",
+                 "producer: router/shared items issued", "producer: last blind item issued",
+                 "producer: post-plan gate/up items issued", "producer: down items issued"]
+
+
+def decode_timeline_report(provider, buffers) -> None:
+    """One traced token (outside the timed region): for every stamp the minimum / median / maximum over all
+    blocks of its time after the earliest block entered the layer, medians over the middle layers; to stderr."""
+    provider.set_tracing(True)
+    provider.decode_stack(buffers[0], buffers[1])
+    provider.sync_metrics()
+    timelines = provider.decode_block_timelines()          # [block][layer][stamp], nanoseconds
+    provider.set_tracing(False)
+    blocks, layers = len(timelines), len(timelines[0])
+    middle = range(2, layers - 1) if layers >= 4 else range(layers)
+    sys.stderr.write(f"decode timeline, {blocks} blocks, layers {middle.start}..{middle.stop - 1}: "
+                     "us after the earliest block enters the layer (min / median / max over blocks)\n")
+    for k, name in enumerate(DECODE_STAMPS):
+        low, mid, high = [], [], []
+        for layer in middle:
+            base = min(timelines[b][layer][0] for b in range(blocks))
+            values = sorted((timelines[b][layer][k] - base) / 1000.0 for b in range(blocks) if timelines[b][layer][k] > 0)
+            if values:
+                low.append(values[0]); mid.append(values[len(values) // 2]); high.append(values[-1])
+        if low:
+            sys.stderr.write(f"  {name:42s} {statistics.median(low):7.2f} {statistics.median(mid):7.2f} "
+                             f"{statistics.median(high):7.2f}\n")
 
 
 def expert_parallel_parity(package, provider, synth, device, rank: int, world: int, dist) -> dict:
@@ -399,7 +446,7 @@ def apply_routing(provider, synth, device, routing: str) -> None:
 
 
 def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing: str, weights=None,
-                          flags: int = 0) -> dict:
+                          flags: int = 0, kernel_times_wanted: bool = False) -> dict:
     """Device-timed prefill of ONE MoE layer (BASELINE config 2: T = 8192, Zipf(1.1) router bias)."""
     import torch
 
@@ -427,14 +474,53 @@ def prefill_layer_numbers(package, device, tokens: int, iterations: int, routing
         torch.cuda.synchronize()
         provider.sync_metrics()
         ms = start.elapsed_time(stop) / iterations
+        kernel_times = None
+        if kernel_times_wanted:
+            kernel_times = prefill_kernel_times(
+                lambda: provider.launch_selected_moe(post_attention=h2, residual_hidden=resid, model_layer=0, out=out))
+            provider.sync_metrics()
     finally:
         provider.release()
     peak, kind = measured_tensor_peak()
     tflops = tokens * PREFILL_FLOP_PER_TOKEN / (ms * 1.0e-3) / 1.0e12
-    return {"workload": f"prefill_T{tokens}_1layer_{routing} (BASELINE config 2)", "tokens": tokens,
-            "ms_per_layer": ms, "tokens_per_s": tokens / (ms * 1.0e-3), "achieved_tflops": tflops,
-            "peak_tflops": peak, "peak_source": kind, "frac": tflops / peak, "bound": "tensor",
-            "flop_per_layer": tokens * PREFILL_FLOP_PER_TOKEN, "kernel_launches_per_layer": int(per_call)}
+    numbers = {"workload": f"prefill_T{tokens}_1layer_{routing} (BASELINE config 2)", "tokens": tokens,
+               "ms_per_layer": ms, "tokens_per_s": tokens / (ms * 1.0e-3), "achieved_tflops": tflops,
+               "peak_tflops": peak, "peak_source": kind, "frac": tflops / peak, "bound": "tensor",
+               "flop_per_layer": tokens * PREFILL_FLOP_PER_TOKEN, "kernel_launches_per_layer": int(per_call)}
+    if kernel_times is not None:
+        numbers["kernel_times"] = kernel_times
+    return numbers
+
+
+def prefill_kernel_times(launch_layer, layers: int = 10) -> dict:
+    """Device time of every kernel inside a running layer (CUPTI activity records through torch.profiler, outside
+    the timed region): per kernel the calls per layer and the mean microseconds, and the start / end of every
+    kernel of the last layer relative to its first kernel.  Streams run concurrently as in production, so this
+    is the timeline that an ncu launch list (serialised, cold) cannot give."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as profiler:
+        for _ in range(layers):
+            launch_layer()
+        torch.cuda.synchronize()
+    events = sorted((e for e in profiler.events() if e.device_type.name == "CUDA"), key=lambda e: e.time_range.start)
+    if not events:
+        return {"note": "no CUPTI activity records"}
+    totals: dict[str, list[float]] = {}
+    for event in events:
+        entry = totals.setdefault(event.name[:72], [0, 0.0])
+        entry[0] += 1
+        entry[1] += event.device_time
+    last = events[-(len(events) // layers):]
+    origin = last[0].time_range.start
+    return {"layers": layers,
+            "span_us_per_layer": (events[-1].time_range.end - events[0].time_range.start) / layers,
+            "kernels": {name: {"calls_per_layer": count / layers, "mean_us": total / count}
+                        for name, (count, total) in totals.items()},
+            "last_layer_timeline_us": [[round(e.time_range.start - origin, 1), round(e.time_range.end - origin, 1),
+                                        e.name[:48]] for e in last]}
 
 
 def prefill_stack_numbers(package, device, tokens: int, layers: int, iterations: int, routing: str) -> dict:
@@ -751,7 +837,8 @@ def run_prefill(args) -> None:
             "hbm_frac": numbers["hbm_frac"],
             "gpu_launches": numbers["kernel_launches_per_pass"] * args.steps, "clocks": clocks}))
         return
-    numbers = prefill_layer_numbers(package, device, args.tokens, max(args.steps, 1), args.routing, flags=args.flags)
+    numbers = prefill_layer_numbers(package, device, args.tokens, max(args.steps, 1), args.routing, flags=args.flags,
+                                    kernel_times_wanted=args.kernel_times)
     clocks = sampler.stop()
     line = {"metric": "moe_prefill_tokens_per_second", "value": numbers["tokens_per_s"], "unit": "tokens/s",
             "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": numbers["ms_per_layer"],
@@ -761,6 +848,15 @@ def run_prefill(args) -> None:
                          "unit": "TFLOP/s", "frac": numbers["frac"], "traffic": None,
                          "peak_source": numbers["peak_source"]},
             "gpu_launches": numbers["kernel_launches_per_layer"] * args.steps, "clocks": clocks}
+    if "kernel_times" in numbers:
+        table = numbers["kernel_times"]
+        sys.stderr.write(f"kernel times inside a running layer, {table.get('layers')} layers, "
+                         f"{table.get('span_us_per_layer', 0.0):.1f} us per layer\n")
+        for name, entry in table.get("kernels", {}).items():
+            sys.stderr.write(f"  {entry['calls_per_layer']:4.1f} x {entry['mean_us']:8.1f} us  {name}\n")
+        for begin, end, name in table.get("last_layer_timeline_us", []):
+            sys.stderr.write(f"  {begin:8.1f} -> {end:8.1f}  {name}\n")
+        line["kernel_times"] = {name: round(entry["mean_us"], 1) for name, entry in table.get("kernels", {}).items()}
     print(json.dumps(line))
 
 
@@ -783,6 +879,13 @@ def main() -> None:
                         help="--workload prefill on N > 1 GPUs: parts of the dispatch / products / return pipeline")
     parser.add_argument("--flags", type=int, default=0,
                         help="--workload prefill, one layer: AIMA_MOE_FLAG_* bits for A/B runs (qualification)")
+    parser.add_argument("--decode-timeline", action="store_true",
+                        help="decode: after the timed region, trace one token and print the all-block phase times to stderr")
+    parser.add_argument("--decode-hot", action="store_true",
+                        help="decode profiling aid: +20 router bias on eight fixed experts (not the benchmark config)")
+    parser.add_argument("--kernel-times", action="store_true",
+                        help="--workload prefill, one layer: after the timed region, record every kernel's device "
+                             "time inside ten running layers (CUPTI) and print the table to stderr")
     parser.add_argument("--stack-layers", type=int, default=1,
                         help="--workload prefill: run this many layers through the stack entry point (config 3: 40)")
     args = parser.parse_args()

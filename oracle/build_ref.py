@@ -99,6 +99,9 @@ def compile_library(name: str, contraction: list[str]) -> Path:
     return target
 
 
+sys.path.insert(0, str(HERE))
+
+
 def build(force: bool = False) -> list[Path]:
     """Returns the built libraries; an empty list when the reference checkout is absent."""
     libraries = [OUT / "libmoe_ref.so", OUT / "libmoe_ref_fma.so"]
@@ -109,6 +112,9 @@ def build(force: bool = False) -> list[Path]:
     if not force and all(path.is_file() and path.stat().st_mtime > newest for path in libraries):
         return libraries
     extract()
+    import reference_torch        # the torch functions of the same checkout, for the benchmark's reference arm
+
+    reference_torch.write_extracted()
     compile_library("libmoe_ref.so", ["-ffp-contract=off"])
     compile_library("libmoe_ref_fma.so", ["-ffp-contract=fast", "-mfma"])
     return libraries

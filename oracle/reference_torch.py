@@ -6,7 +6,8 @@ The functions are closures nested inside run_with_torch
 the module cannot simply be imported and used.  Instead the `def` bodies are cut out of the
 reference checkout with `ast` at run time and executed in a namespace that binds their free
 variables to the values the pure-torch, CPU variant of the engine runs with (no Triton kernels,
-BF16, top-8, hidden 2048).  Nothing is copied into this repository.
+BF16, top-8, hidden 2048).  Nothing is copied into this repository; oracle/build_ref.py saves the
+cut text under oracle/_ref/ (ignored by git) for machines without the checkout.
 
   router_topk :7775   routing_weights :7786   expanded_routed_moe :7791   build_dispatch_table :7806
   resident_routed_moe :7904   shared_expert :8240   rmsnorm :5110
@@ -28,23 +29,45 @@ NAMES = ("router_topk", "routing_weights", "expanded_routed_moe", "build_dispatc
          "resident_routed_moe", "shared_expert", "rmsnorm")
 
 
+EXTRACTED = Path(__file__).resolve().parent / "_ref" / "reference_torch_functions.py"
+
+
 def available() -> bool:
-    return SOURCE.is_file()
+    return SOURCE.is_file() or EXTRACTED.is_file()
+
+
+def cut_functions() -> dict[str, tuple[str, int]]:
+    """name -> (source text of the def, dedented; its line in the reference file), from the checkout."""
+    text = SOURCE.read_text()
+    tree = ast.parse(text)
+    found: dict[str, ast.FunctionDef] = {}
+    for node in ast.walk(tree):
+        if isinstance(node, ast.FunctionDef) and node.name in NAMES and node.name not in found:
+            found[node.name] = node
+    missing = [name for name in NAMES if name not in found]
+    if missing:
+        raise RuntimeError(f"reference functions not found: {missing}")
+    return {name: (textwrap.dedent(" " * found[name].col_offset + ast.get_source_segment(text, found[name])),
+                   found[name].lineno) for name in NAMES}
+
+
+def write_extracted() -> Path | None:
+    """Saves the cut functions under oracle/_ref/ (ignored by git), so that a machine without the reference
+    checkout -- a GPU box timing the reference arm of the benchmark -- can still run them."""
+    if not SOURCE.is_file():
+        return EXTRACTED if EXTRACTED.is_file() else None
+    EXTRACTED.parent.mkdir(exist_ok=True)
+    pieces = ["# GENERATED from the reference checkout by oracle/reference_torch.py -- not tracked, do not edit.\n"]
+    for name, (source, line) in cut_functions().items():
+        pieces.append(f"# ---- {name}: benchmarks/shape-lab/four_layer_mini_engine.py:{line} ----\n{source}\n\n")
+    EXTRACTED.write_text("".join(pieces))
+    return EXTRACTED
 
 
 class ReferenceTorch:
     """The reference's functions, bound for `tokens` rows on the CPU."""
 
     def __init__(self, tokens: int, moe_chunk_size: int = 1 << 30) -> None:
-        text = SOURCE.read_text()
-        tree = ast.parse(text)
-        found: dict[str, ast.FunctionDef] = {}
-        for node in ast.walk(tree):
-            if isinstance(node, ast.FunctionDef) and node.name in NAMES and node.name not in found:
-                found[node.name] = node
-        missing = [name for name in NAMES if name not in found]
-        if missing:
-            raise RuntimeError(f"reference functions not found: {missing}")
         never = lambda *args, **kwargs: False   # every "use the Triton kernel?" switch: no
         self.namespace: dict[str, Any] = {
             "torch": torch, "F": F, "Any": Any,
@@ -59,12 +82,14 @@ class ReferenceTorch:
             "should_use_triton_shared_expert_fused_down": never,
         }
         self.lines = {}
-        for name in NAMES:
-            node = found[name]
-            segment = ast.get_source_segment(text, node)
-            exec(compile(textwrap.dedent(" " * node.col_offset + segment), f"<reference {name}>", "exec"),
-                 self.namespace)
-            self.lines[name] = node.lineno
+        if SOURCE.is_file():
+            for name, (source, line) in cut_functions().items():
+                exec(compile(source, f"<reference {name}>", "exec"), self.namespace)
+                self.lines[name] = line
+        elif EXTRACTED.is_file():
+            exec(compile(EXTRACTED.read_text(), str(EXTRACTED), "exec"), self.namespace)
+        else:
+            raise RuntimeError("neither the reference checkout nor oracle/_ref/reference_torch_functions.py is present")
 
     def __getattr__(self, name: str) -> Any:
         if name in NAMES:
