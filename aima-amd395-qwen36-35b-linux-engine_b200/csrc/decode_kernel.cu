@@ -647,6 +647,21 @@ moe_decode_persistent_kernel(const DecodeParams p) {
     auto stamp = [&](int li, int k) {
       if (ctid == 0) stamp_now(li, k);
     };
+    if (p.n_layers > 1) {
+      // The output words between the layers of a launch are only written by launches of several layers, while
+      // every launch advances the epoch: a word left by such a launch 65 535 epochs ago carries the tag this
+      // launch expects.  Every block therefore clears the words it writes (its output rows, every copy, both
+      // buffers) before anything else; a reader gets to them only after this block's logits and activations
+      // of the first layer, which come later in program order.
+      if (ctid < nh) {
+#pragma unroll
+        for (int rep = 0; rep < kDecodeReplicas; ++rep) {
+          st_strong_u32(p.xbuf0 + rep * kHidden + h0 + ctid, 0u);
+          st_strong_u32(p.xbuf1 + rep * kHidden + h0 + ctid, 0u);
+        }
+      }
+      __threadfence();
+    }
     if (kEp) {
       // Expert parallelism leaves the activation words of positions this GPU does not use unwritten, possibly
       // for many calls, and a 16-bit tag comes round again: every call starts by clearing the words this block
@@ -671,10 +686,10 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       stamp(li, 0);
       const uint32_t* xw_src = (li & 1) ? p.xbuf1 : p.xbuf0;     // tagged words written by layer li - 1
       uint32_t* xw_dst = (li & 1) ? p.xbuf0 : p.xbuf1;
-      const unsigned tag_in = (epoch0 + li) & 0xffffu;           // tag of layer li - 1
-      const unsigned tag_out = (epoch0 + li + 1) & 0xffffu;
-      // activation words of this layer: a 16-bit tag that is never zero, so a cleared word matches no layer
-      const uint32_t act_tag = (((epoch0 + static_cast<unsigned>(li) + 1u) % 0xffffu) + 1u) << 16;
+      // 16-bit tags that are never zero (a cleared word matches no layer): ((epoch) mod 65535) + 1
+      const unsigned tag_in = ((epoch0 + static_cast<unsigned>(li)) % 0xffffu) + 1u;           // tag of layer li - 1
+      const unsigned tag_out = ((epoch0 + static_cast<unsigned>(li) + 1u) % 0xffffu) + 1u;
+      const uint32_t act_tag = tag_out << 16;                     // activation words of this layer
       // ---- layer input into shared memory (packed BF16) ----
       if (first) {
         if (ctid < kHidden / 8) {
@@ -1257,7 +1272,9 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       stamp(li, 10);
     }
     if (c == 0 && ctid == 0 && *abort_flag == 0) {
-      *p.epoch_base = epoch0 + static_cast<unsigned>(p.n_layers);
+      // the counter lives in [0, 65535 * 65536): the 16-bit tags, (epoch mod 65535) + 1, then stay consecutive
+      // when it comes round (a plain 32-bit wrap would repeat one tag in two successive layers)
+      *p.epoch_base = (epoch0 + static_cast<unsigned>(p.n_layers)) % kDecodeEpochPeriod;
     }
   }
   __syncthreads();

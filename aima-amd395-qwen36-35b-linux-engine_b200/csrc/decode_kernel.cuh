@@ -27,6 +27,7 @@ constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU exp
 // block c reads copy c % kDecodeReplicas: 148 readers of the same few L2 lines
 // otherwise queue at the L2 slices that own them.
 constexpr int kDecodeReplicas = 8;
+constexpr unsigned kDecodeEpochPeriod = 65535u * 65536u;   // the device-resident epoch counter counts modulo this
 constexpr int kDecodeDefaultInFlight = 0;     // ring items outstanding per block (0: no limit)
 constexpr int kDecodeLogitWords = 2 * kDecodeReplicas * kExperts;   // real + predicted, 64-bit words
 constexpr int kDecodeActStride = 9 * kInter + 64;   // 32-bit words per activation copy; word 9*512 = the shared gate logit

@@ -838,6 +838,18 @@ AIMA_EXPORT int aima_moe_ep_connect(aima_moe_handle* handle, uint32_t peer, cons
   return AIMA_MOE_OK;
 }
 
+AIMA_EXPORT int aima_moe_debug_set_decode_epoch(aima_moe_handle* handle, uint32_t epoch) {
+  if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
+  std::lock_guard<std::mutex> lock(handle->mutex);
+  if (const int wrong_device = check_current_device(handle); wrong_device != AIMA_MOE_OK) return wrong_device;
+  // after everything enqueued so far: the kernels read the word when they start
+  epoch %= kDecodeEpochPeriod;
+  cudaError_t error = cudaDeviceSynchronize();
+  if (error == cudaSuccess) error = cudaMemcpy(handle->epoch_base, &epoch, sizeof epoch, cudaMemcpyHostToDevice);
+  if (error != cudaSuccess) return fail_cuda(error, "cudaMemcpy decode epoch");
+  return AIMA_MOE_OK;
+}
+
 AIMA_EXPORT int aima_moe_set_tracing(aima_moe_handle* handle, int enabled) {
   if (handle == nullptr) return fail(AIMA_MOE_ERR_INVALID_ARGUMENT, "handle is null");
   std::lock_guard<std::mutex> lock(handle->mutex);

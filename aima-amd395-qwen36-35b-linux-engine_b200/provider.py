@@ -134,6 +134,7 @@ EXPORTS = [
      [c_void_p, ctypes.POINTER(c_float), c_uint32, ctypes.POINTER(c_uint32)]),
     ("aima_moe_set_forced_routing", c_int, [c_void_p, c_void_p, c_void_p, c_uint32]),
     ("aima_moe_set_tracing", c_int, [c_void_p, c_int]),
+    ("aima_moe_debug_set_decode_epoch", c_int, [c_void_p, c_uint32]),
     ("aima_moe_read_decode_timeline", c_int,
      [c_void_p, ctypes.POINTER(c_uint64), c_uint32, ctypes.POINTER(c_uint32)]),
     ("aima_moe_read_decode_block_timelines", c_int,
@@ -462,6 +463,10 @@ class MoeProvider:
 
     def set_tracing(self, enabled: bool) -> None:
         self.lib.check(self.lib.aima_moe_set_tracing(self.handle, int(enabled)))
+
+    def debug_set_decode_epoch(self, epoch: int) -> None:
+        """Qualification: presets the epoch counter the decode kernel's exchange tags derive from."""
+        self.lib.check(self.lib.aima_moe_debug_set_decode_epoch(self.handle, epoch & 0xFFFFFFFF))
 
     def decode_timeline(self) -> list[list[int]]:
         """Per layer of the last traced decode launch: 12 GPU nanosecond stamps."""

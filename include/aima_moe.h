@@ -342,11 +342,17 @@ int aima_moe_ep_connect(aima_moe_handle* handle, uint32_t peer, const void* ipc_
  * the blocks of the decode kernel stamp the GPU's nanosecond timer at
  * AIMA_MOE_DECODE_TRACE_STAMPS points of every layer (layer start, norm done,
  * router/shared rows done, logits arrived, layer plan published, routed gate/up
- * done, activation barrier, activations loaded, (same), down dots done, output
- * stored, (same)).  read_decode_timeline synchronises and copies block 0's
+ * done, activations of all blocks polled and packed, block agrees to go on, first
+ * down item landed, down dots done, output stored, down items consumed).  read_decode_timeline synchronises and copies block 0's
  * layers x AIMA_MOE_DECODE_TRACE_STAMPS stamps of the last decode launch. */
 #define AIMA_MOE_DECODE_TRACE_STAMPS 12
 int aima_moe_set_tracing(aima_moe_handle* handle, int enabled);
+
+/* Qualification only (no counterpart in the reference): sets the device-resident epoch counter from which
+ * the decode kernel derives the tags of its exchange words, after synchronising the device.  Tests use it to
+ * reach the point where the 16-bit tags of the words between layers come round again (every 65 535 epochs)
+ * without running that many layers. */
+int aima_moe_debug_set_decode_epoch(aima_moe_handle* handle, uint32_t epoch);
 int aima_moe_read_decode_timeline(aima_moe_handle* handle, uint64_t* stamps_ns,
                                   uint32_t capacity, uint32_t* written);
 /* The same for EVERY block of the decode kernel, which is what shows the skew between blocks at the

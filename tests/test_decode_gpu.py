@@ -113,6 +113,38 @@ def test_decode_stack_free_running_is_bit_exact(provider, oracle, gpu_layers, sy
     assert torch.equal(z.cpu(), single)
 
 
+def test_words_between_layers_survive_the_wrap_of_their_tags(provider, gpu_layers, synth):
+    """The words that carry a layer's output to the next layer hold a 16-bit tag, ((epoch) mod 65535) + 1.
+    A stack launch at epoch E leaves words with the tags of E + 1 ..; a stack launch 65 535 epochs later expects
+    exactly those tags again and must not take the old words for its own.  The epoch is preset with the
+    qualification hook: the second launch gets a different input, and its result must be the one a launch
+    at an unrelated epoch gives (single-layer launches in between, which advance the epoch without
+    writing those words, are part of the scenario)."""
+    device = torch.device("cuda", 0)
+    x_a = synth.activations(SEED + 610, 1, "residual", 0)[0].to(device)
+    x_b = synth.activations(SEED + 611, 1, "residual", 0)[0].to(device)
+    out = torch.empty_like(x_a)
+    provider.debug_set_decode_epoch(1000)
+    provider.decode_stack(x_b, out, first_layer=0, n_layers=3)
+    provider.sync_metrics()
+    want_b = out.clone()
+    provider.debug_set_decode_epoch(5000)
+    provider.decode_stack(x_a, out, first_layer=0, n_layers=3)         # leaves words tagged for epochs 5001 ..
+    provider.decode_layer(x_a, 0)                                       # a single-layer launch in between
+    provider.sync_metrics()
+    assert not torch.equal(out, want_b)
+    for wraps in (1, 2):
+        provider.debug_set_decode_epoch(5000 + wraps * 65535)           # the same tags come round
+        provider.decode_stack(x_b, out, first_layer=0, n_layers=3)
+        provider.sync_metrics()
+        assert torch.equal(out, want_b), f"stale words of an earlier launch were read after {wraps} wrap(s)"
+    provider.debug_set_decode_epoch(65535 * 65536 - 2)                  # the counter itself comes round inside a launch
+    provider.decode_stack(x_b, out, first_layer=0, n_layers=3)
+    provider.decode_stack(x_b, out, first_layer=0, n_layers=3)          # and the next launch starts from its small values
+    provider.sync_metrics()
+    assert torch.equal(out, want_b)
+
+
 def test_decode_is_deterministic_across_runs(provider, gpu_layers, synth):
     device = torch.device("cuda", 0)
     x = synth.activations(SEED + 400, 1, "residual", 0)[0].to(device)
