@@ -157,6 +157,40 @@ def test_decode_is_deterministic_across_runs(provider, gpu_layers, synth):
     assert len(digests) == 1
 
 
+def test_two_thousand_free_running_steps_are_reproducible_with_and_without_prediction(package, gpu_layers, synth):
+    """A soak of the hand-overs: 2000 tokens through a three-layer stack, each output fed back as the next input
+    (18 000 grid-wide hand-overs by tagged words, the expert prediction right or wrong as the routing falls), run
+    twice with prediction and once without: the three final vectors -- and the vectors after every 250th step --
+    are the same bits, finite, and no bounded wait has run out.  A race between a writer and a late reader of
+    an exchange word would show as a difference or as a timeout status."""
+    device = torch.device("cuda", 0)
+    runs = []
+    for flags in (0, 0, package.provider.FLAG_NO_DECODE_PREDICTION):
+        provider = package.MoeProvider(layers=3, max_prefill_tokens=0, flags=flags)
+        try:
+            for layer in range(3):
+                provider.bind_layer(layer, gpu_layers(layer)["cuda"])
+            buffers = [synth.activations(SEED + 900, 1, "residual", 0)[0].to(device), None]
+            buffers[1] = torch.empty_like(buffers[0])
+            checkpoints = []
+            for step in range(2000):
+                provider.decode_stack(buffers[step & 1], buffers[(step + 1) & 1], first_layer=0, n_layers=3)
+                if step % 250 == 249:
+                    # keep the residual stream bounded: the stack has no attention half to balance it
+                    current = buffers[(step + 1) & 1]
+                    checkpoints.append(current.clone())
+                    current.copy_((current.float() / current.float().abs().max().clamp_min(1.0)).to(torch.bfloat16))
+            metrics = provider.sync_metrics()
+            assert metrics.device_status == 0
+            runs.append(checkpoints)
+        finally:
+            provider.release()
+    for a, b, c in zip(*runs):
+        assert torch.isfinite(a.float()).all()
+        assert torch.equal(a, b), "two runs with prediction differ"
+        assert torch.equal(a, c), "prediction changed the result"
+
+
 def test_decode_argument_checks(provider, package, synth):
     device = torch.device("cuda", 0)
     x = synth.activations(1, 1)[0].to(device)

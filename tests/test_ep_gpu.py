@@ -214,6 +214,16 @@ def _rank_main(rank: int, world: int, port: int, results) -> None:
             outputs.append(_bits(y))
             x, y = y, x
         dist.barrier()
+        # a soak of the hand-overs across GPUs: 600 more free-running steps with no host barrier between them
+        # (ranks run ahead of one another as the tags allow); every rank must end with the same bits
+        for _ in range(600):
+            provider.decode_stack(x, y, 0, 3)
+            x, y = y, x
+        metrics = provider.sync_metrics()
+        if metrics.device_status != 0:
+            raise AssertionError(f"rank {rank}: device status {metrics.device_status} after the soak")
+        soak = _bits(x)
+        dist.barrier()
         provider.release()
         # prefill: 128 tokens per rank through layer 0
         prefill = package.MoeProvider(layers=1, max_prefill_tokens=128 * world, world=world, rank=rank)
@@ -243,6 +253,7 @@ def _rank_main(rank: int, world: int, port: int, results) -> None:
         if not torch.equal(again, out):
             raise AssertionError(f"rank {rank}: pipelined expert-parallel prefill differs from the plain one")
         piped.release()
+        outputs.append(soak)
         results.put((rank, outputs))
     finally:
         dist.destroy_process_group()
@@ -272,6 +283,9 @@ def test_expert_parallel_ranks_match_the_oracle(oracle, synth, world):
             expected = oracle.decode_layer(expected, layer)["out"]
         for rank in range(world):
             assert torch.equal(got[rank][step], expected), f"rank {rank} step {step}"
+    for rank in range(1, world):
+        assert torch.equal(got[rank][4], got[0][4]), f"rank {rank} differs from rank 0 after the soak"
+    assert torch.isfinite(got[0][4].float()).all()
     # prefill rows of all ranks against the oracle (same tolerance as the single-GPU prefill tests)
     h2_all = synth.activations(SEED + 77, 128 * world, "input", 0)
     resid_all = synth.activations(SEED + 77, 128 * world, "residual", 0)
