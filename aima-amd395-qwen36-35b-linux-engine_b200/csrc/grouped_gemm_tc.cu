@@ -344,7 +344,15 @@ grouped_gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb) 
   const int parts = g.parts > 1 ? g.parts : 1;
   const int tile_lo = static_cast<int>(static_cast<long long>(n_tiles_all) * g.part / parts);
   const int tile_hi = static_cast<int>(static_cast<long long>(n_tiles_all) * (g.part + 1) / parts);
-  const int total_units = (tile_hi - tile_lo) * pb.n_chunks;
+  // a bounded wait that ran out earlier in this call (a peer that never answered, a barrier of a kernel before
+  // this one) leaves a status: nothing that follows can be right, so the products are skipped rather than run on
+  // incomplete data until the host reads the status
+  // (one thread samples it for the block, so that all warp roles see the same verdict)
+  volatile int* poison_slot = abort_flag + 1;
+  if (threadIdx.x == 0) *poison_slot = *reinterpret_cast<volatile const int*>(pb.status);
+  __syncthreads();
+  const bool poisoned = *poison_slot != 0;
+  const int total_units = poisoned ? 0 : (tile_hi - tile_lo) * pb.n_chunks;
   const int k_blocks = g.k / kBK;
 
   auto unit_tile = [&](int unit, int& tile, int& chunk, int& expert, int& row0, int& rows) {
@@ -629,7 +637,17 @@ grouped_gemm_tc2_kernel(const __grid_constant__ TcMaps maps, const TcProblem pb)
   pdl_enter();
 
   const int n_tiles = g.tile_count != nullptr ? *g.tile_count : g.max_tiles;
-  const int total_units = n_tiles * pb.n_chunks;
+  // as in the one-SM kernel; the leader samples the status for the pair
+  volatile int* poison_slot = abort_flag + 1;
+  if (threadIdx.x == 0 && leader) {
+    const int seen = *reinterpret_cast<volatile const int*>(pb.status);
+    *poison_slot = seen;
+    asm volatile("st.shared::cluster.u32 [%0], %1;" :: "r"(map_to_rank(smem_u32(const_cast<int*>(poison_slot)), 1)), "r"(seen) : "memory");
+  }
+  __syncthreads();
+  cluster_sync_all();
+  const bool poisoned = *poison_slot != 0;
+  const int total_units = poisoned ? 0 : n_tiles * pb.n_chunks;
   const int n_pairs = gridDim.x >> 1;
   const int pair = blockIdx.x >> 1;
   const int k_blocks = g.k / kBK;
