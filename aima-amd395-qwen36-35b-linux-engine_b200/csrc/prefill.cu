@@ -726,9 +726,12 @@ combine_kernel(const __nv_bfloat16* __restrict__ expert_down,
 
 // ---------------------------------------------------------------------------
 // Expert-parallel prefill over peer memory (NVLink).  Tokens are sharded T / W
-// per GPU, experts 256 / W per GPU.  Dispatch and combine are the gather and
-// the row return below: plain loads from / stores to the peers' exchange
-// regions; the tensor-core kernels only ever read this GPU's own memory.
+// per GPU, experts 256 / W per GPU.  Everything that crosses NVLink is a plain
+// store into a peer's exchange region: every rank's activation rows and routing
+// go to every GPU (all-gathers by peer stores), and the weighted expert rows go
+// to the GPU that owns their token -- from the down kernel's epilogue, or, in
+// the pipelined variant, from the copy kernel below.  The tensor-core kernels
+// only ever READ this GPU's own memory.
 // ---------------------------------------------------------------------------
 struct EpPointers {
   uint8_t* region[8];
@@ -1308,7 +1311,7 @@ int prefill_layer_launch_ep(PrefillWorkspace* ws, const PrefillCall& call, EpPre
 
   mark();
   // 4.-6. dispatch, products and row return, pipelined over `parts` ranges of the plan's tiles:
-  //   inbound stream   rows of part k pulled over NVLink into expert order
+  //   inbound stream   rows of part k copied from this GPU's table of all activations into expert order
   //   caller's stream  gate_up and down products of part k once its rows are here
   //   outbound stream  weighted rows of part k stored to the GPUs that own their tokens
   const int parts = ws->ep_parts >= 1 && ws->ep_parts <= PrefillWorkspace::kMaxParts ? ws->ep_parts : 1;

@@ -634,8 +634,9 @@ def ep_prefill_numbers(package, dist, device, world: int, rank: int, tokens: int
             "peak_source": kind, "frac": tflops / (peak * world),
             "stage_ms_rank0": stages, "exposed_communication_ms": exposed,
             "exposed_communication_fraction_of_layer": exposed / (ms / n_layers),
-            "multi_gpu": f"expert parallel, {per_rank_experts} experts per GPU, dispatch by peer loads, "
-                         "combine by peer stores over NVLink"}
+            "multi_gpu": f"expert parallel, {per_rank_experts} experts per GPU, activations all-gathered by peer "
+                         "stores beside the router, weighted rows returned by peer stores from the down "
+                         "kernel's epilogue (NVLink)"}
 
 
 def run_prefill_expert_parallel(args, world: int, rank: int, local_rank: int) -> None:

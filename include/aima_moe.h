@@ -89,10 +89,10 @@ typedef struct aima_moe_config {
  * gather them by token index itself.  Same bits; the default (fused dispatch) saves the copy kernel
  * and 0.5 GB of traffic per T = 8192 layer. */
 #define AIMA_MOE_FLAG_MATERIALIZED_DISPATCH 8u
-/* Expert-parallel prefill: split the plan's tiles into 2 (or 4) parts and pull the rows of one part
- * over NVLink / store the results of another back while the products of a third run, on three
- * streams.  Same bits.  On 2 GPUs it measured no faster than running the three steps one after
- * the other (the copies and the HBM-bound products slow each other down), so it is off by default. */
+/* Expert-parallel prefill: split the plan's tiles into 2 (or 4) parts and, with copy kernels on two more
+ * streams, put the rows of one part into expert order / store the results of another back to their owners
+ * while the products of a third run.  Same bits.  It measured no faster than the default, in which the gate_up
+ * kernel gathers its rows and the down kernel's epilogue stores its results to their owners itself. */
 #define AIMA_MOE_FLAG_EP_PIPELINE_2 32u
 #define AIMA_MOE_FLAG_EP_PIPELINE_4 64u
 /* Qualification of the certified prefill router: every 64th token is ALSO routed from all 256 canonical
@@ -325,10 +325,11 @@ int aima_moe_sync_metrics(aima_moe_handle* handle, aima_moe_metrics* metrics);
  * bits as a single GPU.  All ranks must launch the same layers in the same order.
  * Prefill: tokens are sharded over the ranks (aima_moe_prefill_launch takes this
  * rank's tokens; `max_prefill_tokens` is the GLOBAL capacity, tokens x world must
- * fit).  Each rank routes its tokens, the routing tables are all-gathered by peer
- * stores, every rank plans the rows that land on its experts, pulls their
- * activations from the owners (dispatch), runs its experts, and stores the
- * weighted rows back to the owners (combine).
+ * fit).  Each rank stores its activation rows and, once routed, its routing tables
+ * into every peer's buffer (all-gathers by peer stores); every rank plans the rows
+ * that land on its experts, gathers them from its own copy of the activations
+ * inside the gate_up kernel (dispatch), runs its experts, and stores the weighted
+ * rows to the owners of their tokens from the down kernel's epilogue (combine).
  * A host that owns a symmetric heap may substitute this rank's own buffer with
  * aima_moe_ep_connect(handle, own rank, NULL, pointer); it must be zero-filled and
  * as large as aima_moe_ep_local_buffer reports. */
