@@ -25,8 +25,11 @@ constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU exp
 // Everything all 148 blocks read back from global memory (router logits, the
 // activation vector, the layer output) is written kDecodeReplicas times, and
 // block c reads copy c % kDecodeReplicas: 148 readers of the same few L2 lines
-// otherwise queue at the L2 slices that own them.
-constexpr int kDecodeReplicas = 8;
+// otherwise queue at the L2 slices that own them.  Every copy costs its writer
+// one atomic, so few copies win: 0.6175 / 0.610 / 0.6175 / 0.628 / 0.650 ms per
+// token with 1 / 2 / 4 / 8 / 16 copies (with plain stores, which the pollers saw
+// late whatever the count, 8 had been the flat optimum).
+constexpr int kDecodeReplicas = 2;
 constexpr unsigned kDecodeEpochPeriod = 65535u * 65536u;   // the device-resident epoch counter counts modulo this
 constexpr int kDecodeDefaultInFlight = 0;     // ring items outstanding per block (0: no limit)
 constexpr int kDecodeLogitWords = 2 * kDecodeReplicas * kExperts;   // real + predicted, 64-bit words

@@ -300,7 +300,7 @@ int aima_moe_gemm_bf16_launch(aima_moe_handle* handle, const void* a, const void
  * threads -- race with each other: issue them on one stream or order them with
  * events.  More layers than the maximum are refused with AIMA_MOE_ERR_CAPACITY. */
 #define AIMA_MOE_NOALLOC_MAX_LAYERS 8
-#define AIMA_MOE_NOALLOC_SCRATCH_BYTES 393216
+#define AIMA_MOE_NOALLOC_SCRATCH_BYTES 131072
 int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_t n_layers,
                                    const void* x_in, void* x_out, float rms_eps,
                                    int32_t* device_status, void* stream);
