@@ -31,7 +31,10 @@ constexpr size_t kEpExchangeBytes = 2ull * kTopK * kHidden * 8;   // per-GPU exp
 // late whatever the count, 8 had been the flat optimum).
 constexpr int kDecodeReplicas = 2;
 constexpr unsigned kDecodeEpochPeriod = 65535u * 65536u;   // the device-resident epoch counter counts modulo this
-constexpr int kDecodeDefaultInFlight = 0;     // ring items outstanding per block (0: no limit)
+// Ring items outstanding per block (0: no limit): before it asks for a slot the producer waits until the item
+// issued this many items ago has landed.  0.6105 ms per token without, 0.704 / 0.601 / 0.601 / 0.600 / 0.602 with a
+// limit of 1 / 2 / 3 / 4 / 6 (A/B inside one call).
+constexpr int kDecodeDefaultInFlight = 4;
 constexpr int kDecodeLogitWords = 2 * kDecodeReplicas * kExperts;   // real + predicted, 64-bit words
 constexpr int kDecodeActStride = 9 * kInter + 64;   // 32-bit words per activation copy; word 9*512 = the shared gate logit
 
