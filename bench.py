@@ -36,10 +36,10 @@ FALLBACK_HBM_GBS = 6650.0
 # all weights of one layer: router, 256 experts (gate_up + down), shared expert, shared gate, norm
 BYTES_PER_LAYER_WEIGHTS = 1_048_576 + 256 * 6_291_456 + 6_291_456 + 4_096 + 4_096
 # dram__bytes_read.sum + dram__bytes_write.sum per layer of the decode kernel, from the ncu capture
-# summarised in profiles/moe_decode_persistent_kernel_stack2.md (2-layer case: 115.75 MB read + 4.98 MB
+# summarised in profiles/moe_decode_persistent_kernel_stack2.md (2-layer case: 115.64 MB read + 4.51 MB
 # written per launch; the next layer's router rows the prediction reads are the same bytes the next
-# layer reads again 18 us later, so they cost no second DRAM read)
-DECODE_TRAFFIC_PER_LAYER = 60_365_000
+# layer reads again 15 us later, so they cost no second DRAM read)
+DECODE_TRAFFIC_PER_LAYER = 60_075_000
 
 
 MIN_TIMED_SECONDS = 1.0      # the K-step loop is repeated until at least this much has been timed
