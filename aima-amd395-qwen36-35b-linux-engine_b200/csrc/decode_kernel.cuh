@@ -49,8 +49,6 @@ struct DecodeParams {
                                  // (the prediction that lets its expert rows be requested early)
   uint32_t* act;                 // [replicas][kDecodeActStride] tagged words (layer tag << 16 | BF16 activation): 8 positions + shared,
                                  // then the shared-expert gate logit as FP32 bits
-  unsigned long long* bar_counter;  // monotonic grid-barrier arrivals
-  unsigned long long* bar_base;     // counter value when this launch starts
   unsigned* epoch_base;             // exchange tags used so far (persists across launches)
   int* status;                   // device status word, 0 = healthy
   const float* router_bias;      // [256] or nullptr

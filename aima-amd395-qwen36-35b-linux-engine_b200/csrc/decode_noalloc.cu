@@ -209,8 +209,6 @@ int aima_moe_decode_layers_noalloc(const aima_moe_layer_weights* layers, uint32_
   params.xbuf1 = reinterpret_cast<uint32_t*>(scratch + kOffX1);
   params.logits = reinterpret_cast<unsigned long long*>(scratch + kOffLogits);
   params.act = reinterpret_cast<uint32_t*>(scratch + kOffAct);
-  params.bar_counter = reinterpret_cast<unsigned long long*>(scratch + kOffSync);
-  params.bar_base = reinterpret_cast<unsigned long long*>(scratch + kOffSync + 128);
   params.epoch_base = reinterpret_cast<unsigned*>(scratch + kOffSync + 192);
   params.status = reinterpret_cast<int*>(scratch + kOffStatus);
   params.router_bias = nullptr;

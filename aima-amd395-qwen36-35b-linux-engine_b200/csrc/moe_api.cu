@@ -77,8 +77,6 @@ struct aima_moe_handle {
   uint32_t* xbuf1 = nullptr;
   unsigned long long* logits = nullptr;
   uint32_t* act = nullptr;
-  unsigned long long* bar_counter = nullptr;
-  unsigned long long* bar_base = nullptr;
   unsigned* epoch_base = nullptr;
   int* status = nullptr;
 
@@ -234,8 +232,6 @@ int launch_decode_range(aima_moe_handle* handle, uint32_t first_layer, uint32_t 
   params.xbuf1 = handle->xbuf1;
   params.logits = handle->logits;
   params.act = handle->act;
-  params.bar_counter = handle->bar_counter;
-  params.bar_base = handle->bar_base;
   params.epoch_base = handle->epoch_base;
   params.status = handle->status;
   params.router_bias = handle->router_bias;
@@ -365,8 +361,6 @@ AIMA_EXPORT int aima_moe_prepare(const aima_moe_config* config, aima_moe_handle*
   error = cudaMemset(handle->decode_scratch, 0, handle->decode_scratch_bytes);
   if (error != cudaSuccess) return cleanup(fail_cuda(error, "cudaMemset decode scratch"));
   uint8_t* cursor = handle->decode_scratch;
-  handle->bar_counter = reinterpret_cast<unsigned long long*>(cursor);
-  handle->bar_base = reinterpret_cast<unsigned long long*>(cursor + 128);
   handle->epoch_base = reinterpret_cast<unsigned*>(cursor + 192);
   cursor += 256;
   handle->status = reinterpret_cast<int*>(cursor); cursor += 256;
