@@ -2,7 +2,7 @@
 for the host.  Test infrastructure -- nothing in the product may load it.
 
 The kernels are not copied into this repository.  At build time their definitions are cut out of
-the reference checkout (AIMA_REFERENCE_ROOT, default /root/reference) into oracle/_ref/ (ignored by
+the reference checkout (its location: AIMA_REFERENCE_ROOT in the environment) into oracle/_ref/ (ignored by
 git), and compiled with g++ against a small stand-in for the HIP device constructs they use
 (oracle/ref_shim/) and the launcher in oracle/ref_driver.cpp.  Taken, by name:
 

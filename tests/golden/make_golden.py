@@ -7,7 +7,7 @@ be called; oracle/reference_torch.py cuts their `def` bodies out of the referenc
 `ast` and executes them with their free variables bound to the pure-torch CPU configuration.  This
 script runs THOSE functions on the seeded synthetic layer of BASELINE config 0 (T in {1, 16}),
 checks that the hand restatement oracle/moe_torch_ref.py gives the same bits, and stores the
-results.  It needs the reference checkout (AIMA_REFERENCE_ROOT, default /root/reference):
+results.  It needs the reference checkout (its location: AIMA_REFERENCE_ROOT in the environment):
 
     python tests/golden/make_golden.py            # regenerate
     python tests/golden/make_golden.py --check    # regenerate in memory and compare with the files
