@@ -614,23 +614,29 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       if (lane == 0) mbar_arrive(empty_bar(item % kRingSlots));
     };
     // canonical 2048-dot of the register-resident vector against one row / two rows at once
-    auto row_dot = [&](const uint8_t* row, const float* xr) -> float {
+    auto row_dot = [&](const uint8_t* row, const uint4* xq) -> float {
       float a = 0.0f;
       const uint4* r0 = reinterpret_cast<const uint4*>(row) + lane;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) a = fma8(xr + 8 * i, r0[i * 32], a);
+#pragma unroll 2
+      for (int i = 0; i < 8; ++i) {
+        float x8[8];
+        unpack8(xq[i * 32], x8);
+        a = fma8(x8, r0[i * 32], a);
+      }
       return butterfly_sum(a);
     };
-    auto pair_dot = [&](const uint8_t* row_a, const uint8_t* row_b, const float* xr, float& a, float& b) {
+    auto pair_dot = [&](const uint8_t* row_a, const uint8_t* row_b, const uint4* xq, float& a, float& b) {
       a = 0.0f; b = 0.0f;
       const uint4* r0 = reinterpret_cast<const uint4*>(row_a) + lane;
       const uint4* r1 = reinterpret_cast<const uint4*>(row_b) + lane;
-#pragma unroll
+#pragma unroll 2
       for (int i = 0; i < 8; ++i) {
         const uint4 w0 = r0[i * 32];
         const uint4 w1 = r1[i * 32];
-        a = fma8(xr + 8 * i, w0, a);
-        b = fma8(xr + 8 * i, w1, b);
+        float x8[8];
+        unpack8(xq[i * 32], x8);
+        a = fma8(x8, w0, a);
+        b = fma8(x8, w1, b);
       }
       a = butterfly_sum(a);
       b = butterfly_sum(b);
@@ -783,11 +789,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       }
       consumer_sync();
       // streaming warps keep h2 in registers: element k = 256 g + 8 lane + j at xr[8 g + j]
-      float xr[64];
-      if (streams) {
-#pragma unroll
-        for (int g = 0; g < 8; ++g) unpack8(reinterpret_cast<const uint4*>(h2_s)[g * 32 + lane], xr + 8 * g);
-      }
+      const uint4* xr = reinterpret_cast<const uint4*>(h2_s) + lane;     // EXPERIMENT: x stays in shared memory
 
       stamp(li, 1);
       // ---- R1: warp m of the group takes row m of {router 2c, router 2c+1, next router 2c, next router 2c+1};
