@@ -613,19 +613,23 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(item % kRingSlots));
     };
-    // canonical 2048-dot of the register-resident vector against one row / two rows at once
-    auto row_dot = [&](const uint8_t* row, const uint4* xq) -> float {
+    // Canonical 2048-dot of the normalised input against one row / two rows at once; the caller merges the
+    // lanes' partials with butterfly_sum after it has handed the slot back.  The input is read from shared
+    // memory (FP32, two float4 per lane and step) in loops unrolled twice: held in 64 registers per thread and
+    // fully unrolled, the same dots took 8 % more time per token (the kernel then sat at its cap of 128
+    // registers); four- or eight-fold unrolling is 1 % slower than twofold, no unrolling 2 %.
+    auto row_dot = [&](const uint8_t* row, const float4* xq) -> float {
       float a = 0.0f;
       const uint4* r0 = reinterpret_cast<const uint4*>(row) + lane;
 #pragma unroll 2
       for (int i = 0; i < 8; ++i) {
-        float x8[8];
-        unpack8(xq[i * 32], x8);
+        const float4 xlo = xq[i * 32], xhi = xq[256 + i * 32];
+        const float x8[8] = {xlo.x, xlo.y, xlo.z, xlo.w, xhi.x, xhi.y, xhi.z, xhi.w};
         a = fma8(x8, r0[i * 32], a);
       }
-      return butterfly_sum(a);
+      return a;
     };
-    auto pair_dot = [&](const uint8_t* row_a, const uint8_t* row_b, const uint4* xq, float& a, float& b) {
+    auto pair_dot = [&](const uint8_t* row_a, const uint8_t* row_b, const float4* xq, float& a, float& b) {
       a = 0.0f; b = 0.0f;
       const uint4* r0 = reinterpret_cast<const uint4*>(row_a) + lane;
       const uint4* r1 = reinterpret_cast<const uint4*>(row_b) + lane;
@@ -633,13 +637,11 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       for (int i = 0; i < 8; ++i) {
         const uint4 w0 = r0[i * 32];
         const uint4 w1 = r1[i * 32];
-        float x8[8];
-        unpack8(xq[i * 32], x8);
+        const float4 xlo = xq[i * 32], xhi = xq[256 + i * 32];
+        const float x8[8] = {xlo.x, xlo.y, xlo.z, xlo.w, xhi.x, xhi.y, xhi.z, xhi.w};
         a = fma8(x8, w0, a);
         b = fma8(x8, w1, b);
       }
-      a = butterfly_sum(a);
-      b = butterfly_sum(b);
     };
     auto hooked_logit = [&](float v, int expert) -> float {
       if (kExtras && p.router_bias != nullptr) v = __fadd_rn(v, p.router_bias[expert]);
@@ -745,7 +747,9 @@ moe_decode_persistent_kernel(const DecodeParams p) {
       //      (native/src/native_pointwise.hip.cpp:109-142): partial t of 256 adds elements t, t + 256, ...
       //      in that order, the partials fold by halving.  Consumer warp j holds partial 8 l + j on lane l: the
       //      butterfly does the halvings of width 128 .. 8, the last three widths are the tree below.
-      //      Then every thread normalises one 8-element chunk into h2_s (the activation region is idle now)
+      //      Then every thread normalises one 8-element chunk into h2_s as FP32 (the activation region is idle now):
+      //      chunk t's elements 0..3 at float4 t, elements 4..7 at float4 256 + t, so that a warp's loads of
+      //      either half are contiguous
       uint8_t* h2_s = reinterpret_cast<uint8_t*>(act_s);
       if (cw < 8) {
         float acc = 0.0f;
@@ -783,13 +787,16 @@ moe_decode_persistent_kernel(const DecodeParams p) {
                             (static_cast<uint32_t>(float_to_bf16_bits(b)) << 16);
           }
           const uint4 out = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          reinterpret_cast<uint4*>(h2_s)[ctid] = out;
+          float f[8];
+          unpack8(out, f);
+          reinterpret_cast<float4*>(h2_s)[ctid] = make_float4(f[0], f[1], f[2], f[3]);
+          reinterpret_cast<float4*>(h2_s)[256 + ctid] = make_float4(f[4], f[5], f[6], f[7]);
           if (kExtras && p.dbg_h2 != nullptr && c == 0) reinterpret_cast<uint4*>(p.dbg_h2)[ctid] = out;
         }
       }
       consumer_sync();
-      // streaming warps keep h2 in registers: element k = 256 g + 8 lane + j at xr[8 g + j]
-      const uint4* xr = reinterpret_cast<const uint4*>(h2_s) + lane;     // EXPERIMENT: x stays in shared memory
+      // element k = 256 g + 8 lane + j of the normalised input is component j & 3 of xr[(j >> 2) * 256 + 32 g]
+      const float4* xr = reinterpret_cast<const float4*>(h2_s) + lane;
 
       stamp(li, 1);
       // ---- R1: warp m of the group takes row m of {router 2c, router 2c+1, next router 2c, next router 2c+1};
@@ -805,6 +812,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
             float v = 0.0f;
             if (has_row) v = row_dot(slot + (predicted ? kHalfBytes : 0) + (member & 1) * kRowBytes, xr);
             release_item(item);
+            if (has_row) v = butterfly_sum(v);
             if (has_row && lane == 0) {
               if (has_router_rows) {
                 const int expert = 2 * c + (member & 1);
@@ -834,6 +842,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
             float a = 0.0f, b = 0.0f;
             if (member < sh_rows) pair_dot(slot + member * kRowBytes, slot + kHalfBytes + member * kRowBytes, xr, a, b);
             release_item(item);
+            if (member < sh_rows) { a = butterfly_sum(a); b = butterfly_sum(b); }
             if (member < sh_rows && lane == 0) {
               const float g = round_bf16(a);
               const float u = round_bf16(b);
@@ -867,6 +876,7 @@ moe_decode_persistent_kernel(const DecodeParams p) {
         float a = 0.0f, bb = 0.0f;
         if (mine) pair_dot(slot + member * kRowBytes, slot + kHalfBytes + member * kRowBytes, xr, a, bb);
         release_item(item);
+        if (mine) { a = butterfly_sum(a); bb = butterfly_sum(bb); }
         if (mine && lane == 0) {
           const uint16_t bits = float_to_bf16_bits(__fmul_rn(det_silu(a), bb));
           // a word with this layer's tag is final for its readers: a blind result waits for the plan
