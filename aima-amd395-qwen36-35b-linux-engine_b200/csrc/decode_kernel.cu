@@ -1114,7 +1114,11 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           need[i] = v < kGroups4 && (row == kTopK || ((active_mask >> row) & 1u) != 0u);
         }
         uint4 w[kPerThread];
+        bool pending[kPerThread];          // a group of words is asked for again only until it has arrived
+#pragma unroll
+        for (int i = 0; i < kPerThread; ++i) pending[i] = need[i];
         uint32_t gate_word = 0u;
+        bool gate_pending = ctid == 0;
         bool ready = false;
         const unsigned long long start = global_timer_ns();
         unsigned spins = 0;
@@ -1122,15 +1126,20 @@ moe_decode_persistent_kernel(const DecodeParams p) {
           bool mine = true;
 #pragma unroll
           for (int i = 0; i < kPerThread; ++i) {
-            if (need[i]) {
-              w[i] = ld_strong_u4(reinterpret_cast<const uint4*>(words) + ctid + i * kDecodeConsumerThreads);
-              mine = mine && (w[i].x >> 16) == tag16 && (w[i].y >> 16) == tag16 && (w[i].z >> 16) == tag16 &&
-                     (w[i].w >> 16) == tag16;
+            if (pending[i]) w[i] = ld_strong_u4(reinterpret_cast<const uint4*>(words) + ctid + i * kDecodeConsumerThreads);
+          }
+          if (gate_pending) gate_word = ld_strong_u32(words + 9 * kInter);
+#pragma unroll
+          for (int i = 0; i < kPerThread; ++i) {
+            if (pending[i]) {
+              pending[i] = !((w[i].x >> 16) == tag16 && (w[i].y >> 16) == tag16 && (w[i].z >> 16) == tag16 &&
+                             (w[i].w >> 16) == tag16);
+              mine = mine && !pending[i];
             }
           }
-          if (ctid == 0) {
-            gate_word = ld_strong_u32(words + 9 * kInter);
-            mine = mine && (gate_word >> 16) == tag16;
+          if (gate_pending) {
+            gate_pending = (gate_word >> 16) != tag16;
+            mine = mine && !gate_pending;
           }
           ready = __all_sync(0xffffffffu, mine);
           if (!ready && (++spins & 63u) == 0u) {
