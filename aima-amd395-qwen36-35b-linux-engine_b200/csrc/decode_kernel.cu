@@ -47,7 +47,8 @@
 //       down products for the block's output elements from the down items,
 //       weighted sum, shared expert, residual add
 //   --- output exchange: the 2048 outputs travel as 32-bit words {tag, bf16};
-//       four warps of every block poll them into shared memory
+//       eight warps of every block poll them into shared memory; after the RMSNorm the
+//       normalised input stays in shared memory as FP32 and the dots read it from there
 //
 // Prediction.  A grid-wide hand-over through L2 costs about 1.5 us of pure latency
 // (store, then a poll round trip), a layer has three of them, and nothing that
