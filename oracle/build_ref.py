@@ -115,6 +115,9 @@ def build(force: bool = False) -> list[Path]:
     import reference_torch        # the torch functions of the same checkout, for the benchmark's reference arm
 
     reference_torch.write_extracted()
+    import reference_triton       # its Triton decode kernels, run under Triton's interpreter by the golden generator
+
+    reference_triton.write_extracted()
     compile_library("libmoe_ref.so", ["-ffp-contract=off"])
     compile_library("libmoe_ref_fma.so", ["-ffp-contract=fast", "-mfma"])
     return libraries
