@@ -20,6 +20,10 @@ launched here with the reference's own grids, block sizes and buffer dtypes:
 
 and the tail `after_attn + (moe_out + shared_out)` of layer_body (:8634-8639) in BF16.
 
+For the LM head with a certified top-1: triton_lm_head_rowwise_int8_gemv_kernel :1223 together with the two plain
+functions around it, quantize_certified_lm_head :3553 and launch_certified_lm_head_int8 :3570, and the
+certificate arithmetic of final_logits (:8656-8676), on a vocabulary small enough for the interpreter.
+
 Nothing is copied into this repository.  Run as a script it writes one case to an .npz file:
 
     TRITON_INTERPRET=1 python oracle/reference_triton.py --regime normal --seed 4321 --out case.npz
@@ -47,7 +51,8 @@ SOURCE = REFERENCE / "benchmarks" / "shape-lab" / "four_layer_mini_engine.py"
 EXTRACTED = HERE / "_ref" / "reference_triton_kernels.py"
 NAMES = ("triton_matvec_kernel", "triton_fused_shared_down_kernel", "triton_router_topk_stage1_kernel",
          "triton_router_topk_stage2_kernel", "triton_router_topk_stage2_softmax_kernel", "triton_rmsnorm_kernel",
-         "raw_row_gate_up_activation_kernel", "raw_row_down_sum_kernel")
+         "raw_row_gate_up_activation_kernel", "raw_row_down_sum_kernel", "triton_lm_head_rowwise_int8_gemv_kernel")
+PLAIN = ("quantize_certified_lm_head", "launch_certified_lm_head_int8")      # ordinary functions, cut the same way
 
 HIDDEN, EXPERTS, TOP_K, INTER = 2048, 256, 8, 512
 REGIMES = ("normal", "ties8", "ties4")
@@ -71,15 +76,16 @@ def cut_kernels() -> dict[str, tuple[str, int]]:
     tree = ast.parse(text)
     found: dict[str, ast.FunctionDef] = {}
     for node in ast.walk(tree):
-        if isinstance(node, ast.FunctionDef) and node.name in NAMES and node.name not in found:
-            if not any("jit" in ast.unparse(d) for d in node.decorator_list):
-                raise RuntimeError(f"{node.name} is not a Triton kernel in the reference")
+        if isinstance(node, ast.FunctionDef) and node.name in NAMES + PLAIN and node.name not in found:
+            is_kernel = any("jit" in ast.unparse(d) for d in node.decorator_list)
+            if is_kernel != (node.name in NAMES):
+                raise RuntimeError(f"{node.name}: Triton kernel or plain function, not what was expected")
             found[node.name] = node
-    missing = [name for name in NAMES if name not in found]
+    missing = [name for name in NAMES + PLAIN if name not in found]
     if missing:
         raise RuntimeError(f"reference kernels not found: {missing}")
     return {name: (textwrap.dedent(" " * found[name].col_offset + ast.get_source_segment(text, found[name])),
-                   found[name].lineno) for name in NAMES}
+                   found[name].lineno) for name in NAMES + PLAIN}
 
 
 def write_extracted() -> Path | None:
@@ -88,10 +94,10 @@ def write_extracted() -> Path | None:
         return EXTRACTED if EXTRACTED.is_file() else None
     EXTRACTED.parent.mkdir(exist_ok=True)
     pieces = ["# GENERATED from the reference checkout by oracle/reference_triton.py -- not tracked, do not edit.\n"
-              "import triton\nimport triton.language as tl\n\n"]
+              "from typing import Any\n\nimport torch\nimport triton\nimport triton.language as tl\n\n"]
     for name, (source, line) in cut_kernels().items():
         pieces.append(f"# ---- {name}: benchmarks/shape-lab/four_layer_mini_engine.py:{line} ----\n"
-                      f"@triton.jit\n{source}\n\n")
+                      f"{'@triton.jit' + chr(10) if name in NAMES else ''}{source}\n\n")
     EXTRACTED.write_text("".join(pieces))
     return EXTRACTED
 
@@ -223,6 +229,43 @@ def decode_half_layer(kernels: Any, after_attn: torch.Tensor, small: dict[str, t
             "routed": routed[0], "shared_input": shared_input, "shared_out": shared_out, "out": out[0]}
 
 
+# ---------------------------------------------------------------------------------------------------
+# LM head with a certified top-1
+# ---------------------------------------------------------------------------------------------------
+def lm_head_inputs(rows: int, seed: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """A [rows, 2048] BF16 N(0, 0.02) matrix and a [1, 2048] BF16 N(0, 1) final hidden state."""
+    generator = torch.Generator().manual_seed(seed)
+    weight = (torch.randn(rows, HIDDEN, generator=generator) * 0.02).to(torch.bfloat16)
+    hidden = torch.randn(1, HIDDEN, generator=generator).to(torch.bfloat16)
+    return weight, hidden
+
+
+def lm_head_certified(kernels: Any, weight: torch.Tensor, final_hidden: torch.Tensor,
+                      quantised: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None) -> dict[str, torch.Tensor]:
+    """final_logits' certified branch (:8656-8676) with the reference's quantiser, launcher and kernel.
+    `quantised` = (int8 rows, scales, residual norms) replaces the reference quantiser's output, so that the
+    certificate can be followed on the very numbers another implementation quantised to."""
+    q_ref, scales_ref, residual_ref = kernels.quantize_certified_lm_head(weight)
+    q, scales, residual = (q_ref, scales_ref, residual_ref) if quantised is None else quantised
+    logits = torch.empty(weight.shape[0], dtype=torch.float32)
+    kernels.launch_certified_lm_head_int8(q, final_hidden, scales, logits)
+    approximate = logits.clone()
+    hidden_l2 = torch.linalg.vector_norm(final_hidden.float())
+    error_bound = residual * hidden_l2
+    lower_max = (logits - error_bound).max()
+    upper = logits + error_bound
+    upper_values, upper_indices = torch.topk(upper, k=1024)
+    shortlist_weight = weight.index_select(0, upper_indices)
+    exact_logits = torch.mm(final_hidden, shortlist_weight.t()).view(-1)
+    certified = bool(lower_max > upper_values[-1])
+    logits.scatter_(0, upper_indices, exact_logits.float())
+    return {"q": q_ref, "scales": scales_ref, "residual_l2": residual_ref, "approximate": approximate,
+            "hidden_l2": hidden_l2.reshape(1), "lower_max": lower_max.reshape(1), "cutoff": upper_values[-1].reshape(1),
+            "shortlist": upper_indices.to(torch.int32), "logits": logits,
+            "certified": torch.tensor([int(certified)], dtype=torch.int32),
+            "top1": torch.argmax(logits).reshape(1).to(torch.int32)}
+
+
 def bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.int16).numpy().view(np.uint16)
 
@@ -237,14 +280,30 @@ def run_case(regime: str, seed: int, stages: str = "all") -> dict[str, np.ndarra
     return stored
 
 
+def run_lm_head_case(rows: int, seed: int, quantised_from: str | None) -> dict[str, np.ndarray]:
+    kernels = load_kernels()
+    weight, hidden = lm_head_inputs(rows, seed)
+    quantised = None
+    if quantised_from is not None:
+        given = np.load(quantised_from)
+        quantised = (torch.from_numpy(given["q"]), torch.from_numpy(given["scales"]), torch.from_numpy(given["residual_l2"]))
+    return {name: tensor.numpy() for name, tensor in lm_head_certified(kernels, weight, hidden, quantised).items()}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
+    parser.add_argument("--lm-head-rows", type=int, default=0, help="run the LM-head case on this many rows instead")
+    parser.add_argument("--quantised-from", default=None, help=".npz with q, scales, residual_l2 to certify with")
     parser.add_argument("--regime", choices=REGIMES, default="normal")
     parser.add_argument("--seed", type=int, default=4321)
     parser.add_argument("--stages", choices=("all", "routing"), default="all")
     parser.add_argument("--out", required=True)
     args = parser.parse_args()
     torch.set_num_threads(1)
+    if args.lm_head_rows > 0:
+        np.savez_compressed(args.out, **run_lm_head_case(args.lm_head_rows, args.seed, args.quantised_from))
+        print(f"wrote {args.out}")
+        return
     np.savez_compressed(args.out, **run_case(args.regime, args.seed, args.stages))
     print(f"wrote {args.out}")
 

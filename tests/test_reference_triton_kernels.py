@@ -1,4 +1,4 @@
-"""The decode path against the reference's OWN Triton kernels.
+"""The decode path, and the LM head with its certified top-1, against the reference's OWN Triton kernels.
 
 tests/golden/decode_triton_<regime>.npz hold what the reference's batch-1 MoE kernels
 (benchmarks/shape-lab/four_layer_mini_engine.py: triton_rmsnorm_kernel, the two-stage router top-8 with its
@@ -117,3 +117,44 @@ def test_cuda_decode_matches_the_reference_triton_kernels(package, built_library
                         "shared": tensors["shared_scaled"][0], "out": out})
     finally:
         provider.release()
+
+
+def test_lm_head_certificate_follows_the_reference(oracle, tmp_path):
+    """The reference's quantiser (quantize_certified_lm_head), launcher and int8 scan kernel
+    (triton_lm_head_rowwise_int8_gemv_kernel, under the interpreter) and the certificate arithmetic of its
+    final_logits, on a 4096-row vocabulary, beside the oracle.  The reference has two statements of the row scale --
+    max / 127 in this Python function, max * fl(1 / 127) in its native kernel, which the oracle follows and is
+    checked against bit for bit elsewhere -- so scales may differ in the last bit and a quantised value by one on
+    such rows; the scan and the certificate are therefore followed on the ORACLE's quantised rows."""
+    if not reference_triton.SOURCE.is_file():
+        pytest.skip("reference checkout not present")
+    pytest.importorskip("triton")
+    rows, seed = 4096, 777
+    weight, hidden = reference_triton.lm_head_inputs(rows, seed)
+    q, scales, residual = oracle.lm_head_quantize(weight)
+    given = tmp_path / "quantised.npz"
+    np.savez(given, q=q.numpy(), scales=scales.numpy(), residual_l2=residual.numpy())
+    out = tmp_path / "reference.npz"
+    subprocess.run([sys.executable, str(Path(reference_triton.__file__)), "--lm-head-rows", str(rows), "--seed", str(seed),
+                    "--quantised-from", str(given), "--out", str(out)], check=True,
+                   env=dict(os.environ, TRITON_INTERPRET="1"), timeout=900)
+    ref = np.load(out)
+    # quantiser
+    assert np.abs(scales.numpy() / ref["scales"] - 1.0).max() <= 1.2e-7
+    same_scale = scales.numpy() == ref["scales"]
+    assert same_scale.mean() > 0.5 and np.array_equal(q.numpy()[same_scale], ref["q"][same_scale])
+    assert np.abs(q.numpy().astype(np.int32) - ref["q"].astype(np.int32)).max() <= 1
+    assert np.abs(residual.numpy() / ref["residual_l2"] - 1.0).max() <= 4.0e-6
+    # scan + certificate
+    got = oracle.lm_head_certify(weight, q, scales, residual, hidden[0])
+    assert int(ref["certified"][0]) == 1 and got["status"] == 0 and got["overflow"] == 0
+    assert abs(got["hidden_l2"] / float(ref["hidden_l2"][0]) - 1.0) <= 2.0e-6
+    assert abs(got["maximum_lower_bound"] - float(ref["lower_max"][0])) <= 2.0e-5
+    shortlist = set(ref["shortlist"].tolist())
+    outside = np.array([i for i in range(rows) if i not in shortlist])
+    assert np.abs(got["logits"].numpy()[outside] - ref["approximate"][outside]).max() <= 2.0e-5
+    candidates = got["candidates"].tolist()
+    assert set(candidates) <= shortlist                       # the oracle keeps only rows that can still win
+    assert np.array_equal(got["logits"].numpy()[candidates], ref["logits"][candidates])    # exact BF16 logits
+    assert got["top1_token"] == int(ref["top1"][0])
+    assert got["top1_logit"] == float(ref["logits"][got["top1_token"]])
