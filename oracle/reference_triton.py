@@ -22,7 +22,9 @@ and the tail `after_attn + (moe_out + shared_out)` of layer_body (:8634-8639) in
 
 For the LM head with a certified top-1: triton_lm_head_rowwise_int8_gemv_kernel :1223 together with the two plain
 functions around it, quantize_certified_lm_head :3553 and launch_certified_lm_head_int8 :3570, and the
-certificate arithmetic of final_logits (:8656-8676), on a vocabulary small enough for the interpreter.
+certificate arithmetic of final_logits (:8656-8676), on a vocabulary small enough for the interpreter.  For the
+fused residual add + RMSNorm at a prefill layer boundary: triton_prefill_fused_add_rmsnorm_kernel :862, launched as
+prefill_fused_add_rmsnorm does (:5130-5149).
 
 Nothing is copied into this repository.  Run as a script it writes one case to an .npz file:
 
@@ -51,7 +53,8 @@ SOURCE = REFERENCE / "benchmarks" / "shape-lab" / "four_layer_mini_engine.py"
 EXTRACTED = HERE / "_ref" / "reference_triton_kernels.py"
 NAMES = ("triton_matvec_kernel", "triton_fused_shared_down_kernel", "triton_router_topk_stage1_kernel",
          "triton_router_topk_stage2_kernel", "triton_router_topk_stage2_softmax_kernel", "triton_rmsnorm_kernel",
-         "raw_row_gate_up_activation_kernel", "raw_row_down_sum_kernel", "triton_lm_head_rowwise_int8_gemv_kernel")
+         "raw_row_gate_up_activation_kernel", "raw_row_down_sum_kernel", "triton_lm_head_rowwise_int8_gemv_kernel",
+         "triton_prefill_fused_add_rmsnorm_kernel")
 PLAIN = ("quantize_certified_lm_head", "launch_certified_lm_head_int8")      # ordinary functions, cut the same way
 
 HIDDEN, EXPERTS, TOP_K, INTER = 2048, 256, 8, 512
@@ -230,6 +233,28 @@ def decode_half_layer(kernels: Any, after_attn: torch.Tensor, small: dict[str, t
 
 
 # ---------------------------------------------------------------------------------------------------
+# Fused residual add + RMSNorm of a prefill layer boundary
+# ---------------------------------------------------------------------------------------------------
+def norm_inputs(rows: int, seed: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    synth = _synth()
+    return (synth.activations(seed, rows, "input", 0), synth.activations(seed, rows, "residual", 0),
+            synth.small_tensor("post_attention_layernorm", seed, 0))
+
+
+def fused_add_rmsnorm(kernels: Any, x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                      eps: float = 1.0e-6) -> dict[str, torch.Tensor]:
+    import triton
+
+    rows = x.shape[0]
+    residual_out = torch.empty(rows, HIDDEN, dtype=torch.bfloat16)
+    norm_out = torch.empty(rows, HIDDEN, dtype=torch.bfloat16)
+    kernels.triton_prefill_fused_add_rmsnorm_kernel[(rows,)](
+        x.reshape(rows * HIDDEN), residual.reshape(rows * HIDDEN), weight, residual_out.reshape(rows * HIDDEN),
+        norm_out.reshape(rows * HIDDEN), HIDDEN, eps, block_h=triton.next_power_of_2(HIDDEN), num_warps=8)
+    return {"residual_out": residual_out, "norm_out": norm_out}
+
+
+# ---------------------------------------------------------------------------------------------------
 # LM head with a certified top-1
 # ---------------------------------------------------------------------------------------------------
 def lm_head_inputs(rows: int, seed: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -293,6 +318,7 @@ def run_lm_head_case(rows: int, seed: int, quantised_from: str | None) -> dict[s
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--lm-head-rows", type=int, default=0, help="run the LM-head case on this many rows instead")
+    parser.add_argument("--norm-rows", type=int, default=0, help="run the fused add + RMSNorm on this many rows instead")
     parser.add_argument("--quantised-from", default=None, help=".npz with q, scales, residual_l2 to certify with")
     parser.add_argument("--regime", choices=REGIMES, default="normal")
     parser.add_argument("--seed", type=int, default=4321)
@@ -300,6 +326,11 @@ def main() -> None:
     parser.add_argument("--out", required=True)
     args = parser.parse_args()
     torch.set_num_threads(1)
+    if args.norm_rows > 0:
+        result = fused_add_rmsnorm(load_kernels(), *norm_inputs(args.norm_rows, args.seed))
+        np.savez_compressed(args.out, **{name: bits(tensor) for name, tensor in result.items()})
+        print(f"wrote {args.out}")
+        return
     if args.lm_head_rows > 0:
         np.savez_compressed(args.out, **run_lm_head_case(args.lm_head_rows, args.seed, args.quantised_from))
         print(f"wrote {args.out}")

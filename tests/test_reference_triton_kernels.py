@@ -158,3 +158,23 @@ def test_lm_head_certificate_follows_the_reference(oracle, tmp_path):
     assert np.array_equal(got["logits"].numpy()[candidates], ref["logits"][candidates])    # exact BF16 logits
     assert got["top1_token"] == int(ref["top1"][0])
     assert got["top1_logit"] == float(ref["logits"][got["top1_token"]])
+
+
+def test_fused_add_rmsnorm_follows_the_reference_kernel(oracle, tmp_path):
+    """triton_prefill_fused_add_rmsnorm_kernel (the boundary between two prefill layers) under the interpreter beside
+    the oracle: the BF16 residual sum bit for bit; the normalised rows bit for bit except where the two orders of the
+    2048-term sum of squares meet a rounding boundary -- at most one BF16 step, on at most 0.1 % of the elements."""
+    if not reference_triton.SOURCE.is_file():
+        pytest.skip("reference checkout not present")
+    pytest.importorskip("triton")
+    rows, seed = 33, 99
+    out = tmp_path / "norm.npz"
+    subprocess.run([sys.executable, str(Path(reference_triton.__file__)), "--norm-rows", str(rows), "--seed", str(seed),
+                    "--out", str(out)], check=True, env=dict(os.environ, TRITON_INTERPRET="1"), timeout=600)
+    ref = np.load(out)
+    x, residual, weight = reference_triton.norm_inputs(rows, seed)
+    residual_out, norm_out = oracle.rmsnorm(x, weight, residual)
+    assert np.array_equal(_bits(residual_out), ref["residual_out"])
+    got, want = _bits(norm_out), ref["norm_out"]
+    assert (got == want).mean() >= 0.999
+    assert np.abs(got.astype(np.int32) - want.astype(np.int32)).max() <= 1        # neighbouring BF16 values
