@@ -6,15 +6,27 @@
  * CPU baseline of the benchmark.  The product (the CUDA library) never links,
  * loads or calls it.
  *
- * PARITY UNPINNED for routed-expert values: the reference repository ships no
- * numeric fixtures for this path (its oracle .bin files are not committed).
- * What is pinned here: the order-independent known-answer hashes of the
- * reference's wvSplitK pattern probe (native/src/bf16_wvsplitk.hip.cpp:218-333,
- * benchmarks/results/native-wvsplitk-v0.1.0.json:52,73), the all-ones GEMM
- * value (native/src/bf16_gemm.hip.cpp:281-291) and, through committed golden
- * vectors produced with torch CPU ops, the torch statement of the layer
- * (benchmarks/shape-lab/four_layer_mini_engine.py:7775-7804, 8286-8303,
- * 8634-8639, 5127-5128).
+ * How it is pinned to the reference's own code (the reference repository ships
+ * no numeric fixtures for this path; its oracle .bin files are not committed):
+ *   - its scalar kernels (top-8 with tie order and softmax, SwiGLU and sigmoid
+ *     pointwise stages, 8-way tree sum, add pair, both RMSNorm kernels, block-32
+ *     dispatch count, LM-head row quantisation) compiled for the host from the
+ *     checkout and run beside every stage (oracle/build_ref.py,
+ *     tests/test_oracle_vs_reference_kernels.py);
+ *   - its torch functions for the half-layer, cut out of the checkout and
+ *     executed (oracle/reference_torch.py, tests/golden/config0_T*.npz);
+ *   - its Triton kernels for the batch-1 path, the fused add + RMSNorm and the
+ *     LM-head scan, run under Triton's interpreter (oracle/reference_triton.py,
+ *     tests/golden/decode_triton_*.npz): ids in order, norm, routing weights,
+ *     routed sum and layer output agree bit for bit on the committed cases;
+ *   - the order-independent known-answer hashes of its wvSplitK pattern probe
+ *     (native/src/bf16_wvsplitk.hip.cpp:218-333,
+ *     benchmarks/results/native-wvsplitk-v0.1.0.json:52,73) and the all-ones
+ *     GEMM value (native/src/bf16_gemm.hip.cpp:281-291).
+ * PARITY UNPINNED for what only the reference's GPU libraries define: the FP32
+ * accumulation order of its prefill GEMMs (hipBLASLt, the fused_moe Triton
+ * kernel), for which routed-expert values at prefill are held to a tolerance,
+ * and the device library's expf beyond one BF16 step.
  *
  * Floating-point contract.  The reference leaves FP32 summation order to its
  * libraries (hipBLASLt, Triton tl.sum).  Routing must be bit-exact, so this
@@ -25,9 +37,10 @@
  *                  group index (k / 8) is congruent to l modulo 32; the 32
  *                  partials are then combined by the butterfly
  *                  p[l] += p[l ^ s] for s = 16, 8, 4, 2, 1.
- *   sumsq(x)       256 partial sums over 8 consecutive elements each, butterfly
- *                  inside each group of 32 partials, then the 8 group sums are
- *                  added left to right.
+ *   sumsq(x)       the order of the reference's RMSNorm kernels
+ *                  (native/src/native_pointwise.hip.cpp:109-142): partial t of
+ *                  256 adds elements t, t + 256, ... in that order, then the
+ *                  partials fold by halving (128, 64, ..., 1).
  *   exp            aima_or_expf below (range reduction + degree-6 polynomial,
  *                  only IEEE fma/mul/add, so CPU and GPU agree bit for bit).
  *   rsqrt          (float)(1.0 / sqrt((double)v)) -- the reference demands the
