@@ -143,7 +143,7 @@ def load_kernels() -> Any:
 # ---------------------------------------------------------------------------------------------------
 # Seeded inputs (no Triton needed: the tests rebuild them to run the oracle on the same data)
 # ---------------------------------------------------------------------------------------------------
-def case_inputs(regime: str, seed: int) -> dict[str, Any]:
+def case_inputs(regime: str, seed: int, layer: int = 0) -> dict[str, Any]:
     """The layer's small weights, the token, and a function that materialises one expert's weights.
 
     normal: N(0, 0.02) weights, N(0, 1) token.   ties8 / ties4: router rows shared by groups of experts, so that
@@ -153,15 +153,15 @@ def case_inputs(regime: str, seed: int) -> dict[str, Any]:
     if regime not in REGIMES:
         raise ValueError(regime)
     synth = _synth()
-    small = synth.layer_small_weights(seed, 0)
+    small = synth.layer_small_weights(seed, layer)
     if regime != "normal":
         period = 64 if regime == "ties8" else 128
         base = small["router"]
         index = torch.tensor([(e % period) // 2 for e in range(EXPERTS)])
         small["router"] = base[index].contiguous()
-    after_attn = synth.activations(seed, 1, "residual", 0)
+    after_attn = synth.activations(seed, 1, "residual", layer)
     return {"small": small, "after_attn": after_attn,
-            "expert": lambda e: (synth.expert_gate_up(seed, 0, e), synth.expert_down(seed, 0, e))}
+            "expert": lambda e: (synth.expert_gate_up(seed, layer, e), synth.expert_down(seed, layer, e))}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -305,6 +305,22 @@ def run_case(regime: str, seed: int, stages: str = "all") -> dict[str, np.ndarra
     return stored
 
 
+def run_chain(seed: int, layers: int) -> dict[str, np.ndarray]:
+    """`layers` MoE half-layers free-running: the output of layer l is the input of layer l + 1 (layer l's weights
+    are the synthetic layer l of `seed`).  Stores every layer's ids, routing weights and output."""
+    kernels = load_kernels()
+    x = case_inputs("normal", seed, 0)["after_attn"]
+    stored: dict[str, np.ndarray] = {"input": bits(x)}
+    for layer in range(layers):
+        inputs = case_inputs("normal", seed, layer)
+        result = decode_half_layer(kernels, x, inputs["small"], inputs["expert"])
+        stored[f"ids{layer}"] = result["ids"].numpy()
+        stored[f"weights{layer}"] = bits(result["weights"])
+        stored[f"out{layer}"] = bits(result["out"])
+        x = result["out"].reshape(1, HIDDEN)
+    return stored
+
+
 def run_lm_head_case(rows: int, seed: int, quantised_from: str | None) -> dict[str, np.ndarray]:
     kernels = load_kernels()
     weight, hidden = lm_head_inputs(rows, seed)
@@ -319,6 +335,7 @@ def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--lm-head-rows", type=int, default=0, help="run the LM-head case on this many rows instead")
     parser.add_argument("--norm-rows", type=int, default=0, help="run the fused add + RMSNorm on this many rows instead")
+    parser.add_argument("--chain", type=int, default=0, help="run this many decode half-layers free-running instead")
     parser.add_argument("--quantised-from", default=None, help=".npz with q, scales, residual_l2 to certify with")
     parser.add_argument("--regime", choices=REGIMES, default="normal")
     parser.add_argument("--seed", type=int, default=4321)
@@ -326,6 +343,10 @@ def main() -> None:
     parser.add_argument("--out", required=True)
     args = parser.parse_args()
     torch.set_num_threads(1)
+    if args.chain > 0:
+        np.savez_compressed(args.out, **run_chain(args.seed, args.chain))
+        print(f"wrote {args.out}")
+        return
     if args.norm_rows > 0:
         result = fused_add_rmsnorm(load_kernels(), *norm_inputs(args.norm_rows, args.seed))
         np.savez_compressed(args.out, **{name: bits(tensor) for name, tensor in result.items()})

@@ -9,11 +9,12 @@ interpreter with the reference's launch parameters.  This script runs it once pe
 It needs the reference checkout (its location: AIMA_REFERENCE_ROOT in the environment) and takes about a
 minute and a half per regime:
 
-    python tests/golden/make_decode_triton_golden.py            # regenerate
+    python tests/golden/make_decode_triton_golden.py            # regenerate (all, or the regimes named)
     python tests/golden/make_decode_triton_golden.py --check    # regenerate into a temporary folder and compare
 
 Stored per regime (BF16 as uint16 bit patterns): h2 [2048], ids [8] int32, scores [8] FP32, weights [8],
-act [8,512], routed [2048], shared_input [1025], shared_out [2048], out [2048].
+act [8,512], routed [2048], shared_input [1025], shared_out [2048], out [2048]; for "chain" the input and every
+layer's ids, weights and out.
 """
 from __future__ import annotations
 
@@ -28,20 +29,25 @@ import numpy as np
 ROOT = Path(__file__).resolve().parents[2]
 HERE = Path(__file__).resolve().parent
 SEED = 4321
-REGIMES = ("normal", "ties8", "ties4")
+REGIMES = ("normal", "ties8", "ties4", "chain")       # "chain": three half-layers free-running, input0/ids/weights/out per layer
+
+
+CHAIN_LAYERS = 3
 
 
 def generate(regime: str, out: Path, stages: str = "all") -> None:
     env = dict(os.environ, TRITON_INTERPRET="1")
-    subprocess.run([sys.executable, str(ROOT / "oracle" / "reference_triton.py"), "--regime", regime,
-                    "--seed", str(SEED), "--stages", stages, "--out", str(out)], check=True, env=env)
+    what = ["--chain", str(CHAIN_LAYERS)] if regime == "chain" else ["--regime", regime, "--stages", stages]
+    subprocess.run([sys.executable, str(ROOT / "oracle" / "reference_triton.py"), *what,
+                    "--seed", str(SEED), "--out", str(out)], check=True, env=env)
 
 
 def main() -> int:
     check = "--check" in sys.argv[1:]
     failures = 0
     with tempfile.TemporaryDirectory() as scratch:
-        for regime in REGIMES:
+        only = [a for a in sys.argv[1:] if not a.startswith("--")]
+        for regime in (only or REGIMES):
             target = HERE / f"decode_triton_{regime}.npz"
             if not check:
                 generate(regime, target)

@@ -178,3 +178,38 @@ def test_fused_add_rmsnorm_follows_the_reference_kernel(oracle, tmp_path):
     got, want = _bits(norm_out), ref["norm_out"]
     assert (got == want).mean() >= 0.999
     assert np.abs(got.astype(np.int32) - want.astype(np.int32)).max() <= 1        # neighbouring BF16 values
+
+
+def test_oracle_chain_matches_the_reference_triton_kernels(oracle):
+    """Three half-layers, each fed the previous one's output, by the reference's kernels and by the oracle.
+    Teacher-forced (every layer gets the reference's input): ids in order and routing weights identical, the output
+    identical except for single elements one BF16 step off (the orders of summation differ).  Free-running (the
+    oracle feeds itself): the reference's own gate for such a chain, rel-L2 <= 0.02, cosine >= 0.999 and the exact
+    expert set (native/src/main.cpp:1808-1815) -- here the ids stay identical in order on every layer."""
+    golden = np.load(GOLDEN / "decode_triton_chain.npz")
+    start = reference_triton.case_inputs("normal", SEED, 0)["after_attn"]
+    assert np.array_equal(_bits(start), golden["input"])
+    forced, free = start, start
+    layer = 0
+    while f"out{layer}" in golden.files:
+        inputs = reference_triton.case_inputs("normal", SEED, layer)
+        ids = [int(e) for e in golden[f"ids{layer}"]]
+        weights = dict(inputs["small"])
+        weights["expert_gate_up_by_id"], weights["expert_down_by_id"] = _by_id(inputs, ids)
+        oracle_layer = oracle.OracleLayer(weights)
+        want = golden[f"out{layer}"]
+        got = oracle.decode_layer(forced, oracle_layer)
+        assert got["ids"].tolist() == ids, layer
+        assert np.array_equal(_bits(got["weights"]), golden[f"weights{layer}"]), layer
+        out = _bits(got["out"])
+        assert (out == want).mean() >= 0.999, layer
+        assert np.abs(out.astype(np.int32) - want.astype(np.int32)).max() <= 1, layer
+        run = oracle.decode_layer(free, oracle_layer)
+        assert run["ids"].tolist() == ids, layer
+        a, b = _floats(_bits(run["out"])), _floats(want)
+        assert float((a - b).norm() / b.norm()) <= 0.02, layer
+        assert float(torch.nn.functional.cosine_similarity(a, b, dim=0)) >= 0.999, layer
+        forced = _floats(want).to(torch.bfloat16).reshape(1, -1)
+        free = run["out"].reshape(1, -1)
+        layer += 1
+    assert layer == 3
