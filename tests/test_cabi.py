@@ -31,6 +31,23 @@ def test_library_exports_every_declared_symbol(package, built_library):
     assert lib.aima_moe_abi_version() >> 16 == 1
 
 
+def test_header_is_plain_c_and_cxx(tmp_path):
+    """The boundary is a C ABI: the header must compile alone as C99 and as C++17 (a cgo, JNI or dlopen host
+    includes nothing else), and a C host must link against the library by name."""
+    import shutil
+    import subprocess
+
+    if shutil.which("gcc") is None or shutil.which("g++") is None:
+        pytest.skip("no host compiler")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-fsyntax-only", "-x", "c", str(HEADER)],
+                   check=True)
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-x", "c++", str(HEADER)],
+                   check=True)
+    host = tmp_path / "host.c"
+    host.write_text('#include "aima_moe.h"\nint main(void) { return (int)(aima_moe_abi_version() >> 16) == 1 ? 0 : 1; }\n')
+    subprocess.run(["gcc", "-std=c99", "-I", str(HEADER.parent), "-c", str(host), "-o", str(tmp_path / "host.o")], check=True)
+
+
 def test_struct_sizes_match_the_header(package):
     p = package.provider
     assert ctypes.sizeof(p.Config) == 12 * 4
