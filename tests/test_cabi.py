@@ -48,6 +48,31 @@ def test_header_is_plain_c_and_cxx(tmp_path):
     subprocess.run(["gcc", "-std=c99", "-I", str(HEADER.parent), "-c", str(host), "-o", str(tmp_path / "host.o")], check=True)
 
 
+def test_the_documented_cxx_loader_compiles_and_resolves_every_symbol(built_library, tmp_path):
+    """The dlopen / dlsym loader printed in INTEGRATION.md, compiled as it stands and run against the library."""
+    import shutil
+    import subprocess
+
+    if shutil.which("g++") is None:
+        pytest.skip("no host compiler")
+    text = (ROOT / "INTEGRATION.md").read_text()
+    block = text.split("```cpp\n", 1)[1].split("```", 1)[0]
+    assert "load_moe_provider" in block
+    source = tmp_path / "loader.cpp"
+    source.write_text(block + """
+int main(int argc, char** argv) {
+  if (argc < 2) return 2;
+  MoeProviderApi api = load_moe_provider(argv[1]);
+  return (api.prepare && api.bind_layer && api.prefill_launch && api.decode_launch && api.sync_metrics &&
+          api.release && api.last_error) ? 0 : 1;
+}
+""")
+    binary = tmp_path / "loader"
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", str(HEADER.parent), str(source), "-o", str(binary), "-ldl"],
+                   check=True)
+    subprocess.run([str(binary), str(built_library)], check=True)
+
+
 def test_struct_sizes_match_the_header(package):
     p = package.provider
     assert ctypes.sizeof(p.Config) == 12 * 4
